@@ -1,0 +1,146 @@
+/*
+ * nitrix_b200_attention.h -- C ABI of the B200 (sm_100a) flash-attention path.
+ *
+ * This is the boundary a foreign-function layer binds (an XLA FFI handler under
+ * JAX, ctypes under PyTorch).  Plain pointers, sizes and strides only; every
+ * pointer is a DEVICE pointer owned by the caller and borrowed for the duration
+ * of the enqueued work.  All work is enqueued on the caller's stream; no entry
+ * point synchronises the device, allocates device memory or frees it.
+ *
+ * The entry points replace, for nitrix.nn's attention, the reference's private
+ * fused-kernel module (reference src/nitrix/_kernels/cuda/attention.py):
+ *
+ *   nb200_sdpa_fwd   <->  _fused_forward_with_lse + _mha_forward   (:547-584, :159-264)
+ *   nb200_sdpa_bwd   <->  _fused_backward + _mha_backward          (:600-653, :390-499)
+ *   nb200_sdpa_plan  <->  _check_tileable (the shape gate)         (:708-765)
+ *
+ * Layout.  q is (B, H, S, D), k is (B, H, T, D), v is (B, H, T, Dv), out and
+ * dout are (B, H, S, Dv); "B" is the product of all leading batch dimensions.
+ * Each tensor is described by four ELEMENT strides (b, h, row, col); the col
+ * stride of q, k, v, out, dout, dq, dk, dv must be 1.  bias and mask are
+ * logically (B, H, S, T) and are described by strides as well: a broadcast axis
+ * has stride 0, so no broadcast copy is ever materialised (the reference
+ * materialises them, :560-569).  mask holds one byte per element, non-zero =
+ * keep (reference _reference.py:165-172).  lse and delta are dense fp32
+ * (B, H, S); lse is the base-2 log-sum-exp of the masked logits, m + log2(l)
+ * (reference attention.py:156).
+ */
+#ifndef NITRIX_B200_ATTENTION_H_
+#define NITRIX_B200_ATTENTION_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define NB200_API __attribute__((visibility("default")))
+#else
+#define NB200_API
+#endif
+
+/* element types */
+enum nb200_dtype { NB200_F32 = 0, NB200_BF16 = 1, NB200_F16 = 2 };
+
+/* status codes (0 = ok; negatives are errors; nothing aborts or traps) */
+enum nb200_status {
+  NB200_OK = 0,
+  NB200_ERR_INVALID = -1,     /* null pointer, bad dtype, bad struct size ...      */
+  NB200_ERR_UNSUPPORTED = -2, /* well-formed but no kernel covers it (e.g. D > 256) */
+  NB200_ERR_ALIGNMENT = -3,   /* pointer / stride alignment a kernel needs is unmet */
+  NB200_ERR_WORKSPACE = -4,   /* workspace missing or smaller than required         */
+  NB200_ERR_LAUNCH = -5,      /* CUDA reported an error when enqueueing             */
+  NB200_ERR_TIMEOUT = -6      /* a bounded device-side wait ran out (status word)   */
+};
+
+/* kernel families; `kernel` in the params selects, nb200_sdpa_plan reports */
+enum nb200_kernel {
+  NB200_KERNEL_AUTO = 0,
+  NB200_KERNEL_SIMT = 1,   /* fp32-arithmetic CUDA-core kernels: any shape / dtype  */
+  NB200_KERNEL_TCGEN05 = 2 /* TMA + tcgen05 (TMEM accumulators): bf16 / fp16 tiles  */
+};
+
+enum nb200_pass { NB200_PASS_FWD = 0, NB200_PASS_BWD = 1 };
+
+typedef struct nb200_sdpa_params {
+  uint32_t struct_size; /* = sizeof(nb200_sdpa_params); checked                      */
+  int32_t dtype;        /* nb200_dtype of q, k, v, out, dout, dq, dk, dv             */
+  int32_t bias_dtype;   /* nb200_dtype of bias and dbias (ignored when bias == NULL) */
+  int32_t B, H, S, T, D, Dv;
+
+  /* forward operands */
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;            /* written by fwd, read by bwd                               */
+  float* lse;           /* (B,H,S) fp32, written by fwd, read by bwd                 */
+  const void* bias;     /* may be NULL                                               */
+  const uint8_t* mask;  /* may be NULL; one byte per element, non-zero keeps         */
+
+  /* backward operands (ignored by fwd) */
+  const void* dout;
+  void* dq;
+  void* dk;
+  void* dv;
+  void* dbias;          /* may be NULL: no bias gradient is produced                 */
+
+  /* scratch: nb200_sdpa_workspace_bytes() says how much each pass needs */
+  void* workspace;
+  size_t workspace_bytes;
+
+  /* element strides (b, h, row, col) */
+  int64_t q_stride[4], k_stride[4], v_stride[4], out_stride[4];
+  int64_t dout_stride[4], dq_stride[4], dk_stride[4], dv_stride[4];
+  int64_t bias_stride[4], mask_stride[4], dbias_stride[4];
+
+  float scale;          /* softmax temperature (reference default 1/sqrt(D))         */
+  int32_t causal;       /* keep key j for query i iff j <= i (aligned at 0)          */
+  int32_t kernel;       /* nb200_kernel: AUTO, or force one family                   */
+
+  /* multi-GPU partition: this call processes flattened (b*H + h) indices in
+   * [bh_begin, bh_end).  Pointers and strides always describe the whole
+   * tensors; bh_begin = 0, bh_end = B*H processes everything. */
+  int32_t bh_begin, bh_end;
+} nb200_sdpa_params;
+
+/* ABI version of the loaded library (== NB200_ABI_VERSION it was built with). */
+NB200_API int nb200_version(void);
+
+/* Message for the last non-OK status returned on the calling thread. */
+NB200_API const char* nb200_last_error(void);
+
+/* Which kernel family would run this problem for `pass`; writes one of
+ * NB200_KERNEL_SIMT / NB200_KERNEL_TCGEN05 to *kernel.  When the params force a
+ * family that does not cover the problem the status says why (the Python layer
+ * turns that into the reference's decline -> warn-once contract,
+ * reference nn/attention/__init__.py:207-220).  Never launches. */
+NB200_API int nb200_sdpa_plan(const nb200_sdpa_params* p, int pass, int* kernel);
+
+/* Scratch bytes `pass` needs for this problem (0 is common). */
+NB200_API int nb200_sdpa_workspace_bytes(const nb200_sdpa_params* p, int pass, size_t* bytes);
+
+/* Forward: out = softmax(scale * q k^T + bias, masked) v and lse.
+ * Replaces reference attention.py:547-584 (glue) and :159-264 (kernel launch). */
+NB200_API int nb200_sdpa_fwd(const nb200_sdpa_params* p, void* cuda_stream);
+
+/* Backward: dq, dk, dv and, when dbias != NULL, dbias (reduced over the
+ * broadcast axes of bias, in bias dtype) from (q, k, v, bias, mask, out, lse,
+ * dout).  Replaces reference attention.py:600-653 and :390-499. */
+NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream);
+
+/* Number of kernels this library has enqueued since load (all threads). */
+NB200_API uint64_t nb200_launch_count(void);
+
+/* Reads (and clears) the device-side status word kernels set when a bounded
+ * wait expires; call after synchronising the stream.  NB200_OK or
+ * NB200_ERR_TIMEOUT.  `device` is the CUDA device ordinal. */
+NB200_API int nb200_device_status(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NITRIX_B200_ATTENTION_H_ */

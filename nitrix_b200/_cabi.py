@@ -1,0 +1,96 @@
+"""ctypes binding of ``include/nitrix_b200_attention.h``.
+
+The library is mandatory: when the shared object is missing the import of this
+module raises, it never degrades to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import functools
+
+from . import _build
+
+ABI_VERSION = 1
+
+F32, BF16, F16 = 0, 1, 2
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_LAUNCH, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
+PASS_FWD, PASS_BWD = 0, 1
+
+_I64x4 = C.c_int64 * 4
+
+
+class SdpaParams(C.Structure):
+    """Mirror of ``nb200_sdpa_params`` (field order and types must match the header)."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("bias_dtype", C.c_int32),
+        ("B", C.c_int32), ("H", C.c_int32), ("S", C.c_int32), ("T", C.c_int32),
+        ("D", C.c_int32), ("Dv", C.c_int32),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("bias", C.c_void_p), ("mask", C.c_void_p),
+        ("dout", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("dbias", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_stride", _I64x4), ("k_stride", _I64x4), ("v_stride", _I64x4), ("out_stride", _I64x4),
+        ("dout_stride", _I64x4), ("dq_stride", _I64x4), ("dk_stride", _I64x4), ("dv_stride", _I64x4),
+        ("bias_stride", _I64x4), ("mask_stride", _I64x4), ("dbias_stride", _I64x4),
+        ("scale", C.c_float),
+        ("causal", C.c_int32),
+        ("kernel", C.c_int32),
+        ("bh_begin", C.c_int32), ("bh_end", C.c_int32),
+    ]
+
+
+EXPORTS = (
+    "nb200_version",
+    "nb200_last_error",
+    "nb200_sdpa_plan",
+    "nb200_sdpa_workspace_bytes",
+    "nb200_sdpa_fwd",
+    "nb200_sdpa_bwd",
+    "nb200_launch_count",
+    "nb200_device_status",
+)
+
+
+class NativeLibraryError(ImportError):
+    """The CUDA shared library is missing, stale or has the wrong ABI."""
+
+
+@functools.lru_cache(maxsize=1)
+def lib() -> C.CDLL:
+    path = _build.lib_path()
+    if not path.exists():
+        raise NativeLibraryError(
+            f"{path} is missing: build it with `python -m nitrix_b200._build` (needs nvcc). "
+            "There is no other implementation to fall back to."
+        )
+    L = C.CDLL(str(path))
+    for name in EXPORTS:
+        if not hasattr(L, name):
+            raise NativeLibraryError(f"{path} does not export {name}")
+    L.nb200_version.restype = C.c_int
+    L.nb200_last_error.restype = C.c_char_p
+    L.nb200_launch_count.restype = C.c_uint64
+    L.nb200_device_status.argtypes = [C.c_int]
+    L.nb200_sdpa_plan.argtypes = [C.POINTER(SdpaParams), C.c_int, C.POINTER(C.c_int)]
+    L.nb200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaParams), C.c_int, C.POINTER(C.c_size_t)]
+    L.nb200_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
+    L.nb200_sdpa_bwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
+    if L.nb200_version() != ABI_VERSION:
+        raise NativeLibraryError(f"{path}: ABI {L.nb200_version()} != expected {ABI_VERSION}")
+    return L
+
+
+def last_error() -> str:
+    return lib().nb200_last_error().decode("utf-8", "replace")
+
+
+def new_params() -> SdpaParams:
+    p = SdpaParams()
+    p.struct_size = C.sizeof(SdpaParams)
+    return p

@@ -1,0 +1,297 @@
+// C-ABI entry points (include/nitrix_b200_attention.h): validation, kernel
+// selection, workspace carving and dispatch.  Nothing here allocates device
+// memory or synchronises; every launch goes to the caller's stream.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+
+#include "sdpa_common.cuh"
+
+namespace nb200 {
+
+static thread_local char g_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+// Set by kernels whose bounded waits run out; read by nb200_device_status().
+__device__ int g_device_status = 0;
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return NB200_ERR_LAUNCH;
+  }
+  return NB200_OK;
+}
+
+int* device_status_word() {
+  int* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
+  return p;
+}
+
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+struct Lowered {
+  Problem pr;
+  int dtype, bias_dtype;
+  bool bias_broadcast;        // some bias axis is broadcast over an extent > 1
+  int64_t bias_extent[4];     // bias' own (un-broadcast) extents
+  int64_t dbias_stride[4];    // caller's dbias strides
+};
+
+bool valid_dtype(int d) { return d == NB200_F32 || d == NB200_BF16 || d == NB200_F16; }
+
+int lower(const nb200_sdpa_params* p, int pass, Lowered* out) {
+  if (!p) { set_error("params is NULL"); return NB200_ERR_INVALID; }
+  if (p->struct_size != sizeof(nb200_sdpa_params)) {
+    set_error("params.struct_size=%u, library expects %zu (ABI mismatch)", p->struct_size,
+              sizeof(nb200_sdpa_params));
+    return NB200_ERR_INVALID;
+  }
+  if (!valid_dtype(p->dtype)) { set_error("unknown dtype %d", p->dtype); return NB200_ERR_INVALID; }
+  if (p->bias && !valid_dtype(p->bias_dtype)) {
+    set_error("unknown bias_dtype %d", p->bias_dtype);
+    return NB200_ERR_INVALID;
+  }
+  if (p->B < 0 || p->H < 0 || p->S < 0 || p->T < 0 || p->D <= 0 || p->Dv <= 0) {
+    set_error("negative extent or empty head dim (B=%d H=%d S=%d T=%d D=%d Dv=%d)", p->B, p->H, p->S, p->T,
+              p->D, p->Dv);
+    return NB200_ERR_INVALID;
+  }
+  const int64_t BH = int64_t(p->B) * p->H;
+  if (p->bh_begin < 0 || p->bh_end < p->bh_begin || p->bh_end > BH) {
+    set_error("bh range [%d, %d) outside [0, %lld)", p->bh_begin, p->bh_end, (long long)BH);
+    return NB200_ERR_INVALID;
+  }
+  const bool empty = BH == 0 || p->S == 0 || p->bh_end == p->bh_begin;
+  if (!empty) {
+    if (!p->q || !p->k || !p->v || !p->out || !p->lse) {
+      set_error("q, k, v, out and lse must be non-NULL");
+      return NB200_ERR_INVALID;
+    }
+    if (pass == NB200_PASS_BWD && (!p->dout || !p->dq || !p->dk || !p->dv)) {
+      set_error("dout, dq, dk and dv must be non-NULL for the backward pass");
+      return NB200_ERR_INVALID;
+    }
+  }
+  if (p->q_stride[3] != 1 || p->k_stride[3] != 1 || p->v_stride[3] != 1 || p->out_stride[3] != 1) {
+    set_error("q, k, v and out need a unit stride on the head dimension");
+    return NB200_ERR_INVALID;
+  }
+  if (pass == NB200_PASS_BWD &&
+      (p->dout_stride[3] != 1 || p->dq_stride[3] != 1 || p->dk_stride[3] != 1 || p->dv_stride[3] != 1)) {
+    set_error("dout, dq, dk and dv need a unit stride on the head dimension");
+    return NB200_ERR_INVALID;
+  }
+  if (pass == NB200_PASS_BWD && p->dbias && !p->bias) {
+    set_error("dbias requested without bias");
+    return NB200_ERR_INVALID;
+  }
+  Problem& pr = out->pr;
+  memset(&pr, 0, sizeof(pr));
+  pr.B = p->B; pr.H = p->H; pr.S = p->S; pr.T = p->T; pr.D = p->D; pr.Dv = p->Dv;
+  pr.bh_begin = p->bh_begin; pr.bh_count = p->bh_end - p->bh_begin;
+  pr.q = p->q; pr.k = p->k; pr.v = p->v; pr.out = p->out; pr.lse = p->lse;
+  pr.bias = p->bias; pr.mask = p->mask;
+  pr.scale = p->scale; pr.causal = p->causal != 0;
+  for (int a = 0; a < 3; ++a) {
+    pr.qs[a] = p->q_stride[a]; pr.ks[a] = p->k_stride[a]; pr.vs[a] = p->v_stride[a];
+    pr.os[a] = p->out_stride[a];
+  }
+  for (int a = 0; a < 4; ++a) { pr.bs[a] = p->bias ? p->bias_stride[a] : 0; pr.ms[a] = p->mask ? p->mask_stride[a] : 0; }
+  out->dtype = p->dtype;
+  out->bias_dtype = p->bias ? p->bias_dtype : p->dtype;
+  out->bias_broadcast = false;
+  const int64_t full[4] = {p->B, p->H, p->S, p->T};
+  for (int a = 0; a < 4; ++a) {
+    const bool bc = !p->bias || p->bias_stride[a] == 0 || full[a] == 1;
+    out->bias_extent[a] = bc ? 1 : full[a];
+    if (p->bias && p->bias_stride[a] == 0 && full[a] > 1) out->bias_broadcast = true;
+    out->dbias_stride[a] = p->dbias_stride[a];
+  }
+  if (pass == NB200_PASS_BWD) {
+    pr.dout = p->dout; pr.dq = p->dq; pr.dk = p->dk; pr.dv = p->dv; pr.dbias = p->dbias;
+    for (int a = 0; a < 3; ++a) {
+      pr.dos[a] = p->dout_stride[a]; pr.dqs[a] = p->dq_stride[a]; pr.dks[a] = p->dk_stride[a];
+      pr.dvs[a] = p->dv_stride[a];
+    }
+    for (int a = 0; a < 4; ++a) pr.dbs[a] = out->bias_extent[a] == 1 ? 0 : p->dbias_stride[a];
+  }
+  return NB200_OK;
+}
+
+int choose(const nb200_sdpa_params* p, const Lowered& lw, int pass, int* kernel) {
+  const char* why = "";
+  const bool tc = tc_supported(lw.pr, lw.dtype, lw.bias_dtype, pass, &why);
+  if (p->kernel == NB200_KERNEL_TCGEN05) {
+    if (!tc) { set_error("tcgen05 kernels do not cover this problem: %s", why); return NB200_ERR_UNSUPPORTED; }
+    *kernel = NB200_KERNEL_TCGEN05;
+    return NB200_OK;
+  }
+  if (p->kernel != NB200_KERNEL_AUTO && p->kernel != NB200_KERNEL_SIMT) {
+    set_error("unknown kernel family %d", p->kernel);
+    return NB200_ERR_INVALID;
+  }
+  if (p->kernel == NB200_KERNEL_AUTO && tc) { *kernel = NB200_KERNEL_TCGEN05; return NB200_OK; }
+  if (lw.pr.D > 256 || lw.pr.Dv > 256) {
+    set_error("head dims above 256 are not supported (D=%d Dv=%d)", lw.pr.D, lw.pr.Dv);
+    return NB200_ERR_UNSUPPORTED;
+  }
+  *kernel = NB200_KERNEL_SIMT;
+  return NB200_OK;
+}
+
+// backward scratch shared by both families: delta, then the optional fp32
+// accumulator for a broadcast bias gradient; family-specific scratch follows.
+struct BwdScratch { size_t delta_off, accum_off, family_off, total; int64_t accum_elems; };
+
+BwdScratch bwd_scratch(const nb200_sdpa_params* p, const Lowered& lw, size_t family_bytes) {
+  BwdScratch s{};
+  size_t off = 0;
+  s.delta_off = off;
+  off += align_up(sizeof(float) * size_t(p->B) * p->H * p->S);
+  s.accum_off = off;
+  s.accum_elems = 0;
+  if (p->dbias && lw.bias_broadcast) {
+    s.accum_elems = lw.bias_extent[0] * lw.bias_extent[1] * lw.bias_extent[2] * lw.bias_extent[3];
+    off += align_up(sizeof(float) * size_t(s.accum_elems));
+  }
+  s.family_off = off;
+  off += align_up(family_bytes);
+  s.total = off;
+  return s;
+}
+
+}  // namespace
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+NB200_API int nb200_version(void) { return NB200_ABI_VERSION; }
+
+NB200_API const char* nb200_last_error(void) { return g_error; }
+
+NB200_API uint64_t nb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+NB200_API int nb200_device_status(int device) {
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    set_error("cudaSetDevice(%d) failed", device);
+    return NB200_ERR_INVALID;
+  }
+  int word = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&word, g_device_status, sizeof(int));
+  if (e == cudaSuccess && word != 0) e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+  if (prev >= 0) cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    set_error("reading the device status word: %s", cudaGetErrorString(e));
+    return NB200_ERR_LAUNCH;
+  }
+  if (word != 0) {
+    set_error("a device-side bounded wait expired (code %d)", word);
+    return NB200_ERR_TIMEOUT;
+  }
+  return NB200_OK;
+}
+
+NB200_API int nb200_sdpa_plan(const nb200_sdpa_params* p, int pass, int* kernel) {
+  if (!kernel) { set_error("kernel out-pointer is NULL"); return NB200_ERR_INVALID; }
+  Lowered lw;
+  if (int rc = lower(p, pass, &lw)) return rc;
+  return choose(p, lw, pass, kernel);
+}
+
+NB200_API int nb200_sdpa_workspace_bytes(const nb200_sdpa_params* p, int pass, size_t* bytes) {
+  if (!bytes) { set_error("bytes out-pointer is NULL"); return NB200_ERR_INVALID; }
+  Lowered lw;
+  if (int rc = lower(p, pass, &lw)) return rc;
+  int kernel = 0;
+  if (int rc = choose(p, lw, pass, &kernel)) return rc;
+  const size_t fam = kernel == NB200_KERNEL_TCGEN05 ? tc_workspace_bytes(lw.pr, lw.dtype, lw.bias_dtype, pass) : 0;
+  *bytes = pass == NB200_PASS_FWD ? align_up(fam) : bwd_scratch(p, lw, fam).total;
+  return NB200_OK;
+}
+
+NB200_API int nb200_sdpa_fwd(const nb200_sdpa_params* p, void* cuda_stream) {
+  Lowered lw;
+  if (int rc = lower(p, NB200_PASS_FWD, &lw)) return rc;
+  int kernel = 0;
+  if (int rc = choose(p, lw, NB200_PASS_FWD, &kernel)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (lw.pr.bh_count == 0 || lw.pr.S == 0) return NB200_OK;
+  if (kernel == NB200_KERNEL_TCGEN05) {
+    const size_t need = tc_workspace_bytes(lw.pr, lw.dtype, lw.bias_dtype, NB200_PASS_FWD);
+    if (need && (!p->workspace || p->workspace_bytes < need)) {
+      set_error("forward needs %zu workspace bytes, got %zu", need, p->workspace ? p->workspace_bytes : size_t(0));
+      return NB200_ERR_WORKSPACE;
+    }
+    return tc_forward(lw.pr, lw.dtype, lw.bias_dtype, p->workspace, p->workspace_bytes, st);
+  }
+  return simt_forward(lw.pr, lw.dtype, lw.bias_dtype, st);
+}
+
+NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream) {
+  Lowered lw;
+  if (int rc = lower(p, NB200_PASS_BWD, &lw)) return rc;
+  int kernel = 0;
+  if (int rc = choose(p, lw, NB200_PASS_BWD, &kernel)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (lw.pr.bh_count == 0) return NB200_OK;
+  const size_t fam = kernel == NB200_KERNEL_TCGEN05 ? tc_workspace_bytes(lw.pr, lw.dtype, lw.bias_dtype, NB200_PASS_BWD) : 0;
+  const BwdScratch sc = bwd_scratch(p, lw, fam);
+  if (!p->workspace || p->workspace_bytes < sc.total) {
+    set_error("backward needs %zu workspace bytes, got %zu", sc.total, p->workspace ? p->workspace_bytes : size_t(0));
+    return NB200_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(p->workspace) % kAlign) {
+    set_error("workspace must be %zu-byte aligned", kAlign);
+    return NB200_ERR_ALIGNMENT;
+  }
+  char* ws = static_cast<char*>(p->workspace);
+  Problem& pr = lw.pr;
+  pr.delta = reinterpret_cast<float*>(ws + sc.delta_off);
+  if (sc.accum_elems) {
+    pr.dbias_accum = reinterpret_cast<float*>(ws + sc.accum_off);
+    // dense strides over bias' own extent; broadcast axes collapse to stride 0
+    int64_t st_dense = 1;
+    for (int a = 3; a >= 0; --a) {
+      pr.dbs[a] = lw.bias_extent[a] == 1 ? 0 : st_dense;
+      st_dense *= lw.bias_extent[a];
+    }
+    cudaError_t e = cudaMemsetAsync(pr.dbias_accum, 0, sizeof(float) * size_t(sc.accum_elems), st);
+    if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
+  }
+  if (pr.S > 0) {
+    if (int rc = launch_delta(pr, lw.dtype, st)) return rc;
+  }
+  int rc;
+  if (kernel == NB200_KERNEL_TCGEN05)
+    rc = tc_backward(pr, lw.dtype, lw.bias_dtype, ws + sc.family_off, fam, st);
+  else
+    rc = simt_backward(pr, lw.dtype, lw.bias_dtype, st);
+  if (rc) return rc;
+  if (sc.accum_elems)
+    return launch_dbias_finish(pr.dbias_accum, pr.dbias, lw.bias_dtype, lw.bias_extent, lw.dbias_stride, st);
+  return NB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,122 @@
+// Host/device pieces shared by the tensor-core (TMA + tcgen05) attention
+// kernels: tensor-map creation, the bit-packed mask, bounded waits with a
+// CTA-wide abort flag, and the softmax-tile helpers.
+#pragma once
+
+#include <cuda.h>
+
+#include "sdpa_common.cuh"
+#include "sm100_primitives.cuh"
+
+namespace nb200 {
+namespace tc {
+
+constexpr int kTile = 128;         // query rows / key columns per tcgen05 tile
+constexpr int kSlotCols = 64;      // 16-bit elements per 128-byte swizzled row
+constexpr int kBoxBytes = kTile * 128;  // one TMA box: 128 rows x 128 bytes
+
+// ---- tensor maps (host) -----------------------------------------------------
+// 4-D map over a (B, H, rows, cols) tensor of 16-bit elements with unit column
+// stride; box = 64 columns x 128 rows, 128-byte swizzle, out-of-bounds -> zero.
+// An axis that is broadcast (stride 0) is encoded with extent 1; kernels pass
+// coordinate 0 for it.  Returns false when the driver entry point is missing or
+// the encode call rejects the layout.
+bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H, int B, int64_t row_stride,
+                   int64_t h_stride, int64_t b_stride, const char** why);
+
+// True when a tensor with these element strides can be described by make_tile_map.
+bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B);
+
+// ---- bit-packed mask ----------------------------------------------------------
+// The byte mask (own extent Bm, Hm, Sm, Tm with strides, broadcast axes = 1) is
+// packed once per call into 32-key words: bits[bm][hm][sm][w], w < words_per_row,
+// bit i of word w = keep(row, 32 w + i).  words_per_row is padded to a multiple
+// of 4 so a row's 128-key group is one aligned 16-byte load; padding bits and
+// keys >= T are 0 (dropped).  With `transposed` a second array indexed
+// [bm][hm][key][w] holds bit i = keep(32 w + i, key) for the key-major kernels.
+struct MaskBits {
+  const uint32_t* rows;     // null when there is no mask
+  const uint32_t* cols;     // transposed copy (backward only) or null
+  int64_t b_stride, h_stride, row_stride;       // in words; 0 on broadcast axes
+  int64_t tb_stride, th_stride, tkey_stride;    // transposed array
+};
+
+struct MaskPackPlan {
+  int64_t extent[4];          // Bm, Hm, Sm(1 or S), 1
+  int words_per_row;          // over T
+  int words_per_col;          // over S (transposed)
+  size_t rows_bytes, cols_bytes;
+};
+MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed);
+int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, MaskBits* out, cudaStream_t stream);
+
+// ---- device helpers -----------------------------------------------------------
+#ifdef __CUDACC__
+
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s of SM clock: far beyond any real wait
+
+// Wait on an mbarrier phase unless the CTA has aborted.  On timeout: raise the
+// CTA abort flag, record `code` in the device status word, return false.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                              int code) {
+  if (sm100::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (true) {
+    if (sm100::mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicExch(status, code);
+        return false;
+      }
+    }
+  }
+}
+
+// After an abort: give copies already in flight time to land before the CTA's
+// shared memory is released (bounded; a healthy copy takes microseconds).
+__device__ __forceinline__ void drain_after_abort() {
+  for (int i = 0; i < 64; ++i) __nanosleep(2000);
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+template <bool kBf16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (kBf16) {
+    return make_float2(bf16_lo(w), bf16_hi(w));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+// 128-bit keep mask of one row against one 128-key tile, combining the packed
+// user mask, the causal bound and the key-length bound.  `n_keep` = number of
+// leading keys of the tile the row may see from causal / length limits
+// (<= 0 none, >= 128 all).
+__device__ __forceinline__ void limit_bits(uint32_t (&w)[4], int n_keep) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int n = n_keep - 32 * i;
+    const uint32_t lim = n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u));
+    w[i] &= lim;
+  }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tc
+}  // namespace nb200

@@ -1,0 +1,246 @@
+// Host side of the tensor-core kernels: coverage gate, workspace plan, tensor
+// maps, the mask bit-packing kernel and the launches.
+#include <mutex>
+
+#include "sdpa_tc_bwd.cuh"
+#include "sdpa_tc_common.cuh"
+#include "sdpa_tc_fwd.cuh"
+
+namespace nb200 {
+namespace tc {
+
+// ---- tensor maps ------------------------------------------------------------
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+}  // namespace
+
+bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return false;
+  if (row_stride <= 0 || row_stride % 8) return false;
+  if (H > 1 && h_stride != 0 && (h_stride % 8 || h_stride < 0)) return false;
+  if (B > 1 && b_stride != 0 && (b_stride % 8 || b_stride < 0)) return false;
+  return true;
+}
+
+bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H, int B, int64_t row_stride,
+                   int64_t h_stride, int64_t b_stride, const char** why) {
+  EncodeFn fn = encode_fn();
+  if (!fn) { if (why) *why = "cuTensorMapEncodeTiled is unavailable"; return false; }
+  // broadcast or singleton axes: extent 1 with a harmless natural stride
+  const bool h_bc = H <= 1 || h_stride == 0, b_bc = B <= 1 || b_stride == 0;
+  const int64_t hs = h_bc ? int64_t(rows) * row_stride : h_stride;
+  const int64_t bs = b_bc ? hs * (h_bc ? 1 : H) : b_stride;
+  cuuint64_t dims[4] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(h_bc ? 1 : H), cuuint64_t(b_bc ? 1 : B)};
+  cuuint64_t strides[3] = {cuuint64_t(row_stride) * 2, cuuint64_t(hs) * 2, cuuint64_t(bs) * 2};
+  cuuint32_t box[4] = {cuuint32_t(kSlotCols), cuuint32_t(kTile), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { if (why) *why = "cuTensorMapEncodeTiled rejected the layout"; return false; }
+  return true;
+}
+
+// ---- mask packing -------------------------------------------------------------
+namespace {
+
+// One CTA packs a 32-row x 32-key tile: row-major words by warp ballot over the
+// keys of a row, transposed words by ballot over the rows of a key.
+__global__ void __launch_bounds__(256) mask_pack_kernel(const uint8_t* mask, int64_t sb, int64_t sh, int64_t ss,
+                                                        int64_t st, int Hm, int Sm, int S, int T,
+                                                        uint32_t* rows_out, int words_per_row,
+                                                        uint32_t* cols_out, int words_per_col) {
+  __shared__ uint8_t tile[32][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bm = blockIdx.z / Hm, hm = blockIdx.z - bm * Hm;
+  const int key0 = blockIdx.x * 32, row0 = blockIdx.y * 32;
+  const uint8_t* base = mask + bm * sb + hm * sh;
+  const int n_rows = cols_out ? S : Sm;  // the transposed copy always spans every query row
+  for (int rl = warp; rl < 32; rl += 8) {
+    const int row = row0 + rl, key = key0 + lane;
+    const bool in = row < n_rows && key < T;
+    const uint8_t v = in ? (base[int64_t(Sm == 1 ? 0 : row) * ss + int64_t(key) * st] != 0) : 0;
+    tile[rl][lane] = v;
+    const uint32_t word = __ballot_sync(0xffffffffu, v != 0);
+    if (lane == 0 && row < Sm)
+      rows_out[(int64_t(blockIdx.z) * Sm + row) * words_per_row + blockIdx.x] = word;
+  }
+  if (!cols_out) return;
+  __syncthreads();
+  for (int kl = warp; kl < 32; kl += 8) {
+    const int key = key0 + kl;
+    const uint32_t word = __ballot_sync(0xffffffffu, tile[lane][kl] != 0);
+    if (lane == 0 && key < T) cols_out[(int64_t(blockIdx.z) * T + key) * words_per_col + blockIdx.y] = word;
+  }
+}
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+}  // namespace
+
+MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed) {
+  MaskPackPlan p{};
+  if (!pr.mask) return p;
+  const int64_t full[4] = {pr.B, pr.H, pr.S, pr.T};
+  for (int a = 0; a < 3; ++a) p.extent[a] = (pr.ms[a] == 0 || full[a] == 1) ? 1 : full[a];
+  p.extent[3] = 1;
+  p.words_per_row = round_up((pr.T + 31) / 32, 4);
+  p.words_per_col = round_up((pr.S + 31) / 32, 4);
+  p.rows_bytes = size_t(p.extent[0] * p.extent[1] * p.extent[2]) * p.words_per_row * 4;
+  p.rows_bytes = (p.rows_bytes + 255) / 256 * 256;
+  p.cols_bytes = transposed ? size_t(p.extent[0] * p.extent[1]) * pr.T * p.words_per_col * 4 : 0;
+  p.cols_bytes = (p.cols_bytes + 255) / 256 * 256;
+  return p;
+}
+
+int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, MaskBits* out, cudaStream_t stream) {
+  *out = MaskBits{};
+  if (!pr.mask) return NB200_OK;
+  uint32_t* rows = static_cast<uint32_t*>(ws);
+  uint32_t* cols = plan.cols_bytes ? reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + plan.rows_bytes) : nullptr;
+  const int Bm = int(plan.extent[0]), Hm = int(plan.extent[1]), Sm = int(plan.extent[2]);
+  const int n_rows = cols ? pr.S : Sm;
+  // padding words beyond ceil(T/32) (and ceil(S/32)) must read as "dropped"
+  cudaError_t e = cudaMemsetAsync(ws, 0, plan.rows_bytes + plan.cols_bytes, stream);
+  if (e != cudaSuccess) { set_error("cudaMemsetAsync(mask bits): %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
+  dim3 grid((pr.T + 31) / 32, (n_rows + 31) / 32, Bm * Hm);
+  mask_pack_kernel<<<grid, 256, 0, stream>>>(pr.mask, pr.ms[0], pr.ms[1], pr.ms[2], pr.ms[3], Hm, Sm, pr.S, pr.T, rows,
+                                             plan.words_per_row, cols, plan.words_per_col);
+  count_launch();
+  if (int rc = check_launch("mask_pack_kernel")) return rc;
+  out->rows = rows;
+  out->row_stride = Sm == 1 ? 0 : plan.words_per_row;
+  out->h_stride = Hm == 1 ? 0 : int64_t(Sm) * plan.words_per_row;
+  out->b_stride = Bm == 1 ? 0 : int64_t(Hm) * Sm * plan.words_per_row;
+  out->cols = cols;
+  out->tkey_stride = plan.words_per_col;
+  out->th_stride = Hm == 1 ? 0 : int64_t(pr.T) * plan.words_per_col;
+  out->tb_stride = Bm == 1 ? 0 : int64_t(Hm) * pr.T * plan.words_per_col;
+  return NB200_OK;
+}
+
+}  // namespace tc
+
+// ---- coverage gate -----------------------------------------------------------
+namespace {
+
+struct BiasPlan { int mode; };
+
+bool bias_plan(const Problem& pr, int dtype, int bias_dtype, BiasPlan* bp, const char** why) {
+  bp->mode = tc::kBiasNone;
+  if (!pr.bias) return true;
+  if (bias_dtype != dtype) { *why = "bias dtype differs from q/k/v dtype"; return false; }
+  const bool row_bc = pr.bs[2] == 0 || pr.S == 1;
+  if (pr.T > 1 && pr.bs[3] != 1) { *why = "bias needs a unit stride over keys"; return false; }
+  if (row_bc) {
+    if (reinterpret_cast<uintptr_t>(pr.bias) % 16 || pr.bs[0] % 8 || pr.bs[1] % 8) {
+      *why = "per-key bias is not 16-byte aligned";
+      return false;
+    }
+    bp->mode = tc::kBiasKey;
+    return true;
+  }
+  if (!tc::tile_map_ok(pr.bias, pr.bs[2], pr.bs[1], pr.bs[0], pr.H, pr.B)) {
+    *why = "bias strides / alignment do not fit a TMA descriptor";
+    return false;
+  }
+  bp->mode = tc::kBiasTile;
+  return true;
+}
+
+}  // namespace
+
+bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const char** why) {
+  const char* dummy;
+  if (!why) why = &dummy;
+  if (dtype != NB200_BF16 && dtype != NB200_F16) { *why = "dtype is not bf16/fp16"; return false; }
+  if (pr.D != pr.Dv || (pr.D != 64 && pr.D != 128)) { *why = "head dims must be equal and 64 or 128"; return false; }
+  if (pr.S <= 0 || pr.T <= 0 || pr.S % tc::kTile || pr.T % tc::kTile) {
+    *why = "query and key lengths must be positive multiples of 128";
+    return false;
+  }
+  if (!tc::tile_map_ok(pr.q, pr.qs[2], pr.qs[1], pr.qs[0], pr.H, pr.B) ||
+      !tc::tile_map_ok(pr.k, pr.ks[2], pr.ks[1], pr.ks[0], pr.H, pr.B) ||
+      !tc::tile_map_ok(pr.v, pr.vs[2], pr.vs[1], pr.vs[0], pr.H, pr.B)) {
+    *why = "q/k/v strides or alignment do not fit a TMA descriptor";
+    return false;
+  }
+  if (reinterpret_cast<uintptr_t>(pr.out) % 16 || pr.os[0] % 8 || pr.os[1] % 8 || pr.os[2] % 8) {
+    *why = "out is not 16-byte aligned";
+    return false;
+  }
+  BiasPlan bp;
+  if (!bias_plan(pr, dtype, bias_dtype, &bp, why)) return false;
+  if (pass == NB200_PASS_BWD) return tc::bwd_supported(pr, dtype, bias_dtype, why);
+  return true;
+}
+
+size_t tc_workspace_bytes(const Problem& pr, int dtype, int bias_dtype, int pass) {
+  if (pass == NB200_PASS_BWD) return tc::bwd_workspace_bytes(pr, dtype, bias_dtype);
+  const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, false);
+  return mp.rows_bytes;
+}
+
+int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  const char* why = "";
+  BiasPlan bp;
+  if (!bias_plan(pr, dtype, bias_dtype, &bp, &why)) { set_error("%s", why); return NB200_ERR_UNSUPPORTED; }
+  const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, false);
+  if (mp.rows_bytes > ws_bytes || (mp.rows_bytes && !ws)) {
+    set_error("forward mask bits need %zu workspace bytes", mp.rows_bytes);
+    return NB200_ERR_WORKSPACE;
+  }
+  tc::FwdArgs a{};
+  if (int rc = tc::launch_mask_pack(pr, mp, ws, &a.mask, stream)) return rc;
+  CUtensorMap tq, tk, tv, tb;
+  if (!tc::make_tile_map(&tq, pr.q, pr.S, pr.D, pr.H, pr.B, pr.qs[2], pr.qs[1], pr.qs[0], &why) ||
+      !tc::make_tile_map(&tk, pr.k, pr.T, pr.D, pr.H, pr.B, pr.ks[2], pr.ks[1], pr.ks[0], &why) ||
+      !tc::make_tile_map(&tv, pr.v, pr.T, pr.Dv, pr.H, pr.B, pr.vs[2], pr.vs[1], pr.vs[0], &why)) {
+    set_error("tensor map: %s", why);
+    return NB200_ERR_LAUNCH;
+  }
+  tb = tq;  // placeholder when the bias is not tiled (never dereferenced)
+  if (bp.mode == tc::kBiasTile &&
+      !tc::make_tile_map(&tb, pr.bias, pr.S, pr.T, pr.H, pr.B, pr.bs[2], pr.bs[1], pr.bs[0], &why)) {
+    set_error("bias tensor map: %s", why);
+    return NB200_ERR_LAUNCH;
+  }
+  a.H = pr.H; a.S = pr.S; a.T = pr.T; a.bh_begin = pr.bh_begin;
+  a.causal = pr.causal; a.scale = pr.scale;
+  a.bias_mode = bp.mode;
+  a.bias_b_mul = (pr.B > 1 && pr.bs[0] != 0) ? 1 : 0;
+  a.bias_h_mul = (pr.H > 1 && pr.bs[1] != 0) ? 1 : 0;
+  a.bias = pr.bias; a.bias_bs = pr.bs[0]; a.bias_hs = pr.bs[1];
+  a.out = pr.out;
+  for (int i = 0; i < 3; ++i) a.os[i] = pr.os[i];
+  a.lse = pr.lse;
+  a.status = device_status_word();
+  if (!a.status) { set_error("device status word is unavailable"); return NB200_ERR_LAUNCH; }
+  const int n_qblocks = (pr.S + 2 * tc::kTile - 1) / (2 * tc::kTile);
+  return tc::launch_fwd(pr.D, dtype == NB200_BF16, tq, tk, tv, tb, a, n_qblocks, pr.bh_count, stream);
+}
+
+int tc_backward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  return tc::launch_bwd(pr, dtype, bias_dtype, ws, ws_bytes, stream);
+}
+
+}  // namespace nb200

@@ -1,0 +1,341 @@
+"""Scaled-dot-product / flash attention on B200, PyTorch-hosted.
+
+Drop-in for the reference's public entry
+``nitrix.nn.attention.scaled_dot_product_attention``
+(reference ``src/nitrix/nn/attention/__init__.py:126-230``): same positional
+and keyword surface ``(q, k, v, *, bias, mask, scale, causal, qk_norm,
+backend)``, same validation errors (``:40-60``), same differentiation contract
+as its ``custom_vjp`` (reference ``src/nitrix/_kernels/cuda/attention.py:661-700``):
+residuals ``(q, k, v, bias, mask, out, lse)``, cotangents
+``(dq, dk, dv, dbias-or-None, None)`` with ``scale`` and ``causal`` static.
+
+Differences, all on purpose:
+
+* tensors are ``torch`` CUDA tensors (device memory, streams); the arithmetic
+  is done by the CUDA library behind ``include/nitrix_b200_attention.h``;
+* bias and mask are passed by stride, never broadcast-materialised, and q/k/v
+  stay in ``(..., h, s, d)`` layout (the reference transposes and materialises,
+  ``attention.py:507-514,560-569``);
+* ``dbias`` is produced only when ``bias.requires_grad`` (the reference always
+  produces it when a bias is present, ``attention.py:408,437``);
+* there is no host fallback: a problem the fused kernels decline runs on the
+  CUDA-core family of the same library, with the reference's warn-once
+  contract.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _cabi
+from ..backend import fallback, resolve_backend
+
+__all__ = ["scaled_dot_product_attention", "default_scale", "qk_rms_norm", "sdpa_forward", "sdpa_backward"]
+
+_QK_RMS_EPS = 1e-6  # reference _reference.py:32
+
+_DTYPES = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
+_KERNELS = {"cuda-sm100": _cabi.KERNEL_AUTO, "cuda-simt": _cabi.KERNEL_SIMT}
+
+
+def default_scale(head_dim: int) -> float:
+    """``1/sqrt(d)`` (reference ``_reference.py:35-49``)."""
+    return 1.0 / math.sqrt(float(head_dim))
+
+
+def qk_rms_norm(z: torch.Tensor) -> torch.Tensor:
+    """RMS-normalise over the head dim, no learnable scale (reference ``_reference.py:52-77``).
+
+    Runs outside the fused kernels' differentiation rule, as in the reference
+    (``nn/attention/__init__.py:193-197``), so autograd chains its gradient.
+    """
+    acc = torch.promote_types(z.dtype, torch.float32)
+    zf = z.to(acc)
+    return (zf * torch.rsqrt(zf.square().mean(-1, keepdim=True) + _QK_RMS_EPS)).to(z.dtype)
+
+
+def _validate(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+    # reference nn/attention/__init__.py:40-60
+    if q.ndim < 3 or k.ndim < 3 or v.ndim < 3:
+        raise ValueError(
+            "scaled_dot_product_attention: q, k, v must have at least 3 dims (..., h, s, d); "
+            f"got ndim {q.ndim}, {k.ndim}, {v.ndim}."
+        )
+    if q.shape[-1] != k.shape[-1]:
+        raise ValueError(
+            f"scaled_dot_product_attention: q/k head-dim mismatch (q d={q.shape[-1]}, k d={k.shape[-1]})."
+        )
+    if k.shape[-2] != v.shape[-2]:
+        raise ValueError(
+            f"scaled_dot_product_attention: k/v key-length mismatch (k t={k.shape[-2]}, v t={v.shape[-2]})."
+        )
+
+
+# ---------------------------------------------------------------------------
+# shape canonicalisation: everything becomes 4-D (B, H, rows, cols)
+# ---------------------------------------------------------------------------
+
+def _to_bhxd(x: torch.Tensor, lead: Tuple[int, ...], h: int) -> torch.Tensor:
+    """(..., h, n, d) -> (B, h, n, d) with the leading dims broadcast to ``lead``."""
+    n, d = x.shape[-2], x.shape[-1]
+    x = x.expand(*lead, h, n, d) if tuple(x.shape[:-3]) != lead or x.shape[-3] != h else x
+    x = x.reshape(-1, h, n, d) if x.ndim != 4 else x
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    return x
+
+
+def _to_own_extent(x: torch.Tensor, lead: Tuple[int, ...], h: int, s: int, t: int) -> torch.Tensor:
+    """bias / mask broadcastable to (*lead, h, s, t) -> 4-D (Bb, Hb, Sb, Tb), each extent 1 or full.
+
+    Only differentiable view/expand ops are used, so a bias gradient of this
+    4-D shape flows back to the caller's bias shape through autograd.  Leading
+    dims are merged without copying whenever they are all broadcast or all
+    present; a partially broadcast multi-dim batch is expanded over the batch.
+    """
+    full = (*lead, h, s, t)
+    if x.ndim > len(full):
+        raise ValueError(f"bias/mask of shape {tuple(x.shape)} has more dims than (..., h, s, t) = {full}")
+    x = x.reshape((1,) * (len(full) - x.ndim) + tuple(x.shape))
+    for have, want in zip(x.shape, full):
+        if have != 1 and have != want:
+            raise ValueError(f"bias/mask of shape {tuple(x.shape)} does not broadcast to {full}")
+    nl = len(lead)
+    lead_have = tuple(x.shape[:nl])
+    if all(a == 1 for a in lead_have):
+        x = x.reshape(1, *x.shape[nl:])
+    elif lead_have == lead:
+        x = x.reshape(-1, *x.shape[nl:])
+    else:
+        x = x.expand(*lead, *x.shape[nl:]).reshape(-1, *x.shape[nl:])
+    return x
+
+
+def _strides4(x: Optional[torch.Tensor], full: Tuple[int, int, int, int]):
+    """Element strides with 0 on every broadcast (extent-1) axis."""
+    arr = (C.c_int64 * 4)()
+    if x is not None:
+        for a in range(4):
+            arr[a] = 0 if (x.shape[a] == 1 and full[a] != 1) else x.stride(a)
+    return arr
+
+
+def _fill_common(p, q, k, v, out, lse, bias, mask, scale, causal, kernel, bh_range):
+    B, H, S, D = q.shape
+    T, Dv = k.shape[2], v.shape[3]
+    p.dtype = _DTYPES[q.dtype]
+    p.B, p.H, p.S, p.T, p.D, p.Dv = B, H, S, T, D, Dv
+    p.q, p.k, p.v, p.out, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    full = (B, H, S, T)
+    for name, ten in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("out_stride", out)):
+        getattr(p, name)[:] = list(ten.stride())
+    if bias is not None:
+        p.bias = bias.data_ptr()
+        p.bias_dtype = _DTYPES[bias.dtype]
+        p.bias_stride = _strides4(bias, full)
+    if mask is not None:
+        p.mask = mask.data_ptr()
+        p.mask_stride = _strides4(mask, full)
+    p.scale = float(scale)
+    p.causal = int(bool(causal))
+    p.kernel = int(kernel)
+    lo, hi = (0, B * H) if bh_range is None else bh_range
+    p.bh_begin, p.bh_end = int(lo), int(hi)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != _cabi.OK:
+        raise RuntimeError(f"{what} failed (status {rc}): {_cabi.last_error()}")
+
+
+def _workspace(p, which: int, device) -> Optional[torch.Tensor]:
+    need = C.c_size_t(0)
+    _check(_cabi.lib().nb200_sdpa_workspace_bytes(C.byref(p), which, C.byref(need)), "nb200_sdpa_workspace_bytes")
+    if need.value == 0:
+        return None
+    ws = torch.empty(need.value, dtype=torch.uint8, device=device)
+    p.workspace = ws.data_ptr()
+    p.workspace_bytes = need.value
+    return ws
+
+
+def _mask_bytes(mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if mask is None:
+        return None
+    if mask.dtype == torch.bool:
+        return mask.view(torch.uint8)
+    if mask.dtype == torch.uint8:
+        return mask
+    return (mask != 0).view(torch.uint8)
+
+
+def planned_kernel(q, k, v, bias=None, mask=None, *, scale=1.0, causal=False, which=_cabi.PASS_FWD,
+                   kernel=_cabi.KERNEL_AUTO) -> int:
+    """Kernel family the library would run for these 4-D operands (no launch)."""
+    p = _cabi.new_params()
+    B, H, S, _ = q.shape
+    out = q  # pointers are not dereferenced by the planner
+    lse = q
+    _fill_common(p, q, k, v, out, lse, bias, _mask_bytes(mask), scale, causal, kernel, None)
+    p.dout = p.dq = p.dk = p.dv = q.data_ptr()
+    p.dout_stride = p.dq_stride = p.out_stride
+    p.dk_stride, p.dv_stride = p.k_stride, p.v_stride
+    chosen = C.c_int(0)
+    _check(_cabi.lib().nb200_sdpa_plan(C.byref(p), which, C.byref(chosen)), "nb200_sdpa_plan")
+    return chosen.value
+
+
+def sdpa_forward(q, k, v, bias=None, mask=None, *, scale: float, causal: bool = False,
+                 kernel: int = _cabi.KERNEL_AUTO, bh_range=None, out=None, lse=None):
+    """Enqueue the forward on the current stream; 4-D operands.  Returns ``(out, lse)``.
+
+    ``q`` (B,H,S,D), ``k`` (B,H,T,D), ``v`` (B,H,T,Dv); ``bias`` / ``mask`` 4-D
+    with each extent 1 (broadcast) or full.  ``lse`` is fp32 (B,H,S), base 2.
+    """
+    B, H, S, _ = q.shape
+    Dv = v.shape[3]
+    if out is None:
+        out = torch.empty((B, H, S, Dv), dtype=q.dtype, device=q.device)
+    if lse is None:
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    p = _cabi.new_params()
+    mask_b = _mask_bytes(mask)
+    _fill_common(p, q, k, v, out, lse, bias, mask_b, scale, causal, kernel, bh_range)
+    ws = _workspace(p, _cabi.PASS_FWD, q.device)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _check(_cabi.lib().nb200_sdpa_fwd(C.byref(p), C.c_void_p(stream)), "nb200_sdpa_fwd")
+    del ws  # same-stream reuse is ordered by the caching allocator
+    return out, lse
+
+
+def sdpa_backward(q, k, v, bias, mask, out, lse, dout, *, scale: float, causal: bool = False,
+                  want_dbias: bool = False, kernel: int = _cabi.KERNEL_AUTO, bh_range=None):
+    """Enqueue the backward on the current stream; returns ``(dq, dk, dv, dbias_or_None)``.
+
+    ``dbias`` has the bias' own 4-D extent (broadcast axes already reduced) and dtype.
+    """
+    if dout.stride(-1) != 1:
+        dout = dout.contiguous()
+    dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+    dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+    dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+    dbias = None
+    p = _cabi.new_params()
+    mask_b = _mask_bytes(mask)
+    _fill_common(p, q, k, v, out, lse, bias, mask_b, scale, causal, kernel, bh_range)
+    p.dout, p.dq, p.dk, p.dv = dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    p.dout_stride[:] = list(dout.stride())
+    p.dq_stride[:] = list(dq.stride())
+    p.dk_stride[:] = list(dk.stride())
+    p.dv_stride[:] = list(dv.stride())
+    if want_dbias:
+        if bias is None:
+            raise ValueError("want_dbias without a bias")
+        dbias = torch.empty(bias.shape, dtype=bias.dtype, device=bias.device)
+        p.dbias = dbias.data_ptr()
+        p.dbias_stride[:] = list(dbias.stride())
+    ws = _workspace(p, _cabi.PASS_BWD, q.device)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _check(_cabi.lib().nb200_sdpa_bwd(C.byref(p), C.c_void_p(stream)), "nb200_sdpa_bwd")
+    del ws  # same-stream reuse is ordered by the caching allocator
+    return dq, dk, dv, dbias
+
+
+class _SDPA(torch.autograd.Function):
+    """Differentiation rule of the fused path (reference ``attention.py:661-700``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, bias, mask, scale, causal, kernel):
+        out, lse = sdpa_forward(q, k, v, bias, mask, scale=scale, causal=causal, kernel=kernel)
+        ctx.save_for_backward(q, k, v, bias, mask, out, lse)
+        ctx.scale, ctx.causal, ctx.kernel = scale, causal, kernel
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        q, k, v, bias, mask, out, lse = ctx.saved_tensors
+        want_dbias = bias is not None and ctx.needs_input_grad[3]
+        dq, dk, dv, dbias = sdpa_backward(q, k, v, bias, mask, out, lse, dout, scale=ctx.scale,
+                                          causal=ctx.causal, want_dbias=want_dbias, kernel=ctx.kernel)
+        return dq, dk, dv, dbias, None, None, None, None
+
+
+def scaled_dot_product_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    mask: Optional[torch.Tensor] = None,
+    scale: Optional[float] = None,
+    causal: bool = False,
+    qk_norm: bool = False,
+    backend: str = "auto",
+    return_lse: bool = False,
+):
+    """``softmax(scale * q k^T + bias [masked]) v`` over the key axis, differentiable.
+
+    Parameters follow the reference entry point: ``q`` ``(..., h, s, d)``, ``k``
+    ``(..., h, t, d)``, ``v`` ``(..., h, t, d_v)``; ``bias`` (additive, applied
+    after scaling) and ``mask`` (boolean, ``True`` keeps) broadcast to
+    ``(..., h, s, t)``; ``causal`` keeps keys ``j <= i`` with indices aligned at
+    zero and is AND-ed with ``mask``; ``scale`` defaults to ``1/sqrt(d)``;
+    ``qk_norm`` RMS-normalises q and k first.  The result has shape
+    ``(..., h, s, d_v)`` and the common dtype of q, k, v.  Computation is fp32
+    (accumulators, softmax) whatever the storage dtype.  A query row with no
+    kept key yields NaN, like the reference's ``jnp`` path.
+
+    ``backend``: ``'auto'`` | ``'cuda-sm100'`` (alias ``'pallas-cuda'``) |
+    ``'cuda-simt'``; see :mod:`nitrix_b200.backend`.
+    """
+    _validate(q, k, v)
+    resolved_scale = default_scale(q.shape[-1]) if scale is None else float(scale)
+    resolved = resolve_backend(backend)
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("scaled_dot_product_attention: q, k, v must be CUDA tensors (no host path exists)")
+    out_dtype = torch.promote_types(torch.promote_types(q.dtype, k.dtype), v.dtype)
+    if out_dtype not in _DTYPES:
+        raise ValueError(f"scaled_dot_product_attention: dtype {out_dtype} is not supported (fp32, bf16, fp16)")
+    q, k, v = q.to(out_dtype), k.to(out_dtype), v.to(out_dtype)
+    if qk_norm:
+        q, k = qk_rms_norm(q), qk_rms_norm(k)
+
+    h, s, d = q.shape[-3:]
+    t, dv = k.shape[-2], v.shape[-1]
+    lead = tuple(torch.broadcast_shapes(q.shape[:-3], k.shape[:-3], v.shape[:-3]))
+    if k.shape[-3] != h or v.shape[-3] != h:
+        raise ValueError(f"scaled_dot_product_attention: head-count mismatch (q {h}, k {k.shape[-3]}, v {v.shape[-3]})")
+    q4, k4, v4 = _to_bhxd(q, lead, h), _to_bhxd(k, lead, h), _to_bhxd(v, lead, h)
+    bias4 = None
+    if bias is not None:
+        if bias.dtype not in _DTYPES:
+            bias = bias.to(torch.float32)
+        bias4 = _to_own_extent(bias, lead, h, s, t)
+    mask4 = None if mask is None else _to_own_extent(mask, lead, h, s, t)
+
+    kernel = _KERNELS[resolved]
+    if resolved == "cuda-sm100":
+        chosen = planned_kernel(q4, k4, v4, bias4, mask4, scale=resolved_scale, causal=causal)
+        if chosen != _cabi.KERNEL_TCGEN05:
+            fallback(
+                function="scaled_dot_product_attention",
+                requested="cuda-sm100",
+                resolved="cuda-simt",
+                reason=(
+                    "the fused tcgen05 kernels take bf16/fp16 with d == d_v in {64, 128} and "
+                    "query/key lengths that are multiples of 128"
+                ),
+                shapes=(tuple(q.shape), tuple(k.shape), tuple(v.shape)),
+                dtype=out_dtype,
+            )
+    out4, lse4 = _SDPA.apply(q4, k4, v4, bias4, mask4, resolved_scale, bool(causal), kernel)
+    out = out4.reshape(*lead, h, s, dv)
+    if return_lse:
+        return out, lse4.reshape(*lead, h, s)
+    return out

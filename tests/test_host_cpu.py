@@ -1,0 +1,175 @@
+"""Host-side logic that needs no GPU: the C ABI loads and exports what the header
+declares, parameter validation, backend resolution, fallback bookkeeping
+(reference ``tests/test_backend.py:19-131``, ``tests/test_nn_attention.py:259-340``)
+and the shard arithmetic."""
+import ctypes as C
+import pathlib
+import re
+import warnings
+
+import pytest
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    from nitrix_b200 import _cabi
+
+    header = (ROOT / "include" / "nitrix_b200_attention.h").read_text()
+    declared = set(re.findall(r"NB200_API\s+[\w\s\*]+?\b(nb200_\w+)\s*\(", header))
+    assert declared, "no NB200_API declarations parsed"
+    assert declared == set(_cabi.EXPORTS)
+    lib = _cabi.lib()
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.nb200_version() == _cabi.ABI_VERSION
+
+
+def test_params_struct_size_matches_library():
+    from nitrix_b200 import _cabi
+
+    p = _cabi.new_params()
+    p.dtype = _cabi.F32
+    p.B = p.H = 1
+    p.S = p.T = 4
+    p.D = p.Dv = 8
+    p.bh_end = 1
+    kernel = C.c_int(0)
+    # struct_size agrees (a mismatch is reported as INVALID with an ABI message) ...
+    rc = _cabi.lib().nb200_sdpa_plan(C.byref(p), _cabi.PASS_FWD, C.byref(kernel))
+    assert "ABI mismatch" not in _cabi.last_error()
+    # ... and null operands are rejected, not dereferenced
+    assert rc == _cabi.ERR_INVALID and "non-NULL" in _cabi.last_error()
+    p.struct_size = 8
+    assert _cabi.lib().nb200_sdpa_plan(C.byref(p), _cabi.PASS_FWD, C.byref(kernel)) == _cabi.ERR_INVALID
+    assert "ABI mismatch" in _cabi.last_error()
+
+
+def _plan(**over):
+    from nitrix_b200 import _cabi
+
+    p = _cabi.new_params()
+    p.dtype = _cabi.BF16
+    p.B, p.H, p.S, p.T, p.D, p.Dv = 2, 4, 256, 256, 64, 64
+    for f in ("q", "k", "v", "out", "lse"):
+        setattr(p, f, 0x1000)
+    for f in ("q_stride", "k_stride", "v_stride", "out_stride"):
+        getattr(p, f)[:] = [4 * 256 * 64, 256 * 64, 64, 1]
+    p.scale = 0.125
+    p.bh_end = 8
+    for key, val in over.items():
+        if isinstance(val, (list, tuple)):
+            getattr(p, key)[:] = list(val)
+        else:
+            setattr(p, key, val)
+    kernel = C.c_int(0)
+    rc = _cabi.lib().nb200_sdpa_plan(C.byref(p), _cabi.PASS_FWD, C.byref(kernel))
+    return rc, kernel.value, _cabi.last_error()
+
+
+def test_plan_validation_errors():
+    from nitrix_b200 import _cabi
+
+    assert _plan(dtype=7)[0] == _cabi.ERR_INVALID
+    assert _plan(D=0)[0] == _cabi.ERR_INVALID
+    assert _plan(bh_end=9)[0] == _cabi.ERR_INVALID
+    assert _plan(q_stride=[1, 1, 1, 2])[0] == _cabi.ERR_INVALID
+    rc, kernel, _ = _plan(kernel=_cabi.KERNEL_SIMT)
+    assert rc == _cabi.OK and kernel == _cabi.KERNEL_SIMT
+    assert _plan(kernel=_cabi.KERNEL_SIMT, D=512, Dv=512)[0] == _cabi.ERR_UNSUPPORTED
+    # fp32 is outside the tensor-core family: forcing it is a decline, not a crash
+    rc, _, msg = _plan(dtype=_cabi.F32, kernel=_cabi.KERNEL_TCGEN05)
+    assert rc == _cabi.ERR_UNSUPPORTED and msg
+
+
+def test_backend_resolution_and_env(monkeypatch):
+    from nitrix_b200 import backend as B
+
+    monkeypatch.delenv("NITRIX_BACKEND", raising=False)
+    monkeypatch.delenv("NITRIX_REPRODUCIBLE", raising=False)
+    with pytest.raises(B.NitrixBackendError):
+        B.resolve_backend("tpu")
+    with pytest.raises(B.NitrixBackendError):
+        B.resolve_backend("jax")
+    monkeypatch.setenv("NITRIX_BACKEND", "bogus")
+    with pytest.raises(B.NitrixBackendError):
+        B.resolve_backend("auto")
+    monkeypatch.setattr(B, "has_sm100_device", lambda: True)
+    monkeypatch.setenv("NITRIX_BACKEND", "cuda-simt")
+    assert B.resolve_backend("auto") == "cuda-simt"
+    assert B.resolve_backend("cuda-sm100") == "cuda-sm100"  # keyword beats env
+    monkeypatch.delenv("NITRIX_BACKEND")
+    assert B.resolve_backend("auto") == "cuda-sm100"
+    assert B.resolve_backend("pallas-cuda") == "cuda-sm100"
+    with B.reproducible():
+        assert B.resolve_backend("auto") == "cuda-simt"
+        assert B.resolve_backend("cuda-sm100") == "cuda-sm100"  # explicit beats mode
+    monkeypatch.setenv("NITRIX_REPRODUCIBLE", "1")
+    assert B.resolve_backend("auto") == "cuda-simt"
+    monkeypatch.setattr(B, "has_sm100_device", lambda: False)
+    with pytest.raises(B.NitrixBackendError):  # no device: loud, never a host path
+        B.resolve_backend("auto")
+
+
+def test_fallback_warns_once_strict_and_silence(monkeypatch):
+    from nitrix_b200 import backend as B
+
+    monkeypatch.delenv("NITRIX_STRICT_BACKEND", raising=False)
+    monkeypatch.delenv("NITRIX_SILENCE_FALLBACK", raising=False)
+    B.reset_fallback_state()
+    kw = dict(function="f", requested="cuda-sm100", resolved="cuda-simt", reason="r", shapes=((1, 2),), dtype="f32")
+    with pytest.warns(B.NitrixBackendFallback):
+        B.fallback(**kw)
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        B.fallback(**kw)  # deduplicated
+        B.fallback(**{**kw, "requested": "cuda-simt"})  # no change, no warning
+    B.reset_fallback_state()
+    with pytest.warns(B.NitrixBackendFallback):
+        B.fallback(**kw)
+    monkeypatch.setenv("NITRIX_SILENCE_FALLBACK", "1")
+    B.reset_fallback_state()
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        B.fallback(**kw)
+    monkeypatch.setenv("NITRIX_STRICT_BACKEND", "1")
+    with pytest.raises(B.NitrixBackendError):
+        B.fallback(**kw)
+
+
+def test_entry_point_validation_errors():
+    from nitrix_b200.nn import attention as A
+
+    x3 = torch.zeros(2, 4, 8)
+    with pytest.raises(ValueError, match="at least 3 dims"):
+        A.scaled_dot_product_attention(torch.zeros(4, 8), x3, x3)
+    with pytest.raises(ValueError, match="head-dim mismatch"):
+        A.scaled_dot_product_attention(x3, torch.zeros(2, 4, 6), x3)
+    with pytest.raises(ValueError, match="key-length mismatch"):
+        A.scaled_dot_product_attention(x3, x3, torch.zeros(2, 5, 8))
+
+
+def test_own_extent_canonicalisation():
+    from nitrix_b200.nn.attention import _to_own_extent
+
+    lead, h, s, t = (2, 3), 4, 5, 6
+    assert _to_own_extent(torch.zeros(4, 5, 6), lead, h, s, t).shape == (1, 4, 5, 6)
+    assert _to_own_extent(torch.zeros(2, 3, 1, 1, 6), lead, h, s, t).shape == (6, 1, 1, 6)
+    assert _to_own_extent(torch.zeros(2, 1, 4, 5, 6), lead, h, s, t).shape == (6, 4, 5, 6)
+    assert _to_own_extent(torch.zeros(6), lead, h, s, t).shape == (1, 1, 1, 6)
+    with pytest.raises(ValueError):
+        _to_own_extent(torch.zeros(7), lead, h, s, t)
+
+
+def test_bh_partition_covers_everything_once():
+    from nitrix_b200.parallel import bh_partition, shard_axis
+
+    for n in (0, 1, 7, 16, 128, 513):
+        for w in (1, 2, 3, 4, 8):
+            spans = [bh_partition(n, w, r) for r in range(w)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    assert shard_axis(32, 8, 8) == "batch" and shard_axis(1, 16, 8) == "heads" and shard_axis(3, 5, 2) == "pairs"

@@ -1,0 +1,313 @@
+"""GPU parity: the CUDA library (through its C ABI) against the CPU oracle.
+
+Structure follows the reference's kernel tests
+(``tests/test_nn_attention_kernel.py``: forward parity ``:83-96``, gradient
+parity with loss ``sum(out**2)`` and max-relative error ``:102-140``) plus its
+golden corpus (``tests/test_nn_attention.py:41-70``).
+
+Tolerances.  fp32: 1e-4 relative (max-abs error over max-abs reference).
+bf16 / fp16: 2e-2 max-abs against the oracle's FP32 result on the same
+(already quantised) inputs, for outputs and for gradients.
+"""
+import pathlib
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+import _cases
+from oracle import sdpa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+GOLD = pathlib.Path(__file__).parent / "golden"
+FP32_REL = 1e-4
+LOWP_ABS = 2e-2
+
+
+def _nb():
+    import nitrix_b200
+    from nitrix_b200.nn import attention
+
+    return nitrix_b200, attention
+
+
+def relerr(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-30))
+
+
+def abserr(a, b):
+    return float((a.double().cpu() - b.double().cpu()).abs().max())
+
+
+def run_both(q, k, v, kw, dtype, backend, dout_seed=5, want_dbias=True):
+    """Library result on the GPU and oracle result on the CPU for the same quantised inputs."""
+    _, att = _nb()
+    kw = dict(kw)
+    bias = kw.pop("bias", None)
+    mask = kw.pop("mask", None)
+    qd, kd, vd = (x.to(dtype) for x in (q, k, v))
+    bd = None if bias is None else bias.to(dtype)
+    dout = torch.from_numpy(np.random.RandomState(dout_seed).standard_normal(
+        (*q.shape[:-1], v.shape[-1])).astype(np.float32)).to(dtype)
+    # oracle in fp32 on the quantised values (fp64 for fp32 inputs)
+    acc = torch.float64 if dtype == torch.float32 else torch.float32
+    ref = O.reference_grads_torch(qd, kd, vd, dout, bias=bd, mask=mask, acc_dtype=acc,
+                                  want_dbias=want_dbias and bias is not None, **kw)
+    dev = "cuda"
+    leaves = [x.to(dev).requires_grad_(True) for x in (qd, kd, vd)]
+    bg = None if bd is None else bd.to(dev).requires_grad_(want_dbias)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = att.scaled_dot_product_attention(*leaves, bias=bg, mask=None if mask is None else mask.to(dev),
+                                               backend=backend, **kw)
+    wrt = leaves + ([bg] if (bg is not None and want_dbias) else [])
+    grads = torch.autograd.grad(out, wrt, grad_outputs=dout.to(dev))
+    torch.cuda.synchronize()
+    got = [out.detach(), *grads] + ([None] if len(grads) == 3 else [])
+    return got, list(ref)
+
+
+def check(got, ref, dtype, names=("out", "dq", "dk", "dv", "dbias")):
+    for name, a, b in zip(names, got, ref):
+        if b is None:
+            assert a is None, name
+            continue
+        assert a.shape == b.shape, (name, a.shape, b.shape)
+        assert a.dtype == dtype, (name, a.dtype)
+        assert torch.isfinite(a).all(), name
+        if dtype == torch.float32:
+            assert relerr(a, b) < FP32_REL, (name, relerr(a, b))
+        else:
+            assert abserr(a, b) < LOWP_ABS * max(1.0, float(b.abs().max())), (name, abserr(a, b))
+
+
+# --------------------------------------------------------------------------
+# golden corpus of the reference (fp32; the CUDA-core family)
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["dense", "windowed_bias", "causal", "cross", "qk_norm"])
+def test_golden_forward(name):
+    nb, att = _nb()
+    z = np.load(GOLD / f"attention_{name}_float32.npz")
+    kw = {"causal": bool(z["causal"])}
+    if "bias" in z.files:
+        kw["bias"] = torch.from_numpy(z["bias"]).cuda()
+    if "qk_norm" in z.files:
+        kw["qk_norm"] = bool(z["qk_norm"])
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        got = att.scaled_dot_product_attention(*(torch.from_numpy(z[n]).cuda() for n in "qkv"), **kw)
+    want = torch.from_numpy(z["out"])
+    # `cross` was stored from TF32 matmuls: it only holds to the fused-kernel budget
+    tol = 2e-3 if name == "cross" else FP32_REL
+    np.testing.assert_allclose(got.cpu().numpy(), want.numpy(), atol=tol, rtol=tol)
+
+
+# --------------------------------------------------------------------------
+# the reference's kernel-test shapes, every operand combination
+# --------------------------------------------------------------------------
+CASES = ["dense", "bias", "causal", "mask", "cross", "bias_causal", "bias_mask", "full_bias_mask",
+         "mask_b1st", "key_padding", "key_bias"]
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_simt_fp32_parity(name):
+    q, k, v, kw = _cases.kernel_case(name)
+    got, ref = run_both(q, k, v, kw, torch.float32, "cuda-simt")
+    check(got, ref, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", ["bias_mask", "causal", "key_padding"])
+def test_simt_low_precision_parity(name, dtype):
+    q, k, v, kw = _cases.kernel_case(name)
+    got, ref = run_both(q, k, v, kw, dtype, "cuda-simt")
+    check(got, ref, dtype)
+
+
+def test_config1_fp32():
+    q, k, v, kw = _cases.config1()
+    got, ref = run_both(q, k, v, kw, torch.float32, "auto")
+    check(got, ref, torch.float32)
+    # masked keys get an exactly-zero bias gradient
+    assert (got[4][1, :, :, -32:] == 0).all()
+
+
+@pytest.mark.parametrize("shape", [dict(s=100, t=77, d=40, dv=24), dict(s=28, t=28, d=16), dict(s=1, t=300, d=96),
+                                   dict(s=130, t=5, d=256, dv=8)])
+def test_simt_ragged_shapes(shape):
+    q, k, v, kw = _cases.kernel_case("full_bias_mask", **shape)
+    got, ref = run_both(q, k, v, kw, torch.float32, "cuda-simt")
+    check(got, ref, torch.float32)
+
+
+def test_causal_cross_lengths_clamped():
+    """causal with s > t and s < t: indices aligned at zero (reference _reference.py:166-170)."""
+    for s, t in ((192, 64), (64, 192)):
+        q, k, v, kw = _cases.kernel_case("causal", s=s, t=t)
+        got, ref = run_both(q, k, v, kw, torch.float32, "cuda-simt")
+        check(got, ref, torch.float32)
+
+
+def test_leading_dims_and_broadcast_bias_grad():
+    """(2, 3, h, s, d) batches; bias (h, s, t) shared over both: dbias is reduced over them."""
+    _, att = _nb()
+    rng = np.random.RandomState(0)
+    mk = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float32))
+    q, k, v, bias = mk(2, 3, 2, 20, 16), mk(2, 3, 2, 24, 16), mk(2, 3, 2, 24, 16), mk(2, 20, 24)
+    dout = mk(2, 3, 2, 20, 16)
+    ref = O.reference_grads_torch(q, k, v, dout, bias=bias, acc_dtype=torch.float64)
+    leaves = [x.cuda().requires_grad_(True) for x in (q, k, v, bias)]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = att.scaled_dot_product_attention(*leaves[:3], bias=leaves[3])
+    grads = torch.autograd.grad(out, leaves, grad_outputs=dout.cuda())
+    check([out.detach(), *grads], list(ref), torch.float32)
+    assert grads[3].shape == bias.shape
+
+
+def test_fully_masked_row_is_nan():
+    _, att = _nb()
+    q = torch.ones(1, 1, 2, 16, device="cuda")
+    kv = torch.ones(1, 1, 3, 16, device="cuda")
+    mask = torch.tensor([[True, True, True], [False, False, False]], device="cuda")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = att.scaled_dot_product_attention(q, kv, kv, mask=mask)
+    assert torch.isfinite(out[0, 0, 0]).all() and torch.isnan(out[0, 0, 1]).all()
+
+
+def test_empty_batch_and_empty_queries():
+    _, att = _nb()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = att.scaled_dot_product_attention(torch.empty(0, 2, 8, 16, device="cuda"),
+                                               torch.empty(0, 2, 8, 16, device="cuda"),
+                                               torch.empty(0, 2, 8, 16, device="cuda"))
+        assert out.shape == (0, 2, 8, 16)
+        out = att.scaled_dot_product_attention(torch.empty(1, 2, 0, 16, device="cuda"),
+                                               torch.randn(1, 2, 8, 16, device="cuda"),
+                                               torch.randn(1, 2, 8, 16, device="cuda"))
+        assert out.shape == (1, 2, 0, 16)
+
+
+def test_bh_range_partition_matches_whole():
+    """Two half-range calls on shared buffers equal one whole call (the multi-GPU slice)."""
+    _, att = _nb()
+    q, k, v, kw = _cases.kernel_case("bias_mask")
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    bias = kw["bias"].cuda().reshape(1, 2, 128, 128)
+    mask = kw["mask"].cuda()
+    from nitrix_b200 import _cabi
+    whole, lse = att.sdpa_forward(q, k, v, bias, mask, scale=0.125, kernel=_cabi.KERNEL_SIMT)
+    out = torch.zeros_like(whole)
+    lse2 = torch.zeros_like(lse)
+    att.sdpa_forward(q, k, v, bias, mask, scale=0.125, kernel=_cabi.KERNEL_SIMT, bh_range=(0, 3), out=out, lse=lse2)
+    att.sdpa_forward(q, k, v, bias, mask, scale=0.125, kernel=_cabi.KERNEL_SIMT, bh_range=(3, 4), out=out, lse=lse2)
+    assert torch.equal(out, whole) and torch.equal(lse, lse2)
+
+
+def test_lse_is_base2_logsumexp():
+    _, att = _nb()
+    q, k, v, kw = _cases.kernel_case("bias")
+    _, lse_ref = O.reference_sdpa_numpy(q.numpy(), k.numpy(), v.numpy(), bias=kw["bias"].numpy(), return_lse=True)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        _, lse = att.scaled_dot_product_attention(q.cuda(), k.cuda(), v.cuda(), bias=kw["bias"].cuda(), return_lse=True)
+    np.testing.assert_allclose(lse.cpu().numpy(), lse_ref, atol=1e-4, rtol=1e-5)
+
+
+def test_backward_workspace_is_far_below_score_matrix():
+    """Gross-memory contract (reference tests/test_nn_attention_kernel.py:197-252): scratch << B*H*S*T*4."""
+    import ctypes as C
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    B, H, S, D = 2, 4, 1024, 64
+    q = torch.empty(B, H, S, D, device="cuda", dtype=torch.bfloat16)
+    p = _cabi.new_params()
+    att._fill_common(p, q, q, q, q, q, None, None, 0.125, False, _cabi.KERNEL_AUTO, None)
+    p.dout = p.dq = p.dk = p.dv = q.data_ptr()
+    for name in ("dout_stride", "dq_stride", "dk_stride", "dv_stride"):
+        getattr(p, name)[:] = list(q.stride())
+    need = C.c_size_t(0)
+    assert _cabi.lib().nb200_sdpa_workspace_bytes(C.byref(p), _cabi.PASS_BWD, C.byref(need)) == 0
+    assert need.value < B * H * S * S * 4 // 8
+
+
+# --------------------------------------------------------------------------
+# tensor-core (TMA + tcgen05) family: bf16 / fp16, D in {64, 128}
+# --------------------------------------------------------------------------
+def _device_ok():
+    from nitrix_b200 import _cabi
+    torch.cuda.synchronize()
+    rc = _cabi.lib().nb200_device_status(torch.cuda.current_device())
+    assert rc == 0, _cabi.last_error()
+
+
+def _assert_plans_tc(q, k, v, kw, dtype, which=0):
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    b, h, s, d = q.shape
+    t = k.shape[2]
+    lead = (b,)
+    bias = kw.get("bias")
+    mask = kw.get("mask")
+    b4 = None if bias is None else att._to_own_extent(bias.to(dtype).cuda(), lead, h, s, t)
+    m4 = None if mask is None else att._to_own_extent(mask.cuda(), lead, h, s, t)
+    chosen = att.planned_kernel(q.to(dtype).cuda(), k.to(dtype).cuda(), v.to(dtype).cuda(), b4, m4,
+                                causal=kw.get("causal", False), which=which)
+    assert chosen == _cabi.KERNEL_TCGEN05
+
+
+TC_CASES = ["dense", "bias", "causal", "mask", "cross", "bias_causal", "full_bias_mask", "mask_b1st",
+            "key_padding", "key_bias"]
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", TC_CASES)
+def test_tc_parity(name, dtype, d):
+    q, k, v, kw = _cases.kernel_case(name, s=256, t=512 if name == "cross" else 384 if "bias" in name else 256, d=d)
+    if "causal" in name:
+        q, k, v, kw = _cases.kernel_case(name, s=384, t=384, d=d)
+    _assert_plans_tc(q, k, v, kw, dtype)
+    got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100")
+    _device_ok()
+    check(got, ref, dtype)
+
+
+def test_tc_single_tile_and_odd_tile_count():
+    for s, t in ((128, 128), (384, 128), (128, 640)):
+        q, k, v, kw = _cases.kernel_case("bias_mask", s=s, t=t, d=64, b=1, h=3)
+        _assert_plans_tc(q, k, v, kw, torch.bfloat16)
+        got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100")
+        _device_ok()
+        check(got, ref, torch.bfloat16)
+
+
+def test_tc_matches_simt_on_same_inputs():
+    """The two kernel families agree with each other far inside the low-precision budget."""
+    _, att = _nb()
+    q, k, v, kw = _cases.kernel_case("bias_causal", s=512, t=512, d=128)
+    args = [x.to(torch.bfloat16).cuda() for x in (q, k, v)]
+    bias = kw["bias"].to(torch.bfloat16).cuda()
+    a = att.scaled_dot_product_attention(*args, bias=bias, causal=True, backend="cuda-sm100")
+    b = att.scaled_dot_product_attention(*args, bias=bias, causal=True, backend="cuda-simt")
+    _device_ok()
+    assert abserr(a, b) < 1e-2
+
+
+def test_tc_noncontiguous_heads_layout():
+    """q/k/v stored (B, S, H, D) and viewed as (B, H, S, D): strides go straight into the TMA maps."""
+    _, att = _nb()
+    g = torch.Generator().manual_seed(0)
+    B, H, S, D = 2, 3, 256, 64
+    qkv = [torch.randn(B, S, H, D, generator=g).to(torch.bfloat16) for _ in range(3)]
+    views_cpu = [x.permute(0, 2, 1, 3) for x in qkv]
+    ref = O.reference_sdpa_torch(*[x.float() for x in views_cpu], causal=True)
+    views = [x.cuda().permute(0, 2, 1, 3) for x in qkv]
+    got = att.scaled_dot_product_attention(*views, causal=True, backend="cuda-sm100")
+    _device_ok()
+    assert abserr(got, ref) < LOWP_ABS
