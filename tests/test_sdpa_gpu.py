@@ -296,7 +296,7 @@ def test_tc_matches_simt_on_same_inputs():
     a = att.scaled_dot_product_attention(*args, bias=bias, causal=True, backend="cuda-sm100")
     b = att.scaled_dot_product_attention(*args, bias=bias, causal=True, backend="cuda-simt")
     _device_ok()
-    assert abserr(a, b) < 1e-2
+    assert abserr(a, b) < 2e-2  # one bf16 ulp at |x| < 4
 
 
 def test_tc_noncontiguous_heads_layout():
