@@ -132,6 +132,24 @@ NB200_API int nb200_sdpa_fwd(const nb200_sdpa_params* p, void* cuda_stream);
  * dout).  Replaces reference attention.py:600-653 and :390-499. */
 NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream);
 
+/* Backward pass for callers that cannot allocate device memory (no counterpart
+ * in the reference, whose runtime allocates scratch for its kernels itself).
+ * Same operands, results and status codes as nb200_sdpa_bwd, but the scratch the
+ * backward needs (row-wise delta; fp32 accumulator of a broadcast bias gradient)
+ * lives in a fixed NB200_STATIC_SCRATCH_BYTES array inside the library image on
+ * every GPU that loads it; p->workspace and p->workspace_bytes are ignored.
+ *  - Allocates nothing: no cudaMalloc / cudaFree, no allocating library call.
+ *  - A problem whose scratch (nb200_sdpa_workspace_bytes, backward pass) exceeds
+ *    NB200_STATIC_SCRATCH_BYTES is rejected with NB200_ERR_WORKSPACE.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current); make that first call before any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous
+ *    call's contents; what must start at zero is cleared on the stream by each
+ *    call.  Calls whose GPU work may overlap (different streams) race on it:
+ *    serialise them. */
+#define NB200_STATIC_SCRATCH_BYTES (8u << 20)
+NB200_API int nb200_sdpa_bwd_static_scratch(const nb200_sdpa_params* p, void* cuda_stream);
+
 /* Number of kernels this library has enqueued since load (all threads). */
 NB200_API uint64_t nb200_launch_count(void);
 

@@ -16,6 +16,7 @@ F32, BF16, F16 = 0, 1, 2
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_LAUNCH, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
 PASS_FWD, PASS_BWD = 0, 1
+STATIC_SCRATCH_BYTES = 8 << 20
 
 _I64x4 = C.c_int64 * 4
 
@@ -52,6 +53,7 @@ EXPORTS = (
     "nb200_sdpa_workspace_bytes",
     "nb200_sdpa_fwd",
     "nb200_sdpa_bwd",
+    "nb200_sdpa_bwd_static_scratch",
     "nb200_launch_count",
     "nb200_device_status",
 )
@@ -81,6 +83,7 @@ def lib() -> C.CDLL:
     L.nb200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaParams), C.c_int, C.POINTER(C.c_size_t)]
     L.nb200_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
     L.nb200_sdpa_bwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
+    L.nb200_sdpa_bwd_static_scratch.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
     if L.nb200_version() != ABI_VERSION:
         raise NativeLibraryError(f"{path}: ABI {L.nb200_version()} != expected {ABI_VERSION}")
     return L
