@@ -1,17 +1,590 @@
-// Tensor-core backward kernels (dq / dk / dv / dbias).
+// Backward flash attention for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// TMEM accumulators; p and ds are recomputed per tile from (q, k, v, bias,
+// mask, lse, delta) as in the reference's backward kernels
+// (reference src/nitrix/_kernels/cuda/attention.py:272-332 `_bwd_kv_kernel`,
+// :335-387 `_bwd_q_kernel`), on 128 x 64 tiles instead of 32 x 32.
+//
+// One kernel template serves both directions:
+//   query-major (kKeyMajor = false): a CTA owns 128 query rows, streams 64-key
+//     steps; S = Q K^T, dP = dO V^T, ds = p (dP - delta); dQ += ds K; writes
+//     dq and, when asked, the dbias tile (ds in bias dtype).
+//   key-major (kKeyMajor = true): a CTA owns 128 keys, streams 64-query steps;
+//     S^T = K Q^T, dP^T = V dO^T; dV += p^T dO; dK += ds^T Q; writes dk, dv.
+// Naming below: X1, X2 are the owner's two 128-row operands (Q, dO | K, V);
+// Y1, Y2 the streamed 64-row operands (K, V | Q, dO).  Per step:
+//   P1 = X1 Y1^T, P2 = X2 Y2^T            (SS tcgen05.mma, 128 x 64, fp32 in TMEM)
+//   E1 = p, E2 = ds as 16-bit             (written over P1 / P2 in TMEM)
+//   ACC1 += E1 Y2 (key-major: dV), ACC2 += E2 Y1 (dQ | dK)
+//                                          (TS tcgen05.mma, Y consumed MN-major)
+// TMEM columns: stage s in {0,1}: P1 at 128 s, P2 at 128 s + 64; ACC1 at 256,
+// ACC2 at 256 + D.  Twelve warps: 0 TMA producer (X once, Y ring), 1 bias
+// producer, 2 MMA issuer, 3 TMEM owner, 4-7 / 8-11 two element-wise groups that
+// take alternate steps (one owner row per thread).  All waits are bounded.
 #include "sdpa_tc_bwd.cuh"
 
 namespace nb200 {
 namespace tc {
 
-bool bwd_supported(const Problem&, int, int, const char** why) {
-  *why = "the tensor-core backward is not available yet";
-  return false;
+using namespace sm100;
+
+namespace {
+
+constexpr int kThreads = 384;
+constexpr int kStep = 64;                     // streamed rows per step
+constexpr int kYBoxBytes = kStep * 128;       // one 64-row x 128-byte TMA box
+
+struct BwdArgs {
+  int H, S, T;
+  int bh_begin;
+  int causal;
+  float scale;
+  int bias_mode;
+  int bias_b_mul, bias_h_mul;
+  const void* bias;             // key mode base
+  int64_t bias_bs, bias_hs;
+  MaskBits mask;
+  int mask_key_only;            // key-major: the mask has no query axis (use mask.rows per key)
+  const float* lse;
+  const float* delta;
+  void* out1; int64_t o1s[3];   // key-major: dv
+  void* out2; int64_t o2s[3];   // dq | dk
+  void* dbias; int64_t dbs[4];  // query-major only; null when not requested
+  int* status;
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kXBytes = kTile * D * 2;                 // one owner operand
+  static constexpr int kYBytes = kStep * D * 2;                 // one streamed operand
+  static constexpr int kYStages = D == 64 ? 4 : 3;
+  static constexpr int kYStageBytes = 2 * kYBytes + 1024;       // Y1, Y2, then lse[64] + delta[64] (key-major)
+  static constexpr int kBiasSlots = 2;                          // 16 KB each
+  static constexpr int kX = 0;
+  static constexpr int kY = kX + 2 * kXBytes;
+  static constexpr int kBias = kY + kYStages * kYStageBytes;
+  static constexpr int kBars = kBias + kBiasSlots * kBoxBytes;
+  // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2]
+  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4;
+  static constexpr int kMisc = kBars + 8 * kNumBars;
+  static constexpr int kTotal = kMisc + 16;
+};
+
+template <int D, bool kBf16, bool kKeyMajor>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
+                   const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
+                   const __grid_constant__ CUtensorMap tm_bias, const BwdArgs a) {
+  using L = BwdSmem<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+  constexpr int NY = L::kYStages;
+  constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, E_READY = PROD_FULL + 2,
+                ACC_DONE = E_READY + 2, B_FULL = ACC_DONE + 1, B_EMPTY = B_FULL + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = a.bh_begin + blockIdx.y;
+  const int b = bh / a.H, h = bh - b * a.H;
+  const int n_owner = kKeyMajor ? a.T : a.S;     // owner axis length
+  const int n_stream = kKeyMajor ? a.S : a.T;    // streamed axis length
+  // causal work per owner tile grows with the query index and shrinks with the key index: heaviest first
+  const int otile = (a.causal && !kKeyMajor) ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int o0 = otile * kTile;
+  int s_begin = 0, s_end = (n_stream + kStep - 1) / kStep;
+  if (a.causal) {
+    if (kKeyMajor) s_begin = min(s_end, o0 / kStep);                       // queries i >= first key
+    else s_end = min(s_end, (min(o0 + kTile, n_owner) + kStep - 1) / kStep);  // keys j <= last query
+  }
+  const int n_steps = s_end - s_begin;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < L::kNumBars; ++i) {
+      uint32_t count = 1;
+      if (i >= E_READY && i < E_READY + 2) count = 128;
+      if (i >= B_EMPTY && i < B_EMPTY + 2) count = 4;
+      mbar_init(bar(i), count);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 3) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tm_acc1 = tmem + 256, tm_acc2 = tmem + 256 + D;
+
+  if (warp == 0) {
+    // ---------------- X / Y producer ----------------
+    if (elect_one() && n_steps > 0) {
+      tma_prefetch_desc(&tm_x1);
+      tma_prefetch_desc(&tm_x2);
+      tma_prefetch_desc(&tm_y1);
+      tma_prefetch_desc(&tm_y2);
+      mbar_expect_tx(bar(X_FULL), 2 * L::kXBytes);
+#pragma unroll
+      for (int x = 0; x < D / 64; ++x) {
+        tma_load_4d(sbase + L::kX + x * kBoxBytes, &tm_x1, bar(X_FULL), x * 64, o0, h, b);
+        tma_load_4d(sbase + L::kX + L::kXBytes + x * kBoxBytes, &tm_x2, bar(X_FULL), x * 64, o0, h, b);
+      }
+      for (int n = 0; n < n_steps; ++n) {
+        const int st = n % NY;
+        if (!wait_or_abort(bar(Y_EMPTY + st), ((n / NY) & 1) ^ 1, abort_flag, a.status, 201)) break;
+        const int r0 = (s_begin + n) * kStep;
+        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+        mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + (kKeyMajor ? 512 : 0));
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x) {
+          tma_load_4d(ybase + x * kYBoxBytes, &tm_y1, bar(Y_FULL + st), x * 64, r0, h, b);
+          tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_y2, bar(Y_FULL + st), x * 64, r0, h, b);
+        }
+        if (kKeyMajor) {
+          // lse and delta of the step's 64 queries: two 256-byte bulk copies on the same barrier
+          const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+          bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, 256, bar(Y_FULL + st));
+          bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, 256, bar(Y_FULL + st));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- bias producer ----------------
+    if (a.bias_mode == kBiasTile && elect_one()) {
+      tma_prefetch_desc(&tm_bias);
+      for (int n = 0; n < n_steps; ++n) {
+        const int slot = n & 1;
+        if (!wait_or_abort(bar(B_EMPTY + slot), ((n >> 1) & 1) ^ 1, abort_flag, a.status, 202)) break;
+        const int r0 = (s_begin + n) * kStep;
+        mbar_expect_tx(bar(B_FULL + slot), kBoxBytes);
+        const uint32_t dst = sbase + L::kBias + slot * kBoxBytes;
+        if (kKeyMajor) {  // 64 query rows x 128 keys: two 64 x 64 boxes
+          tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), o0, r0, h * a.bias_h_mul, b * a.bias_b_mul);
+          tma_load_4d(dst + kYBoxBytes, &tm_bias, bar(B_FULL + slot), o0 + 64, r0, h * a.bias_h_mul, b * a.bias_b_mul);
+        } else {          // 128 query rows x 64 keys: one 64 x 128 box
+          tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), r0, o0, h * a.bias_h_mul, b * a.bias_b_mul);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one() && n_steps > 0) {
+      constexpr uint32_t idesc_prod = make_idesc(kBf16, kTile, kStep, false, false);
+      constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, D, false, true);
+      bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 203);
+      for (int n = 0; n <= n_steps && ok; ++n) {
+        if (n < n_steps) {
+          const int st = n % NY, s = n & 1;
+          ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 204);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+          const uint32_t p1 = tmem + s * 128, p2 = p1 + 64;
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t xo = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+            const uint32_t yo = (kk / 4) * kYBoxBytes + (kk % 4) * 32;
+            mma_ss(p1, make_smem_desc(sbase + L::kX + xo, 16, 1024), make_smem_desc(ybase + yo, 16, 1024), idesc_prod,
+                   kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t xo = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+            const uint32_t yo = (kk / 4) * kYBoxBytes + (kk % 4) * 32;
+            mma_ss(p2, make_smem_desc(sbase + L::kX + L::kXBytes + xo, 16, 1024),
+                   make_smem_desc(ybase + L::kYBytes + yo, 16, 1024), idesc_prod, kk > 0 ? 1u : 0u);
+          }
+          mma_commit(bar(PROD_FULL + s));
+        }
+        if (n > 0) {
+          const int m = n - 1, st = m % NY, s = m & 1;
+          ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 205);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+          const uint32_t e1 = tmem + s * 128, e2 = e1 + 64;
+#pragma unroll
+          for (int kk = 0; kk < kStep / 16; ++kk) {
+            const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
+            if (kKeyMajor)
+              mma_ts(tm_acc1, e1 + kk * 8, make_smem_desc(ybase + L::kYBytes + kk * 2048, kYBoxBytes, 1024), idesc_acc, acc);
+            mma_ts(tm_acc2, e2 + kk * 8, make_smem_desc(ybase + kk * 2048, kYBoxBytes, 1024), idesc_acc, acc);
+          }
+          mma_commit(bar(Y_EMPTY + st));
+          if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- element-wise groups (one owner row per thread) ----------------
+    const int grp = (warp - 4) >> 2;
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int orow = o0 + r;                       // query row (query-major) or key (key-major)
+    const uint32_t lane_addr = uint32_t(wq * 32) << 16;
+    bool ok = true;
+    float lse_row = 0.f, delta_row = 0.f;
+    if (!kKeyMajor && orow < a.S) {
+      const int64_t ro = (int64_t(b) * a.H + h) * a.S + orow;
+      lse_row = a.lse[ro];
+      delta_row = a.delta[ro];
+    }
+    // packed mask words of this owner row
+    const uint32_t* mbits = nullptr;
+    bool key_dropped = false;
+    if (a.mask.rows) {
+      if (!kKeyMajor) {
+        mbits = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride + int64_t(min(orow, a.S - 1)) * a.mask.row_stride;
+      } else if (a.mask_key_only) {
+        const uint32_t* krow = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride;
+        key_dropped = orow >= a.T || !((krow[orow >> 5] >> (orow & 31)) & 1u);
+      } else {
+        mbits = a.mask.cols + b * a.mask.tb_stride + h * a.mask.th_stride + int64_t(min(orow, a.T - 1)) * a.mask.tkey_stride;
+      }
+    }
+    const uint8_t* bias_key = nullptr;
+    float bias_own = 0.f;  // key-major per-key bias: one value for this thread's key
+    if (a.bias_mode == kBiasKey) {
+      bias_key = reinterpret_cast<const uint8_t*>(a.bias) + 2 * (b * a.bias_bs + h * a.bias_hs);
+      if (kKeyMajor && orow < a.T) {
+        const uint16_t raw = *reinterpret_cast<const uint16_t*>(bias_key + 2 * orow);
+        bias_own = kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw));
+      }
+    }
+
+    for (int n = grp; n < n_steps && ok; n += 2) {
+      const int s = n & 1;
+      const int st = n % NY;
+      const int r0 = (s_begin + n) * kStep;          // first streamed row of the step
+      // keep bits over the step's 64 streamed rows
+      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
+      if (mbits) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(mbits + (r0 >> 5)));
+        keep[0] = w.x; keep[1] = w.y;
+      }
+      if (kKeyMajor) {
+        // queries r0 + c: need c < S - r0, and (causal) r0 + c >= key
+        const int hi = a.S - r0;
+        const int lo = a.causal ? orow - r0 : 0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int nh = hi - 32 * i, nl = lo - 32 * i;
+          const uint32_t mh = nh >= 32 ? 0xffffffffu : (nh <= 0 ? 0u : ((1u << nh) - 1u));
+          const uint32_t ml = nl <= 0 ? 0xffffffffu : (nl >= 32 ? 0u : ~((1u << nl) - 1u));
+          keep[i] &= mh & ml;
+        }
+        if (key_dropped) keep[0] = keep[1] = 0u;
+      } else {
+        int n_keep = a.T - r0;
+        if (a.causal) n_keep = min(n_keep, orow - r0 + 1);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int nk = n_keep - 32 * i;
+          keep[i] &= nk >= 32 ? 0xffffffffu : (nk <= 0 ? 0u : ((1u << nk) - 1u));
+        }
+      }
+
+      ok = wait_or_abort(bar(PROD_FULL + s), (n >> 1) & 1, abort_flag, a.status, 206);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tP1 = tmem + s * 128 + lane_addr, tP2 = tP1 + 64;
+      float t[kStep], dp[kStep];
+      {
+        uint32_t raw[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld32(tP1 + c * 32, raw);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) t[c * 32 + i] = __uint_as_float(raw[i]);
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld32(tP2 + c * 32, raw);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) dp[c * 32 + i] = __uint_as_float(raw[i]);
+        }
+      }
+      // logits t = s * scale + bias
+      if (a.bias_mode == kBiasTile) {
+        const int slot = n & 1;
+        ok = wait_or_abort(bar(B_FULL + slot), (n >> 1) & 1, abort_flag, a.status, 207);
+        if (!ok) break;
+        const uint8_t* sl = smem + L::kBias + slot * kBoxBytes;
+        if (kKeyMajor) {
+          // element (query c, key r): box r / 64, row c, 16-byte chunk ((r % 64) / 8) ^ (c % 8)
+          const uint8_t* colbase = sl + (r >> 6) * kYBoxBytes + (r & 7) * 2;
+          const int chunk = (r & 63) >> 3;
+#pragma unroll
+          for (int c = 0; c < kStep; ++c) {
+            const uint16_t raw = *reinterpret_cast<const uint16_t*>(colbase + c * 128 + ((chunk ^ (c & 7)) << 4));
+            const float bv = kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw));
+            t[c] = fmaf(t[c], a.scale, bv);
+          }
+        } else {
+          const uint8_t* srow = sl + r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 w = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 bv = unpack2<kBf16>(ww[e]);
+              t[c * 8 + e * 2] = fmaf(t[c * 8 + e * 2], a.scale, bv.x);
+              t[c * 8 + e * 2 + 1] = fmaf(t[c * 8 + e * 2 + 1], a.scale, bv.y);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
+      } else if (a.bias_mode == kBiasKey && !kKeyMajor) {
+        const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * r0);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 w = __ldg(bk + c);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 bv = unpack2<kBf16>(ww[e]);
+            t[c * 8 + e * 2] = fmaf(t[c * 8 + e * 2], a.scale, bv.x);
+            t[c * 8 + e * 2 + 1] = fmaf(t[c * 8 + e * 2 + 1], a.scale, bv.y);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kStep; ++c) t[c] = fmaf(t[c], a.scale, bias_own);
+      }
+      // p = exp2(t log2e - lse), ds = p (dp - delta)
+      const float4* ld4 = reinterpret_cast<const float4*>(smem + L::kY + st * L::kYStageBytes + 2 * L::kYBytes);
+      uint32_t e1[kStep / 2], e2[kStep / 2];
+#pragma unroll
+      for (int c4 = 0; c4 < kStep / 4; ++c4) {
+        float ls[4], dl[4];
+        if (kKeyMajor) {
+          const float4 lv = ld4[c4], dv4 = ld4[16 + c4];
+          ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
+          dl[0] = dv4.x; dl[1] = dv4.y; dl[2] = dv4.z; dl[3] = dv4.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { ls[e] = lse_row; dl[e] = delta_row; }
+        }
+        float p[4], ds[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = c4 * 4 + e;
+          const bool kp = (keep[c >> 5] >> (c & 31)) & 1u;
+          p[e] = kp ? exp2f(fmaf(t[c], kLog2e, -ls[e])) : 0.f;
+          ds[e] = p[e] * (dp[c] - dl[e]);
+          t[c] = ds[e];  // kept for the dbias store
+        }
+        e1[c4 * 2] = pack2<kBf16>(p[0], p[1]);
+        e1[c4 * 2 + 1] = pack2<kBf16>(p[2], p[3]);
+        e2[c4 * 2] = pack2<kBf16>(ds[0], ds[1]);
+        e2[c4 * 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
+      }
+      if (kKeyMajor) tmem_st32(tP1, e1);
+      tmem_st32(tP2, e2);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar(E_READY + s));
+      if (!kKeyMajor && a.dbias && orow < a.S) {
+        // dbias[row, r0 .. r0+63] = ds in bias dtype (the 16-bit pairs already packed in e2)
+        uint8_t* dst = reinterpret_cast<uint8_t*>(a.dbias) +
+                       2 * (b * a.dbs[0] + h * a.dbs[1] + int64_t(orow) * a.dbs[2] + r0);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(e2[c * 4], e2[c * 4 + 1], e2[c * 4 + 2], e2[c * 4 + 3]);
+      }
+    }
+
+    // ---------------- epilogue ----------------
+    if (!kKeyMajor && a.dbias && a.causal && orow < a.S) {
+      // key steps past the diagonal are never visited: their dbias is exactly zero
+      if (grp == 0) {
+        uint8_t* dst = reinterpret_cast<uint8_t*>(a.dbias) + 2 * (b * a.dbs[0] + h * a.dbs[1] + int64_t(orow) * a.dbs[2]);
+        for (int k0 = s_end * kStep; k0 < a.T; k0 += 8)
+          *reinterpret_cast<uint4*>(dst + 2 * k0) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (ok && n_steps > 0) ok = wait_or_abort(bar(ACC_DONE), 0, abort_flag, a.status, 208);
+    if (ok) {
+      tc_fence_after_sync();
+      // key-major: group 0 writes dv (ACC1), group 1 writes dk (ACC2 * scale).
+      // query-major: both groups write dq (ACC2 * scale), half of the columns each.
+      const uint32_t tacc = ((kKeyMajor && grp == 0) ? tm_acc1 : tm_acc2) + lane_addr;
+      const float mul = (kKeyMajor && grp == 0) ? 1.f : a.scale;
+      void* outp = (kKeyMajor && grp == 0) ? a.out1 : a.out2;
+      const int64_t* os = (kKeyMajor && grp == 0) ? a.o1s : a.o2s;
+      uint8_t* orow_ptr = reinterpret_cast<uint8_t*>(outp) + 2 * (b * os[0] + h * os[1] + int64_t(orow) * os[2]);
+      const int c_begin = kKeyMajor ? 0 : grp * (D / 64);
+      const int c_end = kKeyMajor ? D / 32 : (grp + 1) * (D / 64);
+      for (int c = c_begin; c < c_end; ++c) {
+        uint32_t o[32];
+        if (n_steps > 0) {
+          tmem_ld32(tacc + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (orow < n_owner) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2<kBf16>(__uint_as_float(o[i]) * mul, __uint_as_float(o[i + 1]) * mul);
+            w.y = pack2<kBf16>(__uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul);
+            w.z = pack2<kBf16>(__uint_as_float(o[i + 4]) * mul, __uint_as_float(o[i + 5]) * mul);
+            w.w = pack2<kBf16>(__uint_as_float(o[i + 6]) * mul, __uint_as_float(o[i + 7]) * mul);
+            *reinterpret_cast<uint4*>(orow_ptr + (c * 32 + i) * 2) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) drain_after_abort();
+  if (warp == 3) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
 }
-size_t bwd_workspace_bytes(const Problem&, int, int) { return 0; }
-int launch_bwd(const Problem&, int, int, void*, size_t, cudaStream_t) {
-  set_error("the tensor-core backward is not available yet");
-  return NB200_ERR_UNSUPPORTED;
+
+template <int D, bool kBf16, bool kKeyMajor>
+int launch_one(const CUtensorMap* maps, const BwdArgs& a, int n_tiles, int bh_count, cudaStream_t st) {
+  auto kernel = sdpa_bwd_tc_kernel<D, kBf16, kKeyMajor>;
+  const int smem = BwdSmem<D>::kTotal + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(sdpa_bwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
+    return NB200_ERR_LAUNCH;
+  }
+  dim3 grid(n_tiles, bh_count);
+  kernel<<<grid, kThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);
+  count_launch();
+  return check_launch(kKeyMajor ? "sdpa_bwd_tc_kernel<key-major>" : "sdpa_bwd_tc_kernel<query-major>");
+}
+
+template <bool kKeyMajor>
+int launch_dir(int D, bool bf16, const CUtensorMap* maps, const BwdArgs& a, int n_tiles, int bh_count, cudaStream_t st) {
+  if (D == 64) return bf16 ? launch_one<64, true, kKeyMajor>(maps, a, n_tiles, bh_count, st)
+                           : launch_one<64, false, kKeyMajor>(maps, a, n_tiles, bh_count, st);
+  return bf16 ? launch_one<128, true, kKeyMajor>(maps, a, n_tiles, bh_count, st)
+              : launch_one<128, false, kKeyMajor>(maps, a, n_tiles, bh_count, st);
+}
+
+int bias_mode_of(const Problem& pr) {
+  if (!pr.bias) return kBiasNone;
+  return (pr.bs[2] == 0 || pr.S == 1) ? kBiasKey : kBiasTile;
+}
+
+}  // namespace
+
+bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** why) {
+  // forward coverage (dtype, head dims, lengths, q/k/v/bias layout) was checked by the caller
+  if (pr.dbias_accum) { *why = "gradient of a broadcast bias needs a reduction"; return false; }
+  if (pr.lse && reinterpret_cast<uintptr_t>(pr.lse) % 16) { *why = "lse is not 16-byte aligned"; return false; }
+  if (pr.dout && (!tile_map_ok(pr.dout, pr.dos[2], pr.dos[1], pr.dos[0], pr.H, pr.B))) {
+    *why = "dout strides / alignment do not fit a TMA descriptor";
+    return false;
+  }
+  const void* outs[3] = {pr.dq, pr.dk, pr.dv};
+  const int64_t* strides[3] = {pr.dqs, pr.dks, pr.dvs};
+  for (int i = 0; i < 3; ++i) {
+    if (outs[i] && (reinterpret_cast<uintptr_t>(outs[i]) % 16 || strides[i][0] % 8 || strides[i][1] % 8 ||
+                    strides[i][2] % 8)) {
+      *why = "dq/dk/dv are not 16-byte aligned";
+      return false;
+    }
+  }
+  if (pr.dbias) {
+    // dbias is written as 16-byte row segments in bias dtype; a broadcast bias (reduction needed) is declined
+    const int64_t full[4] = {pr.B, pr.H, pr.S, pr.T};
+    for (int ax = 0; ax < 4; ++ax)
+      if (pr.bs[ax] == 0 && full[ax] > 1) { *why = "gradient of a broadcast bias needs a reduction"; return false; }
+    if (pr.dbs[3] != 1 || reinterpret_cast<uintptr_t>(pr.dbias) % 16 || pr.dbs[0] % 8 || pr.dbs[1] % 8 || pr.dbs[2] % 8) {
+      *why = "dbias layout is not 16-byte aligned with a unit key stride";
+      return false;
+    }
+  }
+  (void)dtype;
+  (void)bias_dtype;
+  return true;
+}
+
+size_t bwd_workspace_bytes(const Problem& pr, int, int) {
+  const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
+  const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
+  return mp.rows_bytes + mp.cols_bytes;
+}
+
+int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  (void)bias_dtype;
+  const char* why = "";
+  const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
+  const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
+  if (mp.rows_bytes + mp.cols_bytes > ws_bytes) {
+    set_error("backward mask bits need %zu workspace bytes", mp.rows_bytes + mp.cols_bytes);
+    return NB200_ERR_WORKSPACE;
+  }
+  BwdArgs a{};
+  if (int rc = launch_mask_pack(pr, mp, ws, &a.mask, stream)) return rc;
+  a.mask_key_only = key_only ? 1 : 0;
+  a.H = pr.H; a.S = pr.S; a.T = pr.T; a.bh_begin = pr.bh_begin;
+  a.causal = pr.causal; a.scale = pr.scale;
+  a.bias_mode = bias_mode_of(pr);
+  a.bias_b_mul = (pr.B > 1 && pr.bs[0] != 0) ? 1 : 0;
+  a.bias_h_mul = (pr.H > 1 && pr.bs[1] != 0) ? 1 : 0;
+  a.bias = pr.bias; a.bias_bs = pr.bs[0]; a.bias_hs = pr.bs[1];
+  a.lse = pr.lse; a.delta = pr.delta;
+  a.status = device_status_word();
+  if (!a.status) { set_error("device status word is unavailable"); return NB200_ERR_LAUNCH; }
+
+  // tensor maps: 128-row boxes for owner operands, 64-row boxes for streamed ones
+  CUtensorMap q128, k128, v128, g128, q64, k64, v64, g64, bias_q, bias_k;
+  bool ok = make_tile_map(&q128, pr.q, pr.S, pr.D, pr.H, pr.B, pr.qs[2], pr.qs[1], pr.qs[0], kTile, &why) &&
+            make_tile_map(&g128, pr.dout, pr.S, pr.D, pr.H, pr.B, pr.dos[2], pr.dos[1], pr.dos[0], kTile, &why) &&
+            make_tile_map(&k128, pr.k, pr.T, pr.D, pr.H, pr.B, pr.ks[2], pr.ks[1], pr.ks[0], kTile, &why) &&
+            make_tile_map(&v128, pr.v, pr.T, pr.D, pr.H, pr.B, pr.vs[2], pr.vs[1], pr.vs[0], kTile, &why) &&
+            make_tile_map(&q64, pr.q, pr.S, pr.D, pr.H, pr.B, pr.qs[2], pr.qs[1], pr.qs[0], kStep, &why) &&
+            make_tile_map(&g64, pr.dout, pr.S, pr.D, pr.H, pr.B, pr.dos[2], pr.dos[1], pr.dos[0], kStep, &why) &&
+            make_tile_map(&k64, pr.k, pr.T, pr.D, pr.H, pr.B, pr.ks[2], pr.ks[1], pr.ks[0], kStep, &why) &&
+            make_tile_map(&v64, pr.v, pr.T, pr.D, pr.H, pr.B, pr.vs[2], pr.vs[1], pr.vs[0], kStep, &why);
+  bias_q = q128;
+  bias_k = q128;
+  if (ok && a.bias_mode == kBiasTile)
+    ok = make_tile_map(&bias_q, pr.bias, pr.S, pr.T, pr.H, pr.B, pr.bs[2], pr.bs[1], pr.bs[0], kTile, &why) &&
+         make_tile_map(&bias_k, pr.bias, pr.S, pr.T, pr.H, pr.B, pr.bs[2], pr.bs[1], pr.bs[0], kStep, &why);
+  if (!ok) { set_error("tensor map: %s", why); return NB200_ERR_LAUNCH; }
+  const bool bf16 = dtype == NB200_BF16;
+
+  // query-major: dq (+ dbias)
+  {
+    BwdArgs aq = a;
+    aq.out2 = pr.dq;
+    for (int i = 0; i < 3; ++i) aq.o2s[i] = pr.dqs[i];
+    aq.dbias = pr.dbias;
+    for (int i = 0; i < 4; ++i) aq.dbs[i] = pr.dbs[i];
+    const CUtensorMap maps[5] = {q128, g128, k64, v64, bias_q};
+    if (int rc = launch_dir<false>(pr.D, bf16, maps, aq, pr.S / kTile, pr.bh_count, stream)) return rc;
+  }
+  // key-major: dk, dv
+  {
+    BwdArgs ak = a;
+    ak.out1 = pr.dv;
+    ak.out2 = pr.dk;
+    for (int i = 0; i < 3; ++i) { ak.o1s[i] = pr.dvs[i]; ak.o2s[i] = pr.dks[i]; }
+    const CUtensorMap maps[5] = {k128, v128, q64, g64, bias_k};
+    if (int rc = launch_dir<true>(pr.D, bf16, maps, ak, pr.T / kTile, pr.bh_count, stream)) return rc;
+  }
+  return NB200_OK;
 }
 
 }  // namespace tc

@@ -15,14 +15,20 @@ constexpr int kTile = 128;         // query rows / key columns per tcgen05 tile
 constexpr int kSlotCols = 64;      // 16-bit elements per 128-byte swizzled row
 constexpr int kBoxBytes = kTile * 128;  // one TMA box: 128 rows x 128 bytes
 
+enum BiasMode : int {
+  kBiasNone = 0,
+  kBiasTile = 1,  // (rows, keys) tiles fetched by TMA into a ring of 16 KB slots
+  kBiasKey = 2    // one value per key, shared by every query row (row stride 0)
+};
+
 // ---- tensor maps (host) -----------------------------------------------------
 // 4-D map over a (B, H, rows, cols) tensor of 16-bit elements with unit column
-// stride; box = 64 columns x 128 rows, 128-byte swizzle, out-of-bounds -> zero.
+// stride; box = 64 columns x `box_rows` rows, 128-byte swizzle, out-of-bounds -> zero.
 // An axis that is broadcast (stride 0) is encoded with extent 1; kernels pass
 // coordinate 0 for it.  Returns false when the driver entry point is missing or
 // the encode call rejects the layout.
 bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H, int B, int64_t row_stride,
-                   int64_t h_stride, int64_t b_stride, const char** why);
+                   int64_t h_stride, int64_t b_stride, int box_rows, const char** why);
 
 // True when a tensor with these element strides can be described by make_tile_map.
 bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B);

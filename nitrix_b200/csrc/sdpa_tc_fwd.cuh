@@ -6,12 +6,6 @@
 namespace nb200 {
 namespace tc {
 
-enum BiasMode : int {
-  kBiasNone = 0,
-  kBiasTile = 1,  // (rows, keys) tiles fetched by TMA into a ring of 128 x 64 slots
-  kBiasKey = 2    // one value per key, shared by every query row (row stride 0)
-};
-
 struct FwdArgs {
   int H, S, T;
   int bh_begin;

@@ -42,7 +42,7 @@ bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t
 }
 
 bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H, int B, int64_t row_stride,
-                   int64_t h_stride, int64_t b_stride, const char** why) {
+                   int64_t h_stride, int64_t b_stride, int box_rows, const char** why) {
   EncodeFn fn = encode_fn();
   if (!fn) { if (why) *why = "cuTensorMapEncodeTiled is unavailable"; return false; }
   // broadcast or singleton axes: extent 1 with a harmless natural stride
@@ -51,7 +51,7 @@ bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H
   const int64_t bs = b_bc ? hs * (h_bc ? 1 : H) : b_stride;
   cuuint64_t dims[4] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(h_bc ? 1 : H), cuuint64_t(b_bc ? 1 : B)};
   cuuint64_t strides[3] = {cuuint64_t(row_stride) * 2, cuuint64_t(hs) * 2, cuuint64_t(bs) * 2};
-  cuuint32_t box[4] = {cuuint32_t(kSlotCols), cuuint32_t(kTile), 1, 1};
+  cuuint32_t box[4] = {cuuint32_t(kSlotCols), cuuint32_t(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -212,15 +212,15 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   tc::FwdArgs a{};
   if (int rc = tc::launch_mask_pack(pr, mp, ws, &a.mask, stream)) return rc;
   CUtensorMap tq, tk, tv, tb;
-  if (!tc::make_tile_map(&tq, pr.q, pr.S, pr.D, pr.H, pr.B, pr.qs[2], pr.qs[1], pr.qs[0], &why) ||
-      !tc::make_tile_map(&tk, pr.k, pr.T, pr.D, pr.H, pr.B, pr.ks[2], pr.ks[1], pr.ks[0], &why) ||
-      !tc::make_tile_map(&tv, pr.v, pr.T, pr.Dv, pr.H, pr.B, pr.vs[2], pr.vs[1], pr.vs[0], &why)) {
+  if (!tc::make_tile_map(&tq, pr.q, pr.S, pr.D, pr.H, pr.B, pr.qs[2], pr.qs[1], pr.qs[0], tc::kTile, &why) ||
+      !tc::make_tile_map(&tk, pr.k, pr.T, pr.D, pr.H, pr.B, pr.ks[2], pr.ks[1], pr.ks[0], tc::kTile, &why) ||
+      !tc::make_tile_map(&tv, pr.v, pr.T, pr.Dv, pr.H, pr.B, pr.vs[2], pr.vs[1], pr.vs[0], tc::kTile, &why)) {
     set_error("tensor map: %s", why);
     return NB200_ERR_LAUNCH;
   }
   tb = tq;  // placeholder when the bias is not tiled (never dereferenced)
   if (bp.mode == tc::kBiasTile &&
-      !tc::make_tile_map(&tb, pr.bias, pr.S, pr.T, pr.H, pr.B, pr.bs[2], pr.bs[1], pr.bs[0], &why)) {
+      !tc::make_tile_map(&tb, pr.bias, pr.S, pr.T, pr.H, pr.B, pr.bs[2], pr.bs[1], pr.bs[0], tc::kTile, &why)) {
     set_error("bias tensor map: %s", why);
     return NB200_ERR_LAUNCH;
   }

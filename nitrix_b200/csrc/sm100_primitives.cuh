@@ -90,6 +90,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
       : "memory");
 }
 
+// Untiled bulk copy global -> this CTA's shared memory (both 16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 // ---- TMEM -------------------------------------------------------------------
 // One warp allocates `cols` (power of two >= 32) columns; the base address is
 // written to shared memory at `dst_smem`.

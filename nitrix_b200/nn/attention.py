@@ -173,7 +173,7 @@ def _mask_bytes(mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 
 
 def planned_kernel(q, k, v, bias=None, mask=None, *, scale=1.0, causal=False, which=_cabi.PASS_FWD,
-                   kernel=_cabi.KERNEL_AUTO) -> int:
+                   kernel=_cabi.KERNEL_AUTO, want_dbias=False) -> int:
     """Kernel family the library would run for these 4-D operands (no launch)."""
     p = _cabi.new_params()
     B, H, S, _ = q.shape
@@ -183,6 +183,9 @@ def planned_kernel(q, k, v, bias=None, mask=None, *, scale=1.0, causal=False, wh
     p.dout = p.dq = p.dk = p.dv = q.data_ptr()
     p.dout_stride = p.dq_stride = p.out_stride
     p.dk_stride, p.dv_stride = p.k_stride, p.v_stride
+    if want_dbias and bias is not None and which == _cabi.PASS_BWD:
+        p.dbias = bias.data_ptr()
+        p.dbias_stride[:] = list(bias.contiguous().stride()) if not bias.is_contiguous() else list(bias.stride())
     chosen = C.c_int(0)
     _check(_cabi.lib().nb200_sdpa_plan(C.byref(p), which, C.byref(chosen)), "nb200_sdpa_plan")
     return chosen.value

@@ -246,7 +246,7 @@ def _device_ok():
     assert rc == 0, _cabi.last_error()
 
 
-def _assert_plans_tc(q, k, v, kw, dtype, which=0):
+def _assert_plans_tc(q, k, v, kw, dtype, which=0, want_dbias=False):
     from nitrix_b200 import _cabi
     _, att = _nb()
     b, h, s, d = q.shape
@@ -257,7 +257,7 @@ def _assert_plans_tc(q, k, v, kw, dtype, which=0):
     b4 = None if bias is None else att._to_own_extent(bias.to(dtype).cuda(), lead, h, s, t)
     m4 = None if mask is None else att._to_own_extent(mask.cuda(), lead, h, s, t)
     chosen = att.planned_kernel(q.to(dtype).cuda(), k.to(dtype).cuda(), v.to(dtype).cuda(), b4, m4,
-                                causal=kw.get("causal", False), which=which)
+                                causal=kw.get("causal", False), which=which, want_dbias=want_dbias)
     assert chosen == _cabi.KERNEL_TCGEN05
 
 
@@ -273,16 +273,36 @@ def test_tc_parity(name, dtype, d):
     if "causal" in name:
         q, k, v, kw = _cases.kernel_case(name, s=384, t=384, d=d)
     _assert_plans_tc(q, k, v, kw, dtype)
-    got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100")
+    # a bias shared over the batch needs a reduction for its gradient (CUDA-core backward);
+    # without dbias, and for every per-batch bias, the backward runs on tensor cores too
+    bias = kw.get("bias")
+    shared_bias = bias is not None and bias.numel() < q.shape[0] * q.shape[1] * q.shape[2] * k.shape[2]
+    for want_dbias in ([True, False] if shared_bias else [True]):
+        if not (shared_bias and want_dbias):
+            _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=want_dbias and bias is not None)
+        got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100", want_dbias=want_dbias)
+        _device_ok()
+        check(got, ref, dtype)
+
+
+def test_tc_backward_full_bias_causal_dbias_zero_past_diagonal():
+    """Per-batch bias + causal: dbias comes from the tensor-core backward and is exactly zero above the diagonal."""
+    q, k, v, kw = _cases.kernel_case("full_bias", s=256, t=256, d=64)
+    kw["causal"] = True
+    _assert_plans_tc(q, k, v, kw, torch.bfloat16, which=1, want_dbias=True)
+    got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100")
     _device_ok()
-    check(got, ref, dtype)
+    check(got, ref, torch.bfloat16)
+    upper = torch.triu(torch.ones(256, 256, dtype=torch.bool), diagonal=1)
+    assert (got[4].cpu()[..., upper] == 0).all()
 
 
 def test_tc_single_tile_and_odd_tile_count():
     for s, t in ((128, 128), (384, 128), (128, 640)):
         q, k, v, kw = _cases.kernel_case("bias_mask", s=s, t=t, d=64, b=1, h=3)
         _assert_plans_tc(q, k, v, kw, torch.bfloat16)
-        got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100")
+        _assert_plans_tc(q, k, v, kw, torch.bfloat16, which=1)
+        got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100", want_dbias=False)
         _device_ok()
         check(got, ref, torch.bfloat16)
 
