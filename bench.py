@@ -214,6 +214,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--backend", default="auto")
+    ap.add_argument("--batch", type=int, default=None, help="override the workload's batch size (profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -251,7 +252,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.lib()
 
-    wl = build_workload(wl_name, dev, seed=rank)
+    wl = build_workload(wl_name, dev, seed=rank, B=args.batch)
+    if args.batch:
+        config["per_gpu_batch"], config["global_batch"] = args.batch, args.batch * world
+        config["workload"] += f" [batch overridden to {args.batch}]"
     q, k, v, kw = wl["q"], wl["k"], wl["v"], wl["kw"]
     bias = kw.get("bias")
     mask = kw.get("mask")

@@ -46,8 +46,8 @@ struct FwdSmem {
   static constexpr int kBias = kV + kStages * kTileBytes;
   static constexpr int kBars = kBias + kBiasSlots * kBoxBytes;
   // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_full[2] p_ready[2] o_done[2]
-  //           bias_full[slots] bias_empty[slots]
-  static constexpr int kNumBars = 2 + 4 * kStages + 6 + 2 * kBiasSlots;
+  //           bias_full[2][slots] (one set per query tile) bias_empty[slots]
+  static constexpr int kNumBars = 2 + 4 * kStages + 6 + 3 * kBiasSlots;
   static constexpr int kMisc = kBars + 8 * kNumBars;      // tmem base (4 B) + abort flag (4 B)
   static constexpr int kTotal = kMisc + 16;
 };
@@ -75,7 +75,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   auto bar = [&](int i) { return smem_u32(bars + i); };
   constexpr int Q_FULL = 0, K_FULL = 2, K_EMPTY = K_FULL + kStages, V_FULL = K_EMPTY + kStages,
                 V_EMPTY = V_FULL + kStages, S_FULL = V_EMPTY + kStages, P_READY = S_FULL + 2, O_DONE = P_READY + 2,
-                B_FULL = O_DONE + 2, B_EMPTY = B_FULL + L::kBiasSlots;
+                B_FULL = O_DONE + 2, B_EMPTY = B_FULL + 2 * L::kBiasSlots;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = a.bh_begin + blockIdx.y;
@@ -158,8 +158,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const int slot = seq % L::kBiasSlots;
             const uint32_t ph = (seq / L::kBiasSlots) & 1;
             if (!wait_or_abort(bar(B_EMPTY + slot), ph ^ 1, abort_flag, a.status, 103)) { ok = false; break; }
-            mbar_expect_tx(bar(B_FULL + slot), kBoxBytes);
-            tma_load_4d(sbase + L::kBias + slot * kBoxBytes, &tm_bias, bar(B_FULL + slot),
+            // the slots are shared by both query tiles, but each tile has its own "full" barriers:
+            // a waiter must see consecutive phases of a barrier, and the tiles alternate on a slot
+            const uint32_t full = bar(B_FULL + g * L::kBiasSlots + slot);
+            mbar_expect_tx(full, kBoxBytes);
+            tma_load_4d(sbase + L::kBias + slot * kBoxBytes, &tm_bias, full,
                         j * kTile + half * kSlotCols, q0 + g * kTile, h * a.bias_h_mul, b * a.bias_b_mul);
           }
         }
@@ -223,6 +226,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int my_nt = nt[g];
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    uint32_t bias_phase = 0;  // bit s = parity this tile's next wait on its "full" barrier of slot s uses
 
     const uint32_t* mrow = nullptr;
     if (a.mask.rows) {
@@ -272,8 +276,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         for (int half = 0; half < 2; ++half) {
           const int seq = seq0 + half;
           const int slot = seq % L::kBiasSlots;
-          ok = wait_or_abort(bar(B_FULL + slot), (seq / L::kBiasSlots) & 1, abort_flag, a.status, 109);
+          ok = wait_or_abort(bar(B_FULL + g * L::kBiasSlots + slot), (bias_phase >> slot) & 1u, abort_flag, a.status,
+                             109);
           if (!ok) break;
+          bias_phase ^= 1u << slot;
           const uint8_t* srow = smem + L::kBias + slot * kBoxBytes + r * 128;
 #pragma unroll
           for (int c = 0; c < 8; ++c) {

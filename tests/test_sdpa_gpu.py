@@ -297,6 +297,16 @@ def test_tc_backward_full_bias_causal_dbias_zero_past_diagonal():
     assert (got[4].cpu()[..., upper] == 0).all()
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_tc_many_tiles_full_bias_mask(d):
+    """Long enough (8 key tiles, 64 CTAs) for the rings to wrap many times with both query tiles active."""
+    q, k, v, kw = _cases.kernel_case("full_bias_mask", b=2, h=4, s=1024, t=1024, d=d)
+    _assert_plans_tc(q, k, v, kw, torch.bfloat16, which=1, want_dbias=True)
+    got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100")
+    _device_ok()
+    check(got, ref, torch.bfloat16)
+
+
 def test_tc_single_tile_and_odd_tile_count():
     for s, t in ((128, 128), (384, 128), (128, 640)):
         q, k, v, kw = _cases.kernel_case("bias_mask", s=s, t=t, d=64, b=1, h=3)
