@@ -154,6 +154,31 @@ __global__ void __launch_bounds__(kWarps * 32) delta_kernel(Problem pr) {
   if (lane == 0) pr.delta[(int64_t(b) * pr.H + h) * pr.S + i] = s;
 }
 
+// 16-bit rows with 16-byte alignment: one 16-byte load of out and of dout per
+// thread, kLanes = Dv / 8 threads per row, shuffle reduction inside the group.
+template <typename T, int kLanes>
+__global__ void __launch_bounds__(256) delta_vec_kernel(Problem pr) {
+  constexpr int kRows = 256 / kLanes;
+  const int sub = threadIdx.x % kLanes;
+  const int i = blockIdx.x * kRows + threadIdx.x / kLanes;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  float s = 0.f;
+  if (i < pr.S) {
+    const T* op = reinterpret_cast<const T*>(pr.out) + b * pr.os[0] + h * pr.os[1] + i * pr.os[2] + sub * 8;
+    const T* gp = reinterpret_cast<const T*>(pr.dout) + b * pr.dos[0] + h * pr.dos[1] + i * pr.dos[2] + sub * 8;
+    const uint4 ov = __ldg(reinterpret_cast<const uint4*>(op));
+    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gp));
+    const T* o8 = reinterpret_cast<const T*>(&ov);
+    const T* g8 = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(o8[e]), to_f32<T>(g8[e]), s);
+  }
+#pragma unroll
+  for (int o = kLanes / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (sub == 0 && i < pr.S) pr.delta[(int64_t(b) * pr.H + h) * pr.S + i] = s;
+}
+
 // ---------------------------------------------------------------------------
 // backward, query side: dq (+ dbias).  One warp per query row, lanes over keys.
 // ---------------------------------------------------------------------------
@@ -401,6 +426,22 @@ int simt_backward(const Problem& pr, int dtype, int bias_dtype, cudaStream_t st)
 
 int launch_delta(const Problem& pr, int dtype, cudaStream_t st) {
   if (pr.bh_count <= 0 || pr.S <= 0) return NB200_OK;
+  const bool aligned = reinterpret_cast<uintptr_t>(pr.out) % 16 == 0 && reinterpret_cast<uintptr_t>(pr.dout) % 16 == 0 &&
+                       pr.os[0] % 8 == 0 && pr.os[1] % 8 == 0 && pr.os[2] % 8 == 0 && pr.dos[0] % 8 == 0 &&
+                       pr.dos[1] % 8 == 0 && pr.dos[2] % 8 == 0;
+  if (dtype != NB200_F32 && aligned && (pr.Dv == 64 || pr.Dv == 128)) {
+    const int lanes = pr.Dv / 8, rows = 256 / lanes;
+    dim3 vgrid((pr.S + rows - 1) / rows, pr.bh_count);
+    if (dtype == NB200_BF16) {
+      if (lanes == 8) delta_vec_kernel<__nv_bfloat16, 8><<<vgrid, 256, 0, st>>>(pr);
+      else delta_vec_kernel<__nv_bfloat16, 16><<<vgrid, 256, 0, st>>>(pr);
+    } else {
+      if (lanes == 8) delta_vec_kernel<__half, 8><<<vgrid, 256, 0, st>>>(pr);
+      else delta_vec_kernel<__half, 16><<<vgrid, 256, 0, st>>>(pr);
+    }
+    count_launch();
+    return check_launch("delta_vec_kernel");
+  }
   dim3 grid((pr.S + kWarps - 1) / kWarps, pr.bh_count);
   switch (dtype) {
     case NB200_F32: delta_kernel<float><<<grid, kWarps * 32, 0, st>>>(pr); break;

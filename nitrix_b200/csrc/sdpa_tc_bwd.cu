@@ -32,6 +32,9 @@ namespace {
 constexpr int kThreads = 384;
 constexpr int kStep = 64;                     // streamed rows per step
 constexpr int kYBoxBytes = kStep * 128;       // one 64-row x 128-byte TMA box
+// register split after start-up (setmaxnreg): 128 * kProducerRegs + 256 * kWorkerRegs <= 65536
+constexpr int kProducerRegs = 72;
+constexpr int kWorkerRegs = 208;
 
 struct BwdArgs {
   int H, S, T;
@@ -121,6 +124,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   const uint32_t tmem = *tmem_slot;
   const uint32_t tm_acc1 = tmem + 256, tm_acc2 = tmem + 256 + D;
 
+  if (warp < 4) {
+  reg_dealloc<kProducerRegs>();
   if (warp == 0) {
     // ---------------- X / Y producer ----------------
     if (elect_one() && n_steps > 0) {
@@ -220,7 +225,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    reg_alloc<kWorkerRegs>();
     // ---------------- element-wise groups (one owner row per thread) ----------------
     const int grp = (warp - 4) >> 2;
     const int wq = warp & 3;
@@ -228,6 +235,10 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     const int orow = o0 + r;                       // query row (query-major) or key (key-major)
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     bool ok = true;
+    // without a bias the scale is folded into the exponent's multiplier: p = exp2(s * (scale log2e) - lse)
+    const bool fold_scale = a.bias_mode == kBiasNone;
+    const float mul = fold_scale ? a.scale * kLog2e : kLog2e;
+    const float2 mul2 = make_float2(mul, mul), scale2 = make_float2(a.scale, a.scale);
     float lse_row = 0.f, delta_row = 0.f;
     if (!kKeyMajor && orow < a.S) {
       const int64_t ro = (int64_t(b) * a.H + h) * a.S + orow;
@@ -293,22 +304,20 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t tP1 = tmem + s * 128 + lane_addr, tP2 = tP1 + 64;
-      float t[kStep], dp[kStep];
+      // both products of the step: four TMEM loads in flight, one wait; handled as fp32 pairs
+      float2 t[kStep / 2], dp[kStep / 2];
       {
-        uint32_t raw[32];
+        uint32_t raw[2 * kStep];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          tmem_ld32(tP1 + c * 32, raw);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) t[c * 32 + i] = __uint_as_float(raw[i]);
+          tmem_ld32(tP1 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
+          tmem_ld32(tP2 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[kStep + c * 32]));
         }
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld32(tP2 + c * 32, raw);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) dp[c * 32 + i] = __uint_as_float(raw[i]);
+        for (int i = 0; i < kStep / 2; ++i) {
+          t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
+          dp[i] = make_float2(__uint_as_float(raw[kStep + 2 * i]), __uint_as_float(raw[kStep + 2 * i + 1]));
         }
       }
       // logits t = s * scale + bias
@@ -322,10 +331,12 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           const uint8_t* colbase = sl + (r >> 6) * kYBoxBytes + (r & 7) * 2;
           const int chunk = (r & 63) >> 3;
 #pragma unroll
-          for (int c = 0; c < kStep; ++c) {
-            const uint16_t raw = *reinterpret_cast<const uint16_t*>(colbase + c * 128 + ((chunk ^ (c & 7)) << 4));
-            const float bv = kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw));
-            t[c] = fmaf(t[c], a.scale, bv);
+          for (int c = 0; c < kStep / 2; ++c) {
+            const uint16_t r0w = *reinterpret_cast<const uint16_t*>(colbase + (2 * c) * 128 + ((chunk ^ ((2 * c) & 7)) << 4));
+            const uint16_t r1w =
+                *reinterpret_cast<const uint16_t*>(colbase + (2 * c + 1) * 128 + ((chunk ^ ((2 * c + 1) & 7)) << 4));
+            const float2 bv = unpack2<kBf16>(uint32_t(r0w) | (uint32_t(r1w) << 16));
+            t[c] = __ffma2_rn(t[c], scale2, bv);
           }
         } else {
           const uint8_t* srow = sl + r * 128;
@@ -334,11 +345,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             const uint4 w = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 bv = unpack2<kBf16>(ww[e]);
-              t[c * 8 + e * 2] = fmaf(t[c * 8 + e * 2], a.scale, bv.x);
-              t[c * 8 + e * 2 + 1] = fmaf(t[c * 8 + e * 2 + 1], a.scale, bv.y);
-            }
+            for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
           }
         }
         __syncwarp();
@@ -350,43 +357,41 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           const uint4 w = __ldg(bk + c);
           const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 bv = unpack2<kBf16>(ww[e]);
-            t[c * 8 + e * 2] = fmaf(t[c * 8 + e * 2], a.scale, bv.x);
-            t[c * 8 + e * 2 + 1] = fmaf(t[c * 8 + e * 2 + 1], a.scale, bv.y);
-          }
+          for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
         }
-      } else {
+      } else if (!fold_scale) {
+        const float2 own2 = make_float2(bias_own, bias_own);
 #pragma unroll
-        for (int c = 0; c < kStep; ++c) t[c] = fmaf(t[c], a.scale, bias_own);
+        for (int c = 0; c < kStep / 2; ++c) t[c] = __ffma2_rn(t[c], scale2, own2);
       }
       // p = exp2(t log2e - lse), ds = p (dp - delta)
       const float4* ld4 = reinterpret_cast<const float4*>(smem + L::kY + st * L::kYStageBytes + 2 * L::kYBytes);
       uint32_t e1[kStep / 2], e2[kStep / 2];
+      const bool need_mask = __any_sync(0xffffffffu, (keep[0] & keep[1]) != 0xffffffffu);
 #pragma unroll
       for (int c4 = 0; c4 < kStep / 4; ++c4) {
-        float ls[4], dl[4];
+        float2 nls[2], ndl[2];  // -lse and -delta of the four streamed rows (key-major) or of the owner row
         if (kKeyMajor) {
           const float4 lv = ld4[c4], dv4 = ld4[16 + c4];
-          ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
-          dl[0] = dv4.x; dl[1] = dv4.y; dl[2] = dv4.z; dl[3] = dv4.w;
+          nls[0] = make_float2(-lv.x, -lv.y); nls[1] = make_float2(-lv.z, -lv.w);
+          ndl[0] = make_float2(-dv4.x, -dv4.y); ndl[1] = make_float2(-dv4.z, -dv4.w);
         } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) { ls[e] = lse_row; dl[e] = delta_row; }
+          nls[0] = nls[1] = make_float2(-lse_row, -lse_row);
+          ndl[0] = ndl[1] = make_float2(-delta_row, -delta_row);
         }
-        float p[4], ds[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = c4 * 4 + e;
-          const bool kp = (keep[c >> 5] >> (c & 31)) & 1u;
-          p[e] = kp ? exp2f(fmaf(t[c], kLog2e, -ls[e])) : 0.f;
-          ds[e] = p[e] * (dp[c] - dl[e]);
-          t[c] = ds[e];  // kept for the dbias store
+        for (int e = 0; e < 2; ++e) {
+          const int c = c4 * 2 + e;  // pair index: streamed rows 2c, 2c + 1
+          float2 x = __ffma2_rn(t[c], mul2, nls[e]);
+          if (need_mask) {
+            if (!((keep[c >> 4] >> ((2 * c) & 31)) & 1u)) x.x = -INFINITY;
+            if (!((keep[c >> 4] >> ((2 * c + 1) & 31)) & 1u)) x.y = -INFINITY;
+          }
+          const float2 p = make_float2(ex2(x.x), ex2(x.y));
+          const float2 ds = __fmul2_rn(p, __fadd2_rn(dp[c], ndl[e]));
+          e1[c] = pack2<kBf16>(p.x, p.y);
+          e2[c] = pack2<kBf16>(ds.x, ds.y);
         }
-        e1[c4 * 2] = pack2<kBf16>(p[0], p[1]);
-        e1[c4 * 2 + 1] = pack2<kBf16>(p[2], p[3]);
-        e2[c4 * 2] = pack2<kBf16>(ds[0], ds[1]);
-        e2[c4 * 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
       }
       if (kKeyMajor) tmem_st32(tP1, e1);
       tmem_st32(tP2, e2);

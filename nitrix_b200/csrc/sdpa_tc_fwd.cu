@@ -35,6 +35,9 @@ namespace {
 
 constexpr int kThreads = 384;
 constexpr int kStages = 2;  // K and V ring depth
+// register split after start-up (setmaxnreg): 128 * kProducerRegs + 256 * kSoftmaxRegs <= 65536
+constexpr int kProducerRegs = 56;
+constexpr int kSoftmaxRegs = 216;
 
 template <int D>
 struct FwdSmem {
@@ -113,6 +116,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tm_S[2] = {tmem, tmem + 128};
   const uint32_t tm_O[2] = {tmem + 256, tmem + 256 + D};
 
+  // the softmax warpgroups hold a whole score row in registers; the producer / MMA warpgroup needs few
+  if (warp < 4) {
+  reg_dealloc<kProducerRegs>();
   if (warp == 0) {
     // ---------------- Q / K / V producer ----------------
     if (elect_one()) {
@@ -215,7 +221,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (j > 0) mma_commit(bar(V_EMPTY + stp));
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    reg_alloc<kSoftmaxRegs>();
     // ---------------- softmax (one query row per thread) ----------------
     const int g = (warp - 4) >> 2;
     const int wq = warp & 3;                    // TMEM lane quarter this warp may access
@@ -224,8 +232,13 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     const uint32_t tS = tm_S[g] + lane_addr, tO = tm_O[g] + lane_addr;
     const int my_nt = nt[g];
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;  // m: reference max in logit units (see the lazy rescale below)
     bool ok = true;
+    // no bias and a non-negative scale: the scale is folded into the exponent's multiplier and the max runs on raw scores
+    const bool fold_scale = a.bias_mode == kBiasNone && a.scale >= 0.f;
+    const float mul = fold_scale ? a.scale * kLog2e : kLog2e;   // exponent = (t - m) * mul, base 2
+    const float thr = mul > 0.f ? 8.f / mul : INFINITY;         // reference max lags the true max by at most 2^8
+    const float2 scale2 = make_float2(a.scale, a.scale), mul2 = make_float2(mul, mul);
     uint32_t bias_phase = 0;  // bit s = parity this tile's next wait on its "full" barrier of slot s uses
 
     const uint32_t* mrow = nullptr;
@@ -258,18 +271,17 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!ok) break;
       tc_fence_after_sync();
 
-      float t[kTile];
+      // the whole score row: four TMEM loads in flight, one wait; handled as 64 fp32 pairs
+      float2 t[kTile / 2];
       {
-        uint32_t raw[32];
+        uint32_t raw[kTile];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld32(tS + c * 32, raw);
-          tmem_wait_ld();
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
+        tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) t[c * 32 + i] = __uint_as_float(raw[i]);
-        }
+        for (int i = 0; i < kTile / 2; ++i) t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
       }
-      // logits in natural units: t = s * scale + bias
+      // logits: t = s * scale + bias (natural units); without a bias the scale is folded into the exponent
       if (a.bias_mode == kBiasTile) {
         const int seq0 = bias_seq(j, g, nt[0], nt[1]);
 #pragma unroll
@@ -286,12 +298,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const uint4 w = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 bv = unpack2<kBf16>(ww[e]);
-              const int col = half * 64 + c * 8 + e * 2;
-              t[col] = fmaf(t[col], a.scale, bv.x);
-              t[col + 1] = fmaf(t[col + 1], a.scale, bv.y);
-            }
+            for (int e = 0; e < 4; ++e)
+              t[half * 32 + c * 4 + e] = __ffma2_rn(t[half * 32 + c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
@@ -304,41 +312,43 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const uint4 w = __ldg(bk + c);
           const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 bv = unpack2<kBf16>(ww[e]);
-            const int col = c * 8 + e * 2;
-            t[col] = fmaf(t[col], a.scale, bv.x);
-            t[col + 1] = fmaf(t[col + 1], a.scale, bv.y);
-          }
+          for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
         }
-      } else {
+      } else if (!fold_scale) {
 #pragma unroll
-        for (int i = 0; i < kTile; ++i) t[i] *= a.scale;
+        for (int i = 0; i < kTile / 2; ++i) t[i] = __fmul2_rn(t[i], scale2);
       }
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < kTile; ++i)
-          if (!((keep[i >> 5] >> (i & 31)) & 1u)) t[i] = -INFINITY;
+        for (int i = 0; i < kTile / 2; ++i) {
+          if (!((keep[i >> 4] >> ((2 * i) & 31)) & 1u)) t[i].x = -INFINITY;
+          if (!((keep[i >> 4] >> ((2 * i + 1) & 31)) & 1u)) t[i].y = -INFINITY;
+        }
       }
-      float mx = t[0];
+      // row max: four independent chains of three-input max
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 1; i < kTile; ++i) mx = fmaxf(mx, t[i]);
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f((m - m_use) * kLog2e);
-      const float neg_m2 = -m_use * kLog2e;
-      float sum = 0.f;
+      for (int i = 0; i < kTile / 2; ++i) mx4[i & 3] = max3(mx4[i & 3], t[i].x, t[i].y);
+      const float mx = max3(mx4[0], mx4[1], fmaxf(mx4[2], mx4[3]));
+      // the exponentials use a reference max that is only moved when the true max has run more than
+      // 2^8 ahead of it (so p <= 256 and the running output is rescaled rarely); l uses the same reference
+      const bool bump = mx > m + thr;
+      const float m_use = bump ? mx : m;
+      const float alpha = bump ? ex2((m - m_use) * mul) : 1.f;
+      const float neg = m_use == -INFINITY ? 0.f : -m_use * mul;
+      const float2 neg2 = make_float2(neg, neg);
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[kTile / 2];
 #pragma unroll
-      for (int i = 0; i < kTile; i += 2) {
-        const float p0 = exp2f(fmaf(t[i], kLog2e, neg_m2));
-        const float p1 = exp2f(fmaf(t[i + 1], kLog2e, neg_m2));
-        sum += p0 + p1;
-        pk[i >> 1] = pack2<kBf16>(p0, p1);
+      for (int i = 0; i < kTile / 2; ++i) {
+        const float2 x = __ffma2_rn(t[i], mul2, neg2);
+        const float2 p = make_float2(ex2(x.x), ex2(x.y));
+        sum2[i & 1] = __fadd2_rn(sum2[i & 1], p);
+        pk[i] = pack2<kBf16>(p.x, p.y);
       }
-      l = l * alpha + sum;
-      // rescale the running output when some row of this warp moved its max
-      if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+      l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+      // rescale the running output when some row of this warp moved its reference max
+      if (j > 0 && __any_sync(0xffffffffu, bump)) {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -349,7 +359,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           tmem_st32(tO + c * 32, o);
         }
       }
-      m = m_new;
+      m = m_use;
       // P (16-bit pairs) over the first 64 columns of the S tile
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -386,7 +396,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
       }
-      if (row < a.S) a.lse[(int64_t(b) * a.H + h) * a.S + row] = m * kLog2e + log2f(l);
+      if (row < a.S) a.lse[(int64_t(b) * a.H + h) * a.S + row] = m * mul + log2f(l);
     }
   }
 
