@@ -35,6 +35,11 @@ constexpr int kYBoxBytes = kStep * 128;       // one 64-row x 128-byte TMA box
 // register split after start-up (setmaxnreg): 128 * kProducerRegs + 256 * kWorkerRegs <= 65536
 constexpr int kProducerRegs = 72;
 constexpr int kWorkerRegs = 208;
+// setmaxnreg.inc blocks (without bound) until the CTA's OWN pool -- the registers it was launched with, here
+// kLaunchRegs per thread -- holds enough released registers, so the hand-over must balance at compile time.
+constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) gives: 65536 / 384 rounded down to a multiple of 8
+static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kWorkerRegs - kLaunchRegs) * 256,
+              "worker warps would wait forever for registers the producer warps never release");
 
 struct BwdArgs {
   int H, S, T;
@@ -466,7 +471,14 @@ template <int D, bool kBf16, bool kKeyMajor>
 int launch_one(const CUtensorMap* maps, const BwdArgs& a, int n_tiles, int bh_count, cudaStream_t st) {
   auto kernel = sdpa_bwd_tc_kernel<D, kBf16, kKeyMajor>;
   const int smem = BwdSmem<D>::kTotal + 1024;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
+    // the register hand-over inside the kernel is balanced for exactly kLaunchRegs per thread at launch
+    set_error("sdpa_bwd_tc_kernel was built with %d registers per thread, expected %d", attr.numRegs, kLaunchRegs);
+    return NB200_ERR_LAUNCH;
+  }
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) {
     set_error("cudaFuncSetAttribute(sdpa_bwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
     return NB200_ERR_LAUNCH;

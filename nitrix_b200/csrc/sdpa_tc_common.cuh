@@ -30,6 +30,9 @@ enum BiasMode : int {
 bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H, int B, int64_t row_stride,
                    int64_t h_stride, int64_t b_stride, int box_rows, const char** why);
 
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
 // True when a tensor with these element strides can be described by make_tile_map.
 bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B);
 
@@ -59,10 +62,12 @@ int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, Mask
 // ---- device helpers -----------------------------------------------------------
 #ifdef __CUDACC__
 
-constexpr long long kWaitCycles = 2000000000LL;  // ~1 s of SM clock: far beyond any real wait
+constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s of SM clock: far beyond any real wait (microseconds)
 
 // Wait on an mbarrier phase unless the CTA has aborted.  On timeout: raise the
-// CTA abort flag, record `code` in the device status word, return false.
+// CTA abort flag, record `code` in the device status word, return false.  A
+// status word already set by another CTA aborts this one as well, so one
+// protocol failure ends the whole grid quickly instead of once per CTA.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                               int code) {
   if (sm100::mbar_try_wait(bar, parity)) return true;
@@ -72,6 +77,10 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     if (sm100::mbar_try_wait(bar, parity)) return true;
     if ((++polls & 0xFF) == 0) {
       if (*abort_flag) return false;
+      if (*reinterpret_cast<volatile int*>(status) != 0) {
+        *abort_flag = 1;
+        return false;
+      }
       if (clock64() - t0 > kWaitCycles) {
         *abort_flag = 1;
         atomicExch(status, code);

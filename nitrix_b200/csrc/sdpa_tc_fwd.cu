@@ -6,23 +6,27 @@
 // recurrence (running max m, running sum l, lse = m + log2 l in base 2, causal
 // key tiles past the diagonal skipped) on 128 x 128 tiles instead of 32 x 32.
 //
-// One CTA owns TWO 128-row query tiles of one (batch, head) and streams the key
-// tiles once for both.  Twelve warps:
-//   warp 0      TMA producer for Q (once) and the K / V rings
+// PERSISTENT kernel: one CTA per SM walks a static list of work items; an item
+// is TWO 128-row query tiles of one (batch, head), for which the key tiles are
+// streamed once.  Barriers, TMEM and tensor-map prefetch are set up once per
+// CTA, and the next item's loads and first MMAs run under the current item's
+// epilogue.  Items are ordered heaviest first (causal) and, when the bias is
+// shared over the batch, batch-fastest so concurrent CTAs hit the same bias
+// tiles in L2.  Twelve warps:
+//   warp 0      TMA producer for Q (per item) and the K / V rings
 //   warp 1      TMA producer for the bias ring (128 x 64 slots)
-//   warp 2      issues every tcgen05.mma (one elected lane)
-//   warp 3      owns the TMEM allocation
+//   warp 2      issues the tcgen05.mma chain of query tile 0 (one elected lane)
+//   warp 3      the same for query tile 1; also owns the TMEM allocation
 //   warps 4-7   softmax of query tile 0 (one row per thread)
 //   warps 8-11  softmax of query tile 1
-// TMEM columns: [0,128) S0 / P0, [128,256) S1 / P1, [256,256+D) O0, then O1.
-// P (16-bit) overwrites the first 64 columns of its S tile and feeds the PV
-// MMA as the TMEM A operand; V is consumed from shared memory as an MN-major B
-// operand, so nothing is transposed or staged through shared memory.
-//
-// Per key tile j and query tile g the dependency chain is
-//   QK_g(j) -> softmax_g(j) -> PV_g(j) -> QK_g(j+1),
-// and the two query tiles interleave so one's MMAs run under the other's
-// softmax.  All waits are bounded (sdpa_tc_common.cuh).
+// TMEM (512 columns).  D = 128: [0,128) S0 / P0, [128,256) S1 / P1, then O0, O1;
+// P (16-bit) overwrites the first 64 columns of its S tile, so per query tile the
+// chain QK(j) -> softmax(j) -> PV(j) -> QK(j+1) is serial and the two query tiles
+// interleave.  D = 64 leaves room for separate P tiles ([256,384)), so QK(j+1) is
+// issued as soon as softmax(j) has read S out and runs underneath it.
+// P feeds the PV MMA as the TMEM A operand; V is consumed from shared memory as
+// an MN-major B operand, so nothing is transposed or staged through shared memory.
+// All waits are bounded (sdpa_tc_common.cuh).
 #include "sdpa_tc_common.cuh"
 #include "sdpa_tc_fwd.cuh"
 
@@ -35,9 +39,14 @@ namespace {
 
 constexpr int kThreads = 384;
 constexpr int kStages = 2;  // K and V ring depth
-// register split after start-up (setmaxnreg): 128 * kProducerRegs + 256 * kSoftmaxRegs <= 65536
+// register split after start-up (setmaxnreg): the softmax warps hold a whole score row
 constexpr int kProducerRegs = 56;
 constexpr int kSoftmaxRegs = 216;
+// setmaxnreg.inc blocks (without bound) until the CTA's OWN pool -- the registers it was launched with, here
+// kLaunchRegs per thread -- holds enough released registers, so the hand-over must balance at compile time.
+constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) gives: 65536 / 384 rounded down to a multiple of 8
+static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) * 256,
+              "softmax warps would wait forever for registers the producer warps never release");
 
 template <int D>
 struct FwdSmem {
@@ -48,17 +57,48 @@ struct FwdSmem {
   static constexpr int kV = kK + kStages * kTileBytes;
   static constexpr int kBias = kV + kStages * kTileBytes;
   static constexpr int kBars = kBias + kBiasSlots * kBoxBytes;
-  // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_full[2] p_ready[2] o_done[2]
-  //           bias_full[2][slots] (one set per query tile) bias_empty[slots]
-  static constexpr int kNumBars = 2 + 4 * kStages + 6 + 3 * kBiasSlots;
+  // q_full[2] q_empty[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_full[2] p_ready[2] o_done[2] o_free[2]
+  // s_free[2] pv_done[2] bias_full[2][slots] bias_empty[slots]
+  static constexpr int kNumBars = 4 + 4 * kStages + 12 + 3 * kBiasSlots;
   static constexpr int kMisc = kBars + 8 * kNumBars;      // tmem base (4 B) + abort flag (4 B)
   static constexpr int kTotal = kMisc + 16;
 };
 
-// Bias-ring sequence number of (key tile j, query tile g): slots are produced
-// and consumed in the order  for j: for g (active at j): half 0, half 1.
-__device__ __forceinline__ int bias_seq(int j, int g, int nt0, int nt1) {
-  return 2 * (min(j, nt0) + min(j, nt1) + ((g == 1 && j < nt0) ? 1 : 0));
+// One work item: two query tiles of one (batch, head).
+struct Item {
+  int b, h, q0;
+  int nt[2], nt_max;
+};
+
+__device__ __forceinline__ Item decode_item(const FwdArgs& a, int item) {
+  Item it;
+  // CTAs that run side by side take consecutive items, so the order decides what they share in L2:
+  // head-major, then query block (heaviest causal blocks first), batch fastest.  Neighbours then read the
+  // same K / V (same batch and head, other query blocks) and, when the bias is shared over the batch, the
+  // same bias tiles (same head and query block, other batches).
+  int rank;
+  if (a.head_major) {
+    const int per_head = a.n_qblocks * a.B;
+    it.h = item / per_head;
+    const int rem = item - it.h * per_head;
+    rank = rem / a.B;
+    it.b = rem - rank * a.B;
+  } else {  // a partial (batch, head) range: keep each pair's query blocks together
+    const int bh = a.bh_begin + item / a.n_qblocks;
+    rank = item % a.n_qblocks;
+    it.b = bh / a.H;
+    it.h = bh - it.b * a.H;
+  }
+  const int qblock = a.causal ? (a.n_qblocks - 1 - rank) : rank;
+  it.q0 = qblock * 2 * kTile;
+  const int n_kt = (a.T + kTile - 1) / kTile;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int q0g = it.q0 + g * kTile;
+    it.nt[g] = q0g >= a.S ? 0 : (a.causal ? min(n_kt, q0g / kTile + 1) : n_kt);
+  }
+  it.nt_max = max(it.nt[0], it.nt[1]);
+  return it;
 }
 
 template <int D, bool kBf16>
@@ -68,38 +108,38 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const FwdArgs a) {
   using L = FwdSmem<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 the swizzle needs
+  // the swizzled tiles need a 1024-byte aligned base; the launch reserves the slack for rounding up
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (smem + L::kTotal > smem_raw + a.smem_bytes) {  // never expected; refuse rather than overrun
+    if (threadIdx.x == 0) atomicExch(a.status, 199);
+    return;
+  }
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
 
   auto bar = [&](int i) { return smem_u32(bars + i); };
-  constexpr int Q_FULL = 0, K_FULL = 2, K_EMPTY = K_FULL + kStages, V_FULL = K_EMPTY + kStages,
+  constexpr int Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + kStages, V_FULL = K_EMPTY + kStages,
                 V_EMPTY = V_FULL + kStages, S_FULL = V_EMPTY + kStages, P_READY = S_FULL + 2, O_DONE = P_READY + 2,
-                B_FULL = O_DONE + 2, B_EMPTY = B_FULL + 2 * L::kBiasSlots;
+                O_FREE = O_DONE + 2, S_FREE = O_FREE + 2, PV_DONE = S_FREE + 2, B_FULL = PV_DONE + 2,
+                B_EMPTY = B_FULL + 2 * L::kBiasSlots;
+  // D = 128 fills TMEM (2 x 128 S + 2 x 128 O): P must overwrite S and each query tile's chain is serial.
+  // D = 64 leaves room for separate P tiles, so the next score MMA can run under the current softmax.
+  constexpr bool kAlias = D == 128;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = a.bh_begin + blockIdx.y;
-  const int b = bh / a.H, h = bh - b * a.H;
-  // heavier (later) causal blocks first
-  const int qblock = a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int q0 = qblock * 2 * kTile;
-  const int n_kt = (a.T + kTile - 1) / kTile;
-  int nt[2];
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    const int q0g = q0 + g * kTile;
-    nt[g] = q0g >= a.S ? 0 : (a.causal ? min(n_kt, q0g / kTile + 1) : n_kt);
-  }
-  const int nt_max = max(nt[0], nt[1]);
+  const int n_items = a.n_qblocks * a.bh_count;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < L::kNumBars; ++i) {
       uint32_t count = 1;
-      if (i >= P_READY && i < P_READY + 2) count = 128;                     // every softmax thread
-      if (i >= B_EMPTY && i < B_EMPTY + L::kBiasSlots) count = 4;           // one lane per softmax warp
+      if (i >= P_READY && i < P_READY + 2) count = 4;                       // one lane per softmax warp of the tile
+      if (i >= K_EMPTY && i < K_EMPTY + kStages) count = 2;                 // both MMA issuers
+      if (i >= V_EMPTY && i < V_EMPTY + kStages) count = 2;
+      if (i >= O_FREE && i < O_FREE + 2) count = 4;                         // one lane per softmax warp of the tile
+      if (i >= S_FREE && i < S_FREE + 2) count = 4;
+      if (i >= B_EMPTY && i < B_EMPTY + L::kBiasSlots) count = 4;
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
@@ -114,9 +154,13 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tm_S[2] = {tmem, tmem + 128};
-  const uint32_t tm_O[2] = {tmem + 256, tmem + 256 + D};
+  const uint32_t tm_P[2] = {kAlias ? tmem : tmem + 256, kAlias ? tmem + 128 : tmem + 320};
+  const uint32_t tm_O[2] = {kAlias ? tmem + 256 : tmem + 384, kAlias ? tmem + 256 + D : tmem + 384 + D};
 
-  // the softmax warpgroups hold a whole score row in registers; the producer / MMA warpgroup needs few
+  // Phase bookkeeping across items (every role derives the same numbers from the same item list):
+  //   kv   key tiles streamed so far            -> ring stage kv % kStages, phase (kv / kStages) & 1
+  //   tc_g tiles query tile g has processed     -> phase of s_full / p_ready / s_free / pv_done
+  //   oc_g items in which query tile g was live -> phase of q_full / q_empty / o_done / o_free
   if (warp < 4) {
   reg_dealloc<kProducerRegs>();
   if (warp == 0) {
@@ -125,30 +169,39 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      int kv = 0, oc[2] = {0, 0};
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const Item it = decode_item(a, item);
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        if (nt[g] == 0) continue;
-        mbar_expect_tx(bar(Q_FULL + g), L::kTileBytes);
+        for (int g = 0; g < 2; ++g) {
+          if (it.nt[g] == 0) continue;
+          // the previous item's last score MMA must have finished reading Q_g
+          if (oc[g] > 0) ok = ok && wait_or_abort(bar(Q_EMPTY + g), (oc[g] - 1) & 1, abort_flag, a.status, 100);
+          if (!ok) break;
+          mbar_expect_tx(bar(Q_FULL + g), L::kTileBytes);
 #pragma unroll
-        for (int x = 0; x < D / 64; ++x)
-          tma_load_4d(sbase + L::kQ + g * L::kTileBytes + x * kBoxBytes, &tm_q, bar(Q_FULL + g), x * 64,
-                      q0 + g * kTile, h, b);
-      }
-      for (int j = 0; j < nt_max; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        if (!wait_or_abort(bar(K_EMPTY + st), ph ^ 1, abort_flag, a.status, 101)) break;
-        mbar_expect_tx(bar(K_FULL + st), L::kTileBytes);
+          for (int x = 0; x < D / 64; ++x)
+            tma_load_4d(sbase + L::kQ + g * L::kTileBytes + x * kBoxBytes, &tm_q, bar(Q_FULL + g), x * 64,
+                        it.q0 + g * kTile, it.h, it.b);
+          ++oc[g];
+        }
+        for (int j = 0; j < it.nt_max && ok; ++j, ++kv) {
+          const int st = kv % kStages;
+          const uint32_t ph = (kv / kStages) & 1;
+          if (!wait_or_abort(bar(K_EMPTY + st), ph ^ 1, abort_flag, a.status, 101)) { ok = false; break; }
+          mbar_expect_tx(bar(K_FULL + st), L::kTileBytes);
 #pragma unroll
-        for (int x = 0; x < D / 64; ++x)
-          tma_load_4d(sbase + L::kK + st * L::kTileBytes + x * kBoxBytes, &tm_k, bar(K_FULL + st), x * 64,
-                      j * kTile, h, b);
-        if (!wait_or_abort(bar(V_EMPTY + st), ph ^ 1, abort_flag, a.status, 102)) break;
-        mbar_expect_tx(bar(V_FULL + st), L::kTileBytes);
+          for (int x = 0; x < D / 64; ++x)
+            tma_load_4d(sbase + L::kK + st * L::kTileBytes + x * kBoxBytes, &tm_k, bar(K_FULL + st), x * 64,
+                        j * kTile, it.h, it.b);
+          if (!wait_or_abort(bar(V_EMPTY + st), ph ^ 1, abort_flag, a.status, 102)) { ok = false; break; }
+          mbar_expect_tx(bar(V_FULL + st), L::kTileBytes);
 #pragma unroll
-        for (int x = 0; x < D / 64; ++x)
-          tma_load_4d(sbase + L::kV + st * L::kTileBytes + x * kBoxBytes, &tm_v, bar(V_FULL + st), x * 64,
-                      j * kTile, h, b);
+          for (int x = 0; x < D / 64; ++x)
+            tma_load_4d(sbase + L::kV + st * L::kTileBytes + x * kBoxBytes, &tm_v, bar(V_FULL + st), x * 64,
+                        j * kTile, it.h, it.b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -157,68 +210,110 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tma_prefetch_desc(&tm_bias);
       int seq = 0;
       bool ok = true;
-      for (int j = 0; j < nt_max && ok; ++j) {
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (j >= nt[g]) continue;
-          for (int half = 0; half < 2; ++half, ++seq) {
-            const int slot = seq % L::kBiasSlots;
-            const uint32_t ph = (seq / L::kBiasSlots) & 1;
-            if (!wait_or_abort(bar(B_EMPTY + slot), ph ^ 1, abort_flag, a.status, 103)) { ok = false; break; }
-            // the slots are shared by both query tiles, but each tile has its own "full" barriers:
-            // a waiter must see consecutive phases of a barrier, and the tiles alternate on a slot
-            const uint32_t full = bar(B_FULL + g * L::kBiasSlots + slot);
-            mbar_expect_tx(full, kBoxBytes);
-            tma_load_4d(sbase + L::kBias + slot * kBoxBytes, &tm_bias, full,
-                        j * kTile + half * kSlotCols, q0 + g * kTile, h * a.bias_h_mul, b * a.bias_b_mul);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const Item it = decode_item(a, item);
+        // slots are filled in the order: for each key tile, for each live query tile, column half 0 then 1
+        for (int j = 0; j < it.nt_max && ok; ++j) {
+          for (int g = 0; g < 2 && ok; ++g) {
+            if (j >= it.nt[g]) continue;
+            for (int half = 0; half < 2; ++half, ++seq) {
+              const int slot = seq % L::kBiasSlots;
+              const uint32_t ph = (seq / L::kBiasSlots) & 1;
+              if (!wait_or_abort(bar(B_EMPTY + slot), ph ^ 1, abort_flag, a.status, 103)) { ok = false; break; }
+              // the slots are shared by both query tiles, but each tile has its own "full" barriers:
+              // a waiter must see consecutive phases of a barrier, and the tiles alternate on a slot
+              const uint32_t full = bar(B_FULL + g * L::kBiasSlots + slot);
+              mbar_expect_tx(full, kBoxBytes);
+              tma_load_4d(sbase + L::kBias + slot * kBoxBytes, &tm_bias, full, j * kTile + half * kSlotCols,
+                          it.q0 + g * kTile, it.h * a.bias_h_mul, it.b * a.bias_b_mul);
+            }
           }
         }
       }
     }
-  } else if (warp == 2) {
-    // ---------------- MMA issuer ----------------
+  } else {
+    // ---------------- MMA issuers: warp 2 serves query tile 0, warp 3 query tile 1 ----------------
+    // Each issues its tile's chain in order with blocking waits; the two chains only meet at the K / V
+    // rings, whose "empty" barriers expect one commit from each issuer per key tile (an issuer whose query
+    // tile does not use a key tile commits anyway: with nothing outstanding the arrival is immediate).
+    const int g = warp - 2;
     if (elect_one()) {
       constexpr uint32_t idesc_qk = make_idesc(kBf16, kTile, kTile, false, false);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, kTile, D, false, true);
+      // descriptors are built once; a tile offset only moves the 16-byte start-address field
+      const uint64_t qdesc = make_smem_desc(sbase + L::kQ + g * L::kTileBytes, 16, 1024);
+      uint64_t kdesc[kStages], vdesc[kStages];
+#pragma unroll
+      for (int s = 0; s < kStages; ++s) {
+        kdesc[s] = make_smem_desc(sbase + L::kK + s * L::kTileBytes, 16, 1024);
+        vdesc[s] = make_smem_desc(sbase + L::kV + s * L::kTileBytes, kBoxBytes, 1024);
+      }
+      auto issue_qk = [&](int st) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t off = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+          mma_ss(tm_S[g], qdesc + off, kdesc[st] + off, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(S_FULL + g));
+      };
+      auto issue_pv = [&](int st, bool first_tile) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          mma_ts(tm_O[g], tm_P[g] + kk * 8, vdesc[st] + uint64_t((kk * 2048) >> 4), idesc_pv,
+                 (!first_tile || kk > 0) ? 1u : 0u);
+      };
       bool ok = true;
-      for (int g = 0; g < 2 && ok; ++g)
-        if (nt[g] > 0) ok = wait_or_abort(bar(Q_FULL + g), 0, abort_flag, a.status, 104);
-      for (int j = 0; j <= nt_max && ok; ++j) {
-        const int st = j % kStages;
-        const int stp = (j + kStages - 1) % kStages;  // stage of tile j - 1
-        if (j < nt_max) ok = wait_or_abort(bar(K_FULL + st), (j / kStages) & 1, abort_flag, a.status, 105);
-        if (ok && j > 0) ok = wait_or_abort(bar(V_FULL + stp), ((j - 1) / kStages) & 1, abort_flag, a.status, 106);
-        if (!ok) break;
-        tc_fence_after_sync();
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (j > 0 && j - 1 < nt[g]) {
-            // O_g += P_g(j-1) V(j-1)
-            ok = wait_or_abort(bar(P_READY + g), (j - 1) & 1, abort_flag, a.status, 107);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t vbase = sbase + L::kV + stp * L::kTileBytes;
-#pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk) {
-              const uint64_t bdesc = make_smem_desc(vbase + kk * 2048, kBoxBytes, 1024);
-              mma_ts(tm_O[g], tm_S[g] + kk * 8, bdesc, idesc_pv, (j - 1 > 0 || kk > 0) ? 1u : 0u);
+      int kv = 0, tc = 0, oc = 0;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const Item it = decode_item(a, item);
+        const int nt = it.nt[g];
+        if (nt > 0) ok = wait_or_abort(bar(Q_FULL + g), oc & 1, abort_flag, a.status, 104);
+        // round j: score MMA of key tile j and output MMA of key tile j - 1
+        for (int j = 0; j <= it.nt_max && ok; ++j) {
+          const int st = (kv + j) % kStages, stp = (kv + j - 1) % kStages;
+          auto round_pv = [&]() {
+            if (j == 0) return;
+            const int jj = j - 1;
+            // every issuer observes every ring tile (also the ones its query tile skips): that keeps it to one
+            // arrival per phase of the "empty" barrier
+            ok = wait_or_abort(bar(V_FULL + stp), ((kv + jj) / kStages) & 1, abort_flag, a.status, 106);
+            if (!ok) return;
+            if (jj < nt) {
+              ok = wait_or_abort(bar(P_READY + g), (tc + jj) & 1, abort_flag, a.status, 107);
+              // the previous item's epilogue must have read O_g out before the first tile overwrites it
+              if (ok && jj == 0 && oc > 0) ok = wait_or_abort(bar(O_FREE + g), (oc - 1) & 1, abort_flag, a.status, 115);
+              if (!ok) return;
+              tc_fence_after_sync();
+              issue_pv(stp, jj == 0);
+              if (!kAlias) mma_commit(bar(PV_DONE + g));
+              if (jj == nt - 1) mma_commit(bar(O_DONE + g));
             }
-            if (j == nt[g]) mma_commit(bar(O_DONE + g));
-          }
-          if (j < nt[g]) {
-            // S_g = Q_g K(j)^T
-            const uint32_t qbase = sbase + L::kQ + g * L::kTileBytes;
-            const uint32_t kbase = sbase + L::kK + st * L::kTileBytes;
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-              mma_ss(tm_S[g], make_smem_desc(qbase + off, 16, 1024), make_smem_desc(kbase + off, 16, 1024),
-                     idesc_qk, kk > 0 ? 1u : 0u);
+            mma_commit(bar(V_EMPTY + stp));
+          };
+          auto round_qk = [&]() {
+            if (j < it.nt_max) ok = wait_or_abort(bar(K_FULL + st), ((kv + j) / kStages) & 1, abort_flag, a.status, 105);
+            if (!ok) return;
+            if (j < nt) {
+              const int gt = tc + j;
+              if (!kAlias && gt > 0) ok = wait_or_abort(bar(S_FREE + g), (gt - 1) & 1, abort_flag, a.status, 111);
+              if (!ok) return;
+              tc_fence_after_sync();
+              issue_qk(st);
+              if (j == nt - 1) mma_commit(bar(Q_EMPTY + g));   // Q_g may be reloaded once these are done
             }
-            mma_commit(bar(S_FULL + g));
+            if (j < it.nt_max) mma_commit(bar(K_EMPTY + st));
+          };
+          if constexpr (kAlias) {
+            round_pv();   // P(j-1) lives in S_g: its output MMA goes first
+            if (ok) round_qk();
+          } else {
+            round_qk();   // S_g was read out early in softmax(j-1): the next scores run underneath it
+            if (ok) round_pv();
           }
         }
-        if (!ok) break;
-        if (j < nt_max) mma_commit(bar(K_EMPTY + st));
-        if (j > 0) mma_commit(bar(V_EMPTY + stp));
+        kv += it.nt_max;
+        tc += nt;
+        oc += nt > 0 ? 1 : 0;
       }
     }
   }
@@ -228,175 +323,204 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int g = (warp - 4) >> 2;
     const int wq = warp & 3;                    // TMEM lane quarter this warp may access
     const int r = wq * 32 + lane;               // row within the tile
-    const int row = q0 + g * kTile + r;
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
-    const uint32_t tS = tm_S[g] + lane_addr, tO = tm_O[g] + lane_addr;
-    const int my_nt = nt[g];
-    float m = -INFINITY, l = 0.f;  // m: reference max in logit units (see the lazy rescale below)
+    const uint32_t tS = tm_S[g] + lane_addr, tP = tm_P[g] + lane_addr, tO = tm_O[g] + lane_addr;
     bool ok = true;
     // no bias and a non-negative scale: the scale is folded into the exponent's multiplier and the max runs on raw scores
     const bool fold_scale = a.bias_mode == kBiasNone && a.scale >= 0.f;
     const float mul = fold_scale ? a.scale * kLog2e : kLog2e;   // exponent = (t - m) * mul, base 2
     const float thr = mul > 0.f ? 8.f / mul : INFINITY;         // reference max lags the true max by at most 2^8
     const float2 scale2 = make_float2(a.scale, a.scale), mul2 = make_float2(mul, mul);
-    uint32_t bias_phase = 0;  // bit s = parity this tile's next wait on its "full" barrier of slot s uses
+    uint32_t bias_phase = 0;  // bit s = parity of this tile's next wait on its "full" barrier of slot s
+    int tc = 0, oc = 0, seq_base = 0;
 
-    const uint32_t* mrow = nullptr;
-    if (a.mask.rows) {
-      mrow = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride + int64_t(min(row, a.S - 1)) * a.mask.row_stride;
-    }
-    const uint8_t* bias_key = nullptr;
-    if (a.bias_mode == kBiasKey)
-      bias_key = reinterpret_cast<const uint8_t*>(a.bias) + 2 * (b * a.bias_bs + h * a.bias_hs);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const Item it = decode_item(a, item);
+      const int my_nt = it.nt[g];
+      const int row = it.q0 + g * kTile + r;
+      const int b = it.b, h = it.h;
+      float m = -INFINITY, l = 0.f;  // m: reference max in logit units (see the lazy rescale below)
 
-    for (int j = 0; j < my_nt && ok; ++j) {
-      const int key0 = j * kTile;
-      // keep-bits of this row for this key tile
-      uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-      bool need_mask = false;
-      if (mrow) {
-        const uint4 w = __ldg(reinterpret_cast<const uint4*>(mrow + j * 4));
-        keep[0] = w.x; keep[1] = w.y; keep[2] = w.z; keep[3] = w.w;
-        need_mask = true;
+      const uint32_t* mrow = nullptr;
+      if (a.mask.rows) {
+        mrow = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride + int64_t(min(row, a.S - 1)) * a.mask.row_stride;
       }
-      int n_keep = a.T - key0;
-      if (a.causal) n_keep = min(n_keep, row - key0 + 1);
-      if (n_keep < kTile) {
-        limit_bits(keep, n_keep);
-        need_mask = true;
-      }
-      need_mask = __any_sync(0xffffffffu, need_mask);
+      const uint8_t* bias_key = nullptr;
+      if (a.bias_mode == kBiasKey)
+        bias_key = reinterpret_cast<const uint8_t*>(a.bias) + 2 * (b * a.bias_bs + h * a.bias_hs);
 
-      ok = wait_or_abort(bar(S_FULL + g), j & 1, abort_flag, a.status, 108);
-      if (!ok) break;
-      tc_fence_after_sync();
+      for (int j = 0; j < my_nt && ok; ++j) {
+        const int key0 = j * kTile;
+        const int gt = tc + j;   // this tile's running index for this query tile
+        // keep-bits of this row for this key tile
+        uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        bool need_mask = false;
+        if (mrow) {
+          const uint4 w = __ldg(reinterpret_cast<const uint4*>(mrow + j * 4));
+          keep[0] = w.x; keep[1] = w.y; keep[2] = w.z; keep[3] = w.w;
+          need_mask = true;
+        }
+        int n_keep = a.T - key0;
+        if (a.causal) n_keep = min(n_keep, row - key0 + 1);
+        if (n_keep < kTile) {
+          limit_bits(keep, n_keep);
+          need_mask = true;
+        }
+        need_mask = __any_sync(0xffffffffu, need_mask);
 
-      // the whole score row: four TMEM loads in flight, one wait; handled as 64 fp32 pairs
-      float2 t[kTile / 2];
-      {
-        uint32_t raw[kTile];
+        ok = wait_or_abort(bar(S_FULL + g), gt & 1, abort_flag, a.status, 108);
+        if (!ok) break;
+        tc_fence_after_sync();
+
+        // the whole score row: four TMEM loads in flight, one wait; handled as 64 fp32 pairs
+        float2 t[kTile / 2];
+        {
+          uint32_t raw[kTile];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
-        tmem_wait_ld();
+          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
+          tmem_wait_ld();
+          if constexpr (!kAlias) {
+            // the scores are in registers: S_g may be overwritten by the next tile's MMA right away
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(S_FREE + g));
+          }
 #pragma unroll
-        for (int i = 0; i < kTile / 2; ++i) t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
-      }
-      // logits: t = s * scale + bias (natural units); without a bias the scale is folded into the exponent
-      if (a.bias_mode == kBiasTile) {
-        const int seq0 = bias_seq(j, g, nt[0], nt[1]);
+          for (int i = 0; i < kTile / 2; ++i)
+            t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
+        }
+        // logits: t = s * scale + bias (natural units); without a bias the scale is folded into the exponent
+        if (a.bias_mode == kBiasTile) {
+          // slots filled before this (tile, query tile): every live query tile of the earlier key tiles, and
+          // query tile 0 of this one when this is query tile 1
+          const int seq0 = seq_base + 2 * (min(j, it.nt[0]) + min(j, it.nt[1]) + ((g == 1 && j < it.nt[0]) ? 1 : 0));
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int seq = seq0 + half;
-          const int slot = seq % L::kBiasSlots;
-          ok = wait_or_abort(bar(B_FULL + g * L::kBiasSlots + slot), (bias_phase >> slot) & 1u, abort_flag, a.status,
-                             109);
+          for (int half = 0; half < 2; ++half) {
+            const int slot = (seq0 + half) % L::kBiasSlots;
+            ok = wait_or_abort(bar(B_FULL + g * L::kBiasSlots + slot), (bias_phase >> slot) & 1u, abort_flag, a.status,
+                               109);
+            if (!ok) break;
+            bias_phase ^= 1u << slot;
+            const uint8_t* srow = smem + L::kBias + slot * kBoxBytes + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint4 w = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
+              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                t[half * 32 + c * 4 + e] = __ffma2_rn(t[half * 32 + c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
+          }
           if (!ok) break;
-          bias_phase ^= 1u << slot;
-          const uint8_t* srow = smem + L::kBias + slot * kBoxBytes + r * 128;
+        } else if (a.bias_mode == kBiasKey) {
+          const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * key0);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 w = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
+          for (int c = 0; c < 16; ++c) {
+            const uint4 w = __ldg(bk + c);
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              t[half * 32 + c * 4 + e] = __ffma2_rn(t[half * 32 + c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
+            for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
+        } else if (!fold_scale) {
+#pragma unroll
+          for (int i = 0; i < kTile / 2; ++i) t[i] = __fmul2_rn(t[i], scale2);
         }
-        if (!ok) break;
-      } else if (a.bias_mode == kBiasKey) {
-        const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * key0);
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const uint4 w = __ldg(bk + c);
-          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
+          for (int i = 0; i < kTile / 2; ++i) {
+            if (!((keep[i >> 4] >> ((2 * i) & 31)) & 1u)) t[i].x = -INFINITY;
+            if (!((keep[i >> 4] >> ((2 * i + 1) & 31)) & 1u)) t[i].y = -INFINITY;
+          }
         }
-      } else if (!fold_scale) {
+        // row max: four independent chains of three-input max
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < kTile / 2; ++i) t[i] = __fmul2_rn(t[i], scale2);
-      }
-      if (need_mask) {
+        for (int i = 0; i < kTile / 2; ++i) mx4[i & 3] = max3(mx4[i & 3], t[i].x, t[i].y);
+        const float mx = max3(mx4[0], mx4[1], fmaxf(mx4[2], mx4[3]));
+        // the exponentials use a reference max that is only moved when the true max has run more than
+        // 2^8 ahead of it (so p <= 256 and the running output is rescaled rarely); l uses the same reference
+        const bool bump = mx > m + thr;
+        const float m_use = bump ? mx : m;
+        const float alpha = bump ? ex2((m - m_use) * mul) : 1.f;
+        const float neg = m_use == -INFINITY ? 0.f : -m_use * mul;
+        const float2 neg2 = make_float2(neg, neg);
+        float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        uint32_t pk[kTile / 2];
 #pragma unroll
         for (int i = 0; i < kTile / 2; ++i) {
-          if (!((keep[i >> 4] >> ((2 * i) & 31)) & 1u)) t[i].x = -INFINITY;
-          if (!((keep[i >> 4] >> ((2 * i + 1) & 31)) & 1u)) t[i].y = -INFINITY;
+          const float2 x = __ffma2_rn(t[i], mul2, neg2);
+          const float2 p = make_float2(ex2(x.x), ex2(x.y));
+          sum2[i & 1] = __fadd2_rn(sum2[i & 1], p);
+          pk[i] = pack2<kBf16>(p.x, p.y);
         }
-      }
-      // row max: four independent chains of three-input max
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+        if constexpr (!kAlias) {
+          // O_g and P_g are still in use by the previous tile's output MMA until it has completed
+          // (the first tile of an item follows the previous item's epilogue, which waited for that)
+          if (j > 0) {
+            ok = wait_or_abort(bar(PV_DONE + g), (gt - 1) & 1, abort_flag, a.status, 112);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+        }
+        // rescale the running output when some row of this warp moved its reference max
+        if (j > 0 && __any_sync(0xffffffffu, bump)) {
 #pragma unroll
-      for (int i = 0; i < kTile / 2; ++i) mx4[i & 3] = max3(mx4[i & 3], t[i].x, t[i].y);
-      const float mx = max3(mx4[0], mx4[1], fmaxf(mx4[2], mx4[3]));
-      // the exponentials use a reference max that is only moved when the true max has run more than
-      // 2^8 ahead of it (so p <= 256 and the running output is rescaled rarely); l uses the same reference
-      const bool bump = mx > m + thr;
-      const float m_use = bump ? mx : m;
-      const float alpha = bump ? ex2((m - m_use) * mul) : 1.f;
-      const float neg = m_use == -INFINITY ? 0.f : -m_use * mul;
-      const float2 neg2 = make_float2(neg, neg);
-      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      uint32_t pk[kTile / 2];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < kTile / 2; ++i) {
-        const float2 x = __ffma2_rn(t[i], mul2, neg2);
-        const float2 p = make_float2(ex2(x.x), ex2(x.y));
-        sum2[i & 1] = __fadd2_rn(sum2[i & 1], p);
-        pk[i] = pack2<kBf16>(p.x, p.y);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + c * 32, o);
+          }
+        }
+        m = m_use;
+        // P as 16-bit pairs: 64 columns (over the S tile when aliased)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) tmem_st32(tP + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY + g));
       }
-      l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
-      // rescale the running output when some row of this warp moved its reference max
-      if (j > 0 && __any_sync(0xffffffffu, bump)) {
+
+      // ---------------- epilogue: out = O / l, lse = m * mul + log2 l ----------------
+      if (ok && my_nt > 0) ok = wait_or_abort(bar(O_DONE + g), oc & 1, abort_flag, a.status, 110);
+      if (ok && my_nt > 0) {
+        tc_fence_after_sync();
+        const float inv = 1.f / l;  // l == 0 (no kept key): 0 * inf = NaN, as the reference's softmax gives
+        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + 2 * (b * a.os[0] + h * a.os[1] + int64_t(row) * a.os[2]);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(tO + c * 32, o);
           tmem_wait_ld();
+          if (c == D / 32 - 1) {
+            // O_g is in registers: the next item's first output MMA may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O_FREE + g));
+          }
+          if (row < a.S) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tO + c * 32, o);
-        }
-      }
-      m = m_use;
-      // P (16-bit pairs) over the first 64 columns of the S tile
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t chunk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) chunk[i] = pk[c * 32 + i];
-        tmem_st32(tS + c * 32, chunk);
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(bar(P_READY + g));
-    }
-
-    // ---------------- epilogue: out = O / l, lse = m log2e + log2 l ----------------
-    if (ok && my_nt > 0) ok = wait_or_abort(bar(O_DONE + g), 0, abort_flag, a.status, 110);
-    if (ok && my_nt > 0) {
-      tc_fence_after_sync();
-      const float inv = 1.f / l;  // l == 0 (no kept key): 0 * inf = NaN, as the reference's softmax gives
-      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + 2 * (b * a.os[0] + h * a.os[1] + int64_t(row) * a.os[2]);
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tO + c * 32, o);
-        tmem_wait_ld();
-        if (row < a.S) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack2<kBf16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-            w.y = pack2<kBf16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            w.z = pack2<kBf16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-            w.w = pack2<kBf16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + (c * 32 + i) * 2) = w;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack2<kBf16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              w.y = pack2<kBf16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              w.z = pack2<kBf16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              w.w = pack2<kBf16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + (c * 32 + i) * 2) = w;
+            }
           }
         }
+        if (row < a.S) a.lse[(int64_t(b) * a.H + h) * a.S + row] = m * mul + log2f(l);
       }
-      if (row < a.S) a.lse[(int64_t(b) * a.H + h) * a.S + row] = m * mul + log2f(l);
+      tc += my_nt;
+      oc += my_nt > 0 ? 1 : 0;
+      seq_base += 2 * (it.nt[0] + it.nt[1]);
     }
   }
 
@@ -412,15 +536,27 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 template <int D, bool kBf16>
 int launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tb,
-               const FwdArgs& a, int n_qblocks, int bh_count, cudaStream_t st) {
+               FwdArgs a, cudaStream_t st) {
   auto kernel = sdpa_fwd_tc_kernel<D, kBf16>;
-  const int smem = FwdSmem<D>::kTotal + 1024;  // slack for the 1024-byte round-up
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  constexpr int kLimit = 232448;  // 227 KB per CTA
+  const int smem = FwdSmem<D>::kTotal + 1024 <= kLimit ? FwdSmem<D>::kTotal + 1024 : kLimit;
+  static_assert(FwdSmem<D>::kTotal <= kLimit, "forward shared memory exceeds the per-CTA limit");
+  a.smem_bytes = smem;
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
+    // the register hand-over inside the kernel is balanced for exactly kLaunchRegs per thread at launch
+    set_error("sdpa_fwd_tc_kernel was built with %d registers per thread, expected %d", attr.numRegs, kLaunchRegs);
+    return NB200_ERR_LAUNCH;
+  }
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) {
     set_error("cudaFuncSetAttribute(sdpa_fwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
     return NB200_ERR_LAUNCH;
   }
-  dim3 grid(n_qblocks, bh_count);
+  const int n_items = a.n_qblocks * a.bh_count;
+  const int sms = sm_count();
+  dim3 grid(n_items < sms ? n_items : sms);
   kernel<<<grid, kThreads, smem, st>>>(tq, tk, tv, tb, a);
   count_launch();
   return check_launch("sdpa_fwd_tc_kernel");
@@ -429,11 +565,9 @@ int launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 }  // namespace
 
 int launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-               const CUtensorMap& tb, const FwdArgs& a, int n_qblocks, int bh_count, cudaStream_t st) {
-  if (D == 64) return bf16 ? launch_one<64, true>(tq, tk, tv, tb, a, n_qblocks, bh_count, st)
-                           : launch_one<64, false>(tq, tk, tv, tb, a, n_qblocks, bh_count, st);
-  return bf16 ? launch_one<128, true>(tq, tk, tv, tb, a, n_qblocks, bh_count, st)
-              : launch_one<128, false>(tq, tk, tv, tb, a, n_qblocks, bh_count, st);
+               const CUtensorMap& tb, const FwdArgs& a, cudaStream_t st) {
+  if (D == 64) return bf16 ? launch_one<64, true>(tq, tk, tv, tb, a, st) : launch_one<64, false>(tq, tk, tv, tb, a, st);
+  return bf16 ? launch_one<128, true>(tq, tk, tv, tb, a, st) : launch_one<128, false>(tq, tk, tv, tb, a, st);
 }
 
 }  // namespace tc

@@ -7,8 +7,10 @@ namespace nb200 {
 namespace tc {
 
 struct FwdArgs {
-  int H, S, T;
-  int bh_begin;
+  int B, H, S, T;
+  int bh_begin, bh_count;       // flattened (batch, head) range this launch covers
+  int n_qblocks;                // 256-row query blocks per (batch, head): work items = n_qblocks * bh_count
+  int head_major;               // item order: head, query block, batch (needs the full range); else pair-major
   int causal;
   float scale;
   int bias_mode;
@@ -20,10 +22,11 @@ struct FwdArgs {
   int64_t os[3];                // element strides of out (b, h, row)
   float* lse;
   int* status;
+  int smem_bytes;               // dynamic shared memory the launch requested (filled in by launch_fwd)
 };
 
 int launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-               const CUtensorMap& tb, const FwdArgs& a, int n_qblocks, int bh_count, cudaStream_t st);
+               const CUtensorMap& tb, const FwdArgs& a, cudaStream_t st);
 
 }  // namespace tc
 }  // namespace nb200

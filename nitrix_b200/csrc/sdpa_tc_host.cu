@@ -33,6 +33,18 @@ EncodeFn encode_fn() {
 
 }  // namespace
 
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B) {
   if (reinterpret_cast<uintptr_t>(base) % 16) return false;
   if (row_stride <= 0 || row_stride % 8) return false;
@@ -235,8 +247,12 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.lse = pr.lse;
   a.status = device_status_word();
   if (!a.status) { set_error("device status word is unavailable"); return NB200_ERR_LAUNCH; }
-  const int n_qblocks = (pr.S + 2 * tc::kTile - 1) / (2 * tc::kTile);
-  return tc::launch_fwd(pr.D, dtype == NB200_BF16, tq, tk, tv, tb, a, n_qblocks, pr.bh_count, stream);
+  a.B = pr.B;
+  a.bh_count = pr.bh_count;
+  a.n_qblocks = (pr.S + 2 * tc::kTile - 1) / (2 * tc::kTile);
+  // the whole (batch, head) range: order the items head-major / query block / batch (see decode_item)
+  a.head_major = (pr.bh_begin == 0 && pr.bh_count == pr.B * pr.H) ? 1 : 0;
+  return tc::launch_fwd(pr.D, dtype == NB200_BF16, tq, tk, tv, tb, a, stream);
 }
 
 int tc_backward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
