@@ -107,6 +107,13 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     if (kKeyMajor) s_begin = min(s_end, o0 / kStep);                       // queries i >= first key
     else s_end = min(s_end, (min(o0 + kTile, n_owner) + kStep - 1) / kStep);  // keys j <= last query
   }
+  // key-only mask (key padding): keys at or past the last kept one contribute nothing
+  const int kept = kept_key_length(a.mask, b, h, a.T);
+  if (kKeyMajor) {
+    if (o0 >= kept) s_end = s_begin;                                  // every key of this tile is dropped: dk = dv = 0
+  } else {
+    s_end = max(s_begin, min(s_end, (kept + kStep - 1) / kStep));     // stream the kept keys only
+  }
   const int n_steps = s_end - s_begin;
 
   if (threadIdx.x == 0) {
@@ -414,8 +421,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     }
 
     // ---------------- epilogue ----------------
-    if (!kKeyMajor && a.dbias && a.causal && orow < a.S) {
-      // key steps past the diagonal are never visited: their dbias is exactly zero
+    if (!kKeyMajor && a.dbias && orow < a.S) {
+      // key steps past the diagonal (causal) or past the last kept key are never visited: their dbias is exactly zero
       if (grp == 0) {
         uint8_t* dst = reinterpret_cast<uint8_t*>(a.dbias) + 2 * (b * a.dbs[0] + h * a.dbs[1] + int64_t(orow) * a.dbs[2]);
         for (int k0 = s_end * kStep; k0 < a.T; k0 += 8)
@@ -539,7 +546,7 @@ bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** wh
 size_t bwd_workspace_bytes(const Problem& pr, int, int) {
   const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
   const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
-  return mp.rows_bytes + mp.cols_bytes;
+  return mp.total();
 }
 
 int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
@@ -547,8 +554,8 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   const char* why = "";
   const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
   const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
-  if (mp.rows_bytes + mp.cols_bytes > ws_bytes) {
-    set_error("backward mask bits need %zu workspace bytes", mp.rows_bytes + mp.cols_bytes);
+  if (mp.total() > ws_bytes) {
+    set_error("backward mask bits need %zu workspace bytes", mp.total());
     return NB200_ERR_WORKSPACE;
   }
   BwdArgs a{};

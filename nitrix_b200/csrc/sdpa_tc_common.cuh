@@ -48,14 +48,27 @@ struct MaskBits {
   const uint32_t* cols;     // transposed copy (backward only) or null
   int64_t b_stride, h_stride, row_stride;       // in words; 0 on broadcast axes
   int64_t tb_stride, th_stride, tkey_stride;    // transposed array
+  // Key-only masks (no query axis, e.g. key padding): 1 + index of the last kept key per (bm, hm), so that
+  // kernels skip the key tiles past it altogether.  Null for masks with a query axis.
+  const int* kv_len;
+  int64_t len_b_stride, len_h_stride;
 };
 
 struct MaskPackPlan {
   int64_t extent[4];          // Bm, Hm, Sm(1 or S), 1
   int words_per_row;          // over T
   int words_per_col;          // over S (transposed)
-  size_t rows_bytes, cols_bytes;
+  size_t rows_bytes, cols_bytes, len_bytes;
+  size_t total() const { return rows_bytes + cols_bytes + len_bytes; }
 };
+
+#ifdef __CUDACC__
+// Number of leading keys of (b, h) that can matter: T without a key-only mask, else 1 + last kept key.
+__device__ __forceinline__ int kept_key_length(const MaskBits& m, int b, int h, int T) {
+  if (!m.kv_len) return T;
+  return min(T, m.kv_len[b * m.len_b_stride + h * m.len_h_stride]);
+}
+#endif
 MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed);
 int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, MaskBits* out, cudaStream_t stream);
 

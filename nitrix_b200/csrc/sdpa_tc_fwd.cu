@@ -15,8 +15,8 @@
 // tiles in L2.  Twelve warps:
 //   warp 0      TMA producer for Q (per item) and the K / V rings
 //   warp 1      TMA producer for the bias ring (128 x 64 slots)
-//   warp 2      issues the tcgen05.mma chain of query tile 0 (one elected lane)
-//   warp 3      the same for query tile 1; also owns the TMEM allocation
+//   warp 2      issues tcgen05.mma (one elected lane): D = 64 the chain of query tile 0, D = 128 both chains
+//   warp 3      D = 64: the chain of query tile 1; owns the TMEM allocation
 //   warps 4-7   softmax of query tile 0 (one row per thread)
 //   warps 8-11  softmax of query tile 1
 // TMEM (512 columns).  D = 128: [0,128) S0 / P0, [128,256) S1 / P1, then O0, O1;
@@ -38,7 +38,6 @@ using namespace sm100;
 namespace {
 
 constexpr int kThreads = 384;
-constexpr int kStages = 2;  // K and V ring depth
 // register split after start-up (setmaxnreg): the softmax warps hold a whole score row
 constexpr int kProducerRegs = 56;
 constexpr int kSoftmaxRegs = 216;
@@ -51,7 +50,10 @@ static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs
 template <int D>
 struct FwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;        // one Q / K / V tile
-  static constexpr int kBiasSlots = D == 64 ? 8 : 2;      // 16 KB slots
+  // K and V ring depth.  A TMA tile takes 1-2 us from L2 / HBM while a key tile is consumed in well under
+  // 1 us, so two stages leave the MMAs waiting for loads; D = 64 tiles are small enough for four.
+  static constexpr int kStages = D == 64 ? 4 : 2;
+  static constexpr int kBiasSlots = D == 64 ? 4 : 2;      // 16 KB slots
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + 2 * kTileBytes;
   static constexpr int kV = kK + kStages * kTileBytes;
@@ -91,7 +93,10 @@ __device__ __forceinline__ Item decode_item(const FwdArgs& a, int item) {
   }
   const int qblock = a.causal ? (a.n_qblocks - 1 - rank) : rank;
   it.q0 = qblock * 2 * kTile;
-  const int n_kt = (a.T + kTile - 1) / kTile;
+  // key-only mask (key padding): tiles past the last kept key are skipped; one tile is always visited
+  // so that a batch with no kept key still produces its (NaN) rows
+  const int kept = kept_key_length(a.mask, it.b, it.h, a.T);
+  const int n_kt = max(1, (kept + kTile - 1) / kTile);
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
     const int q0g = it.q0 + g * kTile;
@@ -107,6 +112,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
                    const FwdArgs a) {
   using L = FwdSmem<D>;
+  constexpr int kStages = L::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // the swizzled tiles need a 1024-byte aligned base; the launch reserves the slack for rounding up
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -135,8 +141,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int i = 0; i < L::kNumBars; ++i) {
       uint32_t count = 1;
       if (i >= P_READY && i < P_READY + 2) count = 4;                       // one lane per softmax warp of the tile
-      if (i >= K_EMPTY && i < K_EMPTY + kStages) count = 2;                 // both MMA issuers
-      if (i >= V_EMPTY && i < V_EMPTY + kStages) count = 2;
+      if (i >= K_EMPTY && i < K_EMPTY + kStages) count = kAlias ? 1 : 2;    // one arrival per MMA issuer
+      if (i >= V_EMPTY && i < V_EMPTY + kStages) count = kAlias ? 1 : 2;
       if (i >= O_FREE && i < O_FREE + 2) count = 4;                         // one lane per softmax warp of the tile
       if (i >= S_FREE && i < S_FREE + 2) count = 4;
       if (i >= B_EMPTY && i < B_EMPTY + L::kBiasSlots) count = 4;
@@ -231,89 +237,90 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
     }
-  } else {
-    // ---------------- MMA issuers: warp 2 serves query tile 0, warp 3 query tile 1 ----------------
-    // Each issues its tile's chain in order with blocking waits; the two chains only meet at the K / V
-    // rings, whose "empty" barriers expect one commit from each issuer per key tile (an issuer whose query
-    // tile does not use a key tile commits anyway: with nothing outstanding the arrival is immediate).
-    const int g = warp - 2;
+  } else if (kAlias ? warp == 2 : true) {
+    // ---------------- MMA issuers ----------------
+    // D = 64: warp 2 issues the chain of query tile 0, warp 3 that of query tile 1; a tile's next score MMA
+    //   runs under its own softmax, so the two chains are independent.
+    // D = 128: warp 2 alone issues both chains in a fixed order (tile 0 then tile 1 per round).  The
+    //   serial order staggers the two query tiles, so that one tile's MMAs run under the other's softmax.
+    // An issuer observes every key tile of the rings, also those its query tile skips, and commits once per
+    // tile to the "empty" barriers (with nothing outstanding the arrival is immediate): one arrival per
+    // issuer per phase.
+    const int g_begin = kAlias ? 0 : warp - 2, g_end = kAlias ? 2 : warp - 1;
     if (elect_one()) {
       constexpr uint32_t idesc_qk = make_idesc(kBf16, kTile, kTile, false, false);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, kTile, D, false, true);
       // descriptors are built once; a tile offset only moves the 16-byte start-address field
-      const uint64_t qdesc = make_smem_desc(sbase + L::kQ + g * L::kTileBytes, 16, 1024);
-      uint64_t kdesc[kStages], vdesc[kStages];
+      uint64_t qdesc[2], kdesc[kStages], vdesc[kStages];
+#pragma unroll
+      for (int g = 0; g < 2; ++g) qdesc[g] = make_smem_desc(sbase + L::kQ + g * L::kTileBytes, 16, 1024);
 #pragma unroll
       for (int s = 0; s < kStages; ++s) {
         kdesc[s] = make_smem_desc(sbase + L::kK + s * L::kTileBytes, 16, 1024);
         vdesc[s] = make_smem_desc(sbase + L::kV + s * L::kTileBytes, kBoxBytes, 1024);
       }
-      auto issue_qk = [&](int st) {
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
-          mma_ss(tm_S[g], qdesc + off, kdesc[st] + off, idesc_qk, kk > 0 ? 1u : 0u);
-        }
-        mma_commit(bar(S_FULL + g));
-      };
-      auto issue_pv = [&](int st, bool first_tile) {
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          mma_ts(tm_O[g], tm_P[g] + kk * 8, vdesc[st] + uint64_t((kk * 2048) >> 4), idesc_pv,
-                 (!first_tile || kk > 0) ? 1u : 0u);
-      };
       bool ok = true;
-      int kv = 0, tc = 0, oc = 0;
+      int kv = 0, tc[2] = {0, 0}, oc[2] = {0, 0};
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const Item it = decode_item(a, item);
-        const int nt = it.nt[g];
-        if (nt > 0) ok = wait_or_abort(bar(Q_FULL + g), oc & 1, abort_flag, a.status, 104);
         // round j: score MMA of key tile j and output MMA of key tile j - 1
         for (int j = 0; j <= it.nt_max && ok; ++j) {
-          const int st = (kv + j) % kStages, stp = (kv + j - 1) % kStages;
-          auto round_pv = [&]() {
-            if (j == 0) return;
-            const int jj = j - 1;
-            // every issuer observes every ring tile (also the ones its query tile skips): that keeps it to one
-            // arrival per phase of the "empty" barrier
-            ok = wait_or_abort(bar(V_FULL + stp), ((kv + jj) / kStages) & 1, abort_flag, a.status, 106);
-            if (!ok) return;
-            if (jj < nt) {
-              ok = wait_or_abort(bar(P_READY + g), (tc + jj) & 1, abort_flag, a.status, 107);
+          const int st = (kv + j) % kStages, stp = (kv + j + kStages - 1) % kStages;
+          if (j < it.nt_max) ok = wait_or_abort(bar(K_FULL + st), ((kv + j) / kStages) & 1, abort_flag, a.status, 105);
+          if (ok && j > 0) ok = wait_or_abort(bar(V_FULL + stp), ((kv + j - 1) / kStages) & 1, abort_flag, a.status, 106);
+          if (!ok) break;
+          tc_fence_after_sync();
+          for (int g = g_begin; g < g_end && ok; ++g) {
+            const int nt = it.nt[g];
+            auto round_pv = [&]() {
+              const int jj = j - 1;
+              if (j == 0 || jj >= nt) return;
+              ok = wait_or_abort(bar(P_READY + g), (tc[g] + jj) & 1, abort_flag, a.status, 107);
               // the previous item's epilogue must have read O_g out before the first tile overwrites it
-              if (ok && jj == 0 && oc > 0) ok = wait_or_abort(bar(O_FREE + g), (oc - 1) & 1, abort_flag, a.status, 115);
+              if (ok && jj == 0 && oc[g] > 0)
+                ok = wait_or_abort(bar(O_FREE + g), (oc[g] - 1) & 1, abort_flag, a.status, 115);
               if (!ok) return;
               tc_fence_after_sync();
-              issue_pv(stp, jj == 0);
+#pragma unroll
+              for (int kk = 0; kk < kTile / 16; ++kk)
+                mma_ts(tm_O[g], tm_P[g] + kk * 8, vdesc[stp] + uint64_t((kk * 2048) >> 4), idesc_pv,
+                       (jj > 0 || kk > 0) ? 1u : 0u);
               if (!kAlias) mma_commit(bar(PV_DONE + g));
               if (jj == nt - 1) mma_commit(bar(O_DONE + g));
-            }
-            mma_commit(bar(V_EMPTY + stp));
-          };
-          auto round_qk = [&]() {
-            if (j < it.nt_max) ok = wait_or_abort(bar(K_FULL + st), ((kv + j) / kStages) & 1, abort_flag, a.status, 105);
-            if (!ok) return;
-            if (j < nt) {
-              const int gt = tc + j;
-              if (!kAlias && gt > 0) ok = wait_or_abort(bar(S_FREE + g), (gt - 1) & 1, abort_flag, a.status, 111);
+            };
+            auto round_qk = [&]() {
+              if (j >= nt) return;
+              const int gt = tc[g] + j;
+              if (j == 0) ok = wait_or_abort(bar(Q_FULL + g), oc[g] & 1, abort_flag, a.status, 104);
+              if (ok && !kAlias && gt > 0) ok = wait_or_abort(bar(S_FREE + g), (gt - 1) & 1, abort_flag, a.status, 111);
               if (!ok) return;
               tc_fence_after_sync();
-              issue_qk(st);
+#pragma unroll
+              for (int kk = 0; kk < D / 16; ++kk) {
+                const uint64_t off = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+                mma_ss(tm_S[g], qdesc[g] + off, kdesc[st] + off, idesc_qk, kk > 0 ? 1u : 0u);
+              }
+              mma_commit(bar(S_FULL + g));
               if (j == nt - 1) mma_commit(bar(Q_EMPTY + g));   // Q_g may be reloaded once these are done
+            };
+            if constexpr (kAlias) {
+              round_pv();   // P(j-1) lives in S_g: its output MMA goes first
+              if (ok) round_qk();
+            } else {
+              round_qk();   // S_g was read out early in softmax(j-1): the next scores run underneath it
+              if (ok) round_pv();
             }
-            if (j < it.nt_max) mma_commit(bar(K_EMPTY + st));
-          };
-          if constexpr (kAlias) {
-            round_pv();   // P(j-1) lives in S_g: its output MMA goes first
-            if (ok) round_qk();
-          } else {
-            round_qk();   // S_g was read out early in softmax(j-1): the next scores run underneath it
-            if (ok) round_pv();
           }
+          if (!ok) break;
+          if (j < it.nt_max) mma_commit(bar(K_EMPTY + st));
+          if (j > 0) mma_commit(bar(V_EMPTY + stp));
         }
         kv += it.nt_max;
-        tc += nt;
-        oc += nt > 0 ? 1 : 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          tc[g] += it.nt[g];
+          oc[g] += it.nt[g] > 0 ? 1 : 0;
+        }
       }
     }
   }

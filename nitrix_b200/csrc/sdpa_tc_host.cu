@@ -80,7 +80,7 @@ namespace {
 __global__ void __launch_bounds__(256) mask_pack_kernel(const uint8_t* mask, int64_t sb, int64_t sh, int64_t ss,
                                                         int64_t st, int Hm, int Sm, int S, int T,
                                                         uint32_t* rows_out, int words_per_row,
-                                                        uint32_t* cols_out, int words_per_col) {
+                                                        uint32_t* cols_out, int words_per_col, int* kv_len) {
   __shared__ uint8_t tile[32][33];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bm = blockIdx.z / Hm, hm = blockIdx.z - bm * Hm;
@@ -93,8 +93,11 @@ __global__ void __launch_bounds__(256) mask_pack_kernel(const uint8_t* mask, int
     const uint8_t v = in ? (base[int64_t(Sm == 1 ? 0 : row) * ss + int64_t(key) * st] != 0) : 0;
     tile[rl][lane] = v;
     const uint32_t word = __ballot_sync(0xffffffffu, v != 0);
-    if (lane == 0 && row < Sm)
+    if (lane == 0 && row < Sm) {
       rows_out[(int64_t(blockIdx.z) * Sm + row) * words_per_row + blockIdx.x] = word;
+      // key-only mask: remember the last kept key (1 + index) so that fully dropped tail tiles are skipped
+      if (kv_len && word != 0u) atomicMax(kv_len + blockIdx.z, key0 + 32 - __clz(word));
+    }
   }
   if (!cols_out) return;
   __syncthreads();
@@ -121,6 +124,7 @@ MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed) {
   p.rows_bytes = (p.rows_bytes + 255) / 256 * 256;
   p.cols_bytes = transposed ? size_t(p.extent[0] * p.extent[1]) * pr.T * p.words_per_col * 4 : 0;
   p.cols_bytes = (p.cols_bytes + 255) / 256 * 256;
+  p.len_bytes = p.extent[2] == 1 ? (size_t(p.extent[0] * p.extent[1]) * 4 + 255) / 256 * 256 : 0;
   return p;
 }
 
@@ -132,11 +136,12 @@ int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, Mask
   const int Bm = int(plan.extent[0]), Hm = int(plan.extent[1]), Sm = int(plan.extent[2]);
   const int n_rows = cols ? pr.S : Sm;
   // padding words beyond ceil(T/32) (and ceil(S/32)) must read as "dropped"
-  cudaError_t e = cudaMemsetAsync(ws, 0, plan.rows_bytes + plan.cols_bytes, stream);
+  int* kv_len = plan.len_bytes ? reinterpret_cast<int*>(static_cast<char*>(ws) + plan.rows_bytes + plan.cols_bytes) : nullptr;
+  cudaError_t e = cudaMemsetAsync(ws, 0, plan.total(), stream);
   if (e != cudaSuccess) { set_error("cudaMemsetAsync(mask bits): %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
   dim3 grid((pr.T + 31) / 32, (n_rows + 31) / 32, Bm * Hm);
   mask_pack_kernel<<<grid, 256, 0, stream>>>(pr.mask, pr.ms[0], pr.ms[1], pr.ms[2], pr.ms[3], Hm, Sm, pr.S, pr.T, rows,
-                                             plan.words_per_row, cols, plan.words_per_col);
+                                             plan.words_per_row, cols, plan.words_per_col, kv_len);
   count_launch();
   if (int rc = check_launch("mask_pack_kernel")) return rc;
   out->rows = rows;
@@ -147,6 +152,9 @@ int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, Mask
   out->tkey_stride = plan.words_per_col;
   out->th_stride = Hm == 1 ? 0 : int64_t(pr.T) * plan.words_per_col;
   out->tb_stride = Bm == 1 ? 0 : int64_t(Hm) * pr.T * plan.words_per_col;
+  out->kv_len = kv_len;
+  out->len_h_stride = Hm == 1 ? 0 : 1;
+  out->len_b_stride = Bm == 1 ? 0 : Hm;
   return NB200_OK;
 }
 
@@ -209,7 +217,7 @@ bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const 
 size_t tc_workspace_bytes(const Problem& pr, int dtype, int bias_dtype, int pass) {
   if (pass == NB200_PASS_BWD) return tc::bwd_workspace_bytes(pr, dtype, bias_dtype);
   const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, false);
-  return mp.rows_bytes;
+  return mp.total();
 }
 
 int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
@@ -217,8 +225,8 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   BiasPlan bp;
   if (!bias_plan(pr, dtype, bias_dtype, &bp, &why)) { set_error("%s", why); return NB200_ERR_UNSUPPORTED; }
   const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, false);
-  if (mp.rows_bytes > ws_bytes || (mp.rows_bytes && !ws)) {
-    set_error("forward mask bits need %zu workspace bytes", mp.rows_bytes);
+  if (mp.total() > ws_bytes || (mp.total() && !ws)) {
+    set_error("forward mask bits need %zu workspace bytes", mp.total());
     return NB200_ERR_WORKSPACE;
   }
   tc::FwdArgs a{};
