@@ -71,8 +71,8 @@ struct BwdSmem {
   static constexpr int kY = kX + 2 * kXBytes;
   static constexpr int kBias = kY + kYStages * kYStageBytes;
   static constexpr int kBars = kBias + kBiasSlots * kBoxBytes;
-  // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2]
-  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4;
+  // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2], p_free[2], e_free[2]
+  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4 + 4;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
 };
@@ -92,7 +92,13 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   auto bar = [&](int i) { return smem_u32(bars + i); };
   constexpr int NY = L::kYStages;
   constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, E_READY = PROD_FULL + 2,
-                ACC_DONE = E_READY + 2, B_FULL = ACC_DONE + 1, B_EMPTY = B_FULL + 2;
+                ACC_DONE = E_READY + 2, B_FULL = ACC_DONE + 1, B_EMPTY = B_FULL + 2, P_FREE = B_EMPTY + 2,
+                E_FREE = P_FREE + 2;
+  // D = 64 has TMEM room for E tiles of their own.  Then a stage's products can be recomputed as soon as the
+  // element-wise group has read them out, and the accumulating MMAs trail the products by two steps, so
+  // neither group ever waits for the other's MMAs.  D = 128 overwrites the products and trails by one.
+  constexpr bool kDeep = D == 64;
+  constexpr int kLag = kDeep ? 2 : 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = a.bh_begin + blockIdx.y;
@@ -119,7 +125,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < L::kNumBars; ++i) {
       uint32_t count = 1;
-      if (i >= E_READY && i < E_READY + 2) count = 128;
+      if (i >= E_READY && i < E_READY + 2) count = 4;   // one lane per warp of the group
+      if (i >= P_FREE && i < P_FREE + 2) count = 4;
       if (i >= B_EMPTY && i < B_EMPTY + 2) count = 4;
       mbar_init(bar(i), count);
     }
@@ -134,7 +141,12 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tm_acc1 = tmem + 256, tm_acc2 = tmem + 256 + D;
+  // TMEM columns.  Products: stage s at 128 s (P1) and 128 s + 64 (P2).
+  //   D = 64 (kDeep): E tiles of stage s at 256 + 64 s (E1, 32 columns) and + 32 (E2); ACC1 at 384, ACC2 at 448.
+  //   D = 128: no room for separate E tiles: E1 / E2 overwrite P1 / P2; ACC1 at 256, ACC2 at 384.
+  const uint32_t tm_e = kDeep ? tmem + 256 : tmem;
+  constexpr int kEStage = kDeep ? 64 : 128, kE2Off = kDeep ? 32 : 64;
+  const uint32_t tm_acc1 = tmem + (kDeep ? 384 : 256), tm_acc2 = tm_acc1 + D;
 
   if (warp < 4) {
   reg_dealloc<kProducerRegs>();
@@ -194,44 +206,51 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       constexpr uint32_t idesc_prod = make_idesc(kBf16, kTile, kStep, false, false);
       constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, D, false, true);
       bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 203);
-      for (int n = 0; n <= n_steps && ok; ++n) {
+      // descriptors are built once; an offset only moves the 16-byte start-address field
+      const uint64_t x1desc = make_smem_desc(sbase + L::kX, 16, 1024);
+      const uint64_t x2desc = make_smem_desc(sbase + L::kX + L::kXBytes, 16, 1024);
+      // round n: the two products of step n, then the accumulating MMAs of step n - kLag
+      for (int n = 0; n < n_steps + kLag && ok; ++n) {
         if (n < n_steps) {
           const int st = n % NY, s = n & 1;
           ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 204);
+          // separate E tiles: the stage's products may be overwritten once step n - 2 has read them out
+          if (ok && kDeep && n >= 2) ok = wait_or_abort(bar(P_FREE + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 209);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+          const uint64_t y1desc = make_smem_desc(ybase, 16, 1024), y2desc = make_smem_desc(ybase + L::kYBytes, 16, 1024);
           const uint32_t p1 = tmem + s * 128, p2 = p1 + 64;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t xo = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-            const uint32_t yo = (kk / 4) * kYBoxBytes + (kk % 4) * 32;
-            mma_ss(p1, make_smem_desc(sbase + L::kX + xo, 16, 1024), make_smem_desc(ybase + yo, 16, 1024), idesc_prod,
-                   kk > 0 ? 1u : 0u);
+            const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+            const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
+            mma_ss(p1, x1desc + xo, y1desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
           }
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t xo = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-            const uint32_t yo = (kk / 4) * kYBoxBytes + (kk % 4) * 32;
-            mma_ss(p2, make_smem_desc(sbase + L::kX + L::kXBytes + xo, 16, 1024),
-                   make_smem_desc(ybase + L::kYBytes + yo, 16, 1024), idesc_prod, kk > 0 ? 1u : 0u);
+            const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+            const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
+            mma_ss(p2, x2desc + xo, y2desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
           }
           mma_commit(bar(PROD_FULL + s));
         }
-        if (n > 0) {
-          const int m = n - 1, st = m % NY, s = m & 1;
+        if (n >= kLag) {
+          const int m = n - kLag, st = m % NY, s = m & 1;
           ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 205);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          const uint32_t e1 = tmem + s * 128, e2 = e1 + 64;
+          const uint64_t y1mn = make_smem_desc(ybase, kYBoxBytes, 1024);
+          const uint64_t y2mn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);
+          const uint32_t e1 = tm_e + s * kEStage, e2 = e1 + kE2Off;
 #pragma unroll
           for (int kk = 0; kk < kStep / 16; ++kk) {
             const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
-            if (kKeyMajor)
-              mma_ts(tm_acc1, e1 + kk * 8, make_smem_desc(ybase + L::kYBytes + kk * 2048, kYBoxBytes, 1024), idesc_acc, acc);
-            mma_ts(tm_acc2, e2 + kk * 8, make_smem_desc(ybase + kk * 2048, kYBoxBytes, 1024), idesc_acc, acc);
+            if (kKeyMajor) mma_ts(tm_acc1, e1 + kk * 8, y2mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
+            mma_ts(tm_acc2, e2 + kk * 8, y1mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
           }
+          if (kDeep) mma_commit(bar(E_FREE + s));   // the E tiles of this stage may be rewritten once these are done
           mma_commit(bar(Y_EMPTY + st));
           if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
         }
@@ -326,6 +345,12 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           tmem_ld32(tP2 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[kStep + c * 32]));
         }
         tmem_wait_ld();
+        if constexpr (kDeep) {
+          // both products are in registers: the MMA issuer may recompute this stage
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(P_FREE + s));
+        }
 #pragma unroll
         for (int i = 0; i < kStep / 2; ++i) {
           t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
@@ -405,11 +430,21 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           e2[c] = pack2<kBf16>(ds.x, ds.y);
         }
       }
-      if (kKeyMajor) tmem_st32(tP1, e1);
-      tmem_st32(tP2, e2);
+      if constexpr (kDeep) {
+        // the E tiles of this stage are still being read by the accumulating MMAs of step n - 2
+        if (n >= 2) {
+          ok = wait_or_abort(bar(E_FREE + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 210);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+      }
+      const uint32_t tE1 = tm_e + s * kEStage + lane_addr, tE2 = tE1 + kE2Off;
+      if (kKeyMajor) tmem_st32(tE1, e1);
+      tmem_st32(tE2, e2);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar(E_READY + s));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(E_READY + s));
       if (!kKeyMajor && a.dbias && orow < a.S) {
         // dbias[row, r0 .. r0+63] = ds in bias dtype (the 16-bit pairs already packed in e2)
         uint8_t* dst = reinterpret_cast<uint8_t*>(a.dbias) +
