@@ -42,6 +42,24 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
+# Share of a step's ALGORITHMIC flops (14 S T_eff D per (batch, head): QK^T, PV forward; QK^T, dO V^T, P^T dO,
+# dS^T Q, dS K backward) attributed to each kernel.  The query-major backward recomputes QK^T and dO V^T, which
+# the key-major kernel is already credited with; only its dS K product counts.
+KERNEL_FLOP_SHARE = {
+    "sdpa_fwd_tc_kernel": 4 / 14,
+    "sdpa_bwd_tc_kernel<key-major>": 8 / 14,
+    "sdpa_bwd_tc_kernel<query-major>": 2 / 14,
+    "simt_fwd_kernel": 4 / 14,
+    "simt_bwd_dkv_kernel": 8 / 14,
+    "simt_bwd_dq_kernel": 2 / 14,
+}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/), full-size
+# workload, same command line as the default bench run.
+NCU_TRAFFIC_BYTES = {
+    "c2": {"sdpa_fwd_tc_kernel": 405.9e6, "sdpa_bwd_tc_kernel<key-major>": 601.4e6,
+           "sdpa_bwd_tc_kernel<query-major>": 499.8e6},
+}
+
 METRIC = "fwd+bwd attention TFLOP/s"
 UNIT = "TFLOP/s"
 
@@ -308,6 +326,18 @@ def main():
         barrier()
     launches = lib.nb200_launch_count() - launches0
     assert lib.nb200_device_status(local_rank) == 0, _cabi.last_error()
+    # second pass over the same steps with the library's per-kernel events on (a few microseconds per kernel,
+    # so it is kept out of the headline region): average launch duration of every kernel
+    kernel_ms = {}
+    if rank == 0:
+        lib.nb200_profile(1)
+        for i in range(args.steps):
+            if need_flush:
+                flush.fill_(i & 0xFF)
+            step()
+        torch.cuda.synchronize()
+        kernel_ms = _cabi.kernel_times()
+        lib.nb200_profile(0)
     fwd_ms = [e[0].elapsed_time(e[1]) for e in events]
     bwd_ms = [e[1].elapsed_time(e[2]) for e in events]
     step_ms = statistics.fmean(f + b for f, b in zip(fwd_ms, bwd_ms))
@@ -364,18 +394,26 @@ def main():
 
     peaks = load_peaks()
     f_ms, b_ms = statistics.fmean(fwd_ms), statistics.fmean(bwd_ms)
-    if b_ms >= f_ms:
-        dom, dom_ms, dom_flops = "backward pass (delta + dq/dbias + dk/dv kernels)", b_ms, wl["bwd_flops"]
-    else:
-        dom, dom_ms, dom_flops = "forward kernel", f_ms, wl["fwd_flops"]
-    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     peak = peaks["burst"]
-    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
-                "peak_source": f"bf16 dense burst, of {peaks['source']}",
-                "fwd": {"ms": f_ms, "tflops": wl["fwd_flops"] / (f_ms * 1e-3) / 1e12},
-                "bwd": {"ms": b_ms, "tflops": wl["bwd_flops"] / (b_ms * 1e-3) / 1e12},
-                "step_vs_roofline": max(wl["flops"] / (peak * 1e12), wl["bytes"] / (peaks["hbm"] * 1e9)) / (step_ms * 1e-3)}
+    # dominant kernel: per-kernel CUDA-event times recorded by the library on its launching stream
+    dom = max(kernel_ms, key=lambda n: kernel_ms[n][1]) if kernel_ms else None
+    roofline = None
+    if dom is not None:
+        launches, total_ms = kernel_ms[dom]
+        avg_ms = total_ms / launches
+        share = KERNEL_FLOP_SHARE.get(dom)
+        dom_flops = wl["flops"] * share if share is not None else None
+        achieved = dom_flops / (avg_ms * 1e-3) / 1e12 if dom_flops else None
+        traffic = NCU_TRAFFIC_BYTES.get(wl_name, {}).get(dom) if not args.batch else None
+        roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak if achieved else None, "traffic": traffic,
+                    "avg_launch_ms": avg_ms, "launches": launches,
+                    "algorithmic_flops_per_launch": dom_flops,
+                    "peak_source": f"bf16 dense burst (kernels timed alone), of {peaks['source']}",
+                    "kernels_ms": {n: round(v[1] / v[0], 5) for n, v in sorted(kernel_ms.items())},
+                    "fwd": {"ms": f_ms, "tflops": wl["fwd_flops"] / (f_ms * 1e-3) / 1e12},
+                    "bwd": {"ms": b_ms, "tflops": wl["bwd_flops"] / (b_ms * 1e-3) / 1e12},
+                    "step_vs_roofline": max(wl["flops"] / (peak * 1e12), wl["bytes"] / (peaks["hbm"] * 1e9)) / (step_ms * 1e-3)}
     cpu = None
     if not args.no_cpu_baseline and world == 1:
         val, cores, sample, _ = cpu_reference_step(wl_name, seconds_target=10.0)

@@ -153,6 +153,14 @@ NB200_API int nb200_sdpa_bwd_static_scratch(const nb200_sdpa_params* p, void* cu
 /* Number of kernels this library has enqueued since load (all threads). */
 NB200_API uint64_t nb200_launch_count(void);
 
+/* Per-kernel timing for measurements.  nb200_profile(1) clears earlier records and makes the library record a
+ * CUDA event on the launching stream after each kernel it enqueues; nb200_profile(0) stops and clears.
+ * nb200_profile_read synchronises those events and writes one line per kernel name,
+ * "name<TAB>launches<TAB>total_ms", into buf (NUL-terminated, truncated to `bytes`); it returns the size the
+ * full text needs.  The events cost a few microseconds per kernel: leave this off in production. */
+NB200_API int nb200_profile(int enable);
+NB200_API size_t nb200_profile_read(char* buf, size_t bytes);
+
 /* Reads (and clears) the device-side status word kernels set when a bounded
  * wait expires; call after synchronising the stream.  NB200_OK or
  * NB200_ERR_TIMEOUT.  `device` is the CUDA device ordinal. */

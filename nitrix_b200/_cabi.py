@@ -55,6 +55,8 @@ EXPORTS = (
     "nb200_sdpa_bwd",
     "nb200_sdpa_bwd_static_scratch",
     "nb200_launch_count",
+    "nb200_profile",
+    "nb200_profile_read",
     "nb200_device_status",
 )
 
@@ -79,6 +81,9 @@ def lib() -> C.CDLL:
     L.nb200_last_error.restype = C.c_char_p
     L.nb200_launch_count.restype = C.c_uint64
     L.nb200_device_status.argtypes = [C.c_int]
+    L.nb200_profile.argtypes = [C.c_int]
+    L.nb200_profile_read.argtypes = [C.c_char_p, C.c_size_t]
+    L.nb200_profile_read.restype = C.c_size_t
     L.nb200_sdpa_plan.argtypes = [C.POINTER(SdpaParams), C.c_int, C.POINTER(C.c_int)]
     L.nb200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaParams), C.c_int, C.POINTER(C.c_size_t)]
     L.nb200_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
@@ -97,3 +102,16 @@ def new_params() -> SdpaParams:
     p = SdpaParams()
     p.struct_size = C.sizeof(SdpaParams)
     return p
+
+
+def kernel_times() -> dict:
+    """Per-kernel ``{name: (launches, total_ms)}`` recorded since ``lib().nb200_profile(1)``."""
+    L = lib()
+    need = L.nb200_profile_read(None, 0)
+    buf = C.create_string_buffer(int(need) + 16)
+    L.nb200_profile_read(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split("\t")
+        out[name] = (int(n), float(ms))
+    return out

@@ -6,6 +6,10 @@
 #include <string.h>
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
 
 #include "sdpa_common.cuh"
 
@@ -26,12 +30,34 @@ void set_error(const char* fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
 
+// ---- optional per-kernel timing (nb200_profile / nb200_profile_read) ----------
+// When enabled, an event is recorded on the launching stream after every kernel
+// this library enqueues (and one at the start of each forward / backward call);
+// consecutive events on the in-order stream bracket one kernel each.
+namespace {
+struct ProfMark { const char* name; cudaEvent_t ev; };
+std::atomic<bool> g_prof_on{false};
+std::mutex g_prof_mutex;
+std::vector<ProfMark> g_prof_marks;
+thread_local cudaStream_t g_prof_stream = nullptr;
+
+void prof_mark(const char* name) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  cudaEvent_t ev;
+  if (cudaEventCreate(&ev) != cudaSuccess) { cudaGetLastError(); return; }
+  cudaEventRecord(ev, g_prof_stream);
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_prof_marks.push_back({name, ev});
+}
+}  // namespace
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("%s: %s", what, cudaGetErrorString(e));
     return NB200_ERR_LAUNCH;
   }
+  prof_mark(what);
   return NB200_OK;
 }
 
@@ -213,6 +239,40 @@ NB200_API int nb200_device_status(int device) {
   return NB200_OK;
 }
 
+NB200_API int nb200_profile(int enable) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  for (auto& m : g_prof_marks) cudaEventDestroy(m.ev);
+  g_prof_marks.clear();
+  g_prof_on.store(enable != 0, std::memory_order_relaxed);
+  return NB200_OK;
+}
+
+NB200_API size_t nb200_profile_read(char* buf, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  std::map<std::string, std::pair<long, double>> agg;   // name -> (launches, total ms)
+  for (size_t i = 1; i < g_prof_marks.size(); ++i) {
+    if (!g_prof_marks[i].name) continue;                // a call's start marker brackets nothing
+    if (cudaEventSynchronize(g_prof_marks[i].ev) != cudaSuccess) { cudaGetLastError(); continue; }
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, g_prof_marks[i - 1].ev, g_prof_marks[i].ev) != cudaSuccess) { cudaGetLastError(); continue; }
+    auto& a = agg[g_prof_marks[i].name];
+    a.first += 1;
+    a.second += ms;
+  }
+  std::string out;
+  char line[256];
+  for (auto& kv : agg) {
+    snprintf(line, sizeof(line), "%s\t%ld\t%.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+    out += line;
+  }
+  if (buf && bytes) {
+    const size_t n = out.size() < bytes - 1 ? out.size() : bytes - 1;
+    memcpy(buf, out.data(), n);
+    buf[n] = 0;
+  }
+  return out.size() + 1;
+}
+
 NB200_API int nb200_sdpa_plan(const nb200_sdpa_params* p, int pass, int* kernel) {
   if (!kernel) { set_error("kernel out-pointer is NULL"); return NB200_ERR_INVALID; }
   Lowered lw;
@@ -237,6 +297,8 @@ NB200_API int nb200_sdpa_fwd(const nb200_sdpa_params* p, void* cuda_stream) {
   int kernel = 0;
   if (int rc = choose(p, lw, NB200_PASS_FWD, &kernel)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  g_prof_stream = st;
+  prof_mark(nullptr);   // start of this call's kernels
   if (lw.pr.bh_count == 0 || lw.pr.S == 0) return NB200_OK;
   if (kernel == NB200_KERNEL_TCGEN05) {
     const size_t need = tc_workspace_bytes(lw.pr, lw.dtype, lw.bias_dtype, NB200_PASS_FWD);
@@ -255,6 +317,8 @@ NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream) {
   int kernel = 0;
   if (int rc = choose(p, lw, NB200_PASS_BWD, &kernel)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  g_prof_stream = st;
+  prof_mark(nullptr);   // start of this call's kernels
   if (lw.pr.bh_count == 0) return NB200_OK;
   const size_t fam = kernel == NB200_KERNEL_TCGEN05 ? tc_workspace_bytes(lw.pr, lw.dtype, lw.bias_dtype, NB200_PASS_BWD) : 0;
   const BwdScratch sc = bwd_scratch(p, lw, fam);
