@@ -36,6 +36,10 @@ import sys
 import threading
 import time
 
+# the CPU arm uses every host core; torchrun pins OMP_NUM_THREADS=1 for its children, so lift that before torch loads
+if "reference" in sys.argv or "--impl=reference" in sys.argv:
+    os.environ["OMP_NUM_THREADS"] = os.environ["MKL_NUM_THREADS"] = str(os.cpu_count() or 1)
+
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -399,15 +403,15 @@ def main():
     dom = max(kernel_ms, key=lambda n: kernel_ms[n][1]) if kernel_ms else None
     roofline = None
     if dom is not None:
-        launches, total_ms = kernel_ms[dom]
-        avg_ms = total_ms / launches
+        dom_launches, total_ms = kernel_ms[dom]
+        avg_ms = total_ms / dom_launches
         share = KERNEL_FLOP_SHARE.get(dom)
         dom_flops = wl["flops"] * share if share is not None else None
         achieved = dom_flops / (avg_ms * 1e-3) / 1e12 if dom_flops else None
         traffic = NCU_TRAFFIC_BYTES.get(wl_name, {}).get(dom) if not args.batch else None
         roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak if achieved else None, "traffic": traffic,
-                    "avg_launch_ms": avg_ms, "launches": launches,
+                    "avg_launch_ms": avg_ms, "launches": dom_launches,
                     "algorithmic_flops_per_launch": dom_flops,
                     "peak_source": f"bf16 dense burst (kernels timed alone), of {peaks['source']}",
                     "kernels_ms": {n: round(v[1] / v[0], 5) for n, v in sorted(kernel_ms.items())},
