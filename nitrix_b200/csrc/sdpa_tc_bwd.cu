@@ -20,6 +20,8 @@
 // ACC2 at 256 + D.  Twelve warps: 0 TMA producer (X once, Y ring), 1 bias
 // producer, 2 MMA issuer, 3 TMEM owner, 4-7 / 8-11 two element-wise groups that
 // take alternate steps (one owner row per thread).  All waits are bounded.
+#include <math.h>
+
 #include "sdpa_tc_bwd.cuh"
 
 namespace nb200 {
@@ -47,6 +49,11 @@ struct BwdArgs {
   int causal;
   float scale;
   int bias_mode;
+  // Key-major kernel, tile-mode bias: added by the tensor core, scores^T += bias^T (hi I + lo I) with
+  // hi + lo = 1 / scale split into two 16-bit values (lo = 0 when 1 / scale is exact in 16 bits).  Then
+  // scores * scale holds scale * q.k + bias and the element-wise warps never read the bias column-wise.
+  int bias_mma;
+  float inv_scale_hi, inv_scale_lo;
   int bias_b_mul, bias_h_mul;
   const void* bias;             // key mode base
   int64_t bias_bs, bias_hs;
@@ -70,7 +77,10 @@ struct BwdSmem {
   static constexpr int kX = 0;
   static constexpr int kY = kX + 2 * kXBytes;
   static constexpr int kBias = kY + kYStages * kYStageBytes;
-  static constexpr int kBars = kBias + kBiasSlots * kBoxBytes;
+  // hi * I and lo * I (64 x 64 each), the second operand of the MMAs that add a bias tile to the transposed scores
+  static constexpr int kIdentBytes = 2 * kStep * 128;
+  static constexpr int kIdent = kBias + kBiasSlots * kBoxBytes;
+  static constexpr int kBars = kIdent + kIdentBytes;
   // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2], p_free[2], e_free[2]
   static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4 + 4;
   static constexpr int kMisc = kBars + 8 * kNumBars;
@@ -127,11 +137,29 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       uint32_t count = 1;
       if (i >= E_READY && i < E_READY + 2) count = 4;   // one lane per warp of the group
       if (i >= P_FREE && i < P_FREE + 2) count = 4;
-      if (i >= B_EMPTY && i < B_EMPTY + 2) count = 4;
+      if (i >= B_EMPTY && i < B_EMPTY + 2) count = a.bias_mma ? 1 : 4;   // released by the MMA issuer or by the group's warps
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
     mbar_init_fence();
+  }
+  if constexpr (kKeyMajor) {
+    if (a.bias_mma) {
+      // Two 64 x 64 tiles, hi * I and lo * I with hi + lo = 1 / scale to 16 + 16 bits, as K-major 128-byte-swizzled
+      // operands (rows of 64 elements = 128 bytes).  Tile 0 at kIdent, tile 1 at kIdent + 8 KB.
+      uint4* ident = reinterpret_cast<uint4*>(smem + L::kIdent);
+      for (int idx = threadIdx.x; idx < 2 * kStep * 8; idx += kThreads) {   // one 16-byte chunk each
+        const int tile = idx / (kStep * 8), rem = idx - tile * kStep * 8;
+        const int row = rem >> 3, chunk = (rem & 7) ^ (row & 7);             // logical chunk stored at this slot
+        const int col0 = chunk * 8;                                          // first logical column of the chunk
+        const float val = tile == 0 ? a.inv_scale_hi : a.inv_scale_lo;
+        const uint16_t one = kBf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (row >= col0 && row < col0 + 8) w[(row - col0) >> 1] = uint32_t(one) << (((row - col0) & 1) * 16);
+        ident[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();   // written by threads, read by the tensor core
+    }
   }
   if (warp == 3) {
     tmem_alloc(smem_u32(tmem_slot), 512);
@@ -233,7 +261,27 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
             mma_ss(p2, x2desc + xo, y2desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
           }
+          if (a.bias_mma) {
+            // scores += bias * (I / scale): the bias slot is consumed straight from shared memory by the tensor core
+            const int slot = n & 1;
+            ok = wait_or_abort(bar(B_FULL + slot), (n >> 1) & 1, abort_flag, a.status, 211);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t bslot = sbase + L::kBias + slot * kBoxBytes;
+            // P1[key, q] += bias^T[key, q'] (hi I + lo I)[q', q]: A = the slot (64 q' rows, two 64-key boxes) read
+            // MN-major, B = the identity tiles, K-major
+            constexpr uint32_t idesc_bias = make_idesc(kBf16, kTile, kStep, true, false);
+            const uint64_t adesc = make_smem_desc(bslot, kYBoxBytes, 1024);
+            const int n_tiles = a.inv_scale_lo != 0.f ? 2 : 1;
+            for (int tile = 0; tile < n_tiles; ++tile) {
+              const uint64_t bdesc = make_smem_desc(sbase + L::kIdent + tile * kYBoxBytes, 16, 1024);
+#pragma unroll
+              for (int kk = 0; kk < kStep / 16; ++kk)
+                mma_ss(p1, adesc + uint64_t((kk * 2048) >> 4), bdesc + uint64_t((kk * 32) >> 4), idesc_bias, 1u);
+            }
+          }
           mma_commit(bar(PROD_FULL + s));
+          if (a.bias_mma) mma_commit(bar(B_EMPTY + (n & 1)));   // the slot may be refilled once these MMAs are done
         }
         if (n >= kLag) {
           const int m = n - kLag, st = m % NY, s = m & 1;
@@ -267,7 +315,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     bool ok = true;
     // without a bias the scale is folded into the exponent's multiplier: p = exp2(s * (scale log2e) - lse)
-    const bool fold_scale = a.bias_mode == kBiasNone;
+    // (the same holds when the tensor core has already added bias / scale to the scores)
+    const bool fold_scale = a.bias_mode == kBiasNone || a.bias_mma;
     const float mul = fold_scale ? a.scale * kLog2e : kLog2e;
     const float2 mul2 = make_float2(mul, mul), scale2 = make_float2(a.scale, a.scale);
     float lse_row = 0.f, delta_row = 0.f;
@@ -358,7 +407,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
       }
       // logits t = s * scale + bias
-      if (a.bias_mode == kBiasTile) {
+      if (a.bias_mode == kBiasTile && !a.bias_mma) {
         const int slot = n & 1;
         ok = wait_or_abort(bar(B_FULL + slot), (n >> 1) & 1, abort_flag, a.status, 207);
         if (!ok) break;
@@ -599,6 +648,20 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.H = pr.H; a.S = pr.S; a.T = pr.T; a.bh_begin = pr.bh_begin;
   a.causal = pr.causal; a.scale = pr.scale;
   a.bias_mode = bias_mode_of(pr);
+  a.bias_mma = 0;
+  a.inv_scale_hi = a.inv_scale_lo = 0.f;
+  if (a.bias_mode == kBiasTile && pr.scale != 0.f && isfinite(1.f / pr.scale)) {
+    // 1 / scale as hi + lo, both exact in the 16-bit operand type (lo = 0 for a power-of-two scale)
+    const float inv = 1.f / pr.scale;
+    const float hi = dtype == NB200_BF16 ? __bfloat162float(__float2bfloat16_rn(inv)) : __half2float(__float2half_rn(inv));
+    const float rest = inv - hi;
+    const float lo = dtype == NB200_BF16 ? __bfloat162float(__float2bfloat16_rn(rest)) : __half2float(__float2half_rn(rest));
+    if (isfinite(hi) && hi != 0.f) {
+      a.bias_mma = 1;
+      a.inv_scale_hi = hi;
+      a.inv_scale_lo = lo;
+    }
+  }
   a.bias_b_mul = (pr.B > 1 && pr.bs[0] != 0) ? 1 : 0;
   a.bias_h_mul = (pr.H > 1 && pr.bs[1] != 0) ? 1 : 0;
   a.bias = pr.bias; a.bias_bs = pr.bs[0]; a.bias_hs = pr.bs[1];
@@ -627,6 +690,9 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   // query-major: dq (+ dbias)
   {
     BwdArgs aq = a;
+    // query-major reads the bias row-wise with 16-byte loads, which is cheap; the tensor-core add only pays in
+    // the key-major kernel, where the bias would be read column-wise, two bytes at a time
+    aq.bias_mma = 0;
     aq.out2 = pr.dq;
     for (int i = 0; i < 3; ++i) aq.o2s[i] = pr.dqs[i];
     aq.dbias = pr.dbias;
