@@ -80,9 +80,19 @@ struct BwdSmem {
   // hi * I and lo * I (64 x 64 each), the second operand of the MMAs that add a bias tile to the transposed scores
   static constexpr int kIdentBytes = 2 * kStep * 128;
   static constexpr int kIdent = kBias + kBiasSlots * kBoxBytes;
-  static constexpr int kBars = kIdent + kIdentBytes;
-  // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2], p_free[2], e_free[2]
-  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4 + 4;
+  // Key-major: -lse / (scale log2e) and -delta of a step's 64 queries are added to the two products by one more
+  // K = 16 MMA step each, products += W * C^T with W (128 x 16) the same row of weights for every key and
+  // C (64 x 16) the query's value split over the first columns.  Both are K-major without swizzle: 8-row groups of
+  // 256 bytes = [8 rows x 16 bytes (K 0-7)][8 rows x 16 bytes (K 8-15, zero)].
+  static constexpr int kWeightBytes = (kTile / 8) * 256;
+  static constexpr int kAugTileBytes = (kStep / 8) * 256;
+  static constexpr int kAugSlotBytes = 2 * kAugTileBytes;      // lse tile, delta tile
+  static constexpr int kWeights = kIdent + kIdentBytes;
+  static constexpr int kAug = kWeights + kWeightBytes;          // two slots
+  static constexpr int kBars = kAug + 2 * kAugSlotBytes;
+  // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2], p_free[2], e_free[2],
+  // aug_full[2], aug_free[2]
+  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4 + 4 + 4;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
 };
@@ -103,7 +113,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   constexpr int NY = L::kYStages;
   constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, E_READY = PROD_FULL + 2,
                 ACC_DONE = E_READY + 2, B_FULL = ACC_DONE + 1, B_EMPTY = B_FULL + 2, P_FREE = B_EMPTY + 2,
-                E_FREE = P_FREE + 2;
+                E_FREE = P_FREE + 2, AUG_FULL = E_FREE + 2, AUG_FREE = AUG_FULL + 2;
   // D = 64 has TMEM room for E tiles of their own.  Then a stage's products can be recomputed as soon as the
   // element-wise group has read them out, and the accumulating MMAs trail the products by two steps, so
   // neither group ever waits for the other's MMAs.  D = 128 overwrites the products and trails by one.
@@ -144,6 +154,18 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     mbar_init_fence();
   }
   if constexpr (kKeyMajor) {
+    {
+      // weight rows (w0, w1, w2, 0, ...): a query's addend is sum_j w_j c_j with c_j 16-bit; bf16 has fp32's range,
+      // so three unit weights give 24 bits; fp16 spreads the terms over 2^8, 1, 2^-8 to cover magnitudes up to 1.6e7
+      uint4* wt = reinterpret_cast<uint4*>(smem + L::kWeights);
+      const uint32_t w01 = kBf16 ? 0x3F803F80u : 0x3C005C00u;   // (w0, w1): bf16 (1, 1); fp16 (256, 1)
+      const uint32_t w2 = kBf16 ? 0x00003F80u : 0x00001C00u;    // (w2, 0):  bf16 1; fp16 2^-8
+      for (int idx = threadIdx.x; idx < L::kWeightBytes / 16; idx += kThreads)
+        wt[idx] = (idx & 8) ? make_uint4(0, 0, 0, 0) : make_uint4(w01, w2, 0, 0);
+      uint4* aug = reinterpret_cast<uint4*>(smem + L::kAug);
+      for (int idx = threadIdx.x; idx < 2 * L::kAugSlotBytes / 16; idx += kThreads) aug[idx] = make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();
+    }
     if (a.bias_mma) {
       // Two 64 x 64 tiles, hi * I and lo * I with hi + lo = 1 / scale to 16 + 16 bits, as K-major 128-byte-swizzled
       // operands (rows of 64 elements = 128 bytes).  Tile 0 at kIdent, tile 1 at kIdent + 8 KB.
@@ -280,7 +302,18 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                 mma_ss(p1, adesc + uint64_t((kk * 2048) >> 4), bdesc + uint64_t((kk * 32) >> 4), idesc_bias, 1u);
             }
           }
+          if constexpr (kKeyMajor) {
+            // P1 += W C1^T (C1: -lse / (scale log2e)), P2 += W C2^T (C2: -delta)
+            ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 212);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
+            const uint32_t aslot = sbase + L::kAug + s * L::kAugSlotBytes;
+            mma_ss(p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
+            mma_ss(p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
+          }
           mma_commit(bar(PROD_FULL + s));
+          if (kKeyMajor) mma_commit(bar(AUG_FREE + s));
           if (a.bias_mma) mma_commit(bar(B_EMPTY + (n & 1)));   // the slot may be refilled once these MMAs are done
         }
         if (n >= kLag) {
@@ -303,6 +336,50 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
         }
       }
+    }
+  } else if (kKeyMajor) {
+    // ---------------- warp 3: per-query addends as MMA operands ----------------
+    const float inv_mul = 1.f / (a.scale * kLog2e);
+    bool ok = true;
+    for (int n = 0; n < n_steps && ok; ++n) {
+      const int st = n % NY, s = n & 1;
+      ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 213);
+      if (ok && n >= 2) ok = wait_or_abort(bar(AUG_FREE + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 214);
+      if (!ok) break;
+      const float* ld = reinterpret_cast<const float*>(smem + L::kY + st * L::kYStageBytes + 2 * L::kYBytes);
+      uint8_t* slot = smem + L::kAug + s * L::kAugSlotBytes;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int q = lane + 32 * e;
+        const float c[2] = {-ld[q] * inv_mul, -ld[kStep + q]};
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile) {
+          // c = w0 c0 + w1 c1 + w2 c2 with the remainder carried in fp32
+          float rem = c[tile];
+          uint32_t h[3];
+#pragma unroll
+          for (int j = 0; j < 3; ++j) {
+            const float w = kBf16 ? 1.f : (j == 0 ? 256.f : (j == 1 ? 1.f : 0.00390625f));
+            const float v = rem * (1.f / w);
+            float back;
+            if constexpr (kBf16) {
+              const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+              h[j] = __bfloat16_as_ushort(hv);
+              back = __bfloat162float(hv);
+            } else {
+              const __half hv = __float2half_rn(v);
+              h[j] = __half_as_ushort(hv);
+              back = __half2float(hv);
+            }
+            rem = fmaf(-back, w, rem);
+          }
+          *reinterpret_cast<uint4*>(slot + tile * L::kAugTileBytes + (q >> 3) * 256 + (q & 7) * 16) =
+              make_uint4(h[0] | (h[1] << 16), h[2], 0u, 0u);
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(AUG_FULL + s));
     }
   }
   } else {
@@ -450,31 +527,22 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 #pragma unroll
         for (int c = 0; c < kStep / 2; ++c) t[c] = __ffma2_rn(t[c], scale2, own2);
       }
-      // p = exp2(t log2e - lse), ds = p (dp - delta)
-      const float4* ld4 = reinterpret_cast<const float4*>(smem + L::kY + st * L::kYStageBytes + 2 * L::kYBytes);
+      // p = exp2(t log2e - lse), ds = p (dp - delta); key-major products arrive with -lse and -delta already added
       uint32_t e1[kStep / 2], e2[kStep / 2];
       const bool need_mask = __any_sync(0xffffffffu, (keep[0] & keep[1]) != 0xffffffffu);
 #pragma unroll
       for (int c4 = 0; c4 < kStep / 4; ++c4) {
-        float2 nls[2], ndl[2];  // -lse and -delta of the four streamed rows (key-major) or of the owner row
-        if (kKeyMajor) {
-          const float4 lv = ld4[c4], dv4 = ld4[16 + c4];
-          nls[0] = make_float2(-lv.x, -lv.y); nls[1] = make_float2(-lv.z, -lv.w);
-          ndl[0] = make_float2(-dv4.x, -dv4.y); ndl[1] = make_float2(-dv4.z, -dv4.w);
-        } else {
-          nls[0] = nls[1] = make_float2(-lse_row, -lse_row);
-          ndl[0] = ndl[1] = make_float2(-delta_row, -delta_row);
-        }
+        const float2 nls = make_float2(-lse_row, -lse_row), ndl = make_float2(-delta_row, -delta_row);  // query-major
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int c = c4 * 2 + e;  // pair index: streamed rows 2c, 2c + 1
-          float2 x = __ffma2_rn(t[c], mul2, nls[e]);
+          float2 x = kKeyMajor ? __fmul2_rn(t[c], mul2) : __ffma2_rn(t[c], mul2, nls);
           if (need_mask) {
             if (!((keep[c >> 4] >> ((2 * c) & 31)) & 1u)) x.x = -INFINITY;
             if (!((keep[c >> 4] >> ((2 * c + 1) & 31)) & 1u)) x.y = -INFINITY;
           }
           const float2 p = make_float2(ex2(x.x), ex2(x.y));
-          const float2 ds = __fmul2_rn(p, __fadd2_rn(dp[c], ndl[e]));
+          const float2 ds = kKeyMajor ? __fmul2_rn(p, dp[c]) : __fmul2_rn(p, __fadd2_rn(dp[c], ndl));
           e1[c] = pack2<kBf16>(p.x, p.y);
           e2[c] = pack2<kBf16>(ds.x, ds.y);
         }
@@ -598,6 +666,10 @@ int bias_mode_of(const Problem& pr) {
 bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** why) {
   // forward coverage (dtype, head dims, lengths, q/k/v/bias layout) was checked by the caller
   if (pr.dbias_accum) { *why = "gradient of a broadcast bias needs a reduction"; return false; }
+  if (pr.scale == 0.f || !isfinite(1.f / pr.scale) || !isfinite(pr.scale)) {
+    *why = "scale is zero or not finite";   // the key-major kernel divides lse by scale
+    return false;
+  }
   if (pr.lse && reinterpret_cast<uintptr_t>(pr.lse) % 16) { *why = "lse is not 16-byte aligned"; return false; }
   if (pr.dout && (!tile_map_ok(pr.dout, pr.dos[2], pr.dos[1], pr.dos[0], pr.H, pr.B))) {
     *why = "dout strides / alignment do not fit a TMA descriptor";
