@@ -53,6 +53,7 @@ KERNEL_FLOP_SHARE = {
     "sdpa_fwd_tc_kernel": 4 / 14,
     "sdpa_bwd_tc_kernel<key-major>": 8 / 14,
     "sdpa_bwd_tc_kernel<query-major>": 2 / 14,
+    "sdpa_bwd_tc_kernel<merged>": 10 / 14,      # head dim 64 without a bias gradient: dq, dk, dv from one kernel
     "simt_fwd_kernel": 4 / 14,
     "simt_bwd_dkv_kernel": 8 / 14,
     "simt_bwd_dq_kernel": 2 / 14,

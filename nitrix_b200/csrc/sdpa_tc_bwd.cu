@@ -64,10 +64,11 @@ struct BwdArgs {
   void* out1; int64_t o1s[3];   // key-major: dv
   void* out2; int64_t o2s[3];   // dq | dk
   void* dbias; int64_t dbs[4];  // query-major only; null when not requested
+  float* dq_acc;                // merged kernel: fp32 (bh_count, S, 64) sums of ds K, zero on entry
   int* status;
 };
 
-template <int D>
+template <int D, bool kMerged>
 struct BwdSmem {
   static constexpr int kXBytes = kTile * D * 2;                 // one owner operand
   static constexpr int kYBytes = kStep * D * 2;                 // one streamed operand
@@ -89,20 +90,25 @@ struct BwdSmem {
   static constexpr int kAugSlotBytes = 2 * kAugTileBytes;      // lse tile, delta tile
   static constexpr int kWeights = kIdent + kIdentBytes;
   static constexpr int kAug = kWeights + kWeightBytes;          // two slots
-  static constexpr int kBars = kAug + 2 * kAugSlotBytes;
+  // Merged kernel: ds tiles (128 keys x 64 queries, 16-bit, 128-byte-swizzled rows) of the last four steps.  The
+  // tensor core reads a tile K-major for dK and a pair of tiles MN-major for dQ.  Must stay 1024-byte aligned.
+  static constexpr int kDsSlots = 4;
+  static constexpr int kDs = (kAug + 2 * kAugSlotBytes + 1023) / 1024 * 1024;
+  static constexpr int kBars = kDs + (kMerged ? kDsSlots * kBoxBytes : 0);
   // x_full, y_full[n], y_empty[n], prod_full[2], e_ready[2], acc_done, bias_full[2], bias_empty[2], p_free[2], e_free[2],
-  // aug_full[2], aug_free[2]
-  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4 + 4 + 4;
+  // aug_full[2], aug_free[2], dq_full, dq_free
+  static constexpr int kNumBars = 1 + 2 * kYStages + 2 + 2 + 1 + 4 + 4 + 4 + 2;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
 };
 
-template <int D, bool kBf16, bool kKeyMajor>
+template <int D, bool kBf16, bool kKeyMajor, bool kMerged>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
                    const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
                    const __grid_constant__ CUtensorMap tm_bias, const BwdArgs a) {
-  using L = BwdSmem<D>;
+  static_assert(!kMerged || (kKeyMajor && D == 64), "the merged kernel is the key-major kernel at head dim 64");
+  using L = BwdSmem<D, kMerged>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -113,7 +119,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   constexpr int NY = L::kYStages;
   constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, E_READY = PROD_FULL + 2,
                 ACC_DONE = E_READY + 2, B_FULL = ACC_DONE + 1, B_EMPTY = B_FULL + 2, P_FREE = B_EMPTY + 2,
-                E_FREE = P_FREE + 2, AUG_FULL = E_FREE + 2, AUG_FREE = AUG_FULL + 2;
+                E_FREE = P_FREE + 2, AUG_FULL = E_FREE + 2, AUG_FREE = AUG_FULL + 2, DQ_FULL = AUG_FREE + 2, DQ_FREE = DQ_FULL + 1;
   // D = 64 has TMEM room for E tiles of their own.  Then a stage's products can be recomputed as soon as the
   // element-wise group has read them out, and the accumulating MMAs trail the products by two steps, so
   // neither group ever waits for the other's MMAs.  D = 128 overwrites the products and trails by one.
@@ -148,6 +154,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       if (i >= E_READY && i < E_READY + 2) count = 4;   // one lane per warp of the group
       if (i >= P_FREE && i < P_FREE + 2) count = 4;
       if (i >= B_EMPTY && i < B_EMPTY + 2) count = a.bias_mma ? 1 : 4;   // released by the MMA issuer or by the group's warps
+      if (i == DQ_FREE) count = 8;                       // every element-wise warp has read its part of the dq tile
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
@@ -194,8 +201,10 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   // TMEM columns.  Products: stage s at 128 s (P1) and 128 s + 64 (P2).
   //   D = 64 (kDeep): E tiles of stage s at 256 + 64 s (E1, 32 columns) and + 32 (E2); ACC1 at 384, ACC2 at 448.
   //   D = 128: no room for separate E tiles: E1 / E2 overwrite P1 / P2; ACC1 at 256, ACC2 at 384.
+  //   merged: E1 of stage s at 256 + 32 s (ds goes to shared memory instead of E2), the dq tile (128 queries x 64) at 320.
   const uint32_t tm_e = kDeep ? tmem + 256 : tmem;
-  constexpr int kEStage = kDeep ? 64 : 128, kE2Off = kDeep ? 32 : 64;
+  constexpr int kEStage = kMerged ? 32 : (kDeep ? 64 : 128), kE2Off = kDeep ? 32 : 64;
+  const uint32_t tm_dq = tmem + 320;
   const uint32_t tm_acc1 = tmem + (kDeep ? 384 : 256), tm_acc2 = tm_acc1 + D;
 
   if (warp < 4) {
@@ -325,11 +334,39 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           const uint64_t y1mn = make_smem_desc(ybase, kYBoxBytes, 1024);
           const uint64_t y2mn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);
           const uint32_t e1 = tm_e + s * kEStage, e2 = e1 + kE2Off;
+          if constexpr (kMerged) {
+            // dV += p^T dO (p from TMEM), dK += ds^T Q (ds from its shared-memory tile, K-major)
+            const uint64_t dsk = make_smem_desc(sbase + L::kDs + (m % L::kDsSlots) * kBoxBytes, 16, 1024);
+#pragma unroll
+            for (int kk = 0; kk < kStep / 16; ++kk) {
+              const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
+              mma_ts(tm_acc1, e1 + kk * 8, y2mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
+              mma_ss(tm_acc2, dsk + uint64_t((kk * 32) >> 4), y1mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
+            }
+            if (m & 1) {
+              // dq tile of the pair (m - 1, m): (128 queries x 128 keys) (128 keys x 64) = ds K; A = the two ds tiles
+              // read MN-major (queries contiguous, tiles 16 KB apart), B = the K tile read MN-major
+              const int j = m >> 1;
+              if (j >= 1) {
+                ok = wait_or_abort(bar(DQ_FREE), (j - 1) & 1, abort_flag, a.status, 215);
+                if (!ok) break;
+                tc_fence_after_sync();
+              }
+              constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, D, true, true);
+              const uint64_t dsm = make_smem_desc(sbase + L::kDs + ((m - 1) % L::kDsSlots) * kBoxBytes, kBoxBytes, 1024);
+              const uint64_t kmn = make_smem_desc(sbase + L::kX, kBoxBytes, 1024);
+#pragma unroll
+              for (int kk = 0; kk < kTile / 16; ++kk)
+                mma_ss(tm_dq, dsm + uint64_t((kk * 2048) >> 4), kmn + uint64_t((kk * 2048) >> 4), idesc_dq, kk > 0 ? 1u : 0u);
+              mma_commit(bar(DQ_FULL));
+            }
+          } else {
 #pragma unroll
           for (int kk = 0; kk < kStep / 16; ++kk) {
             const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
             if (kKeyMajor) mma_ts(tm_acc1, e1 + kk * 8, y2mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
             mma_ts(tm_acc2, e2 + kk * 8, y1mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
+          }
           }
           if (kDeep) mma_commit(bar(E_FREE + s));   // the E tiles of this stage may be rewritten once these are done
           mma_commit(bar(Y_EMPTY + st));
@@ -425,10 +462,39 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       }
     }
 
+    // merged: pair j of steps (2j, 2j + 1) leaves a 128-query x 64 dq tile in TMEM; this group adds its 32 columns
+    // of it to the fp32 accumulator in global memory (thread = query row)
+    int next_pair = 0;
+    auto drain_pair = [&](int j) -> bool {
+      if (!wait_or_abort(bar(DQ_FULL), j & 1, abort_flag, a.status, 216)) return false;
+      tc_fence_after_sync();
+      uint32_t v[32];
+      tmem_ld32(tm_dq + lane_addr + grp * 32, v);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_FREE));
+      // The accumulator is laid out so that one warp-wide reduction covers 512 contiguous bytes: per 128-query tile
+      // [column half g][warp w][4-column chunk c][lane][4] holds dq[128 tile + 32 w + lane][32 g + 4 c + 0..3].
+      const int64_t tile = int64_t(blockIdx.y) * (a.S / kTile) + ((s_begin + 2 * j) >> 1);
+      float* dst = a.dq_acc + tile * (kTile * D) + ((grp * 4 + wq) * 8) * 128 + lane * 4;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) red_add_v4(dst + c * 128, v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      return true;
+    };
+
     for (int n = grp; n < n_steps && ok; n += 2) {
       const int s = n & 1;
       const int st = n % NY;
       const int r0 = (s_begin + n) * kStep;          // first streamed row of the step
+      if constexpr (kMerged) {
+        // group 0 takes pair j before step 2j + 4, group 1 after step 2j + 3: both between the pair's MMAs
+        // (issued after the products of step 2j + 3) and the next pair's (after the products of step 2j + 5)
+        if (grp == 0 && n >= 4) {
+          ok = drain_pair(next_pair++);
+          if (!ok) break;
+        }
+      }
       // keep bits over the step's 64 streamed rows
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
       if (mbits) {
@@ -557,11 +623,24 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       }
       const uint32_t tE1 = tm_e + s * kEStage + lane_addr, tE2 = tE1 + kE2Off;
       if (kKeyMajor) tmem_st32(tE1, e1);
-      tmem_st32(tE2, e2);
+      if constexpr (kMerged) {
+        // ds row of this key: 64 queries = 128 bytes, chunks swizzled as TMA would have written them.  The slot was
+        // last read by MMAs issued before this step's products, and those have completed (PROD_FULL came after).
+        uint8_t* dsrow = smem + L::kDs + (n % L::kDsSlots) * kBoxBytes + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(dsrow + ((c ^ (r & 7)) << 4)) = make_uint4(e2[c * 4], e2[c * 4 + 1], e2[c * 4 + 2], e2[c * 4 + 3]);
+        fence_proxy_async_smem();
+      } else {
+        tmem_st32(tE2, e2);
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(E_READY + s));
+      if constexpr (kMerged) {
+        if (grp == 1 && n >= 3) ok = drain_pair(next_pair++);
+      }
       if (!kKeyMajor && a.dbias && orow < a.S) {
         // dbias[row, r0 .. r0+63] = ds in bias dtype (the 16-bit pairs already packed in e2)
         uint8_t* dst = reinterpret_cast<uint8_t*>(a.dbias) +
@@ -580,6 +659,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         for (int k0 = s_end * kStep; k0 < a.T; k0 += 8)
           *reinterpret_cast<uint4*>(dst + 2 * k0) = make_uint4(0, 0, 0, 0);
       }
+    }
+    if constexpr (kMerged) {
+      while (ok && next_pair < n_steps / 2) ok = drain_pair(next_pair++);
     }
     if (ok && n_steps > 0) ok = wait_or_abort(bar(ACC_DONE), 0, abort_flag, a.status, 208);
     if (ok) {
@@ -626,10 +708,10 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   }
 }
 
-template <int D, bool kBf16, bool kKeyMajor>
+template <int D, bool kBf16, bool kKeyMajor, bool kMerged = false>
 int launch_one(const CUtensorMap* maps, const BwdArgs& a, int n_tiles, int bh_count, cudaStream_t st) {
-  auto kernel = sdpa_bwd_tc_kernel<D, kBf16, kKeyMajor>;
-  const int smem = BwdSmem<D>::kTotal + 1024;
+  auto kernel = sdpa_bwd_tc_kernel<D, kBf16, kKeyMajor, kMerged>;
+  const int smem = BwdSmem<D, kMerged>::kTotal + 1024;
   cudaFuncAttributes attr;
   cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
   if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
@@ -645,7 +727,36 @@ int launch_one(const CUtensorMap* maps, const BwdArgs& a, int n_tiles, int bh_co
   dim3 grid(n_tiles, bh_count);
   kernel<<<grid, kThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);
   count_launch();
-  return check_launch(kKeyMajor ? "sdpa_bwd_tc_kernel<key-major>" : "sdpa_bwd_tc_kernel<query-major>");
+  return check_launch(kMerged ? "sdpa_bwd_tc_kernel<merged>"
+                              : (kKeyMajor ? "sdpa_bwd_tc_kernel<key-major>" : "sdpa_bwd_tc_kernel<query-major>"));
+}
+
+// dq = scale * (fp32 sums) in the operand dtype; one thread per 8 head-dim elements (16-byte store)
+template <bool kBf16>
+__global__ void dq_finish_kernel(const float* __restrict__ acc, void* dq, int64_t s_b, int64_t s_h, int64_t s_row, int H,
+                                 int S, int bh_begin, int64_t n_chunks, float scale) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_chunks) return;
+  // consecutive threads take consecutive queries of one 8-column chunk, so the reads are contiguous
+  const int64_t blk = i >> 8;               // 32 queries x 8 chunks per block of 256 threads
+  const int c = int(i >> 5) & 7;            // 8 chunks of 8 elements per 64-wide row
+  const int64_t row = blk * 32 + (i & 31);  // (local pair, query)
+  const int q = int(row % S);
+  const int bh = bh_begin + int(row / S);
+  const int b = bh / H, h = bh - b * H;
+  // accumulator layout (see the merged kernel): per 128-query tile [column half][warp][4-column chunk][lane][4]
+  const int64_t tile = row >> 7;
+  const int wq = int(row >> 5) & 3, lane = int(row) & 31, g = c >> 2, c4 = (c & 3) * 2;
+  const float* src = acc + tile * (128 * 64) + (((g * 4 + wq) * 8 + c4) * 32 + lane) * 4;
+  const float4 lo = __ldg(reinterpret_cast<const float4*>(src));
+  const float4 hi = __ldg(reinterpret_cast<const float4*>(src + 128));
+  uint4 w;
+  w.x = pack2<kBf16>(lo.x * scale, lo.y * scale);
+  w.y = pack2<kBf16>(lo.z * scale, lo.w * scale);
+  w.z = pack2<kBf16>(hi.x * scale, hi.y * scale);
+  w.w = pack2<kBf16>(hi.z * scale, hi.w * scale);
+  uint8_t* dst = reinterpret_cast<uint8_t*>(dq) + 2 * (b * s_b + h * s_h + int64_t(q) * s_row + c * 8);
+  *reinterpret_cast<uint4*>(dst) = w;
 }
 
 template <bool kKeyMajor>
@@ -699,10 +810,19 @@ bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** wh
   return true;
 }
 
+namespace {
+// One kernel for dq, dk and dv (head dim 64, no bias gradient): the key-major kernel also forms ds K per pair of
+// steps and adds it to an fp32 copy of dq, which a last kernel scales and casts.
+bool use_merged(const Problem& pr) { return pr.D == 64 && !pr.dbias; }
+size_t mask_bytes_aligned(const MaskPackPlan& mp) { return (mp.total() + 255) / 256 * 256; }
+}  // namespace
+
 size_t bwd_workspace_bytes(const Problem& pr, int, int) {
   const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
   const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
-  return mp.total();
+  size_t bytes = mask_bytes_aligned(mp);
+  if (use_merged(pr)) bytes += sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D;
+  return bytes;
 }
 
 int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
@@ -710,8 +830,10 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   const char* why = "";
   const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
   const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
-  if (mp.total() > ws_bytes) {
-    set_error("backward mask bits need %zu workspace bytes", mp.total());
+  const bool merged = use_merged(pr);
+  const size_t acc_bytes = merged ? sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D : 0;
+  if (mask_bytes_aligned(mp) + acc_bytes > ws_bytes) {
+    set_error("tensor-core backward needs %zu workspace bytes", mask_bytes_aligned(mp) + acc_bytes);
     return NB200_ERR_WORKSPACE;
   }
   BwdArgs a{};
@@ -759,6 +881,29 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   if (!ok) { set_error("tensor map: %s", why); return NB200_ERR_LAUNCH; }
   const bool bf16 = dtype == NB200_BF16;
 
+  if (merged) {
+    BwdArgs ak = a;
+    ak.dq_acc = reinterpret_cast<float*>(static_cast<char*>(ws) + mask_bytes_aligned(mp));
+    cudaError_t e = cudaMemsetAsync(ak.dq_acc, 0, acc_bytes, stream);
+    if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
+    ak.out1 = pr.dv;
+    ak.out2 = pr.dk;
+    for (int i = 0; i < 3; ++i) { ak.o1s[i] = pr.dvs[i]; ak.o2s[i] = pr.dks[i]; }
+    const CUtensorMap maps[5] = {k128, v128, q64, g64, bias_k};
+    const int rc = bf16 ? launch_one<64, true, true, true>(maps, ak, pr.T / kTile, pr.bh_count, stream)
+                        : launch_one<64, false, true, true>(maps, ak, pr.T / kTile, pr.bh_count, stream);
+    if (rc) return rc;
+    const int64_t n_chunks = int64_t(pr.bh_count) * pr.S * 8;
+    const int blocks = int((n_chunks + 255) / 256);
+    if (bf16)
+      dq_finish_kernel<true><<<blocks, 256, 0, stream>>>(ak.dq_acc, pr.dq, pr.dqs[0], pr.dqs[1], pr.dqs[2], pr.H, pr.S,
+                                                         pr.bh_begin, n_chunks, pr.scale);
+    else
+      dq_finish_kernel<false><<<blocks, 256, 0, stream>>>(ak.dq_acc, pr.dq, pr.dqs[0], pr.dqs[1], pr.dqs[2], pr.H, pr.S,
+                                                          pr.bh_begin, n_chunks, pr.scale);
+    count_launch();
+    return check_launch("dq_finish_kernel");
+  }
   // query-major: dq (+ dbias)
   {
     BwdArgs aq = a;

@@ -169,6 +169,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Four consecutive fp32 values added to global memory by one reduction (16-byte aligned address).
+__device__ __forceinline__ void red_add_v4(float* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(a)),
+               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
+
 // ---- tcgen05.mma ------------------------------------------------------------
 // Instruction descriptor for kind::f16 (bf16 or fp16 operands, fp32 accumulate).
 //   bits  4-5  accumulator format (1 = f32)      bits  7-9  A format (0 = f16, 1 = bf16)
