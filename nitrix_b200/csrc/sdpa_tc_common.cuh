@@ -75,6 +75,7 @@ int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, Mask
 // ---- device helpers -----------------------------------------------------------
 #ifdef __CUDACC__
 
+constexpr uint32_t kWaitHintNs = 16384;         // a waiting thread may sleep this long per try_wait before it re-checks
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s of SM clock: far beyond any real wait (microseconds)
 
 // Wait on an mbarrier phase unless the CTA has aborted.  On timeout: raise the
@@ -87,7 +88,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
-    if (sm100::mbar_try_wait(bar, parity)) return true;
+    if (sm100::mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
     if ((++polls & 0xFF) == 0) {
       if (*abort_flag) return false;
       if (*reinterpret_cast<volatile int*>(status) != 0) {
