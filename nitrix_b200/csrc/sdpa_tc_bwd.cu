@@ -641,13 +641,33 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       if constexpr (kMerged) {
         if (grp == 1 && n >= 3) ok = drain_pair(next_pair++);
       }
-      if (!kKeyMajor && a.dbias && orow < a.S) {
-        // dbias[row, r0 .. r0+63] = ds in bias dtype (the 16-bit pairs already packed in e2)
-        uint8_t* dst = reinterpret_cast<uint8_t*>(a.dbias) +
-                       2 * (b * a.dbs[0] + h * a.dbs[1] + int64_t(orow) * a.dbs[2] + r0);
+      if constexpr (!kKeyMajor) {
+        if (a.dbias) {
+          // dbias[row, r0 .. r0+63] = ds in bias dtype (the 16-bit pairs already packed in e2).  A thread holds one
+          // row, so direct stores would touch 32 lines per instruction; the warp turns its 32 x 64 tile over in
+          // shared memory (two halves of 32 keys; the space of the identity tiles is free in this kernel) and
+          // stores 8 rows x 64 contiguous bytes per instruction.
+          uint8_t* stage = smem + L::kIdent + (warp - 4) * 2048;
+          uint8_t* dbase = reinterpret_cast<uint8_t*>(a.dbias) + 2 * (b * a.dbs[0] + h * a.dbs[1] + r0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(e2[c * 4], e2[c * 4 + 1], e2[c * 4 + 2], e2[c * 4 + 3]);
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              *reinterpret_cast<uint4*>(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
+                  make_uint4(e2[half * 16 + c * 4], e2[half * 16 + c * 4 + 1], e2[half * 16 + c * 4 + 2],
+                             e2[half * 16 + c * 4 + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rl = 8 * i + (lane >> 2), ch = lane & 3;
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + rl * 64 + ((ch ^ ((rl >> 1) & 3)) << 4));
+              const int row = o0 + wq * 32 + rl;
+              if (row < a.S)
+                *reinterpret_cast<uint4*>(dbase + 2 * (int64_t(row) * a.dbs[2] + half * 32 + ch * 8)) = v;
+            }
+            __syncwarp();
+          }
+        }
       }
     }
 

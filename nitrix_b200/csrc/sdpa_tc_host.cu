@@ -108,6 +108,57 @@ __global__ void __launch_bounds__(256) mask_pack_kernel(const uint8_t* mask, int
   }
 }
 
+// Fast path for a mask with a query axis, unit key stride and 16-byte aligned rows: one CTA packs a 256-row x
+// 256-key tile.  Rows are read as 16-byte vectors (16 keys per lane, a warp covers two 256-byte row segments per
+// load); the row-major words go out as they are formed and are kept in shared memory, from which each warp then
+// builds the transposed words of 32 keys by ballot over 32 rows, 8 row-words (32 bytes) per key.
+__global__ void __launch_bounds__(256) mask_pack_tile_kernel(const uint8_t* mask, int64_t sb, int64_t sh, int64_t ss, int Hm,
+                                                             int S, int T, uint32_t* rows_out, int words_per_row,
+                                                             uint32_t* cols_out, int words_per_col) {
+  __shared__ uint32_t sw[256][9];   // [row][key word], padded against bank conflicts
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bm = blockIdx.z / Hm, hm = blockIdx.z - bm * Hm;
+  const int key0 = blockIdx.x * 256, row0 = blockIdx.y * 256;
+  const uint8_t* base = mask + bm * sb + hm * sh + int64_t(row0) * ss + key0;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int rl = warp * 32 + 2 * i + (lane >> 4);     // row within the tile
+    const int chunk = lane & 15;                        // 16 keys
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + int64_t(rl) * ss + chunk * 16));
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    uint32_t bits = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t nz = __vcmpne4(in[e], 0u) & 0x01010101u;          // one bit per non-zero byte
+      bits |= ((nz * 0x01020408u) >> 24 & 0xFu) << (4 * e);            // byte k of the word -> bit k
+    }
+    const uint32_t hi = __shfl_down_sync(0xffffffffu, bits, 1);
+    if (!(lane & 1)) {
+      const uint32_t word = bits | (hi << 16);
+      sw[rl][chunk >> 1] = word;
+      rows_out[(int64_t(blockIdx.z) * S + row0 + rl) * words_per_row + (key0 >> 5) + (chunk >> 1)] = word;
+    }
+  }
+  if (!cols_out) return;
+  __syncthreads();
+  // warp w transposes key word w: lane = key, 8 row-words each
+  uint32_t out[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t w = sw[32 * j + lane][warp];          // lane = row within the group of 32
+    uint32_t mine = 0;
+#pragma unroll
+    for (int b = 0; b < 32; ++b) {
+      const uint32_t t = __ballot_sync(0xffffffffu, (w >> b) & 1u);
+      if (lane == b) mine = t;
+    }
+    out[j] = mine;
+  }
+  uint32_t* dst = cols_out + (int64_t(blockIdx.z) * T + key0 + warp * 32 + lane) * words_per_col + (row0 >> 5);
+  *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
+  *reinterpret_cast<uint4*>(dst + 4) = make_uint4(out[4], out[5], out[6], out[7]);
+}
+
 inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 }  // namespace
@@ -139,11 +190,20 @@ int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, Mask
   int* kv_len = plan.len_bytes ? reinterpret_cast<int*>(static_cast<char*>(ws) + plan.rows_bytes + plan.cols_bytes) : nullptr;
   cudaError_t e = cudaMemsetAsync(ws, 0, plan.total(), stream);
   if (e != cudaSuccess) { set_error("cudaMemsetAsync(mask bits): %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
-  dim3 grid((pr.T + 31) / 32, (n_rows + 31) / 32, Bm * Hm);
-  mask_pack_kernel<<<grid, 256, 0, stream>>>(pr.mask, pr.ms[0], pr.ms[1], pr.ms[2], pr.ms[3], Hm, Sm, pr.S, pr.T, rows,
-                                             plan.words_per_row, cols, plan.words_per_col, kv_len);
+  const bool tiled = Sm == pr.S && pr.S % 256 == 0 && pr.T % 256 == 0 && pr.ms[3] == 1 && pr.ms[2] % 16 == 0 &&
+                     (Bm == 1 || pr.ms[0] % 16 == 0) && (Hm == 1 || pr.ms[1] % 16 == 0) &&
+                     reinterpret_cast<uintptr_t>(pr.mask) % 16 == 0;
+  if (tiled) {
+    dim3 grid(pr.T / 256, pr.S / 256, Bm * Hm);
+    mask_pack_tile_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(pr.mask), pr.ms[0], pr.ms[1], pr.ms[2], Hm,
+                                                    pr.S, pr.T, rows, plan.words_per_row, cols, plan.words_per_col);
+  } else {
+    dim3 grid((pr.T + 31) / 32, (n_rows + 31) / 32, Bm * Hm);
+    mask_pack_kernel<<<grid, 256, 0, stream>>>(pr.mask, pr.ms[0], pr.ms[1], pr.ms[2], pr.ms[3], Hm, Sm, pr.S, pr.T, rows,
+                                               plan.words_per_row, cols, plan.words_per_col, kv_len);
+  }
   count_launch();
-  if (int rc = check_launch("mask_pack_kernel")) return rc;
+  if (int rc = check_launch(tiled ? "mask_pack_tile_kernel" : "mask_pack_kernel")) return rc;
   out->rows = rows;
   out->row_stride = Sm == 1 ? 0 : plan.words_per_row;
   out->h_stride = Hm == 1 ? 0 : int64_t(Sm) * plan.words_per_row;
