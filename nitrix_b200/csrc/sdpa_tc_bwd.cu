@@ -16,10 +16,15 @@
 //   E1 = p, E2 = ds as 16-bit             (written over P1 / P2 in TMEM)
 //   ACC1 += E1 Y2 (key-major: dV), ACC2 += E2 Y1 (dQ | dK)
 //                                          (TS tcgen05.mma, Y consumed MN-major)
-// TMEM columns: stage s in {0,1}: P1 at 128 s, P2 at 128 s + 64; ACC1 at 256,
-// ACC2 at 256 + D.  Twelve warps: 0 TMA producer (X once, Y ring), 1 bias
-// producer, 2 MMA issuer, 3 TMEM owner, 4-7 / 8-11 two element-wise groups that
-// take alternate steps (one owner row per thread).  All waits are bounded.
+// TMEM columns (512): D = 128: products of stage s in {0,1} at 128 s (P1) and 128 s + 64 (P2), E tiles written over
+// them, ACC1 at 256, ACC2 at 384.  D = 64: products as above, E tiles of their own at 256 + 64 s, ACC1 at 384,
+// ACC2 at 448, and the accumulating MMAs trail the products by two steps.
+// Merged variant (key-major, D = 64, no bias gradient): ds goes to shared memory instead of TMEM and also feeds
+// dQ = ds K per pair of steps (a 128 x 64 tile at TMEM column 320), which the element-wise warps add to an fp32
+// accumulator in global memory; the query-major kernel is then not needed.
+// Twelve warps: 0 TMA producer (X once, Y ring), 1 bias producer, 2 MMA issuer, 3 TMEM owner (key-major: also
+// builds the per-query addends -lse / (scale log2e), -delta as MMA operands), 4-7 / 8-11 two element-wise groups
+// that take alternate steps (one owner row per thread).  All waits are bounded.
 #include <math.h>
 
 #include "sdpa_tc_bwd.cuh"
@@ -864,18 +869,8 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.bias_mode = bias_mode_of(pr);
   a.bias_mma = 0;
   a.inv_scale_hi = a.inv_scale_lo = 0.f;
-  if (a.bias_mode == kBiasTile && pr.scale != 0.f && isfinite(1.f / pr.scale)) {
-    // 1 / scale as hi + lo, both exact in the 16-bit operand type (lo = 0 for a power-of-two scale)
-    const float inv = 1.f / pr.scale;
-    const float hi = dtype == NB200_BF16 ? __bfloat162float(__float2bfloat16_rn(inv)) : __half2float(__float2half_rn(inv));
-    const float rest = inv - hi;
-    const float lo = dtype == NB200_BF16 ? __bfloat162float(__float2bfloat16_rn(rest)) : __half2float(__float2half_rn(rest));
-    if (isfinite(hi) && hi != 0.f) {
-      a.bias_mma = 1;
-      a.inv_scale_hi = hi;
-      a.inv_scale_lo = lo;
-    }
-  }
+  if (a.bias_mode == kBiasTile && split_inv_scale(pr.scale, dtype == NB200_BF16, &a.inv_scale_hi, &a.inv_scale_lo))
+    a.bias_mma = 1;
   a.bias_b_mul = (pr.B > 1 && pr.bs[0] != 0) ? 1 : 0;
   a.bias_h_mul = (pr.H > 1 && pr.bs[1] != 0) ? 1 : 0;
   a.bias = pr.bias; a.bias_bs = pr.bs[0]; a.bias_hs = pr.bs[1];

@@ -30,6 +30,10 @@ enum BiasMode : int {
 bool make_tile_map(CUtensorMap* map, const void* base, int rows, int cols, int H, int B, int64_t row_stride,
                    int64_t h_stride, int64_t b_stride, int box_rows, const char** why);
 
+// 1 / scale as hi + lo, both exactly representable in the 16-bit operand type (lo = 0 for a power-of-two scale).
+// False when the scale is zero / not finite or 1 / scale overflows the type.
+bool split_inv_scale(float scale, bool bf16, float* hi, float* lo);
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

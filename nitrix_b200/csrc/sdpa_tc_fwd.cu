@@ -47,21 +47,29 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) gives: 65536
 static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) * 256,
               "softmax warps would wait forever for registers the producer warps never release");
 
-template <int D>
+template <int D, bool kTileBias>
 struct FwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;        // one Q / K / V tile
   // K and V ring depth.  A TMA tile takes 1-2 us from L2 / HBM while a key tile is consumed in well under
   // 1 us, so two stages leave the MMAs waiting for loads; D = 64 tiles are small enough for four.
-  static constexpr int kStages = D == 64 ? 4 : 2;
-  static constexpr int kBiasSlots = D == 64 ? 4 : 2;      // 16 KB slots
+  // With bias tiles D = 64 keeps three stages and five bias slots (a round consumes four); without them five stages.
+  static constexpr int kStages = D == 64 ? (kTileBias ? 3 : 5) : 2;
+  static constexpr int kBiasSlots = kTileBias ? (D == 64 ? 5 : 2) : 1;      // 16 KB slots
+  // D = 64: hi * I and lo * I (64 x 64 each), second operand of the MMAs that add a bias tile to the scores
+  static constexpr int kIdentBytes = (D == 64 && kTileBias) ? 2 * 64 * 128 : 0;
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + 2 * kTileBytes;
   static constexpr int kV = kK + kStages * kTileBytes;
   static constexpr int kBias = kV + kStages * kTileBytes;
-  static constexpr int kBars = kBias + kBiasSlots * kBoxBytes;
+  static constexpr int kIdent = kBias + kBiasSlots * kBoxBytes;
+  static constexpr int kBars = kIdent + kIdentBytes;
   // q_full[2] q_empty[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_full[2] p_ready[2] o_done[2] o_free[2]
   // s_free[2] pv_done[2] bias_full[2][slots] bias_empty[slots]
-  static constexpr int kNumBars = 4 + 4 * kStages + 12 + 3 * kBiasSlots;
+  // Without bias tiles the (single) bias slot holds the operands of the per-key add: the weight tile (128 rows x 16,
+  // no swizzle, 4 KB) and a ring of three 128-key x 16 tiles (4 KB each).
+  static constexpr int kAugSlots = 3;
+  static constexpr int kAugTileBytes = (kTile / 8) * 256;
+  static constexpr int kNumBars = 4 + 4 * kStages + 12 + 3 * kBiasSlots + 2 * kAugSlots;
   static constexpr int kMisc = kBars + 8 * kNumBars;      // tmem base (4 B) + abort flag (4 B)
   static constexpr int kTotal = kMisc + 16;
 };
@@ -106,12 +114,12 @@ __device__ __forceinline__ Item decode_item(const FwdArgs& a, int item) {
   return it;
 }
 
-template <int D, bool kBf16>
+template <int D, bool kBf16, bool kTileBias>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
                    const FwdArgs a) {
-  using L = FwdSmem<D>;
+  using L = FwdSmem<D, kTileBias>;
   constexpr int kStages = L::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // the swizzled tiles need a 1024-byte aligned base; the launch reserves the slack for rounding up
@@ -129,7 +137,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   constexpr int Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + kStages, V_FULL = K_EMPTY + kStages,
                 V_EMPTY = V_FULL + kStages, S_FULL = V_EMPTY + kStages, P_READY = S_FULL + 2, O_DONE = P_READY + 2,
                 O_FREE = O_DONE + 2, S_FREE = O_FREE + 2, PV_DONE = S_FREE + 2, B_FULL = PV_DONE + 2,
-                B_EMPTY = B_FULL + 2 * L::kBiasSlots;
+                B_EMPTY = B_FULL + 2 * L::kBiasSlots, AUG_FULL = B_EMPTY + L::kBiasSlots, AUG_FREE = AUG_FULL + L::kAugSlots;
   // D = 128 fills TMEM (2 x 128 S + 2 x 128 O): P must overwrite S and each query tile's chain is serial.
   // D = 64 leaves room for separate P tiles, so the next score MMA can run under the current softmax.
   constexpr bool kAlias = D == 128;
@@ -145,11 +153,42 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (i >= V_EMPTY && i < V_EMPTY + kStages) count = kAlias ? 1 : 2;
       if (i >= O_FREE && i < O_FREE + 2) count = 4;                         // one lane per softmax warp of the tile
       if (i >= S_FREE && i < S_FREE + 2) count = 4;
-      if (i >= B_EMPTY && i < B_EMPTY + L::kBiasSlots) count = 4;
+      if (i >= B_EMPTY && i < B_EMPTY + L::kBiasSlots) count = a.bias_mma ? 1 : 4;   // MMA issuer or the tile's warps
+      if (i >= AUG_FREE && i < AUG_FREE + L::kAugSlots) count = kAlias ? 1 : 2;        // one arrival per MMA issuer
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
     mbar_init_fence();
+  }
+  if constexpr (D == 64 && kTileBias) {
+    if (a.bias_mma) {
+      // two 64 x 64 K-major, 128-byte-swizzled tiles: tile 0 = hi * I, tile 1 = lo * I
+      uint4* ident = reinterpret_cast<uint4*>(smem + L::kIdent);
+      for (int idx = threadIdx.x; idx < 2 * 64 * 8; idx += kThreads) {   // one 16-byte chunk each
+        const int tile = idx / (64 * 8), rem = idx - tile * 64 * 8;
+        const int row = rem >> 3, chunk = (rem & 7) ^ (row & 7);           // logical chunk stored at this slot
+        const int col0 = chunk * 8;
+        const float val = tile == 0 ? a.inv_scale_hi : a.inv_scale_lo;
+        const uint16_t one = kBf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (row >= col0 && row < col0 + 8) w[(row - col0) >> 1] = uint32_t(one) << (((row - col0) & 1) * 16);
+        ident[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();   // written by threads, read by the tensor core
+    }
+  }
+  if constexpr (!kTileBias) {
+    if (a.key_mma) {
+      // weight rows (w0, w1, w2, 0, ...): bf16 (1, 1, 1); fp16 (256, 1, 2^-8) to cover magnitudes up to 1.6e7
+      uint4* wt = reinterpret_cast<uint4*>(smem + L::kBias);
+      const uint32_t w01 = kBf16 ? 0x3F803F80u : 0x3C005C00u;
+      const uint32_t w2 = kBf16 ? 0x00003F80u : 0x00001C00u;
+      for (int idx = threadIdx.x; idx < L::kAugTileBytes / 16; idx += kThreads)
+        wt[idx] = (idx & 8) ? make_uint4(0, 0, 0, 0) : make_uint4(w01, w2, 0, 0);
+      uint4* aug = reinterpret_cast<uint4*>(smem + L::kBias + L::kAugTileBytes);
+      for (int idx = threadIdx.x; idx < L::kAugSlots * L::kAugTileBytes / 16; idx += kThreads) aug[idx] = make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();
+    }
   }
   if (warp == 3) {
     tmem_alloc(smem_u32(tmem_slot), 512);
@@ -212,6 +251,61 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else if (warp == 1) {
     // ---------------- bias producer ----------------
+    if constexpr (!kTileBias) {
+      if (a.key_mma) {
+        // per-key addends of each streamed key tile as an MMA operand: lane -> keys lane, lane + 32, ...
+        const float inv_scale = 1.f / a.scale;
+        int kv = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+          const Item it = decode_item(a, item);
+          const uint16_t* bk = a.bias_mode == kBiasKey
+                                   ? reinterpret_cast<const uint16_t*>(a.bias) + (it.b * a.bias_bs + it.h * a.bias_hs)
+                                   : nullptr;
+          const uint32_t* mk = a.mask.kv_len ? a.mask.rows + it.b * a.mask.b_stride + it.h * a.mask.h_stride : nullptr;
+          for (int j = 0; j < it.nt_max && ok; ++j, ++kv) {
+            const int slot = kv % L::kAugSlots;
+            if (kv >= L::kAugSlots)
+              ok = wait_or_abort(bar(AUG_FREE + slot), ((kv / L::kAugSlots) - 1) & 1, abort_flag, a.status, 117);
+            if (!ok) break;
+            uint8_t* ctile = smem + L::kBias + L::kAugTileBytes * (1 + slot);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int kl = lane + 32 * e, key = j * kTile + kl;
+              float c = 0.f;
+              if (bk) {
+                const uint16_t raw = __ldg(bk + key);
+                c = (kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw))) * inv_scale;
+              }
+              if (mk && !((__ldg(mk + (key >> 5)) >> (key & 31)) & 1u)) c = -INFINITY;
+              uint32_t h[3] = {0u, 0u, 0u};
+              float rem = c;
+#pragma unroll
+              for (int t3 = 0; t3 < 3; ++t3) {
+                const float w = kBf16 ? 1.f : (t3 == 0 ? 256.f : (t3 == 1 ? 1.f : 0.00390625f));
+                const float v = rem * (1.f / w);
+                float back;
+                if constexpr (kBf16) {
+                  const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+                  h[t3] = __bfloat16_as_ushort(hv);
+                  back = __bfloat162float(hv);
+                } else {
+                  const __half hv = __float2half_rn(v);
+                  h[t3] = __half_as_ushort(hv);
+                  back = __half2float(hv);
+                }
+                if (!(fabsf(back) < INFINITY)) break;   // an infinite (or NaN) term carries the value alone
+                rem = fmaf(-back, w, rem);
+              }
+              *reinterpret_cast<uint4*>(ctile + (kl >> 3) * 256 + (kl & 7) * 16) = make_uint4(h[0] | (h[1] << 16), h[2], 0u, 0u);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(AUG_FULL + slot));
+          }
+        }
+      }
+    }
     if (a.bias_mode == kBiasTile && elect_one()) {
       tma_prefetch_desc(&tm_bias);
       int seq = 0;
@@ -261,6 +355,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       bool ok = true;
       int kv = 0, tc[2] = {0, 0}, oc[2] = {0, 0};
+      int seq_base = 0;            // bias slots filled before this item
+      uint32_t bias_phase = 0;     // bit s = parity of this issuer's next wait on its tile's "full" barrier of slot s
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const Item it = decode_item(a, item);
         // round j: score MMA of key tile j and output MMA of key tile j - 1
@@ -268,6 +364,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const int st = (kv + j) % kStages, stp = (kv + j + kStages - 1) % kStages;
           if (j < it.nt_max) ok = wait_or_abort(bar(K_FULL + st), ((kv + j) / kStages) & 1, abort_flag, a.status, 105);
           if (ok && j > 0) ok = wait_or_abort(bar(V_FULL + stp), ((kv + j - 1) / kStages) & 1, abort_flag, a.status, 106);
+          const int aslot = (kv + j) % L::kAugSlots;
+          if (!kTileBias && a.key_mma && ok && j < it.nt_max)
+            ok = wait_or_abort(bar(AUG_FULL + aslot), ((kv + j) / L::kAugSlots) & 1, abort_flag, a.status, 118);
           if (!ok) break;
           tc_fence_after_sync();
           for (int g = g_begin; g < g_end && ok; ++g) {
@@ -300,6 +399,40 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 const uint64_t off = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
                 mma_ss(tm_S[g], qdesc[g] + off, kdesc[st] + off, idesc_qk, kk > 0 ? 1u : 0u);
               }
+              if constexpr (!kTileBias) {
+                if (a.key_mma) {
+                  // S_g += W C^T: the per-key addends land on every query row
+                  const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kBias, 128, 256);
+                  const uint64_t cdesc = make_smem_desc_noswizzle(sbase + L::kBias + L::kAugTileBytes * (1 + aslot), 128, 256);
+                  mma_ss(tm_S[g], wdesc, cdesc, idesc_qk, 1u);
+                }
+              }
+              if constexpr (D == 64 && kTileBias) {
+                if (a.bias_mma) {
+                  // S_g += bias tile (hi I + lo I): each 64-key half of the tile is one slot, read K-major as it
+                  // was written by TMA.  Slot order as the bias producer fills them.
+                  constexpr uint32_t idesc_bias = make_idesc(kBf16, kTile, 64, false, false);
+                  const int seq0 = seq_base + 2 * (min(j, it.nt[0]) + min(j, it.nt[1]) + ((g == 1 && j < it.nt[0]) ? 1 : 0));
+                  const int n_ident = a.inv_scale_lo != 0.f ? 2 : 1;
+                  for (int half = 0; half < 2 && ok; ++half) {
+                    const int slot = (seq0 + half) % L::kBiasSlots;
+                    ok = wait_or_abort(bar(B_FULL + g * L::kBiasSlots + slot), (bias_phase >> slot) & 1u, abort_flag,
+                                       a.status, 116);
+                    if (!ok) return;
+                    bias_phase ^= 1u << slot;
+                    tc_fence_after_sync();
+                    const uint64_t adesc = make_smem_desc(sbase + L::kBias + slot * kBoxBytes, 16, 1024);
+                    for (int tile = 0; tile < n_ident; ++tile) {
+                      const uint64_t bdesc = make_smem_desc(sbase + L::kIdent + tile * 8192, 16, 1024);
+#pragma unroll
+                      for (int kk = 0; kk < 4; ++kk)
+                        mma_ss(tm_S[g] + half * 64, adesc + uint64_t((kk * 32) >> 4), bdesc + uint64_t((kk * 32) >> 4),
+                               idesc_bias, 1u);
+                    }
+                    mma_commit(bar(B_EMPTY + slot));   // the slot may be refilled once these MMAs are done
+                  }
+                }
+              }
               mma_commit(bar(S_FULL + g));
               if (j == nt - 1) mma_commit(bar(Q_EMPTY + g));   // Q_g may be reloaded once these are done
             };
@@ -313,9 +446,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
           if (!ok) break;
           if (j < it.nt_max) mma_commit(bar(K_EMPTY + st));
+          if (!kTileBias && a.key_mma && j < it.nt_max) mma_commit(bar(AUG_FREE + aslot));
           if (j > 0) mma_commit(bar(V_EMPTY + stp));
         }
         kv += it.nt_max;
+        seq_base += 2 * (it.nt[0] + it.nt[1]);
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           tc[g] += it.nt[g];
@@ -334,7 +469,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t tS = tm_S[g] + lane_addr, tP = tm_P[g] + lane_addr, tO = tm_O[g] + lane_addr;
     bool ok = true;
     // no bias and a non-negative scale: the scale is folded into the exponent's multiplier and the max runs on raw scores
-    const bool fold_scale = a.bias_mode == kBiasNone && a.scale >= 0.f;
+    // (the same holds when the tensor core has already added bias / scale to the scores)
+    const bool key_mma = !kTileBias && a.key_mma;
+    const bool fold_scale = (a.bias_mode == kBiasNone || a.bias_mma || key_mma) && a.scale >= 0.f;
     const float mul = fold_scale ? a.scale * kLog2e : kLog2e;   // exponent = (t - m) * mul, base 2
     const float thr = mul > 0.f ? 8.f / mul : INFINITY;         // reference max lags the true max by at most 2^8
     const float2 scale2 = make_float2(a.scale, a.scale), mul2 = make_float2(mul, mul);
@@ -349,11 +486,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       float m = -INFINITY, l = 0.f;  // m: reference max in logit units (see the lazy rescale below)
 
       const uint32_t* mrow = nullptr;
-      if (a.mask.rows) {
+      if (a.mask.rows && !(key_mma && a.mask.kv_len)) {   // a key-only mask was added to the scores as -inf
         mrow = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride + int64_t(min(row, a.S - 1)) * a.mask.row_stride;
       }
       const uint8_t* bias_key = nullptr;
-      if (a.bias_mode == kBiasKey)
+      if (a.bias_mode == kBiasKey && !key_mma)
         bias_key = reinterpret_cast<const uint8_t*>(a.bias) + 2 * (b * a.bias_bs + h * a.bias_hs);
 
       for (int j = 0; j < my_nt && ok; ++j) {
@@ -365,7 +502,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (mrow) {
           const uint4 w = __ldg(reinterpret_cast<const uint4*>(mrow + j * 4));
           keep[0] = w.x; keep[1] = w.y; keep[2] = w.z; keep[3] = w.w;
-          need_mask = true;
+          need_mask = (w.x & w.y & w.z & w.w) != 0xffffffffu;   // a tile the mask keeps whole needs no selects
         }
         int n_keep = a.T - key0;
         if (a.causal) n_keep = min(n_keep, row - key0 + 1);
@@ -397,7 +534,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
         }
         // logits: t = s * scale + bias (natural units); without a bias the scale is folded into the exponent
-        if (a.bias_mode == kBiasTile) {
+        if (a.bias_mode == kBiasTile && !a.bias_mma) {
           // slots filled before this (tile, query tile): every live query tile of the earlier key tiles, and
           // query tile 0 of this one when this is query tile 1
           const int seq0 = seq_base + 2 * (min(j, it.nt[0]) + min(j, it.nt[1]) + ((g == 1 && j < it.nt[0]) ? 1 : 0));
@@ -421,7 +558,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
           }
           if (!ok) break;
-        } else if (a.bias_mode == kBiasKey) {
+        } else if (a.bias_mode == kBiasKey && !key_mma) {
           const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * key0);
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
@@ -541,13 +678,14 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
 }
 
-template <int D, bool kBf16>
+template <int D, bool kBf16, bool kTileBias>
 int launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tb,
                FwdArgs a, cudaStream_t st) {
-  auto kernel = sdpa_fwd_tc_kernel<D, kBf16>;
+  auto kernel = sdpa_fwd_tc_kernel<D, kBf16, kTileBias>;
+  using L = FwdSmem<D, kTileBias>;
   constexpr int kLimit = 232448;  // 227 KB per CTA
-  const int smem = FwdSmem<D>::kTotal + 1024 <= kLimit ? FwdSmem<D>::kTotal + 1024 : kLimit;
-  static_assert(FwdSmem<D>::kTotal <= kLimit, "forward shared memory exceeds the per-CTA limit");
+  const int smem = L::kTotal + 1024 <= kLimit ? L::kTotal + 1024 : kLimit;
+  static_assert(L::kTotal <= kLimit, "forward shared memory exceeds the per-CTA limit");
   a.smem_bytes = smem;
   cudaFuncAttributes attr;
   cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
@@ -571,10 +709,16 @@ int launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 
 }  // namespace
 
+
 int launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                const CUtensorMap& tb, const FwdArgs& a, cudaStream_t st) {
-  if (D == 64) return bf16 ? launch_one<64, true>(tq, tk, tv, tb, a, st) : launch_one<64, false>(tq, tk, tv, tb, a, st);
-  return bf16 ? launch_one<128, true>(tq, tk, tv, tb, a, st) : launch_one<128, false>(tq, tk, tv, tb, a, st);
+  const bool tiles = a.bias_mode == kBiasTile;
+  if (D == 64) {
+    if (tiles) return bf16 ? launch_one<64, true, true>(tq, tk, tv, tb, a, st) : launch_one<64, false, true>(tq, tk, tv, tb, a, st);
+    return bf16 ? launch_one<64, true, false>(tq, tk, tv, tb, a, st) : launch_one<64, false, false>(tq, tk, tv, tb, a, st);
+  }
+  if (tiles) return bf16 ? launch_one<128, true, true>(tq, tk, tv, tb, a, st) : launch_one<128, false, true>(tq, tk, tv, tb, a, st);
+  return bf16 ? launch_one<128, true, false>(tq, tk, tv, tb, a, st) : launch_one<128, false, false>(tq, tk, tv, tb, a, st);
 }
 
 }  // namespace tc

@@ -15,6 +15,14 @@ struct FwdArgs {
   float scale;
   int bias_mode;
   int bias_b_mul, bias_h_mul;   // 0 when the bias is broadcast over batch / heads (tile mode)
+  // Head dim 64, tile-mode bias, positive scale: the tensor core adds the bias tile to the scores,
+  // S += bias (hi I + lo I) with hi + lo = 1 / scale in the operand dtype, and the softmax warps never read it.
+  int bias_mma;
+  float inv_scale_hi, inv_scale_lo;
+  // Per-key terms (a bias with no query axis, a mask with no query axis) and a positive scale: the tensor core adds
+  // them to every row of the score tile by one K = 16 step, S += W C^T, with C[key] = bias[key] / scale split into
+  // three 16-bit terms (-inf for a dropped key); the softmax warps then neither read the bias nor apply the mask.
+  int key_mma;
   const void* bias;             // key mode: base pointer
   int64_t bias_bs, bias_hs;     // key mode: element strides over batch / heads
   MaskBits mask;

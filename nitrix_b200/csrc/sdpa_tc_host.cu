@@ -163,6 +163,18 @@ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 }  // namespace
 
+bool split_inv_scale(float scale, bool bf16, float* hi, float* lo) {
+  *hi = *lo = 0.f;
+  if (scale == 0.f || !isfinite(scale) || !isfinite(1.f / scale)) return false;
+  const float inv = 1.f / scale;
+  const float h = bf16 ? __bfloat162float(__float2bfloat16_rn(inv)) : __half2float(__float2half_rn(inv));
+  if (!isfinite(h) || h == 0.f) return false;
+  const float rest = inv - h;
+  *hi = h;
+  *lo = bf16 ? __bfloat162float(__float2bfloat16_rn(rest)) : __half2float(__float2half_rn(rest));
+  return true;
+}
+
 MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed) {
   MaskPackPlan p{};
   if (!pr.mask) return p;
@@ -310,6 +322,14 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.bias_b_mul = (pr.B > 1 && pr.bs[0] != 0) ? 1 : 0;
   a.bias_h_mul = (pr.H > 1 && pr.bs[1] != 0) ? 1 : 0;
   a.bias = pr.bias; a.bias_bs = pr.bs[0]; a.bias_hs = pr.bs[1];
+  a.bias_mma = 0;
+  if (pr.D == 64 && bp.mode == tc::kBiasTile && pr.scale > 0.f &&
+      tc::split_inv_scale(pr.scale, dtype == NB200_BF16, &a.inv_scale_hi, &a.inv_scale_lo))
+    a.bias_mma = 1;
+  a.key_mma = 0;
+  if (bp.mode != tc::kBiasTile && pr.scale > 0.f && isfinite(1.f / pr.scale) &&
+      (bp.mode == tc::kBiasKey || a.mask.kv_len != nullptr))
+    a.key_mma = 1;
   a.out = pr.out;
   for (int i = 0; i < 3; ++i) a.os[i] = pr.os[i];
   a.lse = pr.lse;
