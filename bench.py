@@ -61,8 +61,7 @@ KERNEL_FLOP_SHARE = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/), full-size
 # workload, same command line as the default bench run.
 NCU_TRAFFIC_BYTES = {
-    "c2": {"sdpa_fwd_tc_kernel": 203.0e6, "sdpa_bwd_tc_kernel<key-major>": 615.5e6,
-           "sdpa_bwd_tc_kernel<query-major>": 506.3e6},
+    "c2": {"sdpa_fwd_tc_kernel": 203.8e6, "sdpa_bwd_tc_kernel<merged>": 796.9e6},
 }
 
 METRIC = "fwd+bwd attention TFLOP/s"
