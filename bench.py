@@ -356,26 +356,15 @@ def main():
             host_in["bias"] = bias.detach().cpu().pin_memory()
         if mask is not None:
             host_in["mask"] = mask.cpu().pin_memory()
-        host_out = None
-        h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+        # batch chunks move up, run and come down on three streams at once (nitrix_b200.nn.host_pipeline)
+        from nitrix_b200.nn.host_pipeline import HostPipeline
+        pipe = HostPipeline(host_in, device=dev, causal=causal, scale=scale, want_dbias=wl["want_dbias"],
+                            chunks=8, backend=args.backend)
+        h2d = pipe.h2d_bytes()
 
         def e2e_step():
-            nonlocal host_out
-            d = {n: t.to(dev, non_blocking=True) for n, t in host_in.items()}
-            lv = [d["q"].requires_grad_(True), d["k"].requires_grad_(True), d["v"].requires_grad_(True)]
-            b_ = d.get("bias")
-            if b_ is not None and wl["want_dbias"]:
-                b_.requires_grad_(True)
-                lv.append(b_)
-            out = att.scaled_dot_product_attention(lv[0], lv[1], lv[2], bias=b_, mask=d.get("mask"), causal=causal,
-                                                   scale=scale, backend=args.backend)
-            grads = torch.autograd.grad(out, lv, grad_outputs=d["dout"])
-            res = [out.detach(), *grads]
-            if host_out is None:
-                host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in res]
-            for h, t in zip(host_out, res):
-                h.copy_(t, non_blocking=True)
-            return sum(t.numel() * t.element_size() for t in res)
+            pipe.run()
+            return pipe.d2h_bytes()
 
         d2h = e2e_step()
         e2e_step()
@@ -389,7 +378,8 @@ def main():
         barrier()
         e2e_ms = max_over_ranks(e0.elapsed_time(e1) / n_e2e, dev)
         e2e = {"value": world * wl["flops"] / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+               "how": f"{len(pipe.slices)} batch chunks pipelined over copy-in / kernel / copy-out streams"}
 
     if rank != 0:
         if world > 1:
