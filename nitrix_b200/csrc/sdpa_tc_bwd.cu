@@ -232,7 +232,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         if (!wait_or_abort(bar(Y_EMPTY + st), ((n / NY) & 1) ^ 1, abort_flag, a.status, 201)) break;
         const int r0 = (s_begin + n) * kStep;
         const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-        mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + (kKeyMajor ? 512 : 0));
+        // lse / delta rows of the step that exist (S is a multiple of 8, so the copy stays a multiple of 16 bytes)
+        const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+        mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + (kKeyMajor ? 2 * row_bytes : 0));
 #pragma unroll
         for (int x = 0; x < D / 64; ++x) {
           tma_load_4d(ybase + x * kYBoxBytes, &tm_y1, bar(Y_FULL + st), x * 64, r0, h, b);
@@ -241,8 +243,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         if (kKeyMajor) {
           // lse and delta of the step's 64 queries: two 256-byte bulk copies on the same barrier
           const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
-          bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, 256, bar(Y_FULL + st));
-          bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, 256, bar(Y_FULL + st));
+          bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
+          bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
         }
       }
     }
@@ -393,7 +395,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int q = lane + 32 * e;
-        const float c[2] = {-ld[q] * inv_mul, -ld[kStep + q]};
+        // queries past S were not copied (their columns are masked; the addend must still be finite)
+        const bool live = (s_begin + n) * kStep + q < a.S;
+        const float c[2] = {live ? -ld[q] * inv_mul : 0.f, live ? -ld[kStep + q] : 0.f};
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile) {
           // c = w0 c0 + w1 c1 + w2 c2 with the remainder carried in fp32
@@ -588,7 +592,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * r0);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const uint4 w = __ldg(bk + c);
+          const uint4 w = r0 + 8 * c < a.T ? __ldg(bk + c) : make_uint4(0, 0, 0, 0);   // T is a multiple of 8
           const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
@@ -667,7 +671,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
               const int rl = 8 * i + (lane >> 2), ch = lane & 3;
               const uint4 v = *reinterpret_cast<const uint4*>(stage + rl * 64 + ((ch ^ ((rl >> 1) & 3)) << 4));
               const int row = o0 + wq * 32 + rl;
-              if (row < a.S)
+              if (row < a.S && r0 + half * 32 + ch * 8 < a.T)
                 *reinterpret_cast<uint4*>(dbase + 2 * (int64_t(row) * a.dbs[2] + half * 32 + ch * 8)) = v;
             }
             __syncwarp();
@@ -838,7 +842,7 @@ bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** wh
 namespace {
 // One kernel for dq, dk and dv (head dim 64, no bias gradient): the key-major kernel also forms ds K per pair of
 // steps and adds it to an fp32 copy of dq, which a last kernel scales and casts.
-bool use_merged(const Problem& pr) { return pr.D == 64 && !pr.dbias; }
+bool use_merged(const Problem& pr) { return pr.D == 64 && !pr.dbias && pr.S % kTile == 0; }
 size_t mask_bytes_aligned(const MaskPackPlan& mp) { return (mp.total() + 255) / 256 * 256; }
 }  // namespace
 
@@ -905,8 +909,8 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     ak.out2 = pr.dk;
     for (int i = 0; i < 3; ++i) { ak.o1s[i] = pr.dvs[i]; ak.o2s[i] = pr.dks[i]; }
     const CUtensorMap maps[5] = {k128, v128, q64, g64, bias_k};
-    const int rc = bf16 ? launch_one<64, true, true, true>(maps, ak, pr.T / kTile, pr.bh_count, stream)
-                        : launch_one<64, false, true, true>(maps, ak, pr.T / kTile, pr.bh_count, stream);
+    const int rc = bf16 ? launch_one<64, true, true, true>(maps, ak, (pr.T + kTile - 1) / kTile, pr.bh_count, stream)
+                        : launch_one<64, false, true, true>(maps, ak, (pr.T + kTile - 1) / kTile, pr.bh_count, stream);
     if (rc) return rc;
     const int64_t n_chunks = int64_t(pr.bh_count) * pr.S * 8;
     const int blocks = int((n_chunks + 255) / 256);
@@ -930,7 +934,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     aq.dbias = pr.dbias;
     for (int i = 0; i < 4; ++i) aq.dbs[i] = pr.dbs[i];
     const CUtensorMap maps[5] = {q128, g128, k64, v64, bias_q};
-    if (int rc = launch_dir<false>(pr.D, bf16, maps, aq, pr.S / kTile, pr.bh_count, stream)) return rc;
+    if (int rc = launch_dir<false>(pr.D, bf16, maps, aq, (pr.S + kTile - 1) / kTile, pr.bh_count, stream)) return rc;
   }
   // key-major: dk, dv
   {
@@ -939,7 +943,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     ak.out2 = pr.dk;
     for (int i = 0; i < 3; ++i) { ak.o1s[i] = pr.dvs[i]; ak.o2s[i] = pr.dks[i]; }
     const CUtensorMap maps[5] = {k128, v128, q64, g64, bias_k};
-    if (int rc = launch_dir<true>(pr.D, bf16, maps, ak, pr.T / kTile, pr.bh_count, stream)) return rc;
+    if (int rc = launch_dir<true>(pr.D, bf16, maps, ak, (pr.T + kTile - 1) / kTile, pr.bh_count, stream)) return rc;
   }
   return NB200_OK;
 }

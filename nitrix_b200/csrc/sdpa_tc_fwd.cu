@@ -273,11 +273,13 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             for (int e = 0; e < 4; ++e) {
               const int kl = lane + 32 * e, key = j * kTile + kl;
               float c = 0.f;
-              if (bk) {
+              if (key >= a.T) {
+                c = -INFINITY;   // past the last key (the tile is padded with zero rows)
+              } else if (bk) {
                 const uint16_t raw = __ldg(bk + key);
                 c = (kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw))) * inv_scale;
               }
-              if (mk && !((__ldg(mk + (key >> 5)) >> (key & 31)) & 1u)) c = -INFINITY;
+              if (mk && key < a.T && !((__ldg(mk + (key >> 5)) >> (key & 31)) & 1u)) c = -INFINITY;
               uint32_t h[3] = {0u, 0u, 0u};
               float rem = c;
 #pragma unroll
@@ -562,7 +564,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * key0);
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
-            const uint4 w = __ldg(bk + c);
+            const uint4 w = key0 + 8 * c < a.T ? __ldg(bk + c) : make_uint4(0, 0, 0, 0);   // T is a multiple of 8
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) t[c * 4 + e] = __ffma2_rn(t[c * 4 + e], scale2, unpack2<kBf16>(ww[e]));

@@ -266,8 +266,10 @@ bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const 
   if (!why) why = &dummy;
   if (dtype != NB200_BF16 && dtype != NB200_F16) { *why = "dtype is not bf16/fp16"; return false; }
   if (pr.D != pr.Dv || (pr.D != 64 && pr.D != 128)) { *why = "head dims must be equal and 64 or 128"; return false; }
-  if (pr.S <= 0 || pr.T <= 0 || pr.S % tc::kTile || pr.T % tc::kTile) {
-    *why = "query and key lengths must be positive multiples of 128";
+  // Lengths need not fill whole 128-row tiles: TMA zero-fills rows past the end, the kernels mask keys past T and
+  // store only rows below S.  Multiples of 8 keep every 16-byte row segment (bias, dbias, lse, packed rows) whole.
+  if (pr.S <= 0 || pr.T <= 0 || pr.S % 8 || pr.T % 8) {
+    *why = "query and key lengths must be positive multiples of 8";
     return false;
   }
   if (!tc::tile_map_ok(pr.q, pr.qs[2], pr.qs[1], pr.qs[0], pr.H, pr.B) ||

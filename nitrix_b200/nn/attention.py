@@ -332,7 +332,7 @@ def scaled_dot_product_attention(
                 resolved="cuda-simt",
                 reason=(
                     "the fused tcgen05 kernels take bf16/fp16 with d == d_v in {64, 128} and "
-                    "query/key lengths that are multiples of 128"
+                    "query/key lengths that are multiples of 8"
                 ),
                 shapes=(tuple(q.shape), tuple(k.shape), tuple(v.shape)),
                 dtype=out_dtype,

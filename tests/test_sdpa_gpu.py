@@ -285,6 +285,41 @@ def test_tc_parity(name, dtype, d):
         check(got, ref, dtype)
 
 
+RAGGED = [dict(s=200, t=200), dict(s=136, t=328), dict(s=392, t=72), dict(s=8, t=8), dict(s=256, t=200)]
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("shape", RAGGED)
+@pytest.mark.parametrize("name", ["dense", "bias_causal", "full_bias_mask", "key_padding", "key_bias", "causal"])
+def test_tc_ragged_lengths(name, shape, d):
+    """Lengths that do not fill whole 128-row tiles (multiples of 8) stay on the tensor-core kernels: rows past the
+    end are zero-filled by TMA, keys past T are masked, nothing is stored past S."""
+    q, k, v, kw = _cases.kernel_case(name, d=d, **shape)
+    dtype = torch.bfloat16
+    _assert_plans_tc(q, k, v, kw, dtype)
+    bias = kw.get("bias")
+    shared_bias = bias is not None and bias.numel() < q.shape[0] * q.shape[1] * q.shape[2] * k.shape[2]
+    want_dbias = bias is not None and not shared_bias
+    _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=want_dbias)
+    got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100", want_dbias=want_dbias)
+    _device_ok()
+    check(got, ref, dtype)
+
+
+def test_tc_ragged_fp16_and_odd_multiple_falls_back():
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    q, k, v, kw = _cases.kernel_case("bias_mask", s=264, t=136, d=64)
+    _assert_plans_tc(q, k, v, kw, torch.float16)
+    got, ref = run_both(q, k, v, kw, torch.float16, "cuda-sm100", want_dbias=False)
+    _device_ok()
+    check(got, ref, torch.float16)
+    # a length that is not a multiple of 8 is declined (CUDA-core kernels take it)
+    q, k, v, kw = _cases.kernel_case("dense", s=100, t=100, d=64)
+    chosen = att.planned_kernel(q.bfloat16().cuda(), k.bfloat16().cuda(), v.bfloat16().cuda(), None, None, causal=False)
+    assert chosen == _cabi.KERNEL_SIMT
+
+
 def test_tc_backward_full_bias_causal_dbias_zero_past_diagonal():
     """Per-batch bias + causal: dbias comes from the tensor-core backward and is exactly zero above the diagonal."""
     q, k, v, kw = _cases.kernel_case("full_bias", s=256, t=256, d=64)
