@@ -153,17 +153,59 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   }
   const int n_steps = s_end - s_begin;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < L::kNumBars; ++i) {
-      uint32_t count = 1;
-      if (i >= E_READY && i < E_READY + 2) count = 4;   // one lane per warp of the group
-      if (i >= P_FREE && i < P_FREE + 2) count = 4;
-      if (i >= B_EMPTY && i < B_EMPTY + 2) count = a.bias_mma ? 1 : 4;   // released by the MMA issuer or by the group's warps
-      if (i == DQ_FREE) count = 8;                       // every element-wise warp has read its part of the dq tile
-      mbar_init(bar(i), count);
-    }
-    *abort_flag = 0;
+  // Start-up is a visible share of a short CTA's life (16 steps at L = 2048), so it is kept short: the barriers are
+  // initialised by one thread each, and thread 0 then starts the first copies (owner tiles, first ring stages, first
+  // bias slots) itself, so that their latency runs under the rest of the start-up (operand tiles below, TMEM
+  // allocation, register hand-over) instead of after it.
+  if (threadIdx.x < L::kNumBars) {
+    const int i = threadIdx.x;
+    uint32_t count = 1;
+    if (i >= E_READY && i < E_READY + 2) count = 4;   // one lane per warp of the group
+    if (i >= P_FREE && i < P_FREE + 2) count = 4;
+    if (i >= B_EMPTY && i < B_EMPTY + 2) count = a.bias_mma ? 1 : 4;   // released by the MMA issuer or by the group's warps
+    if (i == DQ_FREE) count = 8;                       // every element-wise warp has read its part of the dq tile
+    mbar_init(bar(i), count);
+    if (i == 0) *abort_flag = 0;
     mbar_init_fence();
+  }
+  __syncwarp();
+  static_assert(L::kNumBars <= 64, "barrier initialisation assumes the first two warps cover all barriers");
+  // named barrier over the first two warps: every barrier is initialised before thread 0 hands any of them to TMA
+  if (threadIdx.x < 64) asm volatile("bar.sync 1, 64;" ::: "memory");
+  if (threadIdx.x == 0 && n_steps > 0) {
+    mbar_expect_tx(bar(X_FULL), 2 * L::kXBytes);
+#pragma unroll
+    for (int x = 0; x < D / 64; ++x) {
+      tma_load_4d(sbase + L::kX + x * kBoxBytes, &tm_x1, bar(X_FULL), x * 64, o0, h, b);
+      tma_load_4d(sbase + L::kX + L::kXBytes + x * kBoxBytes, &tm_x2, bar(X_FULL), x * 64, o0, h, b);
+    }
+    const int n_first = n_steps < NY ? n_steps : NY;
+    for (int n = 0; n < n_first; ++n) {
+      const int r0 = (s_begin + n) * kStep;
+      const uint32_t ybase = sbase + L::kY + n * L::kYStageBytes;
+      const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+      mbar_expect_tx(bar(Y_FULL + n), 2 * L::kYBytes + (kKeyMajor ? 2 * row_bytes : 0));
+#pragma unroll
+      for (int x = 0; x < D / 64; ++x) {
+        tma_load_4d(ybase + x * kYBoxBytes, &tm_y1, bar(Y_FULL + n), x * 64, r0, h, b);
+        tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_y2, bar(Y_FULL + n), x * 64, r0, h, b);
+      }
+      if (kKeyMajor) {
+        const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+        bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + n));
+        bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + n));
+      }
+      if (a.bias_mode == kBiasTile && n < 2) {
+        mbar_expect_tx(bar(B_FULL + n), kBoxBytes);
+        const uint32_t dst = sbase + L::kBias + n * kBoxBytes;
+        if (kKeyMajor) {
+          tma_load_4d(dst, &tm_bias, bar(B_FULL + n), o0, r0, h * a.bias_h_mul, b * a.bias_b_mul);
+          tma_load_4d(dst + kYBoxBytes, &tm_bias, bar(B_FULL + n), o0 + 64, r0, h * a.bias_h_mul, b * a.bias_b_mul);
+        } else {
+          tma_load_4d(dst, &tm_bias, bar(B_FULL + n), r0, o0, h * a.bias_h_mul, b * a.bias_b_mul);
+        }
+      }
+    }
   }
   if constexpr (kKeyMajor) {
     {
@@ -216,18 +258,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
   reg_dealloc<kProducerRegs>();
   if (warp == 0) {
     // ---------------- X / Y producer ----------------
-    if (elect_one() && n_steps > 0) {
-      tma_prefetch_desc(&tm_x1);
-      tma_prefetch_desc(&tm_x2);
-      tma_prefetch_desc(&tm_y1);
-      tma_prefetch_desc(&tm_y2);
-      mbar_expect_tx(bar(X_FULL), 2 * L::kXBytes);
-#pragma unroll
-      for (int x = 0; x < D / 64; ++x) {
-        tma_load_4d(sbase + L::kX + x * kBoxBytes, &tm_x1, bar(X_FULL), x * 64, o0, h, b);
-        tma_load_4d(sbase + L::kX + L::kXBytes + x * kBoxBytes, &tm_x2, bar(X_FULL), x * 64, o0, h, b);
-      }
-      for (int n = 0; n < n_steps; ++n) {
+    // (the owner tiles and the first NY stages were issued during start-up)
+    if (elect_one() && n_steps > NY) {
+      for (int n = NY; n < n_steps; ++n) {
         const int st = n % NY;
         if (!wait_or_abort(bar(Y_EMPTY + st), ((n / NY) & 1) ^ 1, abort_flag, a.status, 201)) break;
         const int r0 = (s_begin + n) * kStep;
@@ -250,9 +283,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     }
   } else if (warp == 1) {
     // ---------------- bias producer ----------------
+    // (the first two slots were issued during start-up)
     if (a.bias_mode == kBiasTile && elect_one()) {
-      tma_prefetch_desc(&tm_bias);
-      for (int n = 0; n < n_steps; ++n) {
+      for (int n = 2; n < n_steps; ++n) {
         const int slot = n & 1;
         if (!wait_or_abort(bar(B_EMPTY + slot), ((n >> 1) & 1) ^ 1, abort_flag, a.status, 202)) break;
         const int r0 = (s_begin + n) * kStep;
