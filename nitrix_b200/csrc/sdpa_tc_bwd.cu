@@ -59,6 +59,10 @@ struct BwdArgs {
   // scores * scale holds scale * q.k + bias and the element-wise warps never read the bias column-wise.
   int bias_mma;
   float inv_scale_hi, inv_scale_lo;
+  // Query-major kernel, per-key terms (a bias or a mask with no query axis) and a positive scale: added to the scores
+  // by one K = 16 MMA step, scores += W C^T with C[key] = bias[key] / scale in three 16-bit terms, -inf for a dropped
+  // key; the element-wise warps then neither read the bias nor apply that mask.
+  int key_aug;
   int bias_b_mul, bias_h_mul;
   const void* bias;             // key mode base
   int64_t bias_bs, bias_hs;
@@ -207,7 +211,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       }
     }
   }
-  if constexpr (kKeyMajor) {
+  if (kKeyMajor || a.key_aug) {
     {
       // weight rows (w0, w1, w2, 0, ...): a query's addend is sum_j w_j c_j with c_j 16-bit; bf16 has fp32's range,
       // so three unit weights give 24 bits; fp16 spreads the terms over 2^8, 1, 2^-8 to cover magnitudes up to 1.6e7
@@ -220,7 +224,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       for (int idx = threadIdx.x; idx < 2 * L::kAugSlotBytes / 16; idx += kThreads) aug[idx] = make_uint4(0, 0, 0, 0);
       fence_proxy_async_smem();
     }
-    if (a.bias_mma) {
+    if (kKeyMajor && a.bias_mma) {
       // Two 64 x 64 tiles, hi * I and lo * I with hi + lo = 1 / scale to 16 + 16 bits, as K-major 128-byte-swizzled
       // operands (rows of 64 elements = 128 bytes).  Tile 0 at kIdent, tile 1 at kIdent + 8 KB.
       uint4* ident = reinterpret_cast<uint4*>(smem + L::kIdent);
@@ -361,8 +365,18 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             mma_ss(p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
             mma_ss(p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
           }
+          if constexpr (!kKeyMajor) {
+            if (a.key_aug) {
+              // P1 += W C^T: the per-key addends land on every query row
+              ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 212);
+              if (!ok) break;
+              tc_fence_after_sync();
+              const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
+              mma_ss(p1, wdesc, make_smem_desc_noswizzle(sbase + L::kAug + s * L::kAugSlotBytes, 128, 256), idesc_prod, 1u);
+            }
+          }
           mma_commit(bar(PROD_FULL + s));
-          if (kKeyMajor) mma_commit(bar(AUG_FREE + s));
+          if (kKeyMajor || a.key_aug) mma_commit(bar(AUG_FREE + s));
           if (a.bias_mma) mma_commit(bar(B_EMPTY + (n & 1)));   // the slot may be refilled once these MMAs are done
         }
         if (n >= kLag) {
@@ -414,7 +428,60 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
       }
     }
-  } else if (kKeyMajor) {
+  } else if (!kKeyMajor) {
+    // ---------------- warp 3 (query-major): per-key addends as an MMA operand ----------------
+    if (a.key_aug) {
+      const float inv_scale = 1.f / a.scale;
+      const uint16_t* bk = a.bias_mode == kBiasKey
+                               ? reinterpret_cast<const uint16_t*>(a.bias) + (b * a.bias_bs + h * a.bias_hs)
+                               : nullptr;
+      const uint32_t* mk = a.mask_key_only ? a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride : nullptr;
+      bool ok = true;
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int s = n & 1;
+        if (n >= 2) ok = wait_or_abort(bar(AUG_FREE + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 214);
+        if (!ok) break;
+        uint8_t* slot = smem + L::kAug + s * L::kAugSlotBytes;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kl = lane + 32 * e, key = (s_begin + n) * kStep + kl;
+          float c = 0.f;
+          if (key >= a.T) {
+            c = -INFINITY;   // past the last key (the tile is padded with zero rows)
+          } else {
+            if (bk) {
+              const uint16_t raw = __ldg(bk + key);
+              c = (kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw))) * inv_scale;
+            }
+            if (mk && !((__ldg(mk + (key >> 5)) >> (key & 31)) & 1u)) c = -INFINITY;
+          }
+          uint32_t hh[3] = {0u, 0u, 0u};
+          float rem = c;
+#pragma unroll
+          for (int j = 0; j < 3; ++j) {
+            const float w = kBf16 ? 1.f : (j == 0 ? 256.f : (j == 1 ? 1.f : 0.00390625f));
+            const float v = rem * (1.f / w);
+            float back;
+            if constexpr (kBf16) {
+              const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+              hh[j] = __bfloat16_as_ushort(hv);
+              back = __bfloat162float(hv);
+            } else {
+              const __half hv = __float2half_rn(v);
+              hh[j] = __half_as_ushort(hv);
+              back = __half2float(hv);
+            }
+            if (!(fabsf(back) < INFINITY)) break;   // an infinite (or NaN) term carries the value alone
+            rem = fmaf(-back, w, rem);
+          }
+          *reinterpret_cast<uint4*>(slot + (kl >> 3) * 256 + (kl & 7) * 16) = make_uint4(hh[0] | (hh[1] << 16), hh[2], 0u, 0u);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(AUG_FULL + s));
+      }
+    }
+  } else {
     // ---------------- warp 3: per-query addends as MMA operands ----------------
     const float inv_mul = 1.f / (a.scale * kLog2e);
     bool ok = true;
@@ -472,7 +539,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     bool ok = true;
     // without a bias the scale is folded into the exponent's multiplier: p = exp2(s * (scale log2e) - lse)
     // (the same holds when the tensor core has already added bias / scale to the scores)
-    const bool fold_scale = a.bias_mode == kBiasNone || a.bias_mma;
+    const bool key_aug = !kKeyMajor && a.key_aug;
+    const bool fold_scale = a.bias_mode == kBiasNone || a.bias_mma || key_aug;
     const float mul = fold_scale ? a.scale * kLog2e : kLog2e;
     const float2 mul2 = make_float2(mul, mul), scale2 = make_float2(a.scale, a.scale);
     float lse_row = 0.f, delta_row = 0.f;
@@ -486,7 +554,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     bool key_dropped = false;
     if (a.mask.rows) {
       if (!kKeyMajor) {
-        mbits = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride + int64_t(min(orow, a.S - 1)) * a.mask.row_stride;
+        if (!(key_aug && a.mask_key_only))   // a key-only mask was added to the scores as -inf
+          mbits = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride + int64_t(min(orow, a.S - 1)) * a.mask.row_stride;
       } else if (a.mask_key_only) {
         const uint32_t* krow = a.mask.rows + b * a.mask.b_stride + h * a.mask.h_stride;
         key_dropped = orow >= a.T || !((krow[orow >> 5] >> (orow & 31)) & 1u);
@@ -621,7 +690,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
-      } else if (a.bias_mode == kBiasKey && !kKeyMajor) {
+      } else if (a.bias_mode == kBiasKey && !kKeyMajor && !key_aug) {
         const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * r0);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -962,6 +1031,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     // query-major reads the bias row-wise with 16-byte loads, which is cheap; the tensor-core add only pays in
     // the key-major kernel, where the bias would be read column-wise, two bytes at a time
     aq.bias_mma = 0;
+    aq.key_aug = (a.bias_mode != kBiasTile && (a.bias_mode == kBiasKey || key_only) && pr.scale > 0.f) ? 1 : 0;
     aq.out2 = pr.dq;
     for (int i = 0; i < 3; ++i) aq.o2s[i] = pr.dqs[i];
     aq.dbias = pr.dbias;
