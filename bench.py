@@ -4,7 +4,7 @@
 ``python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|c1] [--impl ours|reference]``
 
 A *step* is one forward + backward pass of ``scaled_dot_product_attention``
-over one synthetic batch of the named workload (BASELINE.json ``configs``;
+over one synthetic batch of the named workload (the five benchmark configurations;
 default ``c2``: bf16, B=8, H=16, L=2048, D=64, causal, ALiBi bias (1,H,L,L),
 gradients for q, k, v).  Throughput counts ALGORITHMIC flops only:
 ``14 * B * H * S * T_eff * D`` per step (4 forward + 10 backward, causal halves
@@ -12,8 +12,8 @@ the pairs, key padding counts kept keys only); softmax work is not counted.
 
 One JSON line is printed by rank 0 with
 
-* ``value``: whole-job TFLOP/s with operands resident in HBM, timed with CUDA
-  events, max over ranks (multi-GPU: every rank runs the full workload on its
+* ``value``: whole-job TFLOP/s with operands resident in HBM: K replays of a
+  CUDA graph of one step between two CUDA events, max over ranks (multi-GPU: every rank runs the full workload on its
   own shard of a batch N times larger -> weak scaling, no collective);
 * ``e2e``: the same metric through the public entry point with HOST (pinned)
   operands: H2D of q, k, v, bias, mask, dout and D2H of out, dq, dk, dv (dbias)
