@@ -10,7 +10,11 @@ struct FwdArgs {
   int B, H, S, T;
   int bh_begin, bh_count;       // flattened (batch, head) range this launch covers
   int n_qblocks;                // 256-row query blocks per (batch, head): work items = n_qblocks * bh_count
-  int head_major;               // item order: head, query block, batch (needs the full range); else pair-major
+  // Item order (both need the full (batch, head) range; a partial range is pair-major):
+  //   1: head, query block, batch fastest -- neighbours share a head's K / V and bias in L2;
+  //   2: query block (heaviest first), head, batch, dealt in rows of alternating direction -- evens out causal
+  //      work when a CTA gets only a few items, at the price of K / V locality.
+  int head_major;
   int causal;
   float scale;
   int bias_mode;

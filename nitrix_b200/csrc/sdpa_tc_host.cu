@@ -342,6 +342,9 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.n_qblocks = (pr.S + 2 * tc::kTile - 1) / (2 * tc::kTile);
   // the whole (batch, head) range: order the items head-major / query block / batch (see decode_item)
   a.head_major = (pr.bh_begin == 0 && pr.bh_count == pr.B * pr.H) ? 1 : 0;
+  // causal items differ in length by up to the number of key tiles; with few items per CTA that imbalance costs
+  // more than the K / V locality of the head-major order
+  if (a.head_major && pr.causal && int64_t(a.n_qblocks) * pr.bh_count <= 16 * int64_t(tc::sm_count())) a.head_major = 2;
   return tc::launch_fwd(pr.D, dtype == NB200_BF16, tq, tk, tv, tb, a, stream);
 }
 
