@@ -42,11 +42,33 @@ __device__ __forceinline__ float warp_sum(float x) {
 template <typename T>
 __device__ __forceinline__ void stage_tile(float* dst, int ld, const T* src, int64_t row_stride,
                                            int row0, int limit, int dim) {
-  for (int idx = threadIdx.x; idx < kTile * dim; idx += blockDim.x) {
-    int r = idx / dim, c = idx - r * dim;
-    int row = row0 + r;
-    dst[r * ld + c] = row < limit ? to_f32<T>(src[row * row_stride + c]) : 0.f;
+  // one warp per row, lanes over the columns: coalesced, and no division per element
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (int r = warp; r < kTile; r += n_warps) {
+    const int row = row0 + r;
+    const T* srow = src + row * row_stride;
+    float* drow = dst + r * ld;
+    if (row < limit) {
+      for (int c = lane; c < dim; c += 32) drow[c] = to_f32<T>(srow[c]);
+    } else {
+      for (int c = lane; c < dim; c += 32) drow[c] = 0.f;
+    }
   }
+}
+
+// Dot product of two fp32 rows in shared memory: four independent chains (the order of the sum is fixed, so
+// results stay run-to-run identical).
+__device__ __forceinline__ float dot_rows(const float* a, const float* b, int n) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int d = 0;
+  for (; d + 4 <= n; d += 4) {
+    s0 = fmaf(a[d], b[d], s0);
+    s1 = fmaf(a[d + 1], b[d + 1], s1);
+    s2 = fmaf(a[d + 2], b[d + 2], s2);
+    s3 = fmaf(a[d + 3], b[d + 3], s3);
+  }
+  for (; d < n; ++d) s0 = fmaf(a[d], b[d], s0);
+  return (s0 + s1) + (s2 + s3);
 }
 
 __device__ __forceinline__ bool keep_entry(const Problem& pr, int b, int h, int i, int j) {
@@ -100,10 +122,9 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(Problem pr, int b
     __syncthreads();
     if (!row_ok) continue;
     const int j = kt + lane;
-    float dot = 0.f;
     const float* qrow = Qs + warp * D;
     const float* krow = Ks + lane * DP;
-    for (int d = 0; d < D; ++d) dot = fmaf(qrow[d], krow[d], dot);
+    const float dot = dot_rows(qrow, krow, D);
     const bool keep = keep_entry(pr, b, h, i, j);
     float s2 = keep ? fmaf(dot, s2scale, bias2(pr, bias_dtype, b, h, i, j)) : -INFINITY;
     const float m_new = fmaxf(m, warp_max(s2));
@@ -119,6 +140,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(Problem pr, int b
       const float* vrow = Vs + jj * Dv;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; ++c) {
+        if (32 * c >= Dv) break;   // warp-uniform: chunks past the head dim cost nothing
         const int col = lane + 32 * c;
         if (col < Dv) acc[c] = fmaf(pj, vrow[col], acc[c]);
       }
@@ -218,13 +240,12 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_dq_kernel(Problem pr, in
     __syncthreads();
     if (!row_ok) continue;
     const int j = kt + lane;
-    float dot = 0.f, dp = 0.f;
     const float* qrow = Qs + warp * D;
     const float* krow = Ks + lane * DP;
-    for (int d = 0; d < D; ++d) dot = fmaf(qrow[d], krow[d], dot);
+    const float dot = dot_rows(qrow, krow, D);
     const float* grow = Gs + warp * Dv;
     const float* vrow = Vs + lane * DVP;
-    for (int d = 0; d < Dv; ++d) dp = fmaf(grow[d], vrow[d], dp);
+    const float dp = dot_rows(grow, vrow, Dv);
     const bool keep = keep_entry(pr, b, h, i, j);
     const float p = keep ? exp2f(fmaf(dot, s2scale, bias2(pr, bias_dtype, b, h, i, j)) - lse) : 0.f;
     const float ds = p * (dp - delta);
@@ -241,6 +262,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_dq_kernel(Problem pr, in
       const float* kr = Ks + jj * DP;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; ++c) {
+        if (32 * c >= D) break;    // warp-uniform
         const int col = lane + 32 * c;
         if (col < D) acc[c] = fmaf(dsj, kr[col], acc[c]);
       }
@@ -306,13 +328,12 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_dkv_kernel(Problem pr, i
     __syncthreads();
     if (!key_ok) continue;
     const int i = qt + lane;
-    float dot = 0.f, dp = 0.f;
     const float* qrow = Qt + lane * DP;
     const float* krow = Kr + warp * D;
-    for (int d = 0; d < D; ++d) dot = fmaf(qrow[d], krow[d], dot);
+    const float dot = dot_rows(qrow, krow, D);
     const float* grow = Gt + lane * DVP;
     const float* vrow = Vr + warp * Dv;
-    for (int d = 0; d < Dv; ++d) dp = fmaf(grow[d], vrow[d], dp);
+    const float dp = dot_rows(grow, vrow, Dv);
     const bool keep = keep_entry(pr, b, h, i, j);
     const float p = keep ? exp2f(fmaf(dot, s2scale, bias2(pr, bias_dtype, b, h, i, j)) - Ls[lane]) : 0.f;
     const float ds = p * (dp - Ds[lane]);
@@ -323,6 +344,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_dkv_kernel(Problem pr, i
       const float* qr = Qt + ii * DP;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; ++c) {
+        if (32 * c >= D && 32 * c >= Dv) break;   // warp-uniform
         const int col = lane + 32 * c;
         if (col < Dv) dv[c] = fmaf(pi, gr[col], dv[c]);
         if (col < D) dk[c] = fmaf(dsi, qr[col], dk[c]);
