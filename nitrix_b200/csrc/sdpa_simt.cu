@@ -159,6 +159,211 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(Problem pr, int b
 }
 
 // ---------------------------------------------------------------------------
+// forward, register-tiled: the fp32 workhorse (head dims that are multiples of 4 / 32, up to 128)
+// ---------------------------------------------------------------------------
+// A CTA of 128 threads owns 64 query rows and streams 64-key tiles.  Thread (ty, tx) = (tid / 8, tid % 8) holds a
+// 4 x 8 micro-tile of the scores (rows ty + 16 i, keys tx + 8 j) and 4 rows x Dv / 8 columns of the output; both
+// products read their operands from shared memory as float4 (12 loads per 128 FMAs), the probabilities pass through
+// a shared tile.  Row maxima / sums need the 8 threads of a row: three xor-shuffles.  Same recurrence, same masking
+// and NaN semantics as simt_fwd_kernel; the summation order is fixed, so results are run-to-run identical.
+constexpr int kBN = 64, kTiledThreads = 128;
+
+template <typename T>
+__device__ __forceinline__ void stage_rows(float* dst, int ld, const T* src, int64_t row_stride, int row0, int n_rows,
+                                           int limit, int dim) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (int r = warp; r < n_rows; r += n_warps) {
+    const int row = row0 + r;
+    float* drow = dst + r * ld;
+    if (row < limit) {
+      const T* srow = src + row * row_stride;
+      for (int c = lane; c < dim; c += 32) drow[c] = to_f32<T>(srow[c]);
+    } else {
+      for (int c = lane; c < dim; c += 32) drow[c] = 0.f;
+    }
+  }
+}
+
+// fp32 rows whose start and stride are 16-byte aligned: one float4 per thread and iteration
+__device__ __forceinline__ void stage_rows_f4(float* dst, int ld, const float* src, int64_t row_stride, int row0,
+                                              int n_rows, int limit, int dim) {
+  const int per_row = dim >> 2;
+  for (int idx = threadIdx.x; idx < n_rows * per_row; idx += blockDim.x) {
+    const int r = idx / per_row, c4 = idx - r * per_row;
+    const int row = row0 + r;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < limit) v = __ldg(reinterpret_cast<const float4*>(src + row * row_stride) + c4);
+    *reinterpret_cast<float4*>(dst + r * ld + 4 * c4) = v;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void stage_rows_any(float* dst, int ld, const T* src, int64_t row_stride, int row0, int n_rows,
+                                               int limit, int dim) {
+  if constexpr (sizeof(T) == 4) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (row_stride & 3) == 0 && (dim & 3) == 0) {
+      stage_rows_f4(dst, ld, reinterpret_cast<const float*>(src), row_stride, row0, n_rows, limit, dim);
+      return;
+    }
+  }
+  stage_rows<T>(dst, ld, src, row_stride, row0, n_rows, limit, dim);
+}
+
+template <typename T, int kVChunks, int kR>   // kVChunks = Dv / 32; kR rows per thread: the CTA owns 16 kR query rows
+__global__ void __launch_bounds__(kTiledThreads) simt_fwd_tiled_kernel(Problem pr, int bias_dtype) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kBM = 16 * kR;
+  const int D = pr.D, Dv = pr.Dv;
+  const int LDQ = D + 4, LDV = Dv + 4, LDP = kBN + 4;
+  float* Qs = smem;                  // [kBM][LDQ]
+  float* Ks = Qs + kBM * LDQ;        // [kBN][LDQ]
+  float* Vs = Ks + kBN * LDQ;        // [kBN][LDV]
+  float* Ps = Vs + kBN * LDV;        // [kBM][LDP]
+  const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  const int row0 = blockIdx.x * kBM;
+  const T* qp = reinterpret_cast<const T*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
+  const T* kp = reinterpret_cast<const T*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
+  const T* vp = reinterpret_cast<const T*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
+  stage_rows_any<T>(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D);
+  // element offsets of this thread's four rows into bias and mask (the key term is added per element)
+  int64_t boff[kR], moff[kR];
+#pragma unroll
+  for (int i = 0; i < kR; ++i) {
+    const int rr = min(row0 + ty + 16 * i, pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+  }
+
+  float o[kR][kVChunks][4];
+  float m[kR], l[kR];
+#pragma unroll
+  for (int i = 0; i < kR; ++i) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < kVChunks; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[i][c][e] = 0.f;
+  }
+  const float s2scale = pr.scale * kLog2e;
+  // causal: no row of this CTA sees keys past its last row
+  const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
+
+  for (int kt = 0; kt < t_end; kt += kBN) {
+    __syncthreads();   // the previous tile's K, V and P are no longer read
+    stage_rows_any<T>(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D);
+    stage_rows_any<T>(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv);
+    __syncthreads();
+    // ---- scores: s[i][j] = q[ty + 16 i] . k[tx + 8 j] ----
+    float sc[kR][8];
+#pragma unroll
+    for (int i = 0; i < kR; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sc[i][j] = 0.f;
+    for (int d = 0; d < D; d += 4) {
+      float4 qv[kR], kv[8];
+#pragma unroll
+      for (int i = 0; i < kR; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * LDQ + d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 8 * j) * LDQ + d);
+      // one head-dim element at a time over the whole micro-tile: 32 independent FMAs back to back
+#pragma unroll
+      for (int i = 0; i < kR; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc[i][j] = fmaf(qv[i].x, kv[j].x, sc[i][j]);
+#pragma unroll
+      for (int i = 0; i < kR; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc[i][j] = fmaf(qv[i].y, kv[j].y, sc[i][j]);
+#pragma unroll
+      for (int i = 0; i < kR; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc[i][j] = fmaf(qv[i].z, kv[j].z, sc[i][j]);
+#pragma unroll
+      for (int i = 0; i < kR; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc[i][j] = fmaf(qv[i].w, kv[j].w, sc[i][j]);
+    }
+    // ---- logits in base 2, masks, online softmax per row ----
+#pragma unroll
+    for (int i = 0; i < kR; ++i) {
+      const int row = row0 + ty + 16 * i;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int key = kt + tx + 8 * j;
+        bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
+        if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
+        const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
+        sc[i][j] = keep ? fmaf(sc[i][j], s2scale, bias) : -INFINITY;
+        mx = fmaxf(mx, sc[i][j]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float m_new = fmaxf(m[i], mx);
+      const float m_ref = m_new == -INFINITY ? 0.f : m_new;   // nothing kept so far: every p is 0
+      const float alpha = exp2f(m[i] - m_ref);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float p = exp2f(sc[i][j] - m_ref);
+        sum += p;
+        Ps[(ty + 16 * i) * LDP + tx + 8 * j] = p;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      l[i] = l[i] * alpha + sum;
+      m[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < kVChunks; ++c)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][c][e] *= alpha;
+    }
+    __syncthreads();   // P is complete
+    // ---- out[ty + 16 i][4 tx + 32 c + e] += sum_j p[.][j] v[j][.] ----
+    for (int j4 = 0; j4 < kBN; j4 += 4) {
+      float4 pv[kR];
+#pragma unroll
+      for (int i = 0; i < kR; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * LDP + j4);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        float4 vv[kVChunks];
+#pragma unroll
+        for (int c = 0; c < kVChunks; ++c) vv[c] = *reinterpret_cast<const float4*>(Vs + (j4 + jj) * LDV + 4 * tx + 32 * c);
+#pragma unroll
+        for (int i = 0; i < kR; ++i) {
+          const float p = jj == 0 ? pv[i].x : (jj == 1 ? pv[i].y : (jj == 2 ? pv[i].z : pv[i].w));
+#pragma unroll
+          for (int c = 0; c < kVChunks; ++c) {
+            o[i][c][0] = fmaf(p, vv[c].x, o[i][c][0]);
+            o[i][c][1] = fmaf(p, vv[c].y, o[i][c][1]);
+            o[i][c][2] = fmaf(p, vv[c].z, o[i][c][2]);
+            o[i][c][3] = fmaf(p, vv[c].w, o[i][c][3]);
+          }
+        }
+      }
+    }
+  }
+  // ---- out = o / l (NaN for a row with no kept key, as the reference's softmax gives), lse ----
+#pragma unroll
+  for (int i = 0; i < kR; ++i) {
+    const int row = row0 + ty + 16 * i;
+    if (row >= pr.S) continue;
+    const float inv = 1.f / l[i];
+    T* op = reinterpret_cast<T*>(pr.out) + b * pr.os[0] + h * pr.os[1] + row * pr.os[2];
+#pragma unroll
+    for (int c = 0; c < kVChunks; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) op[4 * tx + 32 * c + e] = from_f32<T>(l[i] == 0.f ? NAN : o[i][c][e] * inv);
+    if (tx == 0) pr.lse[(int64_t(b) * pr.H + h) * pr.S + row] = m[i] + log2f(l[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // delta = rowsum(out * dout)   (reference attention.py:621-622, an XLA op there)
 // ---------------------------------------------------------------------------
 template <typename T>
@@ -396,8 +601,39 @@ int prepare(K kernel, size_t smem) {
   return NB200_OK;
 }
 
+template <typename T, int kVChunks, int kR>
+int fwd_tiled_r(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  constexpr int kBM = 16 * kR;
+  const size_t smem = sizeof(float) * (size_t(kBM + kBN) * (pr.D + 4) + size_t(kBN) * (pr.Dv + 4) + size_t(kBM) * (kBN + 4));
+  if (int rc = prepare(simt_fwd_tiled_kernel<T, kVChunks, kR>, smem)) return rc;
+  dim3 grid((pr.S + kBM - 1) / kBM, pr.bh_count);
+  simt_fwd_tiled_kernel<T, kVChunks, kR><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
+  count_launch();
+  return check_launch("simt_fwd_tiled_kernel");
+}
+
+template <typename T, int kVChunks>
+int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  // small problems: 32-row CTAs, so that every SM gets at least two of them
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t ctas64 = int64_t((pr.S + 63) / 64) * pr.bh_count;
+  if (ctas64 < 3 * int64_t(sms > 0 ? sms : 148)) return fwd_tiled_r<T, kVChunks, 2>(pr, bias_dtype, st);
+  return fwd_tiled_r<T, kVChunks, 4>(pr, bias_dtype, st);
+}
+
 template <typename T>
 int fwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  // the register-tiled kernel takes head dims it can read as float4 and split over 8 threads in float4 chunks
+  if (pr.D % 4 == 0 && pr.D <= 128 && pr.Dv % 32 == 0 && pr.Dv <= 128) {
+    switch (pr.Dv / 32) {
+      case 1: return fwd_tiled_t<T, 1>(pr, bias_dtype, st);
+      case 2: return fwd_tiled_t<T, 2>(pr, bias_dtype, st);
+      case 3: return fwd_tiled_t<T, 3>(pr, bias_dtype, st);
+      default: return fwd_tiled_t<T, 4>(pr, bias_dtype, st);
+    }
+  }
   const size_t smem = fwd_smem(pr);
   if (int rc = prepare(simt_fwd_kernel<T>, smem)) return rc;
   dim3 grid((pr.S + kWarps - 1) / kWarps, pr.bh_count);

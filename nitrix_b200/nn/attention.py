@@ -162,6 +162,16 @@ def _workspace(p, which: int, device) -> Optional[torch.Tensor]:
     return ws
 
 
+def _launch(fn, p, device, what: str) -> None:
+    """Call a library entry point on `device`'s current stream (the device is switched only when it is not current)."""
+    stream = torch.cuda.current_stream(device).cuda_stream
+    if device.index is None or device.index == torch.cuda.current_device():
+        _check(fn(C.byref(p), C.c_void_p(stream)), what)
+    else:
+        with torch.cuda.device(device):
+            _check(fn(C.byref(p), C.c_void_p(stream)), what)
+
+
 def _mask_bytes(mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if mask is None:
         return None
@@ -208,9 +218,7 @@ def sdpa_forward(q, k, v, bias=None, mask=None, *, scale: float, causal: bool = 
     mask_b = _mask_bytes(mask)
     _fill_common(p, q, k, v, out, lse, bias, mask_b, scale, causal, kernel, bh_range)
     ws = _workspace(p, _cabi.PASS_FWD, q.device)
-    with torch.cuda.device(q.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        _check(_cabi.lib().nb200_sdpa_fwd(C.byref(p), C.c_void_p(stream)), "nb200_sdpa_fwd")
+    _launch(_cabi.lib().nb200_sdpa_fwd, p, q.device, "nb200_sdpa_fwd")
     del ws  # same-stream reuse is ordered by the caching allocator
     return out, lse
 
@@ -242,9 +250,7 @@ def sdpa_backward(q, k, v, bias, mask, out, lse, dout, *, scale: float, causal: 
         p.dbias = dbias.data_ptr()
         p.dbias_stride[:] = list(dbias.stride())
     ws = _workspace(p, _cabi.PASS_BWD, q.device)
-    with torch.cuda.device(q.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        _check(_cabi.lib().nb200_sdpa_bwd(C.byref(p), C.c_void_p(stream)), "nb200_sdpa_bwd")
+    _launch(_cabi.lib().nb200_sdpa_bwd, p, q.device, "nb200_sdpa_bwd")
     del ws  # same-stream reuse is ordered by the caching allocator
     return dq, dk, dv, dbias
 
@@ -337,7 +343,12 @@ def scaled_dot_product_attention(
                 shapes=(tuple(q.shape), tuple(k.shape), tuple(v.shape)),
                 dtype=out_dtype,
             )
-    out4, lse4 = _SDPA.apply(q4, k4, v4, bias4, mask4, resolved_scale, bool(causal), kernel)
+    needs_grad = torch.is_grad_enabled() and (
+        q4.requires_grad or k4.requires_grad or v4.requires_grad or (bias4 is not None and bias4.requires_grad))
+    if needs_grad:
+        out4, lse4 = _SDPA.apply(q4, k4, v4, bias4, mask4, resolved_scale, bool(causal), kernel)
+    else:   # nothing to differentiate: skip the autograd bookkeeping
+        out4, lse4 = sdpa_forward(q4, k4, v4, bias4, mask4, scale=resolved_scale, causal=bool(causal), kernel=kernel)
     out = out4.reshape(*lead, h, s, dv)
     if return_lse:
         return out, lse4.reshape(*lead, h, s)
