@@ -95,14 +95,22 @@ def reproducible(enabled: bool = True) -> Iterator[None]:
         _reproducible.reset(token)
 
 
+_sm100_by_device: dict = {}
+
+
 def has_sm100_device() -> bool:
-    """True when the current CUDA device is a compute-capability 10.x part."""
+    """True when the current CUDA device is a compute-capability 10.x part (remembered per device index)."""
     try:
         import torch
 
         if not torch.cuda.is_available():
             return False
-        return torch.cuda.get_device_capability()[0] == 10
+        dev = torch.cuda.current_device()
+        known = _sm100_by_device.get(dev)
+        if known is None:
+            known = torch.cuda.get_device_capability(dev)[0] == 10
+            _sm100_by_device[dev] = known
+        return known
     except Exception:
         return False
 

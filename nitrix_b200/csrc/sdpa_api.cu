@@ -62,8 +62,14 @@ int check_launch(const char* what) {
 }
 
 int* device_status_word() {
+  // the symbol's address is fixed per device: looked up once and remembered
+  static int* known[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev >= 0 && known[dev]) return known[dev];
   int* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
+  if (dev >= 0) known[dev] = p;
   return p;
 }
 

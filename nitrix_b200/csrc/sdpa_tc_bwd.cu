@@ -843,17 +843,24 @@ template <int D, bool kBf16, bool kKeyMajor, bool kMerged = false>
 int launch_one(const CUtensorMap* maps, const BwdArgs& a, int n_tiles, int bh_count, cudaStream_t st) {
   auto kernel = sdpa_bwd_tc_kernel<D, kBf16, kKeyMajor, kMerged>;
   const int smem = BwdSmem<D, kMerged>::kTotal + 1024;
-  cudaFuncAttributes attr;
-  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
-  if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
-    // the register hand-over inside the kernel is balanced for exactly kLaunchRegs per thread at launch
-    set_error("sdpa_bwd_tc_kernel was built with %d registers per thread, expected %d", attr.numRegs, kLaunchRegs);
-    return NB200_ERR_LAUNCH;
-  }
-  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(sdpa_bwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
-    return NB200_ERR_LAUNCH;
+  // checked and configured once per device and kernel instance (setting it again would be harmless)
+  static bool ready[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev < 0 || !ready[dev]) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+    if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
+      // the register hand-over inside the kernel is balanced for exactly kLaunchRegs per thread at launch
+      set_error("sdpa_bwd_tc_kernel was built with %d registers per thread, expected %d", attr.numRegs, kLaunchRegs);
+      return NB200_ERR_LAUNCH;
+    }
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(sdpa_bwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
+      return NB200_ERR_LAUNCH;
+    }
+    if (dev >= 0) ready[dev] = true;
   }
   dim3 grid(n_tiles, bh_count);
   kernel<<<grid, kThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);

@@ -702,17 +702,24 @@ int launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   const int smem = L::kTotal + 1024 <= kLimit ? L::kTotal + 1024 : kLimit;
   static_assert(L::kTotal <= kLimit, "forward shared memory exceeds the per-CTA limit");
   a.smem_bytes = smem;
-  cudaFuncAttributes attr;
-  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
-  if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
-    // the register hand-over inside the kernel is balanced for exactly kLaunchRegs per thread at launch
-    set_error("sdpa_fwd_tc_kernel was built with %d registers per thread, expected %d", attr.numRegs, kLaunchRegs);
-    return NB200_ERR_LAUNCH;
-  }
-  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(sdpa_fwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
-    return NB200_ERR_LAUNCH;
+  // checked and configured once per device and kernel instance (setting it again would be harmless)
+  static bool ready[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev < 0 || !ready[dev]) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+    if (e != cudaSuccess || attr.numRegs != kLaunchRegs) {
+      // the register hand-over inside the kernel is balanced for exactly kLaunchRegs per thread at launch
+      set_error("sdpa_fwd_tc_kernel was built with %d registers per thread, expected %d", attr.numRegs, kLaunchRegs);
+      return NB200_ERR_LAUNCH;
+    }
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(sdpa_fwd_tc_kernel, %d): %s", smem, cudaGetErrorString(e));
+      return NB200_ERR_LAUNCH;
+    }
+    if (dev >= 0) ready[dev] = true;
   }
   const int n_items = a.n_qblocks * a.bh_count;
   const int sms = sm_count();

@@ -201,6 +201,26 @@ def planned_kernel(q, k, v, bias=None, mask=None, *, scale=1.0, causal=False, wh
     return chosen.value
 
 
+_plan_cache: dict = {}
+
+
+def _meta(x: Optional[torch.Tensor]):
+    # everything the planner looks at: dtype, extents, strides and the 16-byte alignment of the base address
+    return None if x is None else (x.dtype, tuple(x.shape), x.stride(), x.data_ptr() & 15)
+
+
+def _planned_kernel_cached(q, k, v, bias, mask, scale, causal) -> int:
+    """Forward plan for these operands, remembered by their layout (the planner is pure in it)."""
+    key = (_meta(q), _meta(k), _meta(v), _meta(bias), _meta(mask), scale > 0.0, bool(causal), q.device.index)
+    chosen = _plan_cache.get(key)
+    if chosen is None:
+        chosen = planned_kernel(q, k, v, bias, mask, scale=scale, causal=causal)
+        if len(_plan_cache) >= 512:
+            _plan_cache.clear()
+        _plan_cache[key] = chosen
+    return chosen
+
+
 def sdpa_forward(q, k, v, bias=None, mask=None, *, scale: float, causal: bool = False,
                  kernel: int = _cabi.KERNEL_AUTO, bh_range=None, out=None, lse=None):
     """Enqueue the forward on the current stream; 4-D operands.  Returns ``(out, lse)``.
@@ -317,7 +337,8 @@ def scaled_dot_product_attention(
 
     h, s, d = q.shape[-3:]
     t, dv = k.shape[-2], v.shape[-1]
-    lead = tuple(torch.broadcast_shapes(q.shape[:-3], k.shape[:-3], v.shape[:-3]))
+    lq, lk, lv = tuple(q.shape[:-3]), tuple(k.shape[:-3]), tuple(v.shape[:-3])
+    lead = lq if (lq == lk and lq == lv) else tuple(torch.broadcast_shapes(lq, lk, lv))
     if k.shape[-3] != h or v.shape[-3] != h:
         raise ValueError(f"scaled_dot_product_attention: head-count mismatch (q {h}, k {k.shape[-3]}, v {v.shape[-3]})")
     q4, k4, v4 = _to_bhxd(q, lead, h), _to_bhxd(k, lead, h), _to_bhxd(v, lead, h)
@@ -330,7 +351,7 @@ def scaled_dot_product_attention(
 
     kernel = _KERNELS[resolved]
     if resolved == "cuda-sm100":
-        chosen = planned_kernel(q4, k4, v4, bias4, mask4, scale=resolved_scale, causal=causal)
+        chosen = _planned_kernel_cached(q4, k4, v4, bias4, mask4, resolved_scale, causal)
         if chosen != _cabi.KERNEL_TCGEN05:
             fallback(
                 function="scaled_dot_product_attention",
