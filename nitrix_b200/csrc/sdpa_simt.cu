@@ -184,17 +184,22 @@ __device__ __forceinline__ void stage_rows(float* dst, int ld, const T* src, int
   }
 }
 
-// fp32 rows whose start and stride are 16-byte aligned: one float4 per thread and iteration
+// fp32 rows whose start and stride are 16-byte aligned: asynchronous 16-byte copies straight into shared memory, all
+// in flight at once (a load-then-store loop pays the global latency once per iteration); rows past `limit` are
+// zero-filled by a copy of source size 0.  The caller's __syncthreads() follows the wait below.
 __device__ __forceinline__ void stage_rows_f4(float* dst, int ld, const float* src, int64_t row_stride, int row0,
                                               int n_rows, int limit, int dim) {
   const int per_row = dim >> 2;
   for (int idx = threadIdx.x; idx < n_rows * per_row; idx += blockDim.x) {
     const int r = idx / per_row, c4 = idx - r * per_row;
     const int row = row0 + r;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row < limit) v = __ldg(reinterpret_cast<const float4*>(src + row * row_stride) + c4);
-    *reinterpret_cast<float4*>(dst + r * ld + 4 * c4) = v;
+    const bool in = row < limit;
+    const float* g = src + (in ? row : 0) * row_stride + 4 * c4;
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(dst + r * ld + 4 * c4));
+    const int bytes = in ? 16 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(g), "r"(bytes) : "memory");
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 template <typename T>
@@ -360,6 +365,180 @@ __global__ void __launch_bounds__(kTiledThreads) simt_fwd_tiled_kernel(Problem p
 #pragma unroll
       for (int e = 0; e < 4; ++e) op[4 * tx + 32 * c + e] = from_f32<T>(l[i] == 0.f ? NAN : o[i][c][e] * inv);
     if (tx == 0) pr.lse[(int64_t(b) * pr.H + h) * pr.S + row] = m[i] + log2f(l[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// forward for fp32 operands on the warp-level tensor-core path: 3 x TF32
+// ---------------------------------------------------------------------------
+// Every fp32 operand x is split as hi = tf32(x), lo = tf32(x - hi); a product a b is taken as
+// a_hi b_hi + a_hi b_lo + a_lo b_hi (three mma.sync.m16n8k8 TF32 instructions, fp32 accumulate), which keeps about
+// 21 bits -- inside the 1e-4 relative budget of the fp32 path.  A CTA of 4 warps owns 64 query rows, a warp 16 of
+// them against the whole 64-key tile: scores and output live in accumulator fragments (row g = lane / 4 and g + 8,
+// columns 2 t, 2 t + 1 with t = lane % 4), so row maxima / sums need the 4 lanes of a quad.  The probabilities go
+// from the score fragment straight into the A operand of P V: within an 8-key block operand column t stands for
+// key 2 t and column t + 4 for key 2 t + 1, and the V rows are fetched in that order.
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+  hi = to_tf32(x);
+  lo = to_tf32(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// c += a b with both operands split: the three leading terms
+__device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                           const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
+  mma_tf32(c, al, bh);
+  mma_tf32(c, ah, bl);
+  mma_tf32(c, ah, bh);
+}
+
+template <int kDvBlocks>   // Dv / 8
+__global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, int bias_dtype) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kBM = 64;
+  const int D = pr.D, Dv = pr.Dv;
+  const int LDQ = D + 4, LDV = Dv + 4;   // + 4: rows 16 bytes apart modulo 128, fragment loads hit distinct banks
+  float* Qs = smem;                  // [kBM][LDQ]
+  float* Ks = Qs + kBM * LDQ;        // [kBN][LDQ]
+  float* Vs = Ks + kBN * LDQ;        // [kBN][LDV]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  const int row0 = blockIdx.x * kBM;
+  const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
+  const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
+  const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
+  stage_rows_any<float>(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D);
+
+  // this thread's two rows: r[0] = 16 warp + g, r[1] = r[0] + 8
+  const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = min(row0 + lr[i], pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+  }
+  float o[kDvBlocks][4];
+#pragma unroll
+  for (int nb = 0; nb < kDvBlocks; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nb][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const float s2scale = pr.scale * kLog2e;
+  const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
+
+  for (int kt = 0; kt < t_end; kt += kBN) {
+    __syncthreads();   // the previous tile's K and V are no longer read
+    stage_rows_any<float>(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D);
+    stage_rows_any<float>(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv);
+    __syncthreads();
+    // ---- scores: 8 blocks of 8 keys ----
+    float sc[8][4];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[nb][e] = 0.f;
+    for (int kk = 0; kk < D; kk += 8) {
+      uint32_t ah[4], al[4];
+      split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
+      split_tf32(Qs[lr[1] * LDQ + kk + t], ah[1], al[1]);
+      split_tf32(Qs[lr[0] * LDQ + kk + t + 4], ah[2], al[2]);
+      split_tf32(Qs[lr[1] * LDQ + kk + t + 4], ah[3], al[3]);
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t], bh2[0], bl2[0]);
+        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t + 4], bh2[1], bl2[1]);
+        mma_3xtf32(sc[nb], ah, al, bh2, bl2);
+      }
+    }
+    // ---- logits in base 2, masks, online softmax (rows g and g + 8 of the warp's 16) ----
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
+        bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
+        if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
+        const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
+        sc[nb][e] = keep ? fmaf(sc[nb][e], s2scale, bias) : -INFINITY;
+        mx[i] = fmaxf(mx[i], sc[nb][e]);
+      }
+    float alpha[2], m_ref[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float m_new = fmaxf(m[i], mx[i]);
+      m_ref[i] = m_new == -INFINITY ? 0.f : m_new;   // nothing kept so far: every p is 0
+      alpha[i] = exp2f(m[i] - m_ref[i]);
+      m[i] = m_new;
+    }
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f(sc[nb][e] - m_ref[e >> 1]);
+        sc[nb][e] = p;
+        sum[e >> 1] += p;
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+      l[i] = l[i] * alpha[i] + sum[i];
+    }
+#pragma unroll
+    for (int nb = 0; nb < kDvBlocks; ++nb) {
+      o[nb][0] *= alpha[0];
+      o[nb][1] *= alpha[0];
+      o[nb][2] *= alpha[1];
+      o[nb][3] *= alpha[1];
+    }
+    // ---- out += P V: key block kb supplies operand columns (t -> key 2 t, t + 4 -> key 2 t + 1) ----
+#pragma unroll
+    for (int kb = 0; kb < 8; ++kb) {
+      uint32_t ah[4], al[4];
+      split_tf32(sc[kb][0], ah[0], al[0]);   // row g,     key 2 t
+      split_tf32(sc[kb][2], ah[1], al[1]);   // row g + 8, key 2 t
+      split_tf32(sc[kb][1], ah[2], al[2]);   // row g,     key 2 t + 1
+      split_tf32(sc[kb][3], ah[3], al[3]);   // row g + 8, key 2 t + 1
+      const float* v0 = Vs + (8 * kb + 2 * t) * LDV + g;
+      const float* v1 = v0 + LDV;
+#pragma unroll
+      for (int nb = 0; nb < kDvBlocks; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(v0[8 * nb], bh2[0], bl2[0]);
+        split_tf32(v1[8 * nb], bh2[1], bl2[1]);
+        mma_3xtf32(o[nb], ah, al, bh2, bl2);
+      }
+    }
+  }
+  // ---- out = o / l (NaN for a row with no kept key, as the reference's softmax gives), lse ----
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + lr[i];
+    if (row >= pr.S) continue;
+    const float inv = 1.f / l[i];
+    float* op = reinterpret_cast<float*>(pr.out) + b * pr.os[0] + h * pr.os[1] + row * pr.os[2];
+#pragma unroll
+    for (int nb = 0; nb < kDvBlocks; ++nb) {
+      op[8 * nb + 2 * t] = l[i] == 0.f ? NAN : o[nb][2 * i] * inv;
+      op[8 * nb + 2 * t + 1] = l[i] == 0.f ? NAN : o[nb][2 * i + 1] * inv;
+    }
+    if (t == 0) pr.lse[(int64_t(b) * pr.H + h) * pr.S + row] = m[i] + log2f(l[i]);
   }
 }
 
@@ -623,8 +802,29 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   return fwd_tiled_r<T, kVChunks, 4>(pr, bias_dtype, st);
 }
 
+template <int kDvBlocks>
+int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  const size_t smem = sizeof(float) * (size_t(64 + kBN) * (pr.D + 4) + size_t(kBN) * (pr.Dv + 4));
+  if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
+  dim3 grid((pr.S + 63) / 64, pr.bh_count);
+  fwd_tf32x3_kernel<kDvBlocks><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
+  count_launch();
+  return check_launch("fwd_tf32x3_kernel");
+}
+
 template <typename T>
 int fwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  if constexpr (sizeof(T) == 4) {
+    // fp32 operands with head dims in whole 8-column MMA blocks: 3 x TF32 on the warp-level tensor-core path
+    if (pr.D % 8 == 0 && pr.D <= 128 && pr.Dv % 8 == 0 && pr.Dv <= 128) {
+      switch (pr.Dv / 8) {
+        case 4: return fwd_tf32x3_t<4>(pr, bias_dtype, st);
+        case 8: return fwd_tf32x3_t<8>(pr, bias_dtype, st);
+        case 16: return fwd_tf32x3_t<16>(pr, bias_dtype, st);
+        default: break;
+      }
+    }
+  }
   // the register-tiled kernel takes head dims it can read as float4 and split over 8 threads in float4 chunks
   if (pr.D % 4 == 0 && pr.D <= 128 && pr.Dv % 32 == 0 && pr.Dv <= 128) {
     switch (pr.Dv / 32) {
