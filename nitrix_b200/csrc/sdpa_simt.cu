@@ -199,15 +199,18 @@ __device__ __forceinline__ void stage_rows_f4(float* dst, int ld, const float* s
     const int bytes = in ? 16 : 0;
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(g), "r"(bytes) : "memory");
   }
-  asm volatile("cp.async.wait_all;" ::: "memory");
 }
+__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// `wait = false` leaves the asynchronous copies in flight (stage_wait() completes them); the synchronous fall-back
+// path has always finished on return.
 template <typename T>
 __device__ __forceinline__ void stage_rows_any(float* dst, int ld, const T* src, int64_t row_stride, int row0, int n_rows,
-                                               int limit, int dim) {
+                                               int limit, int dim, bool wait = true) {
   if constexpr (sizeof(T) == 4) {
     if ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (row_stride & 3) == 0 && (dim & 3) == 0) {
       stage_rows_f4(dst, ld, reinterpret_cast<const float*>(src), row_stride, row0, n_rows, limit, dim);
+      if (wait) stage_wait();
       return;
     }
   }
@@ -408,8 +411,8 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   const int D = pr.D, Dv = pr.Dv;
   const int LDQ = D + 4, LDV = Dv + 4;   // + 4: rows 16 bytes apart modulo 128, fragment loads hit distinct banks
   float* Qs = smem;                  // [kBM][LDQ]
-  float* Ks = Qs + kBM * LDQ;        // [kBN][LDQ]
-  float* Vs = Ks + kBN * LDQ;        // [kBN][LDV]
+  float* Kbuf = Qs + kBM * LDQ;      // 2 x [kBN][LDQ]
+  float* Vbuf = Kbuf + 2 * kBN * LDQ;  // 2 x [kBN][LDV]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
   const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
   const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
-  stage_rows_any<float>(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D);
+  stage_rows_any<float>(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D, false);
 
   // this thread's two rows: r[0] = 16 warp + g, r[1] = r[0] + 8
   const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
@@ -437,11 +440,21 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   const float s2scale = pr.scale * kLog2e;
   const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
 
-  for (int kt = 0; kt < t_end; kt += kBN) {
-    __syncthreads();   // the previous tile's K and V are no longer read
-    stage_rows_any<float>(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D);
-    stage_rows_any<float>(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv);
-    __syncthreads();
+  // K / V tiles are double-buffered: tile i + 1 is copied while tile i is computed, one barrier per tile
+  if (t_end > 0) {
+    stage_rows_any<float>(Kbuf, LDQ, kp, pr.ks[2], 0, kBN, pr.T, D, false);
+    stage_rows_any<float>(Vbuf, LDV, vp, pr.vs[2], 0, kBN, pr.T, Dv, false);
+  }
+  int it = 0;
+  for (int kt = 0; kt < t_end; kt += kBN, ++it) {
+    stage_wait();
+    __syncthreads();   // tile `it` (and, the first time, Q) has landed; nobody reads the other buffer any more
+    const float* Ks = Kbuf + (it & 1) * kBN * LDQ;
+    const float* Vs = Vbuf + (it & 1) * kBN * LDV;
+    if (kt + kBN < t_end) {
+      stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
+      stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
+    }
     // ---- scores: 8 blocks of 8 keys ----
     float sc[8][4];
 #pragma unroll
@@ -804,7 +817,7 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
 
 template <int kDvBlocks>
 int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
-  const size_t smem = sizeof(float) * (size_t(64 + kBN) * (pr.D + 4) + size_t(kBN) * (pr.Dv + 4));
+  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4));
   if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_kernel<kDvBlocks><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
