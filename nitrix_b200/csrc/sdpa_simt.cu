@@ -1,20 +1,19 @@
-// CUDA-core (SIMT) attention kernels: fp32 arithmetic on any dtype, any shape.
+// Attention kernels outside the tcgen05 family: fp32 arithmetic on any dtype, any shape.
 //
-// These cover what the tensor-core kernels decline (fp32 inputs, head dims
-// other than 64/128, ragged S/T, d_v != d, arbitrary bias/mask strides), so the
-// library never needs a host fallback.  They follow the same flash recurrence
-// as the reference's fused kernels (reference src/nitrix/_kernels/cuda/
-// attention.py:85-156 forward, :272-387 backward) but in true fp32 FMA
-// arithmetic: base-2 online softmax carry (m, l), lse = m + log2(l), recompute
-// of p = exp2(s - lse) in the backward, one kernel for dq(+dbias) and one for
-// dk, dv.  A fully masked query row yields NaN like the reference's jnp path
-// (reference src/nitrix/nn/attention/_reference.py:133-135).
+// These cover what the tcgen05 kernels decline (fp32 inputs, head dims other than 64/128, lengths that are not
+// multiples of 8, d_v != d, arbitrary bias/mask strides), so the library never needs a host fallback.  They follow the
+// same flash recurrence as the reference's fused kernels (reference src/nitrix/_kernels/cuda/attention.py:85-156
+// forward, :272-387 backward): base-2 online softmax carry (m, l), lse = m + log2(l), recompute of
+// p = exp2(s - lse) in the backward, one kernel for dq(+dbias) and one for dk, dv.  A fully masked query row yields
+// NaN like the reference's jnp path (reference src/nitrix/nn/attention/_reference.py:133-135).
 //
-// Work decomposition: one warp owns one query row (forward, dq) or one key row
-// (dk/dv); the 32 lanes of a warp take 32 consecutive rows of the opposite
-// operand, which a CTA stages in shared memory as fp32 and shares among its
-// warps.  Row sums use warp shuffles; nothing is atomically accumulated except
-// the optional broadcast-bias gradient.
+// Forward, by operand type and head dims:
+//   fwd_tf32x3_kernel      fp32 operands, head dims multiples of 8 (<= 128): 3 x TF32 on mma.sync.m16n8k8
+//   simt_fwd_tiled_kernel  head dims multiples of 4 / 32 (<= 128): register-tiled FMA, float4 shared-memory operands
+//   simt_fwd_kernel        everything else: one warp per query row, 32 lanes over 32 keys
+// Backward: one warp owns one query row (dq) or one key row (dk/dv); the 32 lanes take 32 consecutive rows of the
+// opposite operand, staged in shared memory as fp32.  Row sums use warp shuffles; nothing is atomically accumulated
+// except the optional broadcast-bias gradient, and every sum runs in a fixed order.
 #include <math.h>
 
 #include "sdpa_common.cuh"
