@@ -11,7 +11,9 @@
 //   fwd_tf32x3_kernel      fp32 operands, head dims multiples of 8 (<= 128): 3 x TF32 on mma.sync.m16n8k8
 //   simt_fwd_tiled_kernel  head dims multiples of 4 / 32 (<= 128): register-tiled FMA, float4 shared-memory operands
 //   simt_fwd_kernel        everything else: one warp per query row, 32 lanes over 32 keys
-// Backward: one warp owns one query row (dq) or one key row (dk/dv); the 32 lanes take 32 consecutive rows of the
+// Backward, fp32 operands on grids of >= 96 CTAs: bwd_dq_tf32x3_kernel (D in {32, 64, 128}) and
+// bwd_dkv_tf32x3_kernel (D == Dv in {32, 64}), the same 3 x TF32 tiling.  Otherwise:
+// one warp owns one query row (dq) or one key row (dk/dv); the 32 lanes take 32 consecutive rows of the
 // opposite operand, staged in shared memory as fp32.  Row sums use warp shuffles; nothing is atomically accumulated
 // except the optional broadcast-bias gradient, and every sum runs in a fixed order.
 #include <math.h>
@@ -680,6 +682,309 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_dq_kernel(Problem pr, in
 }
 
 // ---------------------------------------------------------------------------
+// backward, query side, fp32 operands: 3 x TF32 on mma.sync (same tiling as fwd_tf32x3_kernel)
+// ---------------------------------------------------------------------------
+// A warp owns 16 query rows against a 64-key tile: S = Q K^T and dP = dO V^T in accumulator fragments,
+// p = exp2(s - lse), ds = p (dP - delta) in place, then dQ += ds K with the ds fragment as the A operand (key 2 t /
+// 2 t + 1 of a block stand in operand columns t / t + 4; the K rows are fetched in that order).
+template <int kDBlocks>   // D / 8
+__global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr, int bias_dtype) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kBM = 64;
+  const int D = pr.D, Dv = pr.Dv;
+  const int LDQ = D + 4, LDV = Dv + 4;
+  float* Qs = smem;                    // [kBM][LDQ]
+  float* Gs = Qs + kBM * LDQ;          // [kBM][LDV]   dout rows
+  float* Kbuf = Gs + kBM * LDV;        // 2 x [kBN][LDQ]
+  float* Vbuf = Kbuf + 2 * kBN * LDQ;  // 2 x [kBN][LDV]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  const int row0 = blockIdx.x * kBM;
+  const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
+  const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
+  const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
+  const float* gp = reinterpret_cast<const float*>(pr.dout) + b * pr.dos[0] + h * pr.dos[1];
+  stage_rows_any<float>(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D, false);
+  stage_rows_any<float>(Gs, LDV, gp, pr.dos[2], row0, kBM, pr.S, Dv, false);
+
+  const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2], dboff[2];
+  float lse[2], delta[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = min(row0 + lr[i], pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+    dboff[i] = b * pr.dbs[0] + h * pr.dbs[1] + rr * pr.dbs[2];
+    const int64_t ridx = (int64_t(b) * pr.H + h) * pr.S + rr;
+    lse[i] = pr.lse[ridx];
+    delta[i] = pr.delta[ridx];
+  }
+  float dq[kDBlocks][4];
+#pragma unroll
+  for (int nb = 0; nb < kDBlocks; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dq[nb][e] = 0.f;
+  const float s2scale = pr.scale * kLog2e;
+  const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
+  const bool want_db = pr.dbias != nullptr || pr.dbias_accum != nullptr;
+
+  if (t_end > 0) {
+    stage_rows_any<float>(Kbuf, LDQ, kp, pr.ks[2], 0, kBN, pr.T, D, false);
+    stage_rows_any<float>(Vbuf, LDV, vp, pr.vs[2], 0, kBN, pr.T, Dv, false);
+  }
+  int it = 0;
+  for (int kt = 0; kt < t_end; kt += kBN, ++it) {
+    stage_wait();
+    __syncthreads();
+    const float* Ks = Kbuf + (it & 1) * kBN * LDQ;
+    const float* Vs = Vbuf + (it & 1) * kBN * LDV;
+    if (kt + kBN < t_end) {
+      stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
+      stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
+    }
+    float sc[8][4], dp[8][4];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[nb][e] = dp[nb][e] = 0.f;
+    for (int kk = 0; kk < D; kk += 8) {
+      uint32_t ah[4], al[4];
+      split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
+      split_tf32(Qs[lr[1] * LDQ + kk + t], ah[1], al[1]);
+      split_tf32(Qs[lr[0] * LDQ + kk + t + 4], ah[2], al[2]);
+      split_tf32(Qs[lr[1] * LDQ + kk + t + 4], ah[3], al[3]);
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t], bh2[0], bl2[0]);
+        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t + 4], bh2[1], bl2[1]);
+        mma_3xtf32(sc[nb], ah, al, bh2, bl2);
+      }
+    }
+    for (int kk = 0; kk < Dv; kk += 8) {
+      uint32_t ah[4], al[4];
+      split_tf32(Gs[lr[0] * LDV + kk + t], ah[0], al[0]);
+      split_tf32(Gs[lr[1] * LDV + kk + t], ah[1], al[1]);
+      split_tf32(Gs[lr[0] * LDV + kk + t + 4], ah[2], al[2]);
+      split_tf32(Gs[lr[1] * LDV + kk + t + 4], ah[3], al[3]);
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(Vs[(8 * nb + g) * LDV + kk + t], bh2[0], bl2[0]);
+        split_tf32(Vs[(8 * nb + g) * LDV + kk + t + 4], bh2[1], bl2[1]);
+        mma_3xtf32(dp[nb], ah, al, bh2, bl2);
+      }
+    }
+    // ---- p = exp2(logit2 - lse), ds = p (dP - delta); ds replaces the score fragment ----
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
+        bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
+        if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
+        const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
+        const float p = keep ? exp2f(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
+        const float ds = p * (dp[nb][e] - delta[i]);
+        sc[nb][e] = ds;
+        if (want_db && key < pr.T && row < pr.S) {
+          const int64_t off = dboff[i] + key * pr.dbs[3];
+          if (pr.dbias_accum) {
+            if (ds != 0.f) atomicAdd(pr.dbias_accum + off, ds);
+          } else {
+            store_from_f32(pr.dbias, off, bias_dtype, ds);
+          }
+        }
+      }
+    // ---- dQ += ds K ----
+#pragma unroll
+    for (int kb = 0; kb < 8; ++kb) {
+      uint32_t ah[4], al[4];
+      split_tf32(sc[kb][0], ah[0], al[0]);   // row g,     key 2 t
+      split_tf32(sc[kb][2], ah[1], al[1]);   // row g + 8, key 2 t
+      split_tf32(sc[kb][1], ah[2], al[2]);   // row g,     key 2 t + 1
+      split_tf32(sc[kb][3], ah[3], al[3]);   // row g + 8, key 2 t + 1
+      const float* k0 = Ks + (8 * kb + 2 * t) * LDQ + g;
+      const float* k1 = k0 + LDQ;
+#pragma unroll
+      for (int nb = 0; nb < kDBlocks; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(k0[8 * nb], bh2[0], bl2[0]);
+        split_tf32(k1[8 * nb], bh2[1], bl2[1]);
+        mma_3xtf32(dq[nb], ah, al, bh2, bl2);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + lr[i];
+    if (row >= pr.S) continue;
+    // causal rows never visit keys past the CTA's last row, yet a dense dbias is written everywhere: exact zeros
+    if (want_db && !pr.dbias_accum && t_end < pr.T) {
+      for (int key = ((t_end + kBN - 1) / kBN) * kBN + t; key < pr.T; key += 4)
+        store_from_f32(pr.dbias, dboff[i] + key * pr.dbs[3], bias_dtype, 0.f);
+    }
+    float* dqp = reinterpret_cast<float*>(pr.dq) + b * pr.dqs[0] + h * pr.dqs[1] + row * pr.dqs[2];
+#pragma unroll
+    for (int nb = 0; nb < kDBlocks; ++nb) {
+      dqp[8 * nb + 2 * t] = dq[nb][2 * i] * pr.scale;
+      dqp[8 * nb + 2 * t + 1] = dq[nb][2 * i + 1] * pr.scale;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// backward, key side, fp32 operands: 3 x TF32 on mma.sync
+// ---------------------------------------------------------------------------
+// A warp owns 16 keys against a 64-query tile: S^T = K Q^T and dP^T = V dO^T in accumulator fragments (row = key,
+// column = query), p and ds in place, then dV += p^T-fragment dO and dK += ds-fragment Q with the fragments as A
+// operands (query 2 t / 2 t + 1 of a block stand in operand columns t / t + 4).  lse and delta of the tile's
+// queries sit in shared memory.  Head dims D == Dv in {32, 64} (two accumulator sets must fit in registers).
+template <int kBlocks>   // D / 8 == Dv / 8
+__global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem pr, int bias_dtype) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kBK = 64;
+  const int D = pr.D, LD = D + 4;
+  float* Ks = smem;                    // [kBK][LD]  owner keys
+  float* Vs = Ks + kBK * LD;           // [kBK][LD]
+  float* Qbuf = Vs + kBK * LD;         // 2 x [kBN][LD]
+  float* Gbuf = Qbuf + 2 * kBN * LD;   // 2 x [kBN][LD]  dout rows
+  float* Lbuf = Gbuf + 2 * kBN * LD;   // 2 x [kBN]  lse
+  float* Dbuf = Lbuf + 2 * kBN;        // 2 x [kBN]  delta
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  const int key0 = blockIdx.x * kBK;
+  const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
+  const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
+  const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
+  const float* gp = reinterpret_cast<const float*>(pr.dout) + b * pr.dos[0] + h * pr.dos[1];
+  const int64_t rbase = (int64_t(b) * pr.H + h) * pr.S;
+  stage_rows_any<float>(Ks, LD, kp, pr.ks[2], key0, kBK, pr.T, D, false);
+  stage_rows_any<float>(Vs, LD, vp, pr.vs[2], key0, kBK, pr.T, D, false);
+
+  const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int kk = min(key0 + lr[i], pr.T - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + kk * pr.bs[3] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + kk * pr.ms[3] : 0;
+  }
+  float dk[kBlocks][4], dv[kBlocks][4];
+#pragma unroll
+  for (int nb = 0; nb < kBlocks; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dk[nb][e] = dv[nb][e] = 0.f;
+  const float s2scale = pr.scale * kLog2e;
+  // causal: queries before this CTA's first key see none of its keys
+  const int s_begin = pr.causal ? min(pr.S, key0) : 0;
+
+  auto prefetch = [&](int qt, int buf) {
+    stage_rows_any<float>(Qbuf + buf * kBN * LD, LD, qp, pr.qs[2], qt, kBN, pr.S, D, false);
+    stage_rows_any<float>(Gbuf + buf * kBN * LD, LD, gp, pr.dos[2], qt, kBN, pr.S, D, false);
+    if (threadIdx.x < kBN) {
+      const int q = qt + threadIdx.x;
+      Lbuf[buf * kBN + threadIdx.x] = q < pr.S ? pr.lse[rbase + q] : 0.f;
+      Dbuf[buf * kBN + threadIdx.x] = q < pr.S ? pr.delta[rbase + q] : 0.f;
+    }
+  };
+  if (s_begin < pr.S) prefetch(s_begin, 0);
+  int it = 0;
+  for (int qt = s_begin; qt < pr.S; qt += kBN, ++it) {
+    stage_wait();
+    __syncthreads();   // tile `it` (and, the first time, K and V) has landed; nobody reads the other buffers any more
+    const float* Qt = Qbuf + (it & 1) * kBN * LD;
+    const float* Gt = Gbuf + (it & 1) * kBN * LD;
+    const float* Lt = Lbuf + (it & 1) * kBN;
+    const float* Dt = Dbuf + (it & 1) * kBN;
+    if (qt + kBN < pr.S) prefetch(qt + kBN, (it + 1) & 1);
+    float sc[8][4], dp[8][4];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[nb][e] = dp[nb][e] = 0.f;
+    for (int kk = 0; kk < D; kk += 8) {
+      uint32_t ah[4], al[4], ch[4], cl[4];
+      split_tf32(Ks[lr[0] * LD + kk + t], ah[0], al[0]);
+      split_tf32(Ks[lr[1] * LD + kk + t], ah[1], al[1]);
+      split_tf32(Ks[lr[0] * LD + kk + t + 4], ah[2], al[2]);
+      split_tf32(Ks[lr[1] * LD + kk + t + 4], ah[3], al[3]);
+      split_tf32(Vs[lr[0] * LD + kk + t], ch[0], cl[0]);
+      split_tf32(Vs[lr[1] * LD + kk + t], ch[1], cl[1]);
+      split_tf32(Vs[lr[0] * LD + kk + t + 4], ch[2], cl[2]);
+      split_tf32(Vs[lr[1] * LD + kk + t + 4], ch[3], cl[3]);
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(Qt[(8 * nb + g) * LD + kk + t], bh2[0], bl2[0]);
+        split_tf32(Qt[(8 * nb + g) * LD + kk + t + 4], bh2[1], bl2[1]);
+        mma_3xtf32(sc[nb], ah, al, bh2, bl2);
+        split_tf32(Gt[(8 * nb + g) * LD + kk + t], bh2[0], bl2[0]);
+        split_tf32(Gt[(8 * nb + g) * LD + kk + t + 4], bh2[1], bl2[1]);
+        mma_3xtf32(dp[nb], ch, cl, bh2, bl2);
+      }
+    }
+    // ---- p (kept in sc) and ds (kept in dp); row = key, column = query ----
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1, ql = 8 * nb + 2 * t + (e & 1);
+        const int key = key0 + lr[i], q = qt + ql;
+        bool keep = key < pr.T && q < pr.S && !(pr.causal && key > q);
+        if (keep && pr.mask) keep = pr.mask[moff[i] + q * pr.ms[2]] != 0;
+        const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + q * pr.bs[2], bias_dtype) : 0.f;
+        const float p = keep ? exp2f(fmaf(sc[nb][e], s2scale, bias) - Lt[ql]) : 0.f;
+        sc[nb][e] = p;
+        dp[nb][e] = p * (dp[nb][e] - Dt[ql]);
+      }
+    // ---- dV += p dO, dK += ds Q (contraction over the tile's queries) ----
+#pragma unroll
+    for (int qb = 0; qb < 8; ++qb) {
+      uint32_t ph[4], pl[4], sh[4], sl[4];
+      split_tf32(sc[qb][0], ph[0], pl[0]);
+      split_tf32(sc[qb][2], ph[1], pl[1]);
+      split_tf32(sc[qb][1], ph[2], pl[2]);
+      split_tf32(sc[qb][3], ph[3], pl[3]);
+      split_tf32(dp[qb][0], sh[0], sl[0]);
+      split_tf32(dp[qb][2], sh[1], sl[1]);
+      split_tf32(dp[qb][1], sh[2], sl[2]);
+      split_tf32(dp[qb][3], sh[3], sl[3]);
+      const float* g0 = Gt + (8 * qb + 2 * t) * LD + g;
+      const float* q0 = Qt + (8 * qb + 2 * t) * LD + g;
+#pragma unroll
+      for (int nb = 0; nb < kBlocks; ++nb) {
+        uint32_t bh2[2], bl2[2];
+        split_tf32(g0[8 * nb], bh2[0], bl2[0]);
+        split_tf32(g0[LD + 8 * nb], bh2[1], bl2[1]);
+        mma_3xtf32(dv[nb], ph, pl, bh2, bl2);
+        split_tf32(q0[8 * nb], bh2[0], bl2[0]);
+        split_tf32(q0[LD + 8 * nb], bh2[1], bl2[1]);
+        mma_3xtf32(dk[nb], sh, sl, bh2, bl2);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int key = key0 + lr[i];
+    if (key >= pr.T) continue;
+    float* dkp = reinterpret_cast<float*>(pr.dk) + b * pr.dks[0] + h * pr.dks[1] + key * pr.dks[2];
+    float* dvp = reinterpret_cast<float*>(pr.dv) + b * pr.dvs[0] + h * pr.dvs[1] + key * pr.dvs[2];
+#pragma unroll
+    for (int nb = 0; nb < kBlocks; ++nb) {
+      dkp[8 * nb + 2 * t] = dk[nb][2 * i] * pr.scale;
+      dkp[8 * nb + 2 * t + 1] = dk[nb][2 * i + 1] * pr.scale;
+      dvp[8 * nb + 2 * t] = dv[nb][2 * i];
+      dvp[8 * nb + 2 * t + 1] = dv[nb][2 * i + 1];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // backward, key side: dk, dv.  One warp per key row, lanes over queries.
 // ---------------------------------------------------------------------------
 template <typename T>
@@ -859,11 +1164,48 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   const size_t smem = bwd_smem(pr);
   if (int rc = prepare(simt_bwd_dq_kernel<T>, smem)) return rc;
   if (int rc = prepare(simt_bwd_dkv_kernel<T>, smem)) return rc;
-  if (pr.S > 0) {
+  bool dq_done = false;
+  if constexpr (sizeof(T) == 4) {
+    // fp32 operands with head dims in whole 8-column MMA blocks: 3 x TF32 on the warp-level tensor-core path
+    // (a grid of fewer than ~100 CTAs of 64 rows leaves most SMs idle: tiny problems keep the 8-row CUDA-core CTAs)
+    if (pr.S > 0 && pr.Dv % 8 == 0 && pr.Dv <= 128 && (pr.D == 32 || pr.D == 64 || pr.D == 128) &&
+        int64_t((pr.S + 63) / 64) * pr.bh_count >= 96) {
+      const size_t sm = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(64 + 2 * kBN) * (pr.Dv + 4));
+      dim3 gq((pr.S + 63) / 64, pr.bh_count);
+      int rc = NB200_OK;
+      if (pr.D == 32) {
+        if ((rc = prepare(bwd_dq_tf32x3_kernel<4>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<4><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      } else if (pr.D == 64) {
+        if ((rc = prepare(bwd_dq_tf32x3_kernel<8>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<8><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      } else {
+        if ((rc = prepare(bwd_dq_tf32x3_kernel<16>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<16><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      }
+      if (rc) return rc;
+      count_launch();
+      if (int rc2 = check_launch("bwd_dq_tf32x3_kernel")) return rc2;
+      dq_done = true;
+    }
+  }
+  if (pr.S > 0 && !dq_done) {
     dim3 gq((pr.S + kWarps - 1) / kWarps, pr.bh_count);
     simt_bwd_dq_kernel<T><<<gq, kWarps * 32, smem, st>>>(pr, bias_dtype);
     count_launch();
     if (int rc = check_launch("simt_bwd_dq_kernel")) return rc;
+  }
+  if constexpr (sizeof(T) == 4) {
+    if (pr.T > 0 && pr.D == pr.Dv && (pr.D == 32 || pr.D == 64) && int64_t((pr.T + 63) / 64) * pr.bh_count >= 96) {
+      const size_t sm = sizeof(float) * (size_t(6 * 64) * (pr.D + 4) + 4 * kBN);
+      dim3 gk((pr.T + 63) / 64, pr.bh_count);
+      int rc = NB200_OK;
+      if (pr.D == 32) {
+        if ((rc = prepare(bwd_dkv_tf32x3_kernel<4>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<4><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      } else {
+        if ((rc = prepare(bwd_dkv_tf32x3_kernel<8>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<8><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      }
+      if (rc) return rc;
+      count_launch();
+      return check_launch("bwd_dkv_tf32x3_kernel");
+    }
   }
   if (pr.T > 0) {
     dim3 gk((pr.T + kWarps - 1) / kWarps, pr.bh_count);

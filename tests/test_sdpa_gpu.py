@@ -119,6 +119,17 @@ def test_simt_fp32_parity(name):
     check(got, ref, torch.float32)
 
 
+@pytest.mark.parametrize("d", [32, 64, 128])
+@pytest.mark.parametrize("name", ["dense", "bias_causal", "full_bias_mask", "key_padding", "key_bias", "cross"])
+def test_fp32_3xtf32_parity(name, d):
+    """fp32 operands at a size where the 3 x TF32 mma.sync kernels run forward and backward (grids of >= 96 CTAs of
+    64 rows; lengths that do not fill the last tile): the fp32 budget of 1e-4 relative holds for out and all gradients."""
+    shape = dict(b=4, h=6, s=344, t=200 if name == "cross" else 344, d=d)
+    q, k, v, kw = _cases.kernel_case(name, **shape)
+    got, ref = run_both(q, k, v, kw, torch.float32, "auto")
+    check(got, ref, torch.float32)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", ["bias_mask", "causal", "key_padding"])
 def test_simt_low_precision_parity(name, dtype):
