@@ -11,8 +11,8 @@
 //   fwd_tf32x3_kernel      fp32 operands, head dims multiples of 8 (<= 128): 3 x TF32 on mma.sync.m16n8k8
 //   simt_fwd_tiled_kernel  head dims multiples of 4 / 32 (<= 128): register-tiled FMA, float4 shared-memory operands
 //   simt_fwd_kernel        everything else: one warp per query row, 32 lanes over 32 keys
-// Backward, fp32 operands on grids of >= 96 CTAs: bwd_dq_tf32x3_kernel (D in {32, 64, 128}) and
-// bwd_dkv_tf32x3_kernel (D == Dv in {32, 64}), the same 3 x TF32 tiling.  Otherwise:
+// Backward, fp32 operands on grids of >= 96 CTAs: bwd_dq_tf32x3_kernel and bwd_dkv_tf32x3_kernel
+// (D == Dv in {32, 64, 128}), the same 3 x TF32 tiling.  Otherwise:
 // one warp owns one query row (dq) or one key row (dk/dv); the 32 lanes take 32 consecutive rows of the
 // opposite operand, staged in shared memory as fp32.  Row sums use warp shuffles; nothing is atomically accumulated
 // except the optional broadcast-bias gradient, and every sum runs in a fixed order.
@@ -842,7 +842,8 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr
 // A warp owns 16 keys against a 64-query tile: S^T = K Q^T and dP^T = V dO^T in accumulator fragments (row = key,
 // column = query), p and ds in place, then dV += p^T-fragment dO and dK += ds-fragment Q with the fragments as A
 // operands (query 2 t / 2 t + 1 of a block stand in operand columns t / t + 4).  lse and delta of the tile's
-// queries sit in shared memory.  Head dims D == Dv in {32, 64} (two accumulator sets must fit in registers).
+// queries sit in shared memory.  Head dims D == Dv in {32, 64, 128} (at 128 the two accumulator sets fill the
+// register file: 255 registers and a few spilled words).
 template <int kBlocks>   // D / 8 == Dv / 8
 __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
@@ -1193,14 +1194,17 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
     if (int rc = check_launch("simt_bwd_dq_kernel")) return rc;
   }
   if constexpr (sizeof(T) == 4) {
-    if (pr.T > 0 && pr.D == pr.Dv && (pr.D == 32 || pr.D == 64) && int64_t((pr.T + 63) / 64) * pr.bh_count >= 96) {
+    if (pr.T > 0 && pr.D == pr.Dv && (pr.D == 32 || pr.D == 64 || pr.D == 128) &&
+        int64_t((pr.T + 63) / 64) * pr.bh_count >= 96) {
       const size_t sm = sizeof(float) * (size_t(6 * 64) * (pr.D + 4) + 4 * kBN);
       dim3 gk((pr.T + 63) / 64, pr.bh_count);
       int rc = NB200_OK;
       if (pr.D == 32) {
         if ((rc = prepare(bwd_dkv_tf32x3_kernel<4>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<4><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
-      } else {
+      } else if (pr.D == 64) {
         if ((rc = prepare(bwd_dkv_tf32x3_kernel<8>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<8><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      } else {
+        if ((rc = prepare(bwd_dkv_tf32x3_kernel<16>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<16><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
       }
       if (rc) return rc;
       count_launch();
