@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define NB200_ABI_VERSION 1
+#define NB200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define NB200_API __attribute__((visibility("default")))
@@ -61,7 +61,12 @@ enum nb200_status {
 enum nb200_kernel {
   NB200_KERNEL_AUTO = 0,
   NB200_KERNEL_SIMT = 1,   /* fp32-arithmetic CUDA-core kernels: any shape / dtype  */
-  NB200_KERNEL_TCGEN05 = 2 /* TMA + tcgen05 (TMEM accumulators): bf16 / fp16 tiles  */
+  NB200_KERNEL_TCGEN05 = 2, /* TMA + tcgen05 (TMEM accumulators): bf16 / fp16 tiles */
+  /* Reported by nb200_sdpa_plan only (not a value for `kernel`): the problem runs in the NB200_KERNEL_SIMT family
+   * on its fp32-operand kernels that split every operand into two TF32 terms and use the warp-level tensor-core
+   * path (3 x TF32, fp32 accuracy) -- the counterpart of what the reference's fused path accepts, fp32 only
+   * (reference attention.py:736-744). */
+  NB200_KERNEL_MMA_TF32X3 = 3
 };
 
 enum nb200_pass { NB200_PASS_FWD = 0, NB200_PASS_BWD = 1 };
@@ -105,7 +110,32 @@ typedef struct nb200_sdpa_params {
    * [bh_begin, bh_end).  Pointers and strides always describe the whole
    * tensors; bh_begin = 0, bh_end = B*H processes everything. */
   int32_t bh_begin, bh_end;
+
+  /* Backward produces the bias gradient iff dbias != NULL or want_dbias != 0.  The flag lets nb200_sdpa_plan and
+   * nb200_sdpa_workspace_bytes answer for a backward with a bias gradient before the dbias buffer exists;
+   * nb200_sdpa_bwd itself needs the pointer (want_dbias with dbias == NULL is NB200_ERR_INVALID there). */
+  int32_t want_dbias;
+
+  /* 0: `mask` is the byte mask described above.  1 or 2: `mask` points to a buffer filled by nb200_mask_pack for
+   * this same problem (same B, H, S, T and mask_stride, which still tell which axes the mask broadcasts over):
+   * 1 = packed without the transposed copy (enough for the forward, and for the backward of a mask with no
+   * query axis), 2 = packed with it (forward and backward).  A packed mask is packed once and reused by the
+   * forward, the backward and any number of later calls; only the tensor-core family consumes it
+   * (NB200_ERR_UNSUPPORTED when the problem runs on the CUDA-core family). */
+  int32_t mask_is_bitpacked;
+
+  /* Fused output all-gather (forward only; the reference has no collective).  The forward kernel stores every
+   * output row it produces into out AND into n_out_peers more buffers with the same shape and strides --
+   * typically the peers' copies of a replicated (B, H, S, Dv) result, mapped into this process with
+   * nb200_ipc_open.  Plain stores over NVLink from the epilogue; the caller synchronises the ranks afterwards
+   * (each rank's rows are complete when its stream has passed the forward and all ranks have met).  Needs the
+   * tensor-core family and 32-byte aligned rows; 0 <= n_out_peers <= NB200_MAX_OUT_PEERS. */
+  int32_t n_out_peers;
+  int32_t reserved0;
+  void* out_peers[7];
 } nb200_sdpa_params;
+
+#define NB200_MAX_OUT_PEERS 7
 
 /* ABI version of the loaded library (== NB200_ABI_VERSION it was built with). */
 NB200_API int nb200_version(void);
@@ -114,7 +144,7 @@ NB200_API int nb200_version(void);
 NB200_API const char* nb200_last_error(void);
 
 /* Which kernel family would run this problem for `pass`; writes one of
- * NB200_KERNEL_SIMT / NB200_KERNEL_TCGEN05 to *kernel.  When the params force a
+ * NB200_KERNEL_SIMT / NB200_KERNEL_TCGEN05 / NB200_KERNEL_MMA_TF32X3 to *kernel.  When the params force a
  * family that does not cover the problem the status says why (the Python layer
  * turns that into the reference's decline -> warn-once contract,
  * reference nn/attention/__init__.py:207-220).  Never launches. */
@@ -169,6 +199,34 @@ NB200_API size_t nb200_profile_read(char* buf, size_t bytes);
  * wait expires; call after synchronising the stream.  NB200_OK or
  * NB200_ERR_TIMEOUT.  `device` is the CUDA device ordinal. */
 NB200_API int nb200_device_status(int device);
+
+/* Bit-packing of a boolean mask, done once and reused (no counterpart in the reference, which re-reads the byte
+ * mask in every kernel, attention.py:118-126, :306-311, :366-371).  nb200_mask_pack_bytes: size of the packed
+ * buffer for the mask described by p (dims, mask, mask_stride); with_transpose != 0 adds the key-major copy the
+ * backward of a mask with a query axis needs (ignored for masks without a query axis).  nb200_mask_pack enqueues
+ * the packing kernel on the stream; `packed` must be 256-byte aligned.  Pass the buffer as p->mask with
+ * p->mask_is_bitpacked = 1 (packed without transpose) or 2 (with). */
+NB200_API int nb200_mask_pack_bytes(const nb200_sdpa_params* p, int with_transpose, size_t* bytes);
+NB200_API int nb200_mask_pack(const nb200_sdpa_params* p, int with_transpose, void* packed, size_t packed_bytes,
+                              void* cuda_stream);
+
+/* Peer mapping for the fused output all-gather (no counterpart in the reference).  One process per GPU:
+ * nb200_ipc_export describes a device allocation of this process (any pointer inside a cudaMalloc'ed block) in
+ * 128 opaque bytes that are sent to the peer processes by any host channel; nb200_ipc_open maps it into the
+ * calling process (enabling peer access between the two GPUs) and returns the device pointer to use in
+ * out_peers; nb200_ipc_close unmaps it.  Nothing is copied and no memory is allocated. */
+typedef struct nb200_ipc_handle { unsigned char bytes[128]; } nb200_ipc_handle;
+NB200_API int nb200_ipc_export(const void* device_ptr, nb200_ipc_handle* handle);
+NB200_API int nb200_ipc_open(const nb200_ipc_handle* handle, void** device_ptr);
+NB200_API int nb200_ipc_close(void* device_ptr);
+
+/* Diagnostic: runs the give-up branch of the bounded mbarrier wait all tensor-core kernels use (no counterpart in
+ * the reference).  One warp waits, with a budget of a few thousand cycles, on a barrier nothing completes; the wait
+ * expires within a few milliseconds, the kernel exits normally and the device status word holds a time-out code.
+ * result_device points to two ints on the device: [0] = 1 if the wait (wrongly) reported completion, else 0;
+ * [1] = the CTA abort flag the wait raised.  After synchronising, nb200_device_status() returns NB200_ERR_TIMEOUT
+ * once and NB200_OK afterwards. */
+NB200_API int nb200_selftest_bounded_wait(int* result_device, void* cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -10,11 +10,11 @@ import functools
 
 from . import _build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 F32, BF16, F16 = 0, 1, 2
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_LAUNCH, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_MMA_TF32X3 = 0, 1, 2, 3
 PASS_FWD, PASS_BWD = 0, 1
 STATIC_SCRATCH_BYTES = 8 << 20
 
@@ -43,7 +43,18 @@ class SdpaParams(C.Structure):
         ("causal", C.c_int32),
         ("kernel", C.c_int32),
         ("bh_begin", C.c_int32), ("bh_end", C.c_int32),
+        ("want_dbias", C.c_int32),
+        ("mask_is_bitpacked", C.c_int32),
+        ("n_out_peers", C.c_int32),
+        ("reserved0", C.c_int32),
+        ("out_peers", C.c_void_p * 7),
     ]
+
+
+class IpcHandle(C.Structure):
+    """Mirror of ``nb200_ipc_handle``: 128 opaque bytes that name a device allocation to another process."""
+
+    _fields_ = [("bytes", C.c_ubyte * 128)]
 
 
 EXPORTS = (
@@ -58,6 +69,12 @@ EXPORTS = (
     "nb200_profile",
     "nb200_profile_read",
     "nb200_device_status",
+    "nb200_selftest_bounded_wait",
+    "nb200_mask_pack_bytes",
+    "nb200_mask_pack",
+    "nb200_ipc_export",
+    "nb200_ipc_open",
+    "nb200_ipc_close",
 )
 
 
@@ -89,6 +106,12 @@ def lib() -> C.CDLL:
     L.nb200_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
     L.nb200_sdpa_bwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
     L.nb200_sdpa_bwd_static_scratch.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
+    L.nb200_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_void_p]
+    L.nb200_mask_pack_bytes.argtypes = [C.POINTER(SdpaParams), C.c_int, C.POINTER(C.c_size_t)]
+    L.nb200_mask_pack.argtypes = [C.POINTER(SdpaParams), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.nb200_ipc_export.argtypes = [C.c_void_p, C.POINTER(IpcHandle)]
+    L.nb200_ipc_open.argtypes = [C.POINTER(IpcHandle), C.POINTER(C.c_void_p)]
+    L.nb200_ipc_close.argtypes = [C.c_void_p]
     if L.nb200_version() != ABI_VERSION:
         raise NativeLibraryError(f"{path}: ABI {L.nb200_version()} != expected {ABI_VERSION}")
     return L

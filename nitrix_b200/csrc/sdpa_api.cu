@@ -62,14 +62,16 @@ int check_launch(const char* what) {
 }
 
 int* device_status_word() {
-  // the symbol's address is fixed per device: looked up once and remembered
-  static int* known[64] = {};
+  // the symbol's address is fixed per device: looked up once and remembered (host threads may race here)
+  static std::atomic<int*> known[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
-  if (dev >= 0 && known[dev]) return known[dev];
+  if (dev >= 0) {
+    if (int* hit = known[dev].load(std::memory_order_acquire)) return hit;
+  }
   int* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
-  if (dev >= 0) known[dev] = p;
+  if (dev >= 0) known[dev].store(p, std::memory_order_release);
   return p;
 }
 
@@ -130,8 +132,16 @@ int lower(const nb200_sdpa_params* p, int pass, Lowered* out) {
     set_error("dout, dq, dk and dv need a unit stride on the head dimension");
     return NB200_ERR_INVALID;
   }
-  if (pass == NB200_PASS_BWD && p->dbias && !p->bias) {
+  if (pass == NB200_PASS_BWD && (p->dbias || p->want_dbias) && !p->bias) {
     set_error("dbias requested without bias");
+    return NB200_ERR_INVALID;
+  }
+  if (p->mask && (p->mask_is_bitpacked < 0 || p->mask_is_bitpacked > 2)) {
+    set_error("mask_is_bitpacked must be 0, 1 or 2 (got %d)", p->mask_is_bitpacked);
+    return NB200_ERR_INVALID;
+  }
+  if (p->n_out_peers < 0 || p->n_out_peers > NB200_MAX_OUT_PEERS) {
+    set_error("n_out_peers must be in [0, %d] (got %d)", NB200_MAX_OUT_PEERS, p->n_out_peers);
     return NB200_ERR_INVALID;
   }
   Problem& pr = out->pr;
@@ -141,6 +151,15 @@ int lower(const nb200_sdpa_params* p, int pass, Lowered* out) {
   pr.q = p->q; pr.k = p->k; pr.v = p->v; pr.out = p->out; pr.lse = p->lse;
   pr.bias = p->bias; pr.mask = p->mask;
   pr.scale = p->scale; pr.causal = p->causal != 0;
+  pr.mask_packed = p->mask ? p->mask_is_bitpacked : 0;
+  pr.want_dbias = (pass == NB200_PASS_BWD && (p->dbias || p->want_dbias)) ? 1 : 0;
+  if (pass == NB200_PASS_FWD) {
+    pr.n_out_peers = p->n_out_peers;
+    for (int i = 0; i < p->n_out_peers; ++i) {
+      if (!p->out_peers[i]) { set_error("out_peers[%d] is NULL", i); return NB200_ERR_INVALID; }
+      pr.out_peers[i] = p->out_peers[i];
+    }
+  }
   for (int a = 0; a < 3; ++a) {
     pr.qs[a] = p->q_stride[a]; pr.ks[a] = p->k_stride[a]; pr.vs[a] = p->v_stride[a];
     pr.os[a] = p->out_stride[a];
@@ -180,8 +199,23 @@ int choose(const nb200_sdpa_params* p, const Lowered& lw, int pass, int* kernel)
     return NB200_ERR_INVALID;
   }
   if (p->kernel == NB200_KERNEL_AUTO && tc) { *kernel = NB200_KERNEL_TCGEN05; return NB200_OK; }
+  if (lw.pr.bh_count > 65535) {
+    // the CUDA-core launches put the (batch, head) index on grid.y
+    set_error("more than 65535 (batch, head) pairs in one call (%d): split the range with bh_begin / bh_end",
+              lw.pr.bh_count);
+    return NB200_ERR_UNSUPPORTED;
+  }
   if (lw.pr.D > 256 || lw.pr.Dv > 256) {
     set_error("head dims above 256 are not supported (D=%d Dv=%d)", lw.pr.D, lw.pr.Dv);
+    return NB200_ERR_UNSUPPORTED;
+  }
+  if (lw.pr.mask_packed) {
+    set_error("a bit-packed mask is consumed by the tensor-core kernels only, and they do not cover this problem (%s): "
+              "pass the byte mask", why);
+    return NB200_ERR_UNSUPPORTED;
+  }
+  if (lw.pr.n_out_peers > 0) {
+    set_error("the fused output all-gather needs the tensor-core kernels, and they do not cover this problem (%s)", why);
     return NB200_ERR_UNSUPPORTED;
   }
   *kernel = NB200_KERNEL_SIMT;
@@ -199,7 +233,7 @@ BwdScratch bwd_scratch(const nb200_sdpa_params* p, const Lowered& lw, size_t fam
   off += align_up(sizeof(float) * size_t(p->B) * p->H * p->S);
   s.accum_off = off;
   s.accum_elems = 0;
-  if (p->dbias && lw.bias_broadcast) {
+  if ((p->dbias || p->want_dbias) && lw.bias_broadcast) {
     s.accum_elems = lw.bias_extent[0] * lw.bias_extent[1] * lw.bias_extent[2] * lw.bias_extent[3];
     off += align_up(sizeof(float) * size_t(s.accum_elems));
   }
@@ -283,7 +317,9 @@ NB200_API int nb200_sdpa_plan(const nb200_sdpa_params* p, int pass, int* kernel)
   if (!kernel) { set_error("kernel out-pointer is NULL"); return NB200_ERR_INVALID; }
   Lowered lw;
   if (int rc = lower(p, pass, &lw)) return rc;
-  return choose(p, lw, pass, kernel);
+  if (int rc = choose(p, lw, pass, kernel)) return rc;
+  if (*kernel == NB200_KERNEL_SIMT && simt_family_uses_tensor_path(lw.pr, lw.dtype, pass)) *kernel = NB200_KERNEL_MMA_TF32X3;
+  return NB200_OK;
 }
 
 NB200_API int nb200_sdpa_workspace_bytes(const nb200_sdpa_params* p, int pass, size_t* bytes) {
@@ -295,6 +331,26 @@ NB200_API int nb200_sdpa_workspace_bytes(const nb200_sdpa_params* p, int pass, s
   const size_t fam = kernel == NB200_KERNEL_TCGEN05 ? tc_workspace_bytes(lw.pr, lw.dtype, lw.bias_dtype, pass) : 0;
   *bytes = pass == NB200_PASS_FWD ? align_up(fam) : bwd_scratch(p, lw, fam).total;
   return NB200_OK;
+}
+
+NB200_API int nb200_mask_pack_bytes(const nb200_sdpa_params* p, int with_transpose, size_t* bytes) {
+  if (!bytes) { set_error("bytes out-pointer is NULL"); return NB200_ERR_INVALID; }
+  Lowered lw;
+  if (int rc = lower(p, NB200_PASS_FWD, &lw)) return rc;
+  if (lw.pr.mask_packed) { set_error("the mask is already packed"); return NB200_ERR_INVALID; }
+  *bytes = align_up(tc_mask_pack_bytes(lw.pr, with_transpose != 0));
+  return NB200_OK;
+}
+
+NB200_API int nb200_mask_pack(const nb200_sdpa_params* p, int with_transpose, void* packed, size_t packed_bytes,
+                              void* cuda_stream) {
+  Lowered lw;
+  if (int rc = lower(p, NB200_PASS_FWD, &lw)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  g_prof_stream = st;
+  prof_mark(nullptr);
+  if (!lw.pr.mask || lw.pr.bh_count == 0 || lw.pr.S == 0 || lw.pr.T == 0) return NB200_OK;
+  return tc_mask_pack(lw.pr, with_transpose != 0, packed, packed_bytes, st);
 }
 
 NB200_API int nb200_sdpa_fwd(const nb200_sdpa_params* p, void* cuda_stream) {
@@ -322,6 +378,10 @@ NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream) {
   if (int rc = lower(p, NB200_PASS_BWD, &lw)) return rc;
   int kernel = 0;
   if (int rc = choose(p, lw, NB200_PASS_BWD, &kernel)) return rc;
+  if (p->want_dbias && !p->dbias) {
+    set_error("want_dbias is set but dbias is NULL");
+    return NB200_ERR_INVALID;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   g_prof_stream = st;
   prof_mark(nullptr);   // start of this call's kernels

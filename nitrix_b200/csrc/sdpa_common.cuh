@@ -37,6 +37,10 @@ struct Problem {
   int64_t bs[4], ms[4], dbs[4];                                          // b, h, row, col
   float scale;
   int causal;
+  int want_dbias;      // the backward produces a bias gradient (dbias may still be null while planning)
+  int mask_packed;     // 0: byte mask; 1 / 2: `mask` is a buffer made by nb200_mask_pack (2: with the transposed copy)
+  int n_out_peers;     // forward: further destinations of every output row (same strides as out)
+  void* out_peers[NB200_MAX_OUT_PEERS];
 };
 
 template <typename T>
@@ -81,6 +85,9 @@ int* device_status_word();
 // ---- SIMT kernels (sdpa_simt.cu) -------------------------------------------
 int simt_forward(const Problem& pr, int dtype, int bias_dtype, cudaStream_t stream);
 int simt_backward(const Problem& pr, int dtype, int bias_dtype, cudaStream_t stream);
+// True when this family runs the problem's `pass` on its 3 x TF32 mma.sync kernels (fp32 operands) rather than on
+// plain FMA units.
+bool simt_family_uses_tensor_path(const Problem& pr, int dtype, int pass);
 // delta = rowsum(out*dout) and, when dbias_accum is used, its zero-fill / final cast
 int launch_delta(const Problem& pr, int dtype, cudaStream_t stream);
 int launch_dbias_finish(const float* accum, void* dbias, int bias_dtype, const int64_t extent[4],
@@ -94,5 +101,8 @@ bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const 
 size_t tc_workspace_bytes(const Problem& pr, int dtype, int bias_dtype, int pass);
 int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
 int tc_backward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
+// Packing of the byte mask into the tensor-core kernels' bit layout, as a call of its own (nb200_mask_pack).
+size_t tc_mask_pack_bytes(const Problem& pr, bool with_transpose);
+int tc_mask_pack(const Problem& pr, bool with_transpose, void* packed, size_t packed_bytes, cudaStream_t stream);
 
 }  // namespace nb200

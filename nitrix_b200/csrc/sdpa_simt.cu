@@ -1222,6 +1222,17 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
 
 }  // namespace
 
+bool simt_family_uses_tensor_path(const Problem& pr, int dtype, int pass) {
+  // mirrors the selection in fwd_t / bwd_t above
+  if (dtype != NB200_F32) return false;
+  const bool dv_ok = pr.Dv == 32 || pr.Dv == 64 || pr.Dv == 128;
+  if (pass == NB200_PASS_FWD) return pr.D % 8 == 0 && pr.D <= 128 && dv_ok;
+  const bool d_ok = pr.D == 32 || pr.D == 64 || pr.D == 128;
+  const bool dq = pr.S > 0 && pr.Dv % 8 == 0 && pr.Dv <= 128 && d_ok && int64_t((pr.S + 63) / 64) * pr.bh_count >= 96;
+  const bool dkv = pr.T > 0 && pr.D == pr.Dv && d_ok && int64_t((pr.T + 63) / 64) * pr.bh_count >= 96;
+  return dq && dkv;
+}
+
 int simt_forward(const Problem& pr, int dtype, int bias_dtype, cudaStream_t st) {
   if (pr.bh_count <= 0 || pr.S <= 0) return NB200_OK;
   switch (dtype) {

@@ -73,6 +73,12 @@ struct BwdArgs {
   void* out1; int64_t o1s[3];   // key-major: dv
   void* out2; int64_t o2s[3];   // dq | dk
   void* dbias; int64_t dbs[4];  // query-major only; null when not requested
+  // Gradient of a bias that is broadcast over some axis: fp32 sums over the broadcast axes, in an accumulator of the
+  // bias' own extent (zero on entry; acc_s = its element strides over (b, h, row), 0 on broadcast axes, unit key
+  // stride).  A bias with a query axis is summed by the query-major kernel (ds tiles added with 16-byte
+  // reductions), a per-key bias by the key-major kernel (each thread sums its key's ds over the queries it
+  // streams and adds once).
+  float* dbias_acc; int64_t acc_s[3];
   float* dq_acc;                // merged kernel: fp32 (bh_count, S, 64) sums of ds K, zero on entry
   int* status;
 };
@@ -573,6 +579,12 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
       }
     }
 
+    // key-major, per-key bias gradient: running sum of this thread's key (the identity tiles are not used then)
+    float* key_ds_sum = reinterpret_cast<float*>(smem + L::kIdent) + (threadIdx.x - 128);
+    if (kKeyMajor && !kMerged && a.dbias_acc) *key_ds_sum = 0.f;
+    float* acc_row = nullptr;                    // query-major, broadcast tile bias: this query's accumulator row
+    if (!kKeyMajor && a.dbias_acc && orow < a.S)
+      acc_row = a.dbias_acc + b * a.acc_s[0] + h * a.acc_s[1] + int64_t(orow) * a.acc_s[2];
     // merged: pair j of steps (2j, 2j + 1) leaves a 128-query x 64 dq tile in TMEM; this group adds its 32 columns
     // of it to the fp32 accumulator in global memory (thread = query row)
     int next_pair = 0;
@@ -710,6 +722,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 #pragma unroll
       for (int c4 = 0; c4 < kStep / 4; ++c4) {
         const float2 nls = make_float2(-lse_row, -lse_row), ndl = make_float2(-delta_row, -delta_row);  // query-major
+        float2 ds4[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int c = c4 * 2 + e;  // pair index: streamed rows 2c, 2c + 1
@@ -722,6 +735,23 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           const float2 ds = kKeyMajor ? __fmul2_rn(p, dp[c]) : __fmul2_rn(p, __fadd2_rn(dp[c], ndl));
           e1[c] = pack2<kBf16>(p.x, p.y);
           e2[c] = pack2<kBf16>(ds.x, ds.y);
+          if constexpr (!kKeyMajor) ds4[e] = ds;
+        }
+        if constexpr (!kKeyMajor) {
+          // broadcast bias: this row's ds of four consecutive keys joins the fp32 sums over the broadcast axes
+          if (acc_row && r0 + 4 * c4 < a.T)
+            red_add_v4(acc_row + r0 + 4 * c4, __float_as_uint(ds4[0].x), __float_as_uint(ds4[0].y),
+                       __float_as_uint(ds4[1].x), __float_as_uint(ds4[1].y));
+        }
+      }
+      if constexpr (kKeyMajor && !kMerged) {
+        // gradient of a per-key bias: this key's ds summed over the step's queries (from the 16-bit values the
+        // tensor core will consume); the running sum waits in shared memory so that it holds no register
+        if (a.dbias_acc) {
+          float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int c = 0; c < kStep / 2; ++c) sum2 = __fadd2_rn(sum2, unpack2<kBf16>(e2[c]));
+          *key_ds_sum += sum2.x + sum2.y;
         }
       }
       if constexpr (kDeep) {
@@ -790,6 +820,11 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         for (int k0 = s_end * kStep; k0 < a.T; k0 += 8)
           *reinterpret_cast<uint4*>(dst + 2 * k0) = make_uint4(0, 0, 0, 0);
       }
+    }
+    if constexpr (kKeyMajor && !kMerged) {
+      // both groups hold a partial sum of the same key (they took alternate steps)
+      if (a.dbias_acc && n_steps > 0 && orow < a.T)
+        atomicAdd(a.dbias_acc + b * a.acc_s[0] + h * a.acc_s[1] + orow, *key_ds_sum);
     }
     if constexpr (kMerged) {
       while (ok && next_pair < n_steps / 2) ok = drain_pair(next_pair++);
@@ -914,13 +949,16 @@ int bias_mode_of(const Problem& pr) {
 
 bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** why) {
   // forward coverage (dtype, head dims, lengths, q/k/v/bias layout) was checked by the caller
-  if (pr.dbias_accum) { *why = "gradient of a broadcast bias needs a reduction"; return false; }
   if (pr.scale == 0.f || !isfinite(1.f / pr.scale) || !isfinite(pr.scale)) {
     *why = "scale is zero or not finite";   // the key-major kernel divides lse by scale
     return false;
   }
   if (pr.lse && reinterpret_cast<uintptr_t>(pr.lse) % 16) { *why = "lse is not 16-byte aligned"; return false; }
-  if (pr.dout && (!tile_map_ok(pr.dout, pr.dos[2], pr.dos[1], pr.dos[0], pr.H, pr.B))) {
+  if (pr.mask_packed == 1 && !mask_key_only(pr)) {
+    *why = "the mask was packed without the transposed copy the backward needs (nb200_mask_pack with_transpose = 1)";
+    return false;
+  }
+  if (pr.dout && (!tile_map_ok(pr.dout, pr.dos[2], pr.dos[1], pr.dos[0], pr.H, pr.B, false))) {
     *why = "dout strides / alignment do not fit a TMA descriptor";
     return false;
   }
@@ -934,11 +972,14 @@ bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** wh
     }
   }
   if (pr.dbias) {
-    // dbias is written as 16-byte row segments in bias dtype; a broadcast bias (reduction needed) is declined
+    // A bias of full extent gets its gradient as 16-byte row segments in bias dtype, straight from the kernel; a
+    // broadcast bias is summed in fp32 (an accumulator of the bias' own extent in the workspace) and cast by
+    // dbias_finish_kernel, which takes any dbias layout.
     const int64_t full[4] = {pr.B, pr.H, pr.S, pr.T};
-    for (int ax = 0; ax < 4; ++ax)
-      if (pr.bs[ax] == 0 && full[ax] > 1) { *why = "gradient of a broadcast bias needs a reduction"; return false; }
-    if (pr.dbs[3] != 1 || reinterpret_cast<uintptr_t>(pr.dbias) % 16 || pr.dbs[0] % 8 || pr.dbs[1] % 8 || pr.dbs[2] % 8) {
+    bool broadcast = false;
+    for (int ax = 0; ax < 4; ++ax) broadcast = broadcast || (pr.bs[ax] == 0 && full[ax] > 1);
+    if (!broadcast && (pr.dbs[3] != 1 || reinterpret_cast<uintptr_t>(pr.dbias) % 16 || pr.dbs[0] % 8 ||
+                       pr.dbs[1] % 8 || pr.dbs[2] % 8)) {
       *why = "dbias layout is not 16-byte aligned with a unit key stride";
       return false;
     }
@@ -951,14 +992,14 @@ bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** wh
 namespace {
 // One kernel for dq, dk and dv (head dim 64, no bias gradient): the key-major kernel also forms ds K per pair of
 // steps and adds it to an fp32 copy of dq, which a last kernel scales and casts.
-bool use_merged(const Problem& pr) { return pr.D == 64 && !pr.dbias && pr.S % kTile == 0; }
-size_t mask_bytes_aligned(const MaskPackPlan& mp) { return (mp.total() + 255) / 256 * 256; }
+bool use_merged(const Problem& pr) { return pr.D == 64 && !pr.want_dbias && pr.S % kTile == 0; }
+size_t round_up_256(size_t x) { return (x + 255) / 256 * 256; }
 }  // namespace
 
 size_t bwd_workspace_bytes(const Problem& pr, int, int) {
-  const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
-  const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
-  size_t bytes = mask_bytes_aligned(mp);
+  size_t mask_ws = 0;
+  mask_plan_for_pass(pr, true, &mask_ws);
+  size_t bytes = round_up_256(mask_ws);
   if (use_merged(pr)) bytes += sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D;
   return bytes;
 }
@@ -966,12 +1007,14 @@ size_t bwd_workspace_bytes(const Problem& pr, int, int) {
 int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
   (void)bias_dtype;
   const char* why = "";
-  const bool key_only = pr.mask && (pr.ms[2] == 0 || pr.S == 1);
-  const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && !key_only);
+  const bool key_only = mask_key_only(pr);
+  size_t mask_ws = 0;
+  const MaskPackPlan mp = mask_plan_for_pass(pr, true, &mask_ws);
+  mask_ws = round_up_256(mask_ws);
   const bool merged = use_merged(pr);
   const size_t acc_bytes = merged ? sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D : 0;
-  if (mask_bytes_aligned(mp) + acc_bytes > ws_bytes) {
-    set_error("tensor-core backward needs %zu workspace bytes", mask_bytes_aligned(mp) + acc_bytes);
+  if (mask_ws + acc_bytes > ws_bytes) {
+    set_error("tensor-core backward needs %zu workspace bytes", mask_ws + acc_bytes);
     return NB200_ERR_WORKSPACE;
   }
   BwdArgs a{};
@@ -1011,7 +1054,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
 
   if (merged) {
     BwdArgs ak = a;
-    ak.dq_acc = reinterpret_cast<float*>(static_cast<char*>(ws) + mask_bytes_aligned(mp));
+    ak.dq_acc = reinterpret_cast<float*>(static_cast<char*>(ws) + mask_ws);
     cudaError_t e = cudaMemsetAsync(ak.dq_acc, 0, acc_bytes, stream);
     if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
     ak.out1 = pr.dv;
@@ -1041,8 +1084,16 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     aq.key_aug = (a.bias_mode != kBiasTile && (a.bias_mode == kBiasKey || key_only) && pr.scale > 0.f) ? 1 : 0;
     aq.out2 = pr.dq;
     for (int i = 0; i < 3; ++i) aq.o2s[i] = pr.dqs[i];
-    aq.dbias = pr.dbias;
-    for (int i = 0; i < 4; ++i) aq.dbs[i] = pr.dbs[i];
+    if (pr.dbias_accum) {
+      // broadcast bias: fp32 sums; the per-key case is summed by the key-major kernel below
+      if (a.bias_mode == kBiasTile) {
+        aq.dbias_acc = pr.dbias_accum;
+        for (int i = 0; i < 3; ++i) aq.acc_s[i] = pr.dbs[i];
+      }
+    } else {
+      aq.dbias = pr.dbias;
+      for (int i = 0; i < 4; ++i) aq.dbs[i] = pr.dbs[i];
+    }
     const CUtensorMap maps[5] = {q128, g128, k64, v64, bias_q};
     if (int rc = launch_dir<false>(pr.D, bf16, maps, aq, (pr.S + kTile - 1) / kTile, pr.bh_count, stream)) return rc;
   }
@@ -1052,6 +1103,10 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     ak.out1 = pr.dv;
     ak.out2 = pr.dk;
     for (int i = 0; i < 3; ++i) { ak.o1s[i] = pr.dvs[i]; ak.o2s[i] = pr.dks[i]; }
+    if (pr.dbias_accum && a.bias_mode == kBiasKey) {
+      ak.dbias_acc = pr.dbias_accum;
+      for (int i = 0; i < 3; ++i) ak.acc_s[i] = pr.dbs[i];
+    }
     const CUtensorMap maps[5] = {k128, v128, q64, g64, bias_k};
     if (int rc = launch_dir<true>(pr.D, bf16, maps, ak, (pr.T + kTile - 1) / kTile, pr.bh_count, stream)) return rc;
   }

@@ -37,8 +37,10 @@ bool split_inv_scale(float scale, bool bf16, float* hi, float* lo);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
-// True when a tensor with these element strides can be described by make_tile_map.
-bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B);
+// True when a tensor with these element strides can be described by make_tile_map.  `allow_broadcast`: a stride-0
+// head / batch axis is acceptable (the bias, whose loads scale their coordinates; not q, k, v, dout).
+bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B,
+                 bool allow_broadcast);
 
 // ---- bit-packed mask ----------------------------------------------------------
 // The byte mask (own extent Bm, Hm, Sm, Tm with strides, broadcast axes = 1) is
@@ -74,6 +76,11 @@ __device__ __forceinline__ int kept_key_length(const MaskBits& m, int b, int h, 
 }
 #endif
 MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed);
+// True when the mask has no query axis (key padding and the like).
+bool mask_key_only(const Problem& pr);
+// Layout of the mask bits a forward / backward call works with, and the workspace bytes it needs for them (none when
+// the caller passes a mask that nb200_mask_pack packed earlier; launch_mask_pack then only forms the views).
+MaskPackPlan mask_plan_for_pass(const Problem& pr, bool backward, size_t* ws_bytes);
 int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, MaskBits* out, cudaStream_t stream);
 
 // ---- device helpers -----------------------------------------------------------
@@ -87,7 +94,7 @@ constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s of SM clock: far beyon
 // status word already set by another CTA aborts this one as well, so one
 // protocol failure ends the whole grid quickly instead of once per CTA.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                              int code) {
+                                              int code, long long budget_cycles = kWaitCycles) {
   if (sm100::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
@@ -99,7 +106,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
         *abort_flag = 1;
         return false;
       }
-      if (clock64() - t0 > kWaitCycles) {
+      if (clock64() - t0 > budget_cycles) {
         *abort_flag = 1;
         atomicExch(status, code);
         return false;

@@ -651,7 +651,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (ok && my_nt > 0) {
         tc_fence_after_sync();
         const float inv = 1.f / l;  // l == 0 (no kept key): 0 * inf = NaN, as the reference's softmax gives
-        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + 2 * (b * a.os[0] + h * a.os[1] + int64_t(row) * a.os[2]);
+        const int64_t out_off = 2 * (b * a.os[0] + h * a.os[1] + int64_t(row) * a.os[2]);
+        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + out_off;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -664,14 +665,21 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (lane == 0) mbar_arrive(bar(O_FREE + g));
           }
           if (row < a.S) {
+            uint4 w[4];
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack2<kBf16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-              w.y = pack2<kBf16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-              w.z = pack2<kBf16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-              w.w = pack2<kBf16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + (c * 32 + i) * 2) = w;
+              uint4& x = w[i >> 3];
+              x.x = pack2<kBf16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              x.y = pack2<kBf16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              x.z = pack2<kBf16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              x.w = pack2<kBf16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + (c * 32 + i) * 2) = x;
+            }
+            // fused all-gather: the same 64 bytes go to every peer's copy, two whole 32-byte sectors per thread
+            for (int pi = 0; pi < a.n_out_peers; ++pi) {
+              uint8_t* prow = reinterpret_cast<uint8_t*>(a.out_peers[pi]) + out_off + c * 64;
+              st_global_v8(prow, w[0], w[1]);
+              st_global_v8(prow + 32, w[2], w[3]);
             }
           }
         }

@@ -33,6 +33,10 @@ struct FwdArgs {
   void* out;
   int64_t os[3];                // element strides of out (b, h, row)
   float* lse;
+  // Fused output all-gather: every output row is also stored to these buffers (same strides as out; peers' copies of
+  // a replicated result mapped into this process).  Rows are 32-byte aligned there (checked on the host).
+  int n_out_peers;
+  void* out_peers[NB200_MAX_OUT_PEERS];
   int* status;
   int smem_bytes;               // dynamic shared memory the launch requested (filled in by launch_fwd)
 };

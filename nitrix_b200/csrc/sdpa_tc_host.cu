@@ -45,11 +45,15 @@ int sm_count() {
   return cached[dev];
 }
 
-bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B) {
+bool tile_map_ok(const void* base, int64_t row_stride, int64_t h_stride, int64_t b_stride, int H, int B,
+                 bool allow_broadcast) {
   if (reinterpret_cast<uintptr_t>(base) % 16) return false;
   if (row_stride <= 0 || row_stride % 8) return false;
-  if (H > 1 && h_stride != 0 && (h_stride % 8 || h_stride < 0)) return false;
-  if (B > 1 && b_stride != 0 && (b_stride % 8 || b_stride < 0)) return false;
+  // A broadcast (stride 0) head or batch axis is encoded with extent 1, and only the bias loads scale their
+  // head / batch coordinate accordingly; q, k, v and dout are addressed by the absolute (b, h), so an expanded
+  // view of them is declined here and runs on the CUDA-core family, which indexes by stride.
+  if (H > 1 && (h_stride % 8 || h_stride < 0 || (h_stride == 0 && !allow_broadcast))) return false;
+  if (B > 1 && (b_stride % 8 || b_stride < 0 || (b_stride == 0 && !allow_broadcast))) return false;
   return true;
 }
 
@@ -191,9 +195,45 @@ MaskPackPlan plan_mask_pack(const Problem& pr, bool transposed) {
   return p;
 }
 
+bool mask_key_only(const Problem& pr) { return pr.mask && (pr.ms[2] == 0 || pr.S == 1); }
+
+MaskPackPlan mask_plan_for_pass(const Problem& pr, bool backward, size_t* ws_bytes) {
+  // a mask without a query axis never needs the transposed copy; a caller-packed mask has the layout it was packed with
+  const bool transposed = !mask_key_only(pr) && (pr.mask_packed ? pr.mask_packed == 2 : backward);
+  const MaskPackPlan mp = plan_mask_pack(pr, pr.mask && transposed);
+  if (ws_bytes) *ws_bytes = pr.mask_packed ? 0 : mp.total();
+  return mp;
+}
+
+namespace {
+// Views into a packed-mask buffer laid out as `plan` says: rows, transposed copy, key lengths.
+void mask_views(const Problem& pr, const MaskPackPlan& plan, void* buf, MaskBits* out) {
+  uint32_t* rows = static_cast<uint32_t*>(buf);
+  uint32_t* cols = plan.cols_bytes ? reinterpret_cast<uint32_t*>(static_cast<char*>(buf) + plan.rows_bytes) : nullptr;
+  int* kv_len = plan.len_bytes ? reinterpret_cast<int*>(static_cast<char*>(buf) + plan.rows_bytes + plan.cols_bytes) : nullptr;
+  const int Hm = int(plan.extent[1]), Bm = int(plan.extent[0]), Sm = int(plan.extent[2]);
+  out->rows = rows;
+  out->row_stride = Sm == 1 ? 0 : plan.words_per_row;
+  out->h_stride = Hm == 1 ? 0 : int64_t(Sm) * plan.words_per_row;
+  out->b_stride = Bm == 1 ? 0 : int64_t(Hm) * Sm * plan.words_per_row;
+  out->cols = cols;
+  out->tkey_stride = plan.words_per_col;
+  out->th_stride = Hm == 1 ? 0 : int64_t(pr.T) * plan.words_per_col;
+  out->tb_stride = Bm == 1 ? 0 : int64_t(Hm) * pr.T * plan.words_per_col;
+  out->kv_len = kv_len;
+  out->len_h_stride = Hm == 1 ? 0 : 1;
+  out->len_b_stride = Bm == 1 ? 0 : Hm;
+}
+}  // namespace
+
 int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, MaskBits* out, cudaStream_t stream) {
   *out = MaskBits{};
   if (!pr.mask) return NB200_OK;
+  if (pr.mask_packed) {
+    // packed earlier by nb200_mask_pack: nothing to launch
+    mask_views(pr, plan, const_cast<uint8_t*>(pr.mask), out);
+    return NB200_OK;
+  }
   uint32_t* rows = static_cast<uint32_t*>(ws);
   uint32_t* cols = plan.cols_bytes ? reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + plan.rows_bytes) : nullptr;
   const int Bm = int(plan.extent[0]), Hm = int(plan.extent[1]), Sm = int(plan.extent[2]);
@@ -216,17 +256,7 @@ int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, Mask
   }
   count_launch();
   if (int rc = check_launch(tiled ? "mask_pack_tile_kernel" : "mask_pack_kernel")) return rc;
-  out->rows = rows;
-  out->row_stride = Sm == 1 ? 0 : plan.words_per_row;
-  out->h_stride = Hm == 1 ? 0 : int64_t(Sm) * plan.words_per_row;
-  out->b_stride = Bm == 1 ? 0 : int64_t(Hm) * Sm * plan.words_per_row;
-  out->cols = cols;
-  out->tkey_stride = plan.words_per_col;
-  out->th_stride = Hm == 1 ? 0 : int64_t(pr.T) * plan.words_per_col;
-  out->tb_stride = Bm == 1 ? 0 : int64_t(Hm) * pr.T * plan.words_per_col;
-  out->kv_len = kv_len;
-  out->len_h_stride = Hm == 1 ? 0 : 1;
-  out->len_b_stride = Bm == 1 ? 0 : Hm;
+  mask_views(pr, plan, ws, out);
   return NB200_OK;
 }
 
@@ -251,7 +281,7 @@ bool bias_plan(const Problem& pr, int dtype, int bias_dtype, BiasPlan* bp, const
     bp->mode = tc::kBiasKey;
     return true;
   }
-  if (!tc::tile_map_ok(pr.bias, pr.bs[2], pr.bs[1], pr.bs[0], pr.H, pr.B)) {
+  if (!tc::tile_map_ok(pr.bias, pr.bs[2], pr.bs[1], pr.bs[0], pr.H, pr.B, true)) {
     *why = "bias strides / alignment do not fit a TMA descriptor";
     return false;
   }
@@ -268,14 +298,18 @@ bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const 
   if (pr.D != pr.Dv || (pr.D != 64 && pr.D != 128)) { *why = "head dims must be equal and 64 or 128"; return false; }
   // Lengths need not fill whole 128-row tiles: TMA zero-fills rows past the end, the kernels mask keys past T and
   // store only rows below S.  Multiples of 8 keep every 16-byte row segment (bias, dbias, lse, packed rows) whole.
+  if (pr.bh_count > 65535 || int64_t(pr.B) * pr.H > 65535) {
+    *why = "more than 65535 (batch, head) pairs (grid limit of the backward and mask-packing launches)";
+    return false;
+  }
   if (pr.S <= 0 || pr.T <= 0 || pr.S % 8 || pr.T % 8) {
     *why = "query and key lengths must be positive multiples of 8";
     return false;
   }
-  if (!tc::tile_map_ok(pr.q, pr.qs[2], pr.qs[1], pr.qs[0], pr.H, pr.B) ||
-      !tc::tile_map_ok(pr.k, pr.ks[2], pr.ks[1], pr.ks[0], pr.H, pr.B) ||
-      !tc::tile_map_ok(pr.v, pr.vs[2], pr.vs[1], pr.vs[0], pr.H, pr.B)) {
-    *why = "q/k/v strides or alignment do not fit a TMA descriptor";
+  if (!tc::tile_map_ok(pr.q, pr.qs[2], pr.qs[1], pr.qs[0], pr.H, pr.B, false) ||
+      !tc::tile_map_ok(pr.k, pr.ks[2], pr.ks[1], pr.ks[0], pr.H, pr.B, false) ||
+      !tc::tile_map_ok(pr.v, pr.vs[2], pr.vs[1], pr.vs[0], pr.H, pr.B, false)) {
+    *why = "q/k/v strides or alignment do not fit a TMA descriptor (expanded views over batch / heads included)";
     return false;
   }
   if (reinterpret_cast<uintptr_t>(pr.out) % 16 || pr.os[0] % 8 || pr.os[1] % 8 || pr.os[2] % 8) {
@@ -290,17 +324,19 @@ bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const 
 
 size_t tc_workspace_bytes(const Problem& pr, int dtype, int bias_dtype, int pass) {
   if (pass == NB200_PASS_BWD) return tc::bwd_workspace_bytes(pr, dtype, bias_dtype);
-  const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, false);
-  return mp.total();
+  size_t bytes = 0;
+  tc::mask_plan_for_pass(pr, false, &bytes);
+  return bytes;
 }
 
 int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
   const char* why = "";
   BiasPlan bp;
   if (!bias_plan(pr, dtype, bias_dtype, &bp, &why)) { set_error("%s", why); return NB200_ERR_UNSUPPORTED; }
-  const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, false);
-  if (mp.total() > ws_bytes || (mp.total() && !ws)) {
-    set_error("forward mask bits need %zu workspace bytes", mp.total());
+  size_t mask_ws = 0;
+  const tc::MaskPackPlan mp = tc::mask_plan_for_pass(pr, false, &mask_ws);
+  if (mask_ws > ws_bytes || (mask_ws && !ws)) {
+    set_error("forward mask bits need %zu workspace bytes", mask_ws);
     return NB200_ERR_WORKSPACE;
   }
   tc::FwdArgs a{};
@@ -335,6 +371,14 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.out = pr.out;
   for (int i = 0; i < 3; ++i) a.os[i] = pr.os[i];
   a.lse = pr.lse;
+  a.n_out_peers = pr.n_out_peers;
+  for (int i = 0; i < pr.n_out_peers; ++i) {
+    a.out_peers[i] = pr.out_peers[i];
+    if (reinterpret_cast<uintptr_t>(pr.out_peers[i]) % 32 || pr.os[0] % 16 || pr.os[1] % 16 || pr.os[2] % 16) {
+      set_error("fused output all-gather: peer rows must be 32-byte aligned");
+      return NB200_ERR_ALIGNMENT;
+    }
+  }
   a.status = device_status_word();
   if (!a.status) { set_error("device status word is unavailable"); return NB200_ERR_LAUNCH; }
   a.B = pr.B;
@@ -346,6 +390,24 @@ int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   // more than the K / V locality of the head-major order
   if (a.head_major && pr.causal && int64_t(a.n_qblocks) * pr.bh_count <= 16 * int64_t(tc::sm_count())) a.head_major = 2;
   return tc::launch_fwd(pr.D, dtype == NB200_BF16, tq, tk, tv, tb, a, stream);
+}
+
+size_t tc_mask_pack_bytes(const Problem& pr, bool with_transpose) {
+  if (!pr.mask) return 0;
+  return tc::plan_mask_pack(pr, with_transpose && !tc::mask_key_only(pr)).total();
+}
+
+int tc_mask_pack(const Problem& pr, bool with_transpose, void* packed, size_t packed_bytes, cudaStream_t stream) {
+  if (!pr.mask) return NB200_OK;
+  if (pr.mask_packed) { set_error("the mask is already packed"); return NB200_ERR_INVALID; }
+  const tc::MaskPackPlan mp = tc::plan_mask_pack(pr, with_transpose && !tc::mask_key_only(pr));
+  if (!packed || packed_bytes < mp.total()) {
+    set_error("the packed mask needs %zu bytes, got %zu", mp.total(), packed ? packed_bytes : size_t(0));
+    return NB200_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(packed) % 256) { set_error("the packed-mask buffer must be 256-byte aligned"); return NB200_ERR_ALIGNMENT; }
+  tc::MaskBits unused;
+  return tc::launch_mask_pack(pr, mp, packed, &unused, stream);
 }
 
 int tc_backward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {

@@ -189,6 +189,14 @@ __device__ __forceinline__ void red_add_v4(float* addr, uint32_t a, uint32_t b, 
                : "memory");
 }
 
+// 32 contiguous bytes to global memory by one store (32-byte aligned address): a whole sector per thread, which is
+// what a store that crosses NVLink to a peer's memory wants.
+__device__ __forceinline__ void st_global_v8(void* addr, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(addr), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+               "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 // ---- tcgen05.mma ------------------------------------------------------------
 // Instruction descriptor for kind::f16 (bf16 or fp16 operands, fp32 accumulate).
 //   bits  4-5  accumulator format (1 = f32)      bits  7-9  A format (0 = f16, 1 = bf16)

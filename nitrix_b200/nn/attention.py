@@ -83,9 +83,14 @@ def _to_bhxd(x: torch.Tensor, lead: Tuple[int, ...], h: int) -> torch.Tensor:
     n, d = x.shape[-2], x.shape[-1]
     x = x.expand(*lead, h, n, d) if tuple(x.shape[:-3]) != lead or x.shape[-3] != h else x
     x = x.reshape(-1, h, n, d) if x.ndim != 4 else x
-    if x.stride(-1) != 1:
+    if x.stride(-1) != 1 or _has_expanded_axis(x):
+        # the tensor-core kernels address q, k, v by absolute (batch, head): an expanded view is materialised
         x = x.contiguous()
     return x
+
+
+def _has_expanded_axis(x: torch.Tensor) -> bool:
+    return any(st == 0 and n > 1 for st, n in zip(x.stride(), x.shape))
 
 
 def _to_own_extent(x: torch.Tensor, lead: Tuple[int, ...], h: int, s: int, t: int) -> torch.Tensor:
@@ -123,6 +128,16 @@ def _strides4(x: Optional[torch.Tensor], full: Tuple[int, int, int, int]):
     return arr
 
 
+class PackedMask:
+    """A boolean mask bit-packed once by ``nb200_mask_pack`` for one problem shape and reused by the forward, the
+    backward and later calls.  ``level`` 1: packed without the key-major copy; 2: with it (what the backward of a
+    mask with a query axis reads).  ``like`` is the 4-D byte mask it was packed from (strides tell the library
+    which axes the mask broadcasts over)."""
+
+    def __init__(self, blob: torch.Tensor, level: int, like: torch.Tensor):
+        self.blob, self.level, self.like = blob, int(level), like
+
+
 def _fill_common(p, q, k, v, out, lse, bias, mask, scale, causal, kernel, bh_range):
     B, H, S, D = q.shape
     T, Dv = k.shape[2], v.shape[3]
@@ -136,7 +151,11 @@ def _fill_common(p, q, k, v, out, lse, bias, mask, scale, causal, kernel, bh_ran
         p.bias = bias.data_ptr()
         p.bias_dtype = _DTYPES[bias.dtype]
         p.bias_stride = _strides4(bias, full)
-    if mask is not None:
+    if isinstance(mask, PackedMask):
+        p.mask = mask.blob.data_ptr()
+        p.mask_stride = _strides4(mask.like, full)
+        p.mask_is_bitpacked = mask.level
+    elif mask is not None:
         p.mask = mask.data_ptr()
         p.mask_stride = _strides4(mask, full)
     p.scale = float(scale)
@@ -172,9 +191,9 @@ def _launch(fn, p, device, what: str) -> None:
             _check(fn(C.byref(p), C.c_void_p(stream)), what)
 
 
-def _mask_bytes(mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    if mask is None:
-        return None
+def _mask_bytes(mask):
+    if mask is None or isinstance(mask, PackedMask):
+        return mask
     if mask.dtype == torch.bool:
         return mask.view(torch.uint8)
     if mask.dtype == torch.uint8:
@@ -194,11 +213,26 @@ def planned_kernel(q, k, v, bias=None, mask=None, *, scale=1.0, causal=False, wh
     p.dout_stride = p.dq_stride = p.out_stride
     p.dk_stride, p.dv_stride = p.k_stride, p.v_stride
     if want_dbias and bias is not None and which == _cabi.PASS_BWD:
-        p.dbias = bias.data_ptr()
-        p.dbias_stride[:] = list(bias.contiguous().stride()) if not bias.is_contiguous() else list(bias.stride())
+        p.want_dbias = 1   # the planner needs no dbias buffer
+        p.dbias_stride[:] = [bias.shape[1] * bias.shape[2] * bias.shape[3], bias.shape[2] * bias.shape[3], bias.shape[3], 1]
     chosen = C.c_int(0)
     _check(_cabi.lib().nb200_sdpa_plan(C.byref(p), which, C.byref(chosen)), "nb200_sdpa_plan")
     return chosen.value
+
+
+def pack_mask(q, k, v, mask, *, with_transpose: bool = True) -> PackedMask:
+    """Bit-pack a 4-D boolean / byte mask for these operands' shape (enqueued on the current stream)."""
+    mask_b = _mask_bytes(mask)
+    p = _cabi.new_params()
+    _fill_common(p, q, k, v, q, q, None, mask_b, 1.0, False, _cabi.KERNEL_AUTO, None)
+    need = C.c_size_t(0)
+    _check(_cabi.lib().nb200_mask_pack_bytes(C.byref(p), int(with_transpose), C.byref(need)), "nb200_mask_pack_bytes")
+    blob = torch.empty(max(int(need.value), 1), dtype=torch.uint8, device=q.device)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _check(_cabi.lib().nb200_mask_pack(C.byref(p), int(with_transpose), C.c_void_p(blob.data_ptr()),
+                                           C.c_size_t(blob.numel()), C.c_void_p(stream)), "nb200_mask_pack")
+    return PackedMask(blob, 2 if with_transpose else 1, mask_b)
 
 
 _plan_cache: dict = {}
@@ -209,12 +243,15 @@ def _meta(x: Optional[torch.Tensor]):
     return None if x is None else (x.dtype, tuple(x.shape), x.stride(), x.data_ptr() & 15)
 
 
-def _planned_kernel_cached(q, k, v, bias, mask, scale, causal) -> int:
-    """Forward plan for these operands, remembered by their layout (the planner is pure in it)."""
-    key = (_meta(q), _meta(k), _meta(v), _meta(bias), _meta(mask), scale > 0.0, bool(causal), q.device.index)
+def _planned_kernel_cached(q, k, v, bias, mask, scale, causal, which=_cabi.PASS_FWD, kernel=_cabi.KERNEL_AUTO,
+                           want_dbias=False) -> int:
+    """Plan for these operands, remembered by their layout (the planner is pure in it)."""
+    key = (_meta(q), _meta(k), _meta(v), _meta(bias), _meta(mask), scale > 0.0, bool(causal), q.device.index,
+           which, kernel, bool(want_dbias))
     chosen = _plan_cache.get(key)
     if chosen is None:
-        chosen = planned_kernel(q, k, v, bias, mask, scale=scale, causal=causal)
+        chosen = planned_kernel(q, k, v, bias, mask, scale=scale, causal=causal, which=which, kernel=kernel,
+                                want_dbias=want_dbias)
         if len(_plan_cache) >= 512:
             _plan_cache.clear()
         _plan_cache[key] = chosen
@@ -244,16 +281,21 @@ def sdpa_forward(q, k, v, bias=None, mask=None, *, scale: float, causal: bool = 
 
 
 def sdpa_backward(q, k, v, bias, mask, out, lse, dout, *, scale: float, causal: bool = False,
-                  want_dbias: bool = False, kernel: int = _cabi.KERNEL_AUTO, bh_range=None):
+                  want_dbias: bool = False, kernel: int = _cabi.KERNEL_AUTO, bh_range=None, grads=None):
     """Enqueue the backward on the current stream; returns ``(dq, dk, dv, dbias_or_None)``.
 
-    ``dbias`` has the bias' own 4-D extent (broadcast axes already reduced) and dtype.
+    ``dbias`` has the bias' own 4-D extent (broadcast axes already reduced) and dtype.  ``grads`` = existing
+    ``(dq, dk, dv, dbias_or_None)`` buffers to write into (several ``bh_range`` calls filling one set of buffers).
     """
-    if dout.stride(-1) != 1:
-        dout = dout.contiguous()
-    dq = torch.empty_like(q, memory_format=torch.contiguous_format)
-    dk = torch.empty_like(k, memory_format=torch.contiguous_format)
-    dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+    if dout.stride(-1) != 1 or _has_expanded_axis(dout):
+        dout = dout.contiguous()   # e.g. the cotangent of out.sum() or out.mean(0) arrives as an expanded view
+    if grads is not None:
+        dq, dk, dv, dbias_buf = grads
+    else:
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+        dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+        dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+        dbias_buf = None
     dbias = None
     p = _cabi.new_params()
     mask_b = _mask_bytes(mask)
@@ -266,7 +308,7 @@ def sdpa_backward(q, k, v, bias, mask, out, lse, dout, *, scale: float, causal: 
     if want_dbias:
         if bias is None:
             raise ValueError("want_dbias without a bias")
-        dbias = torch.empty(bias.shape, dtype=bias.dtype, device=bias.device)
+        dbias = dbias_buf if dbias_buf is not None else torch.empty(bias.shape, dtype=bias.dtype, device=bias.device)
         p.dbias = dbias.data_ptr()
         p.dbias_stride[:] = list(dbias.stride())
     ws = _workspace(p, _cabi.PASS_BWD, q.device)
@@ -279,9 +321,19 @@ class _SDPA(torch.autograd.Function):
     """Differentiation rule of the fused path (reference ``attention.py:661-700``)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, bias, mask, scale, causal, kernel):
-        out, lse = sdpa_forward(q, k, v, bias, mask, scale=scale, causal=causal, kernel=kernel)
+    def forward(ctx, q, k, v, bias, mask, scale, causal, kernel, fused):
+        # On the fused (tensor-core) path the mask is bit-packed ONCE, with the key-major copy, and the same bits
+        # serve the forward and the backward; otherwise each pass reads the byte mask.
+        packed = None
+        if fused and mask is not None:
+            want_dbias = bias is not None and ctx.needs_input_grad[3]
+            if _planned_kernel_cached(q, k, v, bias, mask, scale, causal, _cabi.PASS_BWD, kernel,
+                                      want_dbias) == _cabi.KERNEL_TCGEN05:
+                packed = pack_mask(q, k, v, mask, with_transpose=True)
+        out, lse = sdpa_forward(q, k, v, bias, mask if packed is None else packed, scale=scale, causal=causal,
+                                kernel=kernel)
         ctx.save_for_backward(q, k, v, bias, mask, out, lse)
+        ctx.packed = packed
         ctx.scale, ctx.causal, ctx.kernel = scale, causal, kernel
         ctx.mark_non_differentiable(lse)
         return out, lse
@@ -290,9 +342,9 @@ class _SDPA(torch.autograd.Function):
     def backward(ctx, dout, _dlse):
         q, k, v, bias, mask, out, lse = ctx.saved_tensors
         want_dbias = bias is not None and ctx.needs_input_grad[3]
-        dq, dk, dv, dbias = sdpa_backward(q, k, v, bias, mask, out, lse, dout, scale=ctx.scale,
-                                          causal=ctx.causal, want_dbias=want_dbias, kernel=ctx.kernel)
-        return dq, dk, dv, dbias, None, None, None, None
+        dq, dk, dv, dbias = sdpa_backward(q, k, v, bias, mask if ctx.packed is None else ctx.packed, out, lse, dout,
+                                          scale=ctx.scale, causal=ctx.causal, want_dbias=want_dbias, kernel=ctx.kernel)
+        return dq, dk, dv, dbias, None, None, None, None, None
 
 
 def scaled_dot_product_attention(
@@ -350,16 +402,20 @@ def scaled_dot_product_attention(
     mask4 = None if mask is None else _to_own_extent(mask, lead, h, s, t)
 
     kernel = _KERNELS[resolved]
+    fused = False
     if resolved == "cuda-sm100":
         chosen = _planned_kernel_cached(q4, k4, v4, bias4, mask4, resolved_scale, causal)
-        if chosen != _cabi.KERNEL_TCGEN05:
+        fused = chosen == _cabi.KERNEL_TCGEN05
+        # fp32 operands on the 3 x TF32 tensor kernels are a fused path too (fp32 is the one dtype the reference's
+        # fused kernels accept, attention.py:736-744): only a problem that leaves the tensor paths altogether warns
+        if chosen not in (_cabi.KERNEL_TCGEN05, _cabi.KERNEL_MMA_TF32X3):
             fallback(
                 function="scaled_dot_product_attention",
                 requested="cuda-sm100",
                 resolved="cuda-simt",
                 reason=(
-                    "the fused tcgen05 kernels take bf16/fp16 with d == d_v in {64, 128} and "
-                    "query/key lengths that are multiples of 8"
+                    "the fused tcgen05 kernels take bf16/fp16 with d == d_v in {64, 128} and query/key lengths "
+                    "that are multiples of 8; the fused 3xTF32 kernels take fp32 with d, d_v in {32, 64, 128}"
                 ),
                 shapes=(tuple(q.shape), tuple(k.shape), tuple(v.shape)),
                 dtype=out_dtype,
@@ -367,7 +423,7 @@ def scaled_dot_product_attention(
     needs_grad = torch.is_grad_enabled() and (
         q4.requires_grad or k4.requires_grad or v4.requires_grad or (bias4 is not None and bias4.requires_grad))
     if needs_grad:
-        out4, lse4 = _SDPA.apply(q4, k4, v4, bias4, mask4, resolved_scale, bool(causal), kernel)
+        out4, lse4 = _SDPA.apply(q4, k4, v4, bias4, mask4, resolved_scale, bool(causal), kernel, fused)
     else:   # nothing to differentiate: skip the autograd bookkeeping
         out4, lse4 = sdpa_forward(q4, k4, v4, bias4, mask4, scale=resolved_scale, causal=bool(causal), kernel=kernel)
     out = out4.reshape(*lead, h, s, dv)

@@ -36,8 +36,9 @@ class HostPipeline:
         B = host_in["q"].shape[0]
         bias = host_in.get("bias")
         self.want_dbias = bool(want_dbias and bias is not None)
-        if self.want_dbias and bias.dim() == 4 and bias.shape[0] != B:
-            chunks = 1   # the gradient of a bias shared by the batch sums over all chunks: keep one chunk
+        bias_batched = bias is not None and bias.dim() == 4 and bias.shape[0] == B and B > 1
+        if self.want_dbias and not bias_batched:
+            chunks = 1   # the gradient of a bias shared by the batch (any rank) sums over all chunks: keep one chunk
         chunks = max(1, min(chunks, B))
         bounds = [round(i * B / chunks) for i in range(chunks + 1)]
         self.slices = [slice(bounds[i], bounds[i + 1]) for i in range(chunks) if bounds[i + 1] > bounds[i]]

@@ -44,6 +44,9 @@ def local_slice(x: Optional[torch.Tensor], axis: str, world_size: int, rank: int
     """This rank's view of a (B, H, ...) operand; an axis of extent 1 (broadcast) is kept whole."""
     if x is None:
         return None
+    if axis not in ("batch", "heads"):
+        raise ValueError(f"local_slice: axis must be 'batch' or 'heads', got {axis!r} (a flattened 'pairs' split is "
+                         "expressed with bh_begin / bh_end on the whole tensors)")
     dim = batch_dim if axis == "batch" else head_dim
     n = x.shape[dim]
     if n == 1:
@@ -71,11 +74,34 @@ class _AllGatherCat(torch.autograd.Function):
 
 def all_gather_output(out_local: torch.Tensor, axis: str, group=None, *, batch_dim: int = 0,
                       head_dim: int = 1) -> torch.Tensor:
-    """Replicate the sharded output on every rank (equal shard sizes required)."""
+    """Replicate the sharded output on every rank.
+
+    ``axis`` is ``'batch'`` or ``'heads'`` and every rank must hold a shard of the same size along it (the
+    flattened ``'pairs'`` split of :func:`shard_axis` has no tensor axis to gather along: slice with
+    ``bh_begin`` / ``bh_end`` on a full-size buffer instead).  A bias that is broadcast over the sharded axis is
+    held whole by every rank, so its gradient is a partial sum per rank: the caller adds them with
+    ``torch.distributed.all_reduce`` (see :func:`all_reduce_shared_bias_grad`)."""
+    if axis not in ("batch", "heads"):
+        raise ValueError(f"all_gather_output: axis must be 'batch' or 'heads', got {axis!r}")
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return out_local
     dim = batch_dim if axis == "batch" else head_dim
+    sizes = torch.tensor([out_local.shape[dim]], dtype=torch.int64, device=out_local.device)
+    lo, hi = sizes.clone(), sizes.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+    if int(lo) != int(hi):
+        raise ValueError(f"all_gather_output: shards differ in size along {axis} ({int(lo)}..{int(hi)}); "
+                         "pad the axis or use bh_begin / bh_end on a shared full-size buffer")
     return _AllGatherCat.apply(out_local, dim, group)
+
+
+def all_reduce_shared_bias_grad(dbias: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum, over ranks, the gradient of a bias that every rank holds whole because it is broadcast over the
+    sharded axis (each rank's kernels saw only its own (batch, head) pairs).  In place; returns ``dbias``."""
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=group)
+    return dbias
 
 
 def max_over_ranks(value: float, device=None, group=None) -> float:

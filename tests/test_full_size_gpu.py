@@ -7,6 +7,9 @@ checked two ways:
   GPU in fp32 for those rows only (rows x T scores fit easily) and compared with the kernels' ``out`` and ``dq`` rows
   -- the same formula as ``oracle/sdpa_oracle.py`` (scale, + bias, mask / causal -> -inf, softmax, weights @ v and
   the closed-form row gradient);
+* sampled key blocks: for three 128-key blocks (first tile, a middle tile, last tile) the same restatement walks all
+  query rows in chunks and accumulates ``dv = p^T dO``, ``dk = scale ds^T q`` and the ``dbias`` columns of those keys,
+  which are compared by value with the kernels' ``dk``, ``dv`` and ``dbias``;
 * size-independent identities over the whole result: softmax rows sum to one, so ``sum_keys dv = sum_queries dout``;
   the score gradient of a row sums to zero, so every dbias row sums to zero; logits are bilinear in (q, k), so
   ``<q, dq> = <k, dk>`` per (batch, head).
@@ -51,6 +54,44 @@ def _rows_reference(q, k, v, dout, bias, mask, causal, scale, b, h, rows):
     return out, dq
 
 
+def _keys_reference(q, k, v, dout, bias, mask, causal, scale, b, h, key_blocks, chunk=2048):
+    """fp32 restatement of the oracle's gradients for the keys of `key_blocks` (lists of 128 key indices) of pair
+    (b, h): returns per block (dk, dv, dbias columns).  Queries are walked in chunks of `chunk` rows; each chunk
+    forms its full score rows (so lse and delta are the restatement's own, not the kernels'), then
+    p = softmax, dv += p^T dO, ds = p (dP - delta), dk += scale ds^T q, dbias[:, keys] = ds[:, keys]."""
+    f = torch.float32
+    dev = q.device
+    S, T = q.shape[2], k.shape[2]
+    kk, vv = k[b, h].to(f), v[b, h].to(f)
+    acc = [dict(dk=torch.zeros(len(kb), kk.shape[1], device=dev), dv=torch.zeros(len(kb), vv.shape[1], device=dev),
+                db=torch.zeros(S, len(kb), device=dev)) for kb in key_blocks]
+    for r0 in range(0, S, chunk):
+        rows = torch.arange(r0, min(r0 + chunk, S), device=dev)
+        qr, g = q[b, h, rows].to(f), dout[b, h, rows].to(f)
+        s = (qr @ kk.T) * scale
+        if bias is not None:
+            bb = bias[b if bias.shape[0] > 1 else 0, h if bias.shape[1] > 1 else 0]
+            s = s + (bb[rows] if bb.shape[0] > 1 else bb).to(f)
+        keep = torch.ones(len(rows), T, dtype=torch.bool, device=dev)
+        if mask is not None:
+            mm = mask[b if mask.shape[0] > 1 else 0, h if mask.shape[1] > 1 else 0]
+            keep &= mm[rows] if mm.shape[0] > 1 else mm
+        if causal:
+            keep &= torch.arange(T, device=dev)[None, :] <= rows[:, None]
+        s = s.masked_fill(~keep, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        del s, keep
+        delta = ((p @ vv) * g).sum(-1, keepdim=True)
+        for kb, a in zip(key_blocks, acc):
+            pk = p[:, kb]
+            ds = pk * (g @ vv[kb].T - delta)
+            a["dv"] += pk.T @ g
+            a["dk"] += (ds.T @ qr) * scale
+            a["db"][rows] = ds
+        del p
+    return acc
+
+
 def _close(got, ref, what):
     err = float((got.detach().float() - ref.detach().float()).abs().max())
     lim = ABS * max(1.0, float(ref.abs().max()))
@@ -90,6 +131,21 @@ def test_full_size_configuration(name):
         ref_out, ref_dq = _rows_reference(q.detach(), k.detach(), v.detach(), dout, b4, m4, causal, scale, b, h, rows)
         _close(out[b, h, rows], ref_out, (name, "out", b, h, r0))
         _close(dq[b, h, rows], ref_dq, (name, "dq", b, h, r0))
+
+    # ---- sampled key blocks: dk, dv (and dbias columns) by value ----
+    # three 128-key blocks in two (batch, head) pairs: the first tile, a middle tile at an odd offset, the last tile
+    torch.backends.cuda.matmul.allow_tf32 = False
+    first, mid, last = 0, (L // 2 // 128) * 128 + 128, L - 128
+    plan = [((0, 0), [first, mid]), ((B - 1, H - 1), [last])]
+    for (b, h), starts in plan:
+        blocks = [torch.arange(k0, k0 + 128, device=dev) for k0 in starts]
+        refs = _keys_reference(q.detach(), k.detach(), v.detach(), dout, b4, m4, causal, scale, b, h, blocks)
+        for kb, r in zip(blocks, refs):
+            k0 = int(kb[0])
+            _close(dk[b, h, kb], r["dk"], (name, "dk", b, h, k0))
+            _close(dv[b, h, kb], r["dv"], (name, "dv", b, h, k0))
+            if want_dbias:
+                _close(grads[3][b, h][:, kb], r["db"], (name, "dbias", b, h, k0))
 
     # ---- identities over the whole result ----
     # sum over keys of dv == sum over queries of dout (softmax rows sum to one); fp32 sums of 16-bit values

@@ -173,3 +173,109 @@ def test_bh_partition_covers_everything_once():
             sizes = [b - a for a, b in spans]
             assert max(sizes) - min(sizes) <= 1
     assert shard_axis(32, 8, 8) == "batch" and shard_axis(1, 16, 8) == "heads" and shard_axis(3, 5, 2) == "pairs"
+
+
+def test_plan_reports_the_family_that_runs():
+    """The planner's three answers (no launch, no GPU needed): bf16 at head dim 64 -> tcgen05; fp32 at a head dim
+    the 3 x TF32 kernels take -> the TF32 tensor path (what decides that an fp32 caller gets no fallback warning,
+    as on the reference's fused path, attention.py:736-765); a length that is not a multiple of 8 in bf16, or an
+    fp32 head dim of 40 -> plain CUDA cores."""
+    from nitrix_b200 import _cabi
+
+    assert _plan()[:2] == (_cabi.OK, _cabi.KERNEL_TCGEN05)
+    assert _plan(dtype=_cabi.F32)[:2] == (_cabi.OK, _cabi.KERNEL_MMA_TF32X3)
+    assert _plan(S=100, T=100)[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
+    assert _plan(dtype=_cabi.F32, D=40, Dv=40, q_stride=[4 * 256 * 40, 256 * 40, 40, 1], k_stride=[4 * 256 * 40, 256 * 40, 40, 1],
+                 v_stride=[4 * 256 * 40, 256 * 40, 40, 1], out_stride=[4 * 256 * 40, 256 * 40, 40, 1])[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
+    # an expanded (stride 0) head axis on k is declined by the tensor-core family
+    assert _plan(k_stride=[4 * 256 * 64, 0, 64, 1])[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
+    # the forced family reports why it cannot take a problem
+    rc, _, msg = _plan(S=100, T=100, kernel=_cabi.KERNEL_TCGEN05)
+    assert rc == _cabi.ERR_UNSUPPORTED and "multiples of 8" in msg
+
+
+def test_packed_mask_and_peer_fields_are_validated():
+    from nitrix_b200 import _cabi
+
+    assert _plan(mask=0x2000, mask_stride=[0, 0, 256, 1], mask_is_bitpacked=3)[0] == _cabi.ERR_INVALID
+    # a packed mask needs the tensor-core family
+    rc, _, msg = _plan(mask=0x2000, mask_stride=[0, 0, 256, 1], mask_is_bitpacked=1, kernel=_cabi.KERNEL_SIMT)
+    assert rc == _cabi.ERR_UNSUPPORTED and "bit-packed" in msg
+    assert _plan(mask=0x2000, mask_stride=[0, 0, 256, 1], mask_is_bitpacked=1)[:2] == (_cabi.OK, _cabi.KERNEL_TCGEN05)
+    assert _plan(n_out_peers=8)[0] == _cabi.ERR_INVALID
+    assert _plan(n_out_peers=1)[0] == _cabi.ERR_INVALID          # out_peers[0] is NULL
+    # sizes of the packed buffer: rows only / with the key-major copy / a key-only mask never needs the copy
+    def pack_bytes(stride, with_t):
+        p = _cabi.new_params()
+        p.dtype = _cabi.BF16
+        p.B, p.H, p.S, p.T, p.D, p.Dv = 2, 4, 256, 256, 64, 64
+        for f in ("q", "k", "v", "out", "lse", "mask"):
+            setattr(p, f, 0x1000)
+        for f in ("q_stride", "k_stride", "v_stride", "out_stride"):
+            getattr(p, f)[:] = [4 * 256 * 64, 256 * 64, 64, 1]
+        p.mask_stride[:] = stride
+        p.bh_end = 8
+        n = C.c_size_t(0)
+        assert _cabi.lib().nb200_mask_pack_bytes(C.byref(p), with_t, C.byref(n)) == _cabi.OK, _cabi.last_error()
+        return n.value
+    rows = 2 * 256 * 8 * 4                      # (B, 1, S, T) mask: 2 x 256 rows x 8 words
+    assert pack_bytes([256 * 256, 0, 256, 1], 0) == rows
+    assert pack_bytes([256 * 256, 0, 256, 1], 1) == 2 * rows
+    assert pack_bytes([256, 0, 0, 1], 0) == pack_bytes([256, 0, 0, 1], 1) == 256 + 256   # one row + key counts
+
+
+def test_backward_plan_takes_want_dbias_without_a_buffer():
+    """want_dbias lets the planner and the workspace query answer for a backward with a bias gradient before the
+    dbias buffer exists; a bias shared by the batch stays on tensor cores and adds an fp32 accumulator of the
+    bias' own extent to the scratch."""
+    from nitrix_b200 import _cabi
+
+    def query(want):
+        p = _cabi.new_params()
+        p.dtype = p.bias_dtype = _cabi.BF16
+        p.B, p.H, p.S, p.T, p.D, p.Dv = 2, 4, 256, 256, 128, 128
+        for f in ("q", "k", "v", "out", "lse", "dout", "dq", "dk", "dv", "bias"):
+            setattr(p, f, 0x1000)
+        for f in ("q_stride", "k_stride", "v_stride", "out_stride", "dout_stride", "dq_stride", "dk_stride", "dv_stride"):
+            getattr(p, f)[:] = [4 * 256 * 128, 256 * 128, 128, 1]
+        p.bias_stride[:] = [0, 256 * 256, 256, 1]
+        p.dbias_stride[:] = [4 * 256 * 256, 256 * 256, 256, 1]
+        p.scale, p.bh_end, p.want_dbias = 0.1, 8, want
+        kernel, need = C.c_int(0), C.c_size_t(0)
+        assert _cabi.lib().nb200_sdpa_plan(C.byref(p), _cabi.PASS_BWD, C.byref(kernel)) == _cabi.OK, _cabi.last_error()
+        assert _cabi.lib().nb200_sdpa_workspace_bytes(C.byref(p), _cabi.PASS_BWD, C.byref(need)) == _cabi.OK
+        return kernel.value, need.value
+
+    k0, n0 = query(0)
+    k1, n1 = query(1)
+    assert k0 == k1 == _cabi.KERNEL_TCGEN05
+    assert n1 - n0 == 4 * 256 * 256 * 4           # fp32 accumulator over (1, H, S, T)
+
+
+def test_jax_ffi_layer_is_complete_and_consistent():
+    """The JAX binding cannot run here (no jax, no XLA FFI headers); it must at least compile as Python, import
+    without jax, and agree with the C++ shim on the handler symbols and attribute names, and the shim must use
+    only entry points the header declares."""
+    import py_compile
+
+    py_compile.compile(str(ROOT / "nitrix_b200" / "jax_ffi.py"), doraise=True)
+    from nitrix_b200 import jax_ffi
+
+    shim = (ROOT / "ffi" / "nb200_ffi.cc").read_text()
+    symbols = set(re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\(\s*(\w+)", shim))
+    assert symbols == {jax_ffi.FWD_SYMBOL, jax_ffi.BWD_SYMBOL}
+    fwd_block, bwd_block = shim.split("XLA_FFI_DEFINE_HANDLER_SYMBOL(")[1:3]
+    assert tuple(re.findall(r'\.Attr<\w+>\("(\w+)"\)', fwd_block)) == jax_ffi.FWD_ATTRS
+    assert tuple(re.findall(r'\.Attr<\w+>\("(\w+)"\)', bwd_block)) == jax_ffi.BWD_ATTRS
+    assert fwd_block.count(".Arg<") == 5 and fwd_block.count(".Ret<") == 3
+    assert bwd_block.count(".Arg<") == 8 and bwd_block.count(".Ret<") == 5
+    header = (ROOT / "include" / "nitrix_b200_attention.h").read_text()
+    for called in set(re.findall(r"\b(nb200_\w+)\s*\(", shim)) - symbols:
+        assert re.search(rf"NB200_API[^;]*\b{called}\s*\(", header), called
+    # the trace-time queries go through the C ABI without a GPU: a covered problem gives a size, a declined one raises
+    key = ((2, 4, 256, 64), (2, 4, 256, 64), (2, 4, 256, 64), "bfloat16", None, None, (2, 1, 256, 256), 0.125, False, False)
+    assert jax_ffi._workspace_bytes(0, *key) >= 2 * 256 * 8 * 4
+    with pytest.raises(jax_ffi.NotCovered):
+        jax_ffi._workspace_bytes(0, (1, 2, 8, 512), (1, 2, 8, 512), (1, 2, 8, 512), "float32", None, None, None, 0.1, False, False)
+    with pytest.raises(ImportError):
+        jax_ffi.register()

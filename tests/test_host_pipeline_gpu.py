@@ -24,6 +24,7 @@ def _direct(att, q, k, v, dout, bias, mask, causal, scale, want_dbias):
     ("bias_causal", dict(b=4, h=2, s=256, t=256, d=64), False, 4),     # bias shared by the batch: goes up once
     ("full_bias_mask", dict(b=3, h=2, s=256, t=256, d=128), True, 2),  # per-batch bias and mask, dbias, ragged chunks
     ("key_padding", dict(b=2, h=2, s=128, t=256, d=64), False, 8),     # more chunks asked for than batch rows
+    ("bias_causal", dict(b=4, h=2, s=128, t=128, d=64), True, 4),      # gradient of a bias shared by the batch: sums over all chunks
 ])
 def test_pipeline_matches_direct_call(case, shape, want_dbias, chunks):
     from nitrix_b200.nn import attention as att
@@ -36,8 +37,10 @@ def test_pipeline_matches_direct_call(case, shape, want_dbias, chunks):
     bias, mask, causal = kw.get("bias"), kw.get("mask"), kw.get("causal", False)
     B, H, S, D = q.shape
     T = k.shape[2]
-    if bias is not None:
+    if bias is not None and not (want_dbias and bias.dim() == 3):
         bias = att._to_own_extent(bias.to(dt), (B,), H, S, T)
+    elif bias is not None:
+        bias = bias.to(dt)      # stays (H, S, T): a 3-D bias shared by the batch, with a gradient
     if mask is not None:
         mask = att._to_own_extent(mask, (B,), H, S, T)
     dout = torch.randn(q.shape[:-1] + (v.shape[-1],), generator=torch.Generator().manual_seed(3)).to(dt)

@@ -284,13 +284,12 @@ def test_tc_parity(name, dtype, d):
     if "causal" in name:
         q, k, v, kw = _cases.kernel_case(name, s=384, t=384, d=d)
     _assert_plans_tc(q, k, v, kw, dtype)
-    # a bias shared over the batch needs a reduction for its gradient (CUDA-core backward);
-    # without dbias, and for every per-batch bias, the backward runs on tensor cores too
+    # the gradient of a bias shared over the batch (or over the queries) is summed in fp32 by the tensor-core
+    # backward as well; with and without dbias the backward stays on tensor cores
     bias = kw.get("bias")
     shared_bias = bias is not None and bias.numel() < q.shape[0] * q.shape[1] * q.shape[2] * k.shape[2]
     for want_dbias in ([True, False] if shared_bias else [True]):
-        if not (shared_bias and want_dbias):
-            _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=want_dbias and bias is not None)
+        _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=want_dbias and bias is not None)
         got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100", want_dbias=want_dbias)
         _device_ok()
         check(got, ref, dtype)
@@ -308,9 +307,7 @@ def test_tc_ragged_lengths(name, shape, d):
     q, k, v, kw = _cases.kernel_case(name, d=d, **shape)
     dtype = torch.bfloat16
     _assert_plans_tc(q, k, v, kw, dtype)
-    bias = kw.get("bias")
-    shared_bias = bias is not None and bias.numel() < q.shape[0] * q.shape[1] * q.shape[2] * k.shape[2]
-    want_dbias = bias is not None and not shared_bias
+    want_dbias = kw.get("bias") is not None   # shared biases included: their gradient is summed on tensor cores too
     _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=want_dbias)
     got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100", want_dbias=want_dbias)
     _device_ok()
@@ -387,3 +384,179 @@ def test_tc_noncontiguous_heads_layout():
     got = att.scaled_dot_product_attention(*views, causal=True, backend="cuda-sm100")
     _device_ok()
     assert abserr(got, ref) < LOWP_ABS
+
+
+# --------------------------------------------------------------------------
+# corners of the tensor-core family
+# --------------------------------------------------------------------------
+def test_tc_reference_broadcast_bias_gradient_case():
+    """The reference's own gradient test (tests/test_nn_attention_kernel.py:120-140): a learned bias (h, s, t) shared
+    over the batch, gradient of bias' shape -- here in bf16 on the tensor-core backward, s = t = 256."""
+    q, k, v, kw = _cases.kernel_case("bias", s=256, t=256, d=64)
+    _assert_plans_tc(q, k, v, kw, torch.bfloat16, which=1, want_dbias=True)
+    got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100", want_dbias=True)
+    _device_ok()
+    check(got, ref, torch.bfloat16)
+    assert got[4].shape == kw["bias"].shape
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_tc_bias_shared_over_heads_and_batch_gradient(d):
+    """bias (1, 1, s, t): the fp32 accumulator is shared by every (batch, head) pair."""
+    q, k, v, kw = _cases.kernel_case("dense", b=2, h=3, s=256, t=384, d=d)
+    kw["bias"] = _cases._randn((1, 1, 256, 384), 3)
+    kw["causal"] = True
+    _assert_plans_tc(q, k, v, kw, torch.bfloat16, which=1, want_dbias=True)
+    got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100", want_dbias=True)
+    _device_ok()
+    check(got, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
+def test_tc_per_key_bias_gradient(dtype, d):
+    """bias (1, h, 1, t) with a gradient: each key's ds is summed over queries and batch by the key-major kernel."""
+    q, k, v, kw = _cases.kernel_case("key_bias", b=2, h=2, s=384, t=256, d=d)
+    _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=True)
+    got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100", want_dbias=True)
+    _device_ok()
+    check(got, ref, dtype)
+
+
+def test_tc_expanded_kv_and_expanded_cotangent():
+    """k / v expanded over the batch and over the heads (stride 0), and a cotangent that arrives as an expanded
+    view (loss = out.mean(0)): the tensor-core kernels address q, k, v, dout by absolute (batch, head), so the
+    host layer materialises such views; results must match the oracle on the materialised operands."""
+    _, att = _nb()
+    g = torch.Generator().manual_seed(0)
+    B, H, S, T, D = 3, 4, 256, 256, 64
+    dt = torch.bfloat16
+    q = torch.randn(B, H, S, D, generator=g).to(dt)
+    k1 = torch.randn(1, H, T, D, generator=g).to(dt)      # shared by the batch
+    v1 = torch.randn(1, 1, T, D, generator=g).to(dt)      # shared by batch and heads (multi-query style)
+    k_cpu, v_cpu = k1.expand(B, H, T, D), v1.expand(B, H, T, D)
+    dout = torch.ones(1, H, S, D).to(dt).expand(B, H, S, D) / B     # cotangent of out.mean(0).sum()
+    ref = O.reference_grads_torch(q, k_cpu.contiguous(), v_cpu.contiguous(), dout.contiguous())
+    qg = q.cuda().requires_grad_(True)
+    kg = k1.cuda().requires_grad_(True)
+    vg = v1.cuda().requires_grad_(True)
+    out = att.scaled_dot_product_attention(qg, kg.expand(B, H, T, D), vg.expand(B, H, T, D), backend="cuda-sm100")
+    loss = out.float().mean(0).sum()
+    dq, dk, dv = torch.autograd.grad(loss, [qg, kg, vg])
+    _device_ok()
+    assert abserr(out, ref[0]) < LOWP_ABS
+    assert abserr(dq, ref[1]) < LOWP_ABS * max(1.0, float(ref[1].abs().max()))
+    # gradients of the expanded operands are the sums over the expanded axes
+    rk = ref[2].float().sum(0, keepdim=True)
+    rv = ref[3].float().sum((0, 1), keepdim=True)
+    assert abserr(dk.float(), rk) < LOWP_ABS * max(1.0, float(rk.abs().max()))
+    assert abserr(dv.float(), rv) < LOWP_ABS * max(1.0, float(rv.abs().max()))
+
+
+def test_tc_plan_declines_stride0_qkv_through_the_c_abi():
+    """Called with a stride-0 head axis on k, the library itself declines the tensor-core family (the CUDA-core
+    family indexes by stride and takes it)."""
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    q = torch.randn(2, 4, 128, 64, device="cuda").bfloat16()
+    k = torch.randn(2, 1, 128, 64, device="cuda").bfloat16().expand(2, 4, 128, 64)
+    assert att.planned_kernel(q, k, q, None, None, causal=False) == _cabi.KERNEL_SIMT
+    assert att.planned_kernel(q, q, q, None, None, causal=False) == _cabi.KERNEL_TCGEN05
+
+
+@pytest.mark.parametrize("dtype,backend", [(torch.float32, "auto"), (torch.bfloat16, "cuda-sm100")])
+def test_qk_norm_gradients(dtype, backend):
+    """qk_norm = True through the CUDA path, forward and gradients (reference tests/test_nn_attention_kernel.py:146-191)."""
+    _, att = _nb()
+    q, k, v, kw = _cases.kernel_case("bias_causal", s=256, t=256, d=64)
+    qd, kd, vd, bd = (x.to(dtype) for x in (q, k, v, kw["bias"]))
+    dout = torch.from_numpy(np.random.RandomState(5).standard_normal(q.shape).astype(np.float32)).to(dtype)
+    acc = torch.float64 if dtype == torch.float32 else torch.float32
+    ref = O.reference_grads_torch(qd, kd, vd, dout, bias=bd, causal=True, qk_norm=True, acc_dtype=acc)
+    leaves = [x.cuda().requires_grad_(True) for x in (qd, kd, vd, bd)]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = att.scaled_dot_product_attention(*leaves[:3], bias=leaves[3], causal=True, qk_norm=True, backend=backend)
+    grads = torch.autograd.grad(out, leaves, grad_outputs=dout.cuda())
+    _device_ok()
+    check([out.detach(), *grads], list(ref), dtype)
+
+
+def test_fp32_on_the_fused_tf32_path_does_not_warn_or_raise(monkeypatch):
+    """fp32 is what the reference's fused path accepts silently (attention.py:736-744): with backend='auto' an fp32
+    call that lands on the 3 x TF32 tensor kernels must neither warn nor, under NITRIX_STRICT_BACKEND=1, raise."""
+    nb, att = _nb()
+    from nitrix_b200 import _cabi
+    q, k, v, _ = _cases.kernel_case("dense", s=344, t=344, d=64)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    assert att.planned_kernel(q, k, v, None, None, causal=False) == _cabi.KERNEL_MMA_TF32X3
+    monkeypatch.setenv("NITRIX_STRICT_BACKEND", "1")
+    nb.reset_fallback_state()
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        att.scaled_dot_product_attention(q, k, v)
+    # a head dim the tensor paths do not take still raises under strict mode
+    q2 = torch.randn(1, 2, 64, 40, device="cuda")
+    with pytest.raises(nb.NitrixBackendError):
+        att.scaled_dot_product_attention(q2, q2, q2)
+
+
+def test_packed_mask_is_packed_once_and_reused():
+    """nb200_mask_pack + mask_is_bitpacked: forward and backward on the packed bits equal the byte-mask calls."""
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    for name, shape in (("full_bias_mask", dict(s=256, t=384, d=128)), ("key_padding", dict(s=256, t=256, d=64)),
+                        ("mask_b1st", dict(s=384, t=256, d=64))):
+        q, k, v, kw = _cases.kernel_case(name, **shape)
+        b, h, s, d = q.shape
+        t = k.shape[2]
+        dt = torch.bfloat16
+        q, k, v = (x.to(dt).cuda() for x in (q, k, v))
+        bias = kw.get("bias")
+        bias4 = None if bias is None else att._to_own_extent(bias.to(dt).cuda(), (b,), h, s, t)
+        mask4 = att._to_own_extent(kw["mask"].cuda(), (b,), h, s, t)
+        scale = d ** -0.5
+        out, lse = att.sdpa_forward(q, k, v, bias4, mask4, scale=scale)
+        dout = torch.randn(out.shape, generator=torch.Generator().manual_seed(5)).to(dt).cuda()
+        want = att.sdpa_backward(q, k, v, bias4, mask4, out, lse, dout, scale=scale, want_dbias=bias4 is not None)
+        packed = att.pack_mask(q, k, v, mask4, with_transpose=True)
+        launches = _cabi.lib().nb200_launch_count()
+        out2, lse2 = att.sdpa_forward(q, k, v, bias4, packed, scale=scale)
+        got = att.sdpa_backward(q, k, v, bias4, packed, out2, lse2, dout, scale=scale, want_dbias=bias4 is not None)
+        _device_ok()
+        assert torch.equal(out, out2) and torch.equal(lse, lse2), name
+        for a, b_ in zip(got, want):
+            if b_ is None:
+                assert a is None
+            elif d == 64 and bias4 is None and a is got[0]:
+                assert abserr(a, b_) <= LOWP_ABS        # merged backward: fp32 reduction order
+            else:
+                assert torch.equal(a, b_), name
+        # no packing kernel ran in the packed calls: forward 1 launch; backward delta + kernels only
+        names_after = _cabi.lib().nb200_launch_count() - launches
+        assert names_after <= 5, names_after
+
+
+def test_bounded_wait_times_out_and_reports():
+    """The give-up branch of the kernels' mbarrier wait: a wait nothing completes expires within milliseconds, the
+    kernel returns, the status word reports a time-out once and the library keeps working."""
+    import ctypes as C
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    lib = _cabi.lib()
+    dev = torch.cuda.current_device()
+    torch.cuda.synchronize()
+    assert lib.nb200_device_status(dev) == _cabi.OK
+    result = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    rc = lib.nb200_selftest_bounded_wait(C.c_void_p(result.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == _cabi.OK, _cabi.last_error()
+    torch.cuda.synchronize()                      # returns: the wait was bounded
+    assert result.tolist() == [0, 1]              # reported "not completed" and raised the CTA abort flag
+    assert lib.nb200_device_status(dev) == _cabi.ERR_TIMEOUT
+    assert "901" in _cabi.last_error()
+    assert lib.nb200_device_status(dev) == _cabi.OK      # read-and-clear
+    # and the next real call is healthy
+    q, k, v, kw = _cases.kernel_case("causal", s=256, t=256, d=64)
+    got, ref = run_both(q, k, v, kw, torch.bfloat16, "cuda-sm100")
+    _device_ok()
+    check(got, ref, torch.bfloat16)

@@ -80,6 +80,49 @@ def test_static_scratch_backward_matches_regular_backward_twice():
     _close(got, want, torch.bfloat16)
 
 
+def test_static_scratch_with_tensor_core_backwards_after_a_larger_call():
+    """The tensor-core backwards keep more in the array than delta: packed mask words (row-major, key-major and the
+    per-sequence key counts) and, at head dim 64 without a bias gradient, the fp32 dq sums -- all of which must start
+    from zero although the array still holds an earlier, larger call's contents."""
+    from nitrix_b200 import _cabi
+    from nitrix_b200.nn import attention as att
+
+    def plans_tc(name, dtype, want_dbias, **shape):
+        q, k, v, kw = _cases.kernel_case(name, **shape)
+        b, h, s, _ = q.shape
+        t = k.shape[2]
+        bias, mask = kw.get("bias"), kw.get("mask")
+        b4 = None if bias is None else att._to_own_extent(bias.to(dtype).cuda(), (b,), h, s, t)
+        m4 = None if mask is None else att._to_own_extent(mask.cuda(), (b,), h, s, t)
+        return att.planned_kernel(q.to(dtype).cuda(), k.to(dtype).cuda(), v.to(dtype).cuda(), b4, m4,
+                                  causal=bool(kw.get("causal", False)), which=_cabi.PASS_BWD,
+                                  want_dbias=want_dbias) == _cabi.KERNEL_TCGEN05
+
+    # a larger call first: it leaves dq sums and mask words all over the array
+    big = dict(b=2, h=4, s=512, t=512, d=64)
+    assert plans_tc("mask", torch.bfloat16, False, **big)
+    got, want = _backward_both("mask", torch.bfloat16, False, **big)
+    _close(got, want, torch.bfloat16)
+    # merged backward (head dim 64, 4-D mask, no bias gradient): dq accumulator + both mask copies
+    small = dict(b=2, h=2, s=128, t=256, d=64)
+    assert plans_tc("mask", torch.bfloat16, False, **small)
+    got, want = _backward_both("mask", torch.bfloat16, False, **small)
+    _close(got, want, torch.bfloat16)
+    # key padding at head dim 64: the per-sequence key counts are formed by atomicMax and must start at zero
+    assert plans_tc("key_padding", torch.float16, False, **small)
+    got, want = _backward_both("key_padding", torch.float16, False, **small)
+    _close(got, want, torch.float16)
+    # head dim 128 with a per-batch bias gradient and a mask: query-major + key-major kernels
+    d128 = dict(b=2, h=2, s=256, t=128, d=128)
+    assert plans_tc("full_bias_mask", torch.bfloat16, True, **d128)
+    got, want = _backward_both("full_bias_mask", torch.bfloat16, True, **d128)
+    _close(got, want, torch.bfloat16)
+    # a bias shared by the batch, gradient summed in the array's fp32 accumulator by the tensor-core kernels
+    assert plans_tc("bias_causal", torch.bfloat16, True, **small)
+    got, want = _backward_both("bias_causal", torch.bfloat16, True, **small)
+    _close(got, want, torch.bfloat16)
+
+
 def test_static_scratch_rejects_oversized_problems():
     from nitrix_b200 import _cabi
     from nitrix_b200.nn import attention as att
