@@ -1,33 +1,41 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path: forward + backward TFLOP/s on B200.
 
-``python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|c1] [--impl ours|reference]``
+``python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c1|c2|c4|c5] [--impl ours|reference]``
 
-A *step* is one forward + backward pass of ``scaled_dot_product_attention``
-over one synthetic batch of the named workload (the five benchmark configurations;
-default ``c2``: bf16, B=8, H=16, L=2048, D=64, causal, ALiBi bias (1,H,L,L),
-gradients for q, k, v).  Throughput counts ALGORITHMIC flops only:
-``14 * B * H * S * T_eff * D`` per step (4 forward + 10 backward, causal halves
-the pairs, key padding counts kept keys only); softmax work is not counted.
+A *step* is one forward + backward pass of ``scaled_dot_product_attention`` over one synthetic batch of the named
+workload (the five benchmark configurations).  The default, and the headline ``value``, is ``c3`` -- bf16, B=4, H=32,
+L=4096, D=128, per-batch bias with gradient, (B,1,L,L) boolean mask -- the largest configuration that one GPU holds
+and the only one with a bias gradient and a full mask.  Throughput counts ALGORITHMIC flops only:
+``14 * B * H * S * T_eff * D`` per step (4 forward + 10 backward; causal halves the pairs, key padding counts kept
+keys only); softmax work is not counted.
 
-One JSON line is printed by rank 0 with
+Timing.  One step is captured into a CUDA graph (same kernels, same buffers as eager launches).  The timed region is
+R blocks of K replays (K = ``--steps``), each block bracketed by a barrier + synchronize and two CUDA events; R is
+chosen so that the region lasts about a second, which lets the GPU reach the clock it sustains under load and gives
+the clock sampler time to see it.  ``ms_per_step`` is the median block (max over ranks); the spread of the blocks is
+reported beside it.
 
-* ``value``: whole-job TFLOP/s with operands resident in HBM: K replays of a
-  CUDA graph of one step between two CUDA events, max over ranks (multi-GPU: every rank runs the full workload on its
-  own shard of a batch N times larger -> weak scaling, no collective);
-* ``e2e``: the same metric through the public entry point with HOST (pinned)
-  operands: H2D of q, k, v, bias, mask, dout and D2H of out, dq, dk, dv (dbias)
-  inside the timed region;
-* ``roofline``: achieved vs measured peak for the pass that dominates the step;
-* ``cpu_baseline``: the CPU oracle (torch, all host threads) on a bounded sample.
+Rank 0 prints ONE JSON line:
 
-``--impl reference`` times only that CPU implementation (the reference's own
-``jnp`` path cannot run: jax is not installed; the op-for-op torch restatement
-stands in, ``cpu_baseline.kind = "port"``).
+* ``value``: whole-job TFLOP/s of the headline workload with operands resident in HBM (multi-GPU: every rank runs
+  the full workload on its own batch -> weak scaling, no collective);
+* ``e2e``: the same metric through the public entry point with HOST (pinned) operands: H2D of q, k, v, bias, mask,
+  dout and D2H of out, dq, dk, dv (dbias) inside the timed region;
+* ``roofline``: achieved vs measured peak for the kernel that dominates the step;
+* ``workloads`` (1 GPU): the same measurement for each of the five configurations;
+* ``partition`` (N > 1): the split the configurations name -- c5 with 16 / N heads per GPU, c4 with 32 / N sequences
+  per GPU (strong scaling through ``bh_begin / bh_end``-style slices), with the optional output all-gather timed
+  both as an NCCL collective after the kernels and fused into the forward kernel's epilogue;
+* ``cpu_baseline``: the CPU oracle (torch, all host threads) on a fixed, bounded sample.
+
+``--impl reference`` times only that CPU implementation (the reference's own ``jnp`` path cannot run: jax is not
+installed; the op-for-op torch restatement stands in, ``cpu_baseline.kind = "port"``).
 """
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -53,28 +61,61 @@ KERNEL_FLOP_SHARE = {
     "sdpa_fwd_tc_kernel": 4 / 14,
     "sdpa_bwd_tc_kernel<key-major>": 8 / 14,
     "sdpa_bwd_tc_kernel<query-major>": 2 / 14,
-    "sdpa_bwd_tc_kernel<merged>": 10 / 14,      # head dim 64 without a bias gradient: dq, dk, dv from one kernel
+    "sdpa_bwd_tc_kernel<merged>": 10 / 14,      # one kernel for dq, dk, dv
+    "fwd_tf32x3_kernel": 4 / 14,
+    "bwd_dkv_tf32x3_kernel": 8 / 14,
+    "bwd_dq_tf32x3_kernel": 2 / 14,
     "simt_fwd_kernel": 4 / 14,
+    "simt_fwd_tiled_kernel": 4 / 14,
     "simt_bwd_dkv_kernel": 8 / 14,
     "simt_bwd_dq_kernel": 2 / 14,
 }
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/), full-size
-# workload, same command line as the default bench run.
-NCU_TRAFFIC_BYTES = {
-    "c2": {"sdpa_fwd_tc_kernel": 203.8e6, "sdpa_bwd_tc_kernel<merged>": 796.9e6},
-}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
+# under profiles/ (each entry names its summary).  Filled in only for kernels whose capture was taken from the build
+# that is being timed; a workload without an entry reports traffic = null.
+NCU_TRAFFIC_BYTES = {}
 
 METRIC = "fwd+bwd attention TFLOP/s"
 UNIT = "TFLOP/s"
+HEADLINE = "c3"
 
 WORKLOADS = {
-    # name: (builder, kwargs, dtype string, want_dbias, description)
     "c1": dict(B=2, H=4, L=256, D=64, dtype="f32", desc="fp32 B2 H4 L256 D64 bias(B,H,L,L)+dBias key-mask"),
     "c2": dict(B=8, H=16, L=2048, D=64, dtype="bf16", desc="bf16 B8 H16 L2048 D64 causal ALiBi bias(1,H,L,L)"),
     "c3": dict(B=4, H=32, L=4096, D=128, dtype="bf16", desc="bf16 B4 H32 L4096 D128 bias(B,H,L,L)+dBias mask(B,1,L,L)"),
     "c4": dict(B=32, H=8, L=1024, D=64, dtype="f16", desc="fp16 B32 H8 L1024 D64 key-padding mask"),
     "c5": dict(B=1, H=16, L=65536, D=128, dtype="bf16", desc="bf16 B1 H16 L65536 D128 causal key-bias(1,H,1,L)"),
 }
+# fixed CPU-oracle samples (batch, head pairs; c5 additionally a block of query rows): the same sample every run
+CPU_SAMPLE_PAIRS = {"c1": 8, "c2": 8, "c3": 4, "c4": 8, "c5": 2}
+L2_BYTES = 126e6
+
+
+def workload_bytes(name, B=None, H=None):
+    """Algorithmic bytes of one step: every operand once per pass at its stored dtype and un-broadcast size."""
+    w = WORKLOADS[name]
+    B, H, L, D = B or w["B"], H or w["H"], w["L"], w["D"]
+    esz = 4 if w["dtype"] == "f32" else 2
+    qkv = B * H * L * D * esz
+    by = 4 * qkv + B * H * L * 4                    # fwd: q k v out lse
+    by += 8 * qkv + 2 * B * H * L * 4               # bwd: q k v out dout dq dk dv lse delta
+    bias = {"c1": B * H * L * L, "c2": H * L * L, "c3": B * H * L * L, "c4": 0, "c5": H * L}[name] * esz
+    by += 2 * bias + (bias if name in ("c1", "c3") else 0)
+    mask = {"c1": B * L, "c2": 0, "c3": B * L * L, "c4": B * L, "c5": 0}[name]
+    return float(by + 2 * mask)
+
+
+def make_config(name, world, batch=None):
+    """The `config` object of the JSON line; identical for the GPU arm and the CPU reference arm."""
+    w = WORKLOADS[name]
+    b = batch or w["B"]
+    ws = workload_bytes(name, B=b)
+    cfg = {"workload": f"{name}: {w['desc']}" + (f" [batch overridden to {batch}]" if batch else ""),
+           "per_gpu_batch": b, "global_batch": b * world,
+           "sharding": f"dp{world} over batch x heads, no collective",
+           "launch": "CUDA graph replay of one fwd+bwd step",
+           "l2": ("L2 flushed between steps" if ws < 2 * L2_BYTES else f"operands ({ws / 1e6:.0f} MB) exceed the 126 MB L2")}
+    return cfg
 
 
 def build_workload(name, device, seed=0, B=None, H=None, L=None):
@@ -102,68 +143,103 @@ def build_workload(name, device, seed=0, B=None, H=None, L=None):
     if name == "c4":
         pairs = float(H) * L * float(mask.reshape(B, L).sum().item())
     flops = 14.0 * pairs * D
-    esz = q.element_size()
-    bias = kw.get("bias")
-    by = 3 * q.numel() * esz + q.numel() * esz + B * H * L * 4  # fwd: q k v out lse
-    by += 8 * q.numel() * esz + 2 * B * H * L * 4               # bwd: q k v out dout dq dk dv lse delta
-    if bias is not None:
-        by += 2 * bias.numel() * bias.element_size() + (bias.numel() * bias.element_size() if want_dbias else 0)
-    if mask is not None:
-        by += 2 * mask.numel()
-    return dict(q=q, k=k, v=v, kw=kw, want_dbias=want_dbias, flops=flops, fwd_flops=flops * 4 / 14,
-                bwd_flops=flops * 10 / 14, bytes=float(by), B=B, H=H, L=L, D=D)
+    return dict(q=q, k=k, v=v, kw=kw, want_dbias=want_dbias, flops=flops, bytes=workload_bytes(name, B=B, H=H),
+                B=B, H=H, L=L, D=D)
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs (NVML in a thread; read-only queries)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
-
-    def __enter__(self):
+    def __init__(self, index, period_s=0.02):
+        self.index, self.period, self.samples, self.stop = index, period_s, [], threading.Event()
+        self.thread, self.handle, self.nvml, self.max_mhz = None, None, None, None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-        return self
+            import pynvml
 
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001 - no NVML: fall back to nvidia-smi below
+            self.nvml = None
 
-    def __exit__(self, *exc):
-        if self.proc is not None:
-            time.sleep(0.15)
-            self.proc.terminate()  # the exact child started above
+    @staticmethod
+    def _physical_index(index):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if index < len(ids) and ids[index].isdigit():
+                return int(ids[index])
+        return index
+
+    def _poll_nvml(self):
+        n = self.nvml
+        while not self.stop.is_set():
             try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                reasons = int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)) if hasattr(
+                    n, "nvmlDeviceGetCurrentClocksEventReasons") else int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                util = int(n.nvmlDeviceGetUtilizationRates(self.handle).gpu)
+                self.samples.append((mhz, reasons, util))
+            except Exception:  # noqa: BLE001
+                pass
+            self.stop.wait(self.period)
 
-    def summary(self):
-        sm, mx, reasons = [], [], set()
-        for line in self.lines:
+    def _poll_smi(self):
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={fields}",
+                                     "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                    stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.proc = proc
+        for line in proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                mhz, self.max_mhz = float(parts[0]), float(parts[1])
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+            bits = 0
+            for (name, bit), val in zip(self.REASONS, parts[2:6]):
                 if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+                    bits |= bit
+            self.samples.append((mhz, bits, 100))
+            if self.stop.is_set():
+                break
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._poll_nvml if self.nvml else self._poll_smi, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        proc = getattr(self, "proc", None)
+        if proc is not None:
+            proc.terminate()   # the exact child started above
+            try:
+                proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        loaded = [s for s in self.samples if s[2] >= 50] or self.samples
+        if not loaded:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        bits = 0
+        for s in loaded:
+            bits |= s[1]
+        reasons = sorted(name for name, bit in self.REASONS if bits & bit)
+        return {"sm_mhz": statistics.median(s[0] for s in loaded), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(loaded)}
 
 
 def load_peaks():
@@ -176,69 +252,223 @@ def load_peaks():
     return dict(hbm=6650.0, burst=1590.0, sustained=1400.0, source="fallback")
 
 
-def cpu_reference_step(wl_name, seconds_target=10.0, steps=1, warmup=0):
-    """Times the CPU oracle (fwd + autograd bwd, fp32, all host threads) on a bounded sample of the workload:
-    a subset of (batch, head) pairs (each pair is independent), for c5 additionally a block of query rows.
-    Returns (TFLOP/s, cores, sample description, seconds per step)."""
+def cpu_reference_step(wl_name, repeats=5, warmup=1):
+    """Times the CPU oracle (fwd + autograd bwd, fp32, all host threads) on a FIXED bounded sample of the workload:
+    the first n (batch, head) pairs (each pair is independent), for c5 additionally the last block of query rows.
+    One warm-up run, then `repeats` runs; the median is reported.  Returns (TFLOP/s, cores, sample, seconds, spread)."""
     from oracle import sdpa_oracle as O
 
     torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
     w = WORKLOADS[wl_name]
-    L = w["L"]
-    rows = L
+    L, rows = w["L"], w["L"]
+    n_pairs = min(CPU_SAMPLE_PAIRS[wl_name], w["B"] * w["H"])
     if wl_name == "c5":
-        L, rows = 65536, 512  # one block of 512 query rows (the last, fullest causal block) against all keys
+        rows = 512   # the last (fullest causal) block of 512 query rows against all keys
 
-    def run(n_pairs):
-        if wl_name == "c5":
-            g = torch.Generator().manual_seed(0)
-            D = w["D"]
-            q = torch.randn(1, n_pairs, rows, D, generator=g).bfloat16()
-            k = torch.randn(1, n_pairs, L, D, generator=g).bfloat16()
-            v = torch.randn(1, n_pairs, L, D, generator=g).bfloat16()
-            bias = torch.randn(1, n_pairs, 1, L, generator=g).bfloat16()
-            # rows are the LAST block of the sequence: every key is visible except the strict upper triangle
-            mask = (torch.arange(L)[None, :] <= (L - rows + torch.arange(rows))[:, None])
-            dout = torch.randn(1, n_pairs, rows, D, generator=g).bfloat16()
-            t0 = time.perf_counter()
-            O.reference_grads_torch(q, k, v, dout, bias=bias, mask=mask, want_dbias=False)
-            dt = time.perf_counter() - t0
-            pairs = float(n_pairs) * mask.sum().item()
-            return dt, 14.0 * pairs * D
+    if wl_name == "c5":
+        g = torch.Generator().manual_seed(0)
+        D = w["D"]
+        q = torch.randn(1, n_pairs, rows, D, generator=g).bfloat16()
+        k = torch.randn(1, n_pairs, L, D, generator=g).bfloat16()
+        v = torch.randn(1, n_pairs, L, D, generator=g).bfloat16()
+        bias = torch.randn(1, n_pairs, 1, L, generator=g).bfloat16()
+        mask = (torch.arange(L)[None, :] <= (L - rows + torch.arange(rows))[:, None])
+        dout = torch.randn(1, n_pairs, rows, D, generator=g).bfloat16()
+        flops = 14.0 * float(n_pairs) * float(mask.sum().item()) * D
+        args, kw, want = (q, k, v, dout), dict(bias=bias, mask=mask), False
+    elif wl_name == "c1":
+        sub = build_workload("c1", "cpu")
+        dout = torch.randn(sub["q"].shape, generator=torch.Generator().manual_seed(5)).to(sub["q"].dtype)
+        flops, args, kw, want = sub["flops"], (sub["q"], sub["k"], sub["v"], dout), dict(sub["kw"]), True
+    else:
         sub = build_workload(wl_name, "cpu", B=1, H=n_pairs)
         dout = torch.randn(sub["q"].shape, generator=torch.Generator().manual_seed(5)).to(sub["q"].dtype)
-        kw = dict(sub["kw"])
-        t0 = time.perf_counter()
-        O.reference_grads_torch(sub["q"], sub["k"], sub["v"], dout, want_dbias=sub["want_dbias"], **kw)
-        return time.perf_counter() - t0, sub["flops"]
+        flops, args, kw, want = sub["flops"], (sub["q"], sub["k"], sub["v"], dout), dict(sub["kw"]), sub["want_dbias"]
 
-    t1, _ = run(1)  # calibration (also the warm-up)
-    total_pairs = w["B"] * w["H"]
-    n = max(1, min(total_pairs, int(seconds_target / max(t1, 1e-3))))
-    n = min(n, 16)
-    for _ in range(warmup):
-        run(n)
-    times, flops = [], 0.0
-    for _ in range(max(1, steps)):
-        dt, flops = run(n)
-        times.append(dt)
+    def run():
+        t0 = time.perf_counter()
+        O.reference_grads_torch(*args, want_dbias=want, **kw)
+        return time.perf_counter() - t0
+
+    for _ in range(max(1, warmup)):
+        run()
+    times = [run() for _ in range(max(3, repeats))]
     sec = statistics.median(times)
-    sample = f"{n} of {total_pairs} (batch, head) pairs" + (f", last {rows} query rows of L={L}" if wl_name == "c5" else f" at full L={w['L']}")
-    return flops / sec / 1e12, cores, sample, sec
+    total = w["B"] * w["H"]
+    sample = (f"first {n_pairs} of {total} (batch, head) pairs"
+              + (f", last {rows} query rows of L={L}" if wl_name == "c5" else f" at full L={L}")
+              + f"; median of {len(times)} runs after {max(1, warmup)} warm-up")
+    return flops / sec / 1e12, cores, sample, sec, [min(times), max(times)]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GPU measurement of one workload (whole, or this rank's shard of it)
+# ---------------------------------------------------------------------------------------------------------------
+class Runner:
+    """Operands of one workload on this rank's GPU and the step (fwd + bwd through the public entry point)."""
+
+    def __init__(self, name, dev, backend, seed=0, B=None, H=None):
+        from nitrix_b200.nn import attention as att
+
+        self.att, self.name, self.dev, self.backend = att, name, dev, backend
+        wl = build_workload(name, dev, seed=seed, B=B, H=H)
+        self.wl = wl
+        self.q, self.k, self.v, kw = wl["q"], wl["k"], wl["v"], wl["kw"]
+        self.bias, self.mask = kw.get("bias"), kw.get("mask")
+        self.causal, self.scale = bool(kw.get("causal", False)), kw.get("scale")
+        self.dout = torch.randn(self.q.shape, generator=torch.Generator(device=dev).manual_seed(5 + seed), device=dev,
+                                dtype=torch.float32).to(self.q.dtype)
+        for t in (self.q, self.k, self.v):
+            t.requires_grad_(True)
+        self.wrt = [self.q, self.k, self.v]
+        if self.bias is not None and wl["want_dbias"]:
+            self.bias.requires_grad_(True)
+            self.wrt.append(self.bias)
+        self.need_flush = wl["bytes"] < 2 * L2_BYTES
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.need_flush else None
+        self.graph = None
+
+    def step(self):
+        out = self.att.scaled_dot_product_attention(self.q, self.k, self.v, bias=self.bias, mask=self.mask,
+                                                    causal=self.causal, scale=self.scale, backend=self.backend)
+        grads = torch.autograd.grad(out, self.wrt, grad_outputs=self.dout)
+        return out, grads
+
+    def capture(self):
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.step()
+            for _ in range(2):
+                g.replay()
+            torch.cuda.synchronize()
+            self.graph = g
+            return None
+        except Exception as exc:  # noqa: BLE001 - any capture problem falls back to eager launches
+            torch.cuda.synchronize()
+            self.graph = None
+            return str(exc)[:200]
+
+    def run_once(self, i=0):
+        if self.need_flush:
+            self.flush.fill_(i & 0xFF)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step()
+
+
+def measure(runner, steps, warmup, region_s, barrier, local_rank, agree=float, max_blocks=2000):
+    """Timed region of R blocks x `steps` replays; returns per-step median ms, spread, clocks, launches per step.
+
+    `barrier` brackets every block (all ranks + device synchronize); `agree` turns this rank's calibration time into
+    the number every rank uses (max over ranks), so that all ranks run the same number of blocks.  A workload whose
+    operands fit in L2 has the L2 flushed before every step; the flush is kept out of the step's time by timing
+    each step with its own pair of events inside the block."""
+    from nitrix_b200 import _cabi
+
+    lib = _cabi.lib()
+    import warnings
+    warnings.simplefilter("ignore")
+    for _ in range(max(warmup, 3)):
+        runner.step()
+    torch.cuda.synchronize()
+    launches0 = lib.nb200_launch_count()
+    runner.step()
+    torch.cuda.synchronize()
+    launches_per_step = int(lib.nb200_launch_count() - launches0)
+    graph_error = runner.capture()
+
+    def block():
+        """K steps between a barrier + synchronize on both sides; returns the milliseconds the steps took."""
+        if runner.need_flush:
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            barrier()
+            for i, (a, b) in enumerate(evs):
+                runner.flush.fill_(i & 0xFF)
+                a.record()
+                if runner.graph is not None:
+                    runner.graph.replay()
+                else:
+                    runner.step()
+                b.record()
+            barrier()
+            return sum(a.elapsed_time(b) for a, b in evs)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for i in range(steps):
+            runner.run_once(i)
+        b.record()
+        barrier()
+        return a.elapsed_time(b)
+
+    block_ms = agree(max(block(), 1e-3))   # calibration block: sizes the region
+    blocks = int(min(max_blocks, max(3, round(region_s * 1e3 / block_ms))))
+    times = []
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(blocks):
+            times.append(block() / steps)
+    assert lib.nb200_device_status(local_rank) == 0, _cabi.last_error()
+    return dict(ms=statistics.median(times), spread=[min(times), max(times)], blocks=blocks, clocks=clocks.summary(),
+                launches_per_step=launches_per_step, graph_error=graph_error, region_ms=sum(times) * steps)
+
+
+def kernel_times(runner, steps):
+    """Average launch duration of every kernel of a step: the library records a CUDA event on the launching stream
+    after each kernel it enqueues (eager launches; a few microseconds per kernel, kept out of the headline region)."""
+    from nitrix_b200 import _cabi
+
+    lib = _cabi.lib()
+    lib.nb200_profile(1)
+    for i in range(steps):
+        if runner.need_flush:
+            runner.flush.fill_(i & 0xFF)
+        runner.step()
+    torch.cuda.synchronize()
+    ms = _cabi.kernel_times()
+    lib.nb200_profile(0)
+    return {n: v[1] / v[0] for n, v in ms.items()}, {n: v[0] for n, v in ms.items()}
+
+
+def roofline_record(name, wl, step_ms, kernels, peaks, with_traffic=True):
+    """Roofline of the dominant kernel plus the whole step against both tensor peaks and the HBM bound."""
+    if not kernels:
+        return None
+    dom = max(kernels, key=lambda n: kernels[n])
+    share = KERNEL_FLOP_SHARE.get(dom)
+    dom_flops = wl["flops"] * share if share is not None else None
+    achieved = dom_flops / (kernels[dom] * 1e-3) / 1e12 if dom_flops else None
+    t_burst = max(wl["flops"] / (peaks["burst"] * 1e12), wl["bytes"] / (peaks["hbm"] * 1e9))
+    t_sust = max(wl["flops"] / (peaks["sustained"] * 1e12), wl["bytes"] / (peaks["hbm"] * 1e9))
+    return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["burst"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["burst"] if achieved else None,
+            "frac_of_sustained": achieved / peaks["sustained"] if achieved else None,
+            "traffic": NCU_TRAFFIC_BYTES.get(name, {}).get(dom) if with_traffic else None,
+            "avg_launch_ms": kernels[dom], "algorithmic_flops_per_launch": dom_flops,
+            "peak_source": (f"bf16 dense, of {peaks['source']}: frac uses the burst figure ({peaks['burst']:.0f}; the kernel's "
+                            f"launch time comes from a pass in which it is timed by itself), frac_of_sustained the "
+                            f"seconds-long figure ({peaks['sustained']:.0f})"),
+            "kernels_ms": {n: round(v, 5) for n, v in sorted(kernels.items())},
+            "step_vs_roofline": {"burst": t_burst / (step_ms * 1e-3), "sustained": t_sust / (step_ms * 1e-3),
+                                 "tensor_bound_ms": wl["flops"] / (peaks["burst"] * 1e12) * 1e3,
+                                 "hbm_bound_ms": wl["bytes"] / (peaks["hbm"] * 1e9) * 1e3}}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--backend", default="auto")
     ap.add_argument("--batch", type=int, default=None, help="override the workload's batch size (profiling captures)")
+    ap.add_argument("--region-seconds", type=float, default=1.0, help="length of the headline timed region")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-workload table and the partition record")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -246,18 +476,17 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     wl_name = args.workload
     w = WORKLOADS[wl_name]
-    config = {"workload": f"{wl_name}: {w['desc']}", "per_gpu_batch": w["B"], "global_batch": w["B"] * world,
-              "sharding": f"dp{world} over batch x heads, no collective"}
+    config = make_config(wl_name, world, args.batch)
 
     if args.impl == "reference":
         if rank != 0:
             return
-        val, cores, sample, sec = cpu_reference_step(wl_name, seconds_target=5.0, steps=args.steps if args.steps < 5 else 3,
-                                                     warmup=min(args.warmup, 1))
+        val, cores, sample, sec, spread = cpu_reference_step(wl_name)
         line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+                "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                 "spread_s": spread},
                 "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line))
@@ -265,191 +494,236 @@ def main():
 
     import torch.distributed as dist
     from nitrix_b200 import _cabi
-    from nitrix_b200.nn import attention as att
     from nitrix_b200.parallel import max_over_ranks
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     lib = _cabi.lib()
-
-    wl = build_workload(wl_name, dev, seed=rank, B=args.batch)
-    if args.batch:
-        config["per_gpu_batch"], config["global_batch"] = args.batch, args.batch * world
-        config["workload"] += f" [batch overridden to {args.batch}]"
-    q, k, v, kw = wl["q"], wl["k"], wl["v"], wl["kw"]
-    bias = kw.get("bias")
-    mask = kw.get("mask")
-    causal = bool(kw.get("causal", False))
-    scale = kw.get("scale")
-    dout = torch.randn(q.shape, generator=torch.Generator(device=dev).manual_seed(5 + rank), device=dev,
-                       dtype=torch.float32).to(q.dtype)
-    q.requires_grad_(True)
-    k.requires_grad_(True)
-    v.requires_grad_(True)
-    if bias is not None and wl["want_dbias"]:
-        bias.requires_grad_(True)
-    wrt = [q, k, v] + ([bias] if (bias is not None and wl["want_dbias"]) else [])
-
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    working_set = wl["bytes"]
-    need_flush = working_set < 2 * 126e6
-
-    def step(ev=None):
-        if ev:
-            ev[0].record()
-        out = att.scaled_dot_product_attention(q, k, v, bias=bias, mask=mask, causal=causal, scale=scale,
-                                               backend=args.backend)
-        if ev:
-            ev[1].record()
-        grads = torch.autograd.grad(out, wrt, grad_outputs=dout)
-        if ev:
-            ev[2].record()
-        return out, grads
-
-    import warnings
-    warnings.simplefilter("ignore")
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    launches0 = lib.nb200_launch_count()
-    barrier()
-    with ClockSampler(local_rank) as clocks:
-        for i in range(args.steps):
-            if need_flush:
-                flush.fill_(i & 0xFF)
-            step(events[i])
-        barrier()
-    launches = lib.nb200_launch_count() - launches0
-    assert lib.nb200_device_status(local_rank) == 0, _cabi.last_error()
-    # second pass over the same steps with the library's per-kernel events on (a few microseconds per kernel,
-    # so it is kept out of the headline region): average launch duration of every kernel
-    kernel_ms = {}
-    if rank == 0:
-        lib.nb200_profile(1)
-        for i in range(args.steps):
-            if need_flush:
-                flush.fill_(i & 0xFF)
-            step()
-        torch.cuda.synchronize()
-        kernel_ms = _cabi.kernel_times()
-        lib.nb200_profile(0)
-    fwd_ms = [e[0].elapsed_time(e[1]) for e in events]
-    bwd_ms = [e[1].elapsed_time(e[2]) for e in events]
-    eager_ms = statistics.fmean(f + b for f, b in zip(fwd_ms, bwd_ms))
-    # The step is a handful of sub-millisecond kernels, so host launch latency shows up as soon as several ranks
-    # share the host's cores.  The headline region therefore replays a CUDA graph of one step (same kernels, same
-    # buffers): K replays between two events, a barrier and a synchronize on both sides.  If the capture fails the
-    # eagerly launched steps above are the measurement.
-    step_ms, graphed = eager_ms, False
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        for _ in range(3):
-            graph.replay()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        with ClockSampler(local_rank) as clocks_g:
-            g0.record()
-            for i in range(args.steps):
-                if need_flush:
-                    flush.fill_(i & 0xFF)
-                graph.replay()
-            g1.record()
-            barrier()
-        assert lib.nb200_device_status(local_rank) == 0, _cabi.last_error()
-        step_ms, graphed, clocks = g0.elapsed_time(g1) / args.steps, True, clocks_g
-    except Exception as exc:  # noqa: BLE001 - any capture problem falls back to the eager measurement
-        config["graph_error"] = str(exc)[:200]
-        torch.cuda.synchronize()
-    config["launch"] = "CUDA graph replay of one fwd+bwd step" if graphed else "eager launches"
-    step_ms = max_over_ranks(step_ms, dev)
+    # ---- headline: the whole workload on every rank ----
+    runner = Runner(wl_name, dev, args.backend, seed=rank, B=args.batch)
+    wl = runner.wl
+    m = measure(runner, args.steps, args.warmup, args.region_seconds, barrier, local_rank,
+                agree=lambda x: max_over_ranks(x, dev))
+    if m["graph_error"]:
+        config["launch"], config["graph_error"] = "eager launches", m["graph_error"]
+    step_ms = max_over_ranks(m["ms"], dev)
     value = world * wl["flops"] / (step_ms * 1e-3) / 1e12
+    kernels, kernel_launches = ({}, {})
+    if rank == 0:
+        kernels, kernel_launches = kernel_times(runner, min(args.steps, 10))
 
     # ---- end to end: host operands, copies inside the timed region ----
     e2e = None
     if not args.no_e2e:
-        host_in = {n: t.detach().cpu().pin_memory() for n, t in (("q", q), ("k", k), ("v", v), ("dout", dout))}
-        if bias is not None:
-            host_in["bias"] = bias.detach().cpu().pin_memory()
-        if mask is not None:
-            host_in["mask"] = mask.cpu().pin_memory()
-        # batch chunks move up, run and come down on three streams at once (nitrix_b200.nn.host_pipeline)
-        from nitrix_b200.nn.host_pipeline import HostPipeline
-        pipe = HostPipeline(host_in, device=dev, causal=causal, scale=scale, want_dbias=wl["want_dbias"],
-                            chunks=8, backend=args.backend)
-        h2d = pipe.h2d_bytes()
-
-        def e2e_step():
+        try:
+            host_in = {n: t.detach().cpu().pin_memory() for n, t in (("q", runner.q), ("k", runner.k), ("v", runner.v),
+                                                                    ("dout", runner.dout))}
+            if runner.bias is not None:
+                host_in["bias"] = runner.bias.detach().cpu().pin_memory()
+            if runner.mask is not None:
+                host_in["mask"] = runner.mask.cpu().pin_memory()
+            # batch chunks move up, run and come down on three streams at once (nitrix_b200.nn.host_pipeline)
+            from nitrix_b200.nn.host_pipeline import HostPipeline
+            pipe = HostPipeline(host_in, device=dev, causal=runner.causal, scale=runner.scale, want_dbias=wl["want_dbias"],
+                                chunks=8, backend=args.backend)
+            h2d = pipe.h2d_bytes()
             pipe.run()
-            return pipe.d2h_bytes()
+            d2h = pipe.d2h_bytes()
+            pipe.run()
+            torch.cuda.synchronize()
+            n_e2e = 5 if wl["bytes"] > 1e9 else max(5, min(args.steps, 20))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record()
+            for _ in range(n_e2e):
+                pipe.run()
+            e1.record()
+            barrier()
+            my_ms = e0.elapsed_time(e1) / n_e2e
+            e2e_ms = max_over_ranks(my_ms, dev)
+            e2e = {"value": world * wl["flops"] / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                   "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                   "h2d_gbs_per_rank": h2d / (my_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (my_ms * 1e-3) / 1e9,
+                   "kernel_ms_per_step": step_ms,
+                   "limiter": "host<->device copies (PCIe): copy-in, kernels and copy-out of batch chunks overlap on "
+                              "three streams, so a step lasts as long as its larger copy direction",
+                   "how": f"{len(pipe.slices)} batch chunks pipelined over copy-in / kernel / copy-out streams"}
+            del pipe, host_in
+        except Exception as exc:  # noqa: BLE001 - e.g. pinned host memory refused: report, keep the device numbers
+            e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                   "error": str(exc)[:200]}
+            torch.cuda.synchronize()
 
-        d2h = e2e_step()
-        e2e_step()
-        n_e2e = max(3, min(args.steps, 10))
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        e1.record()
-        barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / n_e2e, dev)
-        e2e = {"value": world * wl["flops"] / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-               "how": f"{len(pipe.slices)} batch chunks pipelined over copy-in / kernel / copy-out streams"}
+    peaks = load_peaks()
+    roofline = roofline_record(wl_name, wl, step_ms, kernels, peaks) if rank == 0 else None
+    headline_clocks = m["clocks"]
+    headline_launches = m["launches_per_step"]
+    del runner
+    torch.cuda.empty_cache()
+
+    # ---- every configuration on one GPU ----
+    workloads = None
+    if world == 1 and not args.no_extra and not args.batch:
+        workloads = []
+        for name in sorted(WORKLOADS):
+            try:
+                if name == wl_name:
+                    mm, kk, ww = m, kernels, wl
+                else:
+                    r = Runner(name, dev, args.backend, seed=0)
+                    mm = measure(r, args.steps, args.warmup, 0.4, barrier, local_rank)
+                    kk, _ = kernel_times(r, min(args.steps, 10))
+                    ww = r.wl
+                    del r
+                    torch.cuda.empty_cache()
+                rec = roofline_record(name, ww, mm["ms"], kk, peaks)
+                mhz = mm["clocks"]["sm_mhz"]
+                workloads.append({"workload": f"{name}: {WORKLOADS[name]['desc']}", "ms_per_step": mm["ms"],
+                                  "ms_spread": mm["spread"], "blocks": mm["blocks"],
+                                  "tflops": ww["flops"] / (mm["ms"] * 1e-3) / 1e12,
+                                  "ms_x_sm_mhz": mm["ms"] * mhz if mhz else None,
+                                  "step_vs_roofline": rec["step_vs_roofline"] if rec else None,
+                                  "dominant_kernel": rec["kernel"] if rec else None, "frac": rec["frac"] if rec else None,
+                                  "kernels_ms": rec["kernels_ms"] if rec else None, "clocks": mm["clocks"],
+                                  "launches_per_step": mm["launches_per_step"],
+                                  "launch": "eager" if mm["graph_error"] else "graph"})
+            except Exception as exc:  # noqa: BLE001
+                workloads.append({"workload": name, "error": str(exc)[:200]})
+                torch.cuda.synchronize()
+
+    # ---- the split the configurations name: c5 heads / c4 sequences over the GPUs of the box ----
+    partition = None
+    if world > 1 and not args.no_extra:
+        partition = partition_record(world, rank, local_rank, dev, args, barrier, peaks)
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    peaks = load_peaks()
-    f_ms, b_ms = statistics.fmean(fwd_ms), statistics.fmean(bwd_ms)
-    peak = peaks["burst"]
-    # dominant kernel: per-kernel CUDA-event times recorded by the library on its launching stream
-    dom = max(kernel_ms, key=lambda n: kernel_ms[n][1]) if kernel_ms else None
-    roofline = None
-    if dom is not None:
-        dom_launches, total_ms = kernel_ms[dom]
-        avg_ms = total_ms / dom_launches
-        share = KERNEL_FLOP_SHARE.get(dom)
-        dom_flops = wl["flops"] * share if share is not None else None
-        achieved = dom_flops / (avg_ms * 1e-3) / 1e12 if dom_flops else None
-        traffic = NCU_TRAFFIC_BYTES.get(wl_name, {}).get(dom) if not args.batch else None
-        roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                    "frac": achieved / peak if achieved else None, "traffic": traffic,
-                    "avg_launch_ms": avg_ms, "launches": dom_launches,
-                    "algorithmic_flops_per_launch": dom_flops,
-                    "peak_source": f"bf16 dense burst (kernels timed alone), of {peaks['source']}",
-                    "kernels_ms": {n: round(v[1] / v[0], 5) for n, v in sorted(kernel_ms.items())},
-                    "fwd": {"ms": f_ms, "tflops": wl["fwd_flops"] / (f_ms * 1e-3) / 1e12},
-                    "bwd": {"ms": b_ms, "tflops": wl["bwd_flops"] / (b_ms * 1e-3) / 1e12},
-                    "eager_ms_per_step": eager_ms,
-                    "step_vs_roofline": max(wl["flops"] / (peak * 1e12), wl["bytes"] / (peaks["hbm"] * 1e9)) / (step_ms * 1e-3)}
     cpu = None
     if not args.no_cpu_baseline and world == 1:
-        val, cores, sample, _ = cpu_reference_step(wl_name, seconds_target=10.0)
-        cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
-    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"],
-            "data": "synthetic",
-            "config": dict(config, l2="L2 flushed between steps" if need_flush else
-                           f"operands ({working_set / 1e6:.0f} MB) exceed the 126 MB L2"),
-            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-            "cpu_baseline": cpu}
+        val, cores, sample, _, spread = cpu_reference_step(wl_name)
+        cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample, "spread_s": spread}
+    mhz = headline_clocks["sm_mhz"]
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "ms_spread": m["spread"], "blocks": m["blocks"],
+            "timed_region_ms": m["region_ms"], "ms_x_sm_mhz": step_ms * mhz if mhz else None,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": config, "clocks": headline_clocks, "e2e": e2e,
+            "gpu_launches": int(headline_launches) * args.steps * m["blocks"], "launches_per_step": headline_launches,
+            "roofline": roofline, "cpu_baseline": cpu, "workloads": workloads, "partition": partition}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def partition_record(world, rank, local_rank, dev, args, barrier, peaks):
+    """c5 with 16 / N heads per GPU and c4 with 32 / N sequences per GPU (strong scaling): every rank builds and
+    runs only its shard; no collective in the timed loop.  For c5 the optional replicated output is timed twice:
+    NCCL all-gather after the forward, and the forward kernel storing straight into the peers' buffers."""
+    import torch.distributed as dist
+    from nitrix_b200 import parallel as P
+    from nitrix_b200.parallel import max_over_ranks
+
+    rec = {}
+    for name, axis in (("c5", "heads"), ("c4", "batch")):
+        w = WORKLOADS[name]
+        item = {"axis": axis}
+        ms = float("nan")
+        flops = 0.0
+        runner = None
+        try:
+            n = w["H"] if axis == "heads" else w["B"]
+            lo, hi = P.bh_partition(n, world, rank)
+            kw = dict(H=hi - lo) if axis == "heads" else dict(B=hi - lo)
+            runner = Runner(name, dev, args.backend, seed=100 + rank, **kw)
+            flops = runner.wl["flops"]
+            item["per_gpu"] = f"{hi - lo} {axis if axis == 'heads' else 'sequences'}"
+        except Exception as exc:  # noqa: BLE001 - every rank still takes part in the collectives below
+            item["error"] = str(exc)[:200]
+        local = None
+        if runner is not None:
+            try:
+                local = measure(runner, args.steps, args.warmup, 0.5, lambda: torch.cuda.synchronize(), local_rank)
+                ms = local["ms"]
+            except Exception as exc:  # noqa: BLE001
+                item["error"] = str(exc)[:200]
+                torch.cuda.synchronize()
+        barrier()
+        ms_max = max_over_ranks(ms, dev)
+        total = torch.tensor([flops], dtype=torch.float64, device=dev)
+        dist.all_reduce(total)
+        item.update({"ms_per_step": ms_max, "tflops": float(total.item()) / (ms_max * 1e-3) / 1e12 if ms_max == ms_max else None,
+                     "clocks": local["clocks"] if local else None})
+        if name == "c5" and runner is not None:
+            item.update(gather_timing(runner, world, rank, dev, barrier))
+        rec[name] = item
+        del runner
+        torch.cuda.empty_cache()
+    return rec
+
+
+def gather_timing(runner, world, rank, dev, barrier, reps=5):
+    """Forward of this rank's heads followed by an NCCL all-gather of the output, against the forward whose epilogue
+    stores the output rows into every rank's buffer itself.  Times are per forward, max over ranks."""
+    import torch.distributed as dist
+    from nitrix_b200 import parallel as P
+    from nitrix_b200.nn import attention as att
+    from nitrix_b200.parallel import max_over_ranks
+
+    out = {}
+    q, k, v, bias = (t.detach() for t in (runner.q, runner.k, runner.v, runner.bias))
+    scale = q.shape[-1] ** -0.5
+    B, Hl, S, D = q.shape
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        barrier()
+        return max_over_ranks(a.elapsed_time(b) / reps, dev)
+
+    try:
+        out["fwd_ms"] = timed(lambda: att.sdpa_forward(q, k, v, bias, None, scale=scale, causal=True))
+        out["fwd_plus_nccl_all_gather_ms"] = timed(
+            lambda: P.all_gather_output(att.sdpa_forward(q, k, v, bias, None, scale=scale, causal=True)[0], "heads"))
+        out["all_gather_bytes_per_rank"] = int(q.numel() * q.element_size())
+    except Exception as exc:  # noqa: BLE001
+        out["gather_error"] = str(exc)[:200]
+        torch.cuda.synchronize()
+    ok = torch.ones(1, dtype=torch.int32, device=dev)
+    rep = None
+    try:
+        rep = P.ReplicatedOutput((B, Hl * world, S, D), q.dtype, dev)
+    except Exception as exc:  # noqa: BLE001
+        out["fused_gather_error"] = str(exc)[:200]
+        ok.zero_()
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 1:
+        view = rep.local.narrow(1, rank * Hl, Hl)
+        peers = rep.peers_of(view)
+
+        def fused():
+            att.sdpa_forward(q, k, v, bias, None, scale=scale, causal=True, out=view, out_peers=peers)
+            rep.wait()
+
+        out["fwd_fused_all_gather_ms"] = timed(fused)
+        rep.close()
+    return out
 
 
 if __name__ == "__main__":

@@ -259,11 +259,13 @@ def _planned_kernel_cached(q, k, v, bias, mask, scale, causal, which=_cabi.PASS_
 
 
 def sdpa_forward(q, k, v, bias=None, mask=None, *, scale: float, causal: bool = False,
-                 kernel: int = _cabi.KERNEL_AUTO, bh_range=None, out=None, lse=None):
+                 kernel: int = _cabi.KERNEL_AUTO, bh_range=None, out=None, lse=None, out_peers=()):
     """Enqueue the forward on the current stream; 4-D operands.  Returns ``(out, lse)``.
 
     ``q`` (B,H,S,D), ``k`` (B,H,T,D), ``v`` (B,H,T,Dv); ``bias`` / ``mask`` 4-D
     with each extent 1 (broadcast) or full.  ``lse`` is fp32 (B,H,S), base 2.
+    ``out_peers``: device addresses (ints) of further buffers with ``out``'s shape and strides that receive every
+    output row as well (the fused all-gather of :mod:`nitrix_b200.parallel`).
     """
     B, H, S, _ = q.shape
     Dv = v.shape[3]
@@ -274,6 +276,9 @@ def sdpa_forward(q, k, v, bias=None, mask=None, *, scale: float, causal: bool = 
     p = _cabi.new_params()
     mask_b = _mask_bytes(mask)
     _fill_common(p, q, k, v, out, lse, bias, mask_b, scale, causal, kernel, bh_range)
+    p.n_out_peers = len(out_peers)
+    for i, ptr in enumerate(out_peers):
+        p.out_peers[i] = int(ptr)
     ws = _workspace(p, _cabi.PASS_FWD, q.device)
     _launch(_cabi.lib().nb200_sdpa_fwd, p, q.device, "nb200_sdpa_fwd")
     del ws  # same-stream reuse is ordered by the caching allocator
