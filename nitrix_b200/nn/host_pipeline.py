@@ -92,7 +92,8 @@ class HostPipeline:
                 if bias is not None and self.batched["bias"]:
                     bias = bias[sl]
                 if bias is not None and self.want_dbias:
-                    bias = bias.requires_grad_(True)
+                    # a fresh leaf over the staging buffer (the buffer itself is overwritten by the next step's copy)
+                    bias = bias.detach().requires_grad_(True)
                     wrt.append(bias)
                 mask = self.dev.get("mask")
                 if mask is not None and self.batched["mask"]:
