@@ -26,6 +26,7 @@
 // builds the per-query addends -lse / (scale log2e), -delta as MMA operands), 4-7 / 8-11 two element-wise groups
 // that take alternate steps (one owner row per thread).  All waits are bounded.
 #include <math.h>
+#include <stdlib.h>
 
 #include "sdpa_tc_bwd.cuh"
 
@@ -48,40 +49,6 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) gives: 65536
 static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kWorkerRegs - kLaunchRegs) * 256,
               "worker warps would wait forever for registers the producer warps never release");
 
-struct BwdArgs {
-  int H, S, T;
-  int bh_begin;
-  int causal;
-  float scale;
-  int bias_mode;
-  // Key-major kernel, tile-mode bias: added by the tensor core, scores^T += bias^T (hi I + lo I) with
-  // hi + lo = 1 / scale split into two 16-bit values (lo = 0 when 1 / scale is exact in 16 bits).  Then
-  // scores * scale holds scale * q.k + bias and the element-wise warps never read the bias column-wise.
-  int bias_mma;
-  float inv_scale_hi, inv_scale_lo;
-  // Query-major kernel, per-key terms (a bias or a mask with no query axis) and a positive scale: added to the scores
-  // by one K = 16 MMA step, scores += W C^T with C[key] = bias[key] / scale in three 16-bit terms, -inf for a dropped
-  // key; the element-wise warps then neither read the bias nor apply that mask.
-  int key_aug;
-  int bias_b_mul, bias_h_mul;
-  const void* bias;             // key mode base
-  int64_t bias_bs, bias_hs;
-  MaskBits mask;
-  int mask_key_only;            // key-major: the mask has no query axis (use mask.rows per key)
-  const float* lse;
-  const float* delta;
-  void* out1; int64_t o1s[3];   // key-major: dv
-  void* out2; int64_t o2s[3];   // dq | dk
-  void* dbias; int64_t dbs[4];  // query-major only; null when not requested
-  // Gradient of a bias that is broadcast over some axis: fp32 sums over the broadcast axes, in an accumulator of the
-  // bias' own extent (zero on entry; acc_s = its element strides over (b, h, row), 0 on broadcast axes, unit key
-  // stride).  A bias with a query axis is summed by the query-major kernel (ds tiles added with 16-byte
-  // reductions), a per-key bias by the key-major kernel (each thread sums its key's ds over the queries it
-  // streams and adds once).
-  float* dbias_acc; int64_t acc_s[3];
-  float* dq_acc;                // merged kernel: fp32 (bh_count, S, 64) sums of ds K, zero on entry
-  int* status;
-};
 
 template <int D, bool kMerged>
 struct BwdSmem {
@@ -994,13 +961,28 @@ namespace {
 // steps and adds it to an fp32 copy of dq, which a last kernel scales and casts.
 bool use_merged(const Problem& pr) { return pr.D == 64 && !pr.want_dbias && pr.S % kTile == 0; }
 size_t round_up_256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Head dim 128: the one-kernel backward of sdpa_tc_bwd_d128.cu (NB200_BWD_D128_ONEPASS=0 in the environment keeps
+// the query-major + key-major pair, for comparisons).
+bool use_d128(const Problem& pr, int dtype) {
+  static const bool enabled = [] {
+    const char* e = getenv("NB200_BWD_D128_ONEPASS");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled || pr.D != 128) return false;
+  const int mode = bias_mode_of(pr);
+  float hi = 0.f, lo = 0.f;
+  const bool bias_mma = mode == kBiasTile && split_inv_scale(pr.scale, dtype == NB200_BF16, &hi, &lo);
+  return d128_merged_supported(pr, mode, bias_mma);
+}
 }  // namespace
 
-size_t bwd_workspace_bytes(const Problem& pr, int, int) {
+size_t bwd_workspace_bytes(const Problem& pr, int dtype, int) {
   size_t mask_ws = 0;
   mask_plan_for_pass(pr, true, &mask_ws);
   size_t bytes = round_up_256(mask_ws);
   if (use_merged(pr)) bytes += sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D;
+  else if (use_d128(pr, dtype)) bytes += d128_acc_bytes(pr);
   return bytes;
 }
 
@@ -1012,7 +994,8 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   const MaskPackPlan mp = mask_plan_for_pass(pr, true, &mask_ws);
   mask_ws = round_up_256(mask_ws);
   const bool merged = use_merged(pr);
-  const size_t acc_bytes = merged ? sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D : 0;
+  const bool d128 = !merged && use_d128(pr, dtype);
+  const size_t acc_bytes = merged ? sizeof(float) * size_t(pr.bh_count) * pr.S * pr.D : (d128 ? d128_acc_bytes(pr) : 0);
   if (mask_ws + acc_bytes > ws_bytes) {
     set_error("tensor-core backward needs %zu workspace bytes", mask_ws + acc_bytes);
     return NB200_ERR_WORKSPACE;
@@ -1074,6 +1057,33 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
                                                           pr.bh_begin, n_chunks, pr.scale);
     count_launch();
     return check_launch("dq_finish_kernel");
+  }
+  if (d128) {
+    // one kernel for dq, dk, dv (and the dbias tiles): fp32 dq sums in the workspace, zero on entry
+    BwdArgs ak = a;
+    ak.dq_acc = reinterpret_cast<float*>(static_cast<char*>(ws) + mask_ws);
+    ak.acc_rows = (pr.S + kStep - 1) / kStep * kStep;
+    cudaError_t e = cudaMemsetAsync(ak.dq_acc, 0, acc_bytes, stream);
+    if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
+    ak.out1 = pr.dv;
+    ak.out2 = pr.dk;
+    for (int i = 0; i < 3; ++i) { ak.o1s[i] = pr.dvs[i]; ak.o2s[i] = pr.dks[i]; }
+    D128Maps maps{k128, v128, q64, g64, bias_k, q64};
+    if (pr.dbias) {
+      ak.dbias = pr.dbias;
+      if (!make_tile_map(&maps.dbias, pr.dbias, pr.S, pr.T, pr.H, pr.B, pr.dbs[2], pr.dbs[1], pr.dbs[0], kStep, &why)) {
+        set_error("dbias tensor map: %s", why);
+        return NB200_ERR_LAUNCH;
+      }
+      if (pr.causal || key_only) {
+        // query / key ranges the kernel never visits (above the diagonal, past the last kept key) get exact zeros
+        e = cudaMemsetAsync(pr.dbias, 0, size_t(pr.B) * pr.H * pr.S * pr.T * 2, stream);
+        if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
+      }
+    }
+    if (int rc = launch_bwd_d128(maps, ak, bf16, a.bias_mode == kBiasTile, (pr.T + kTile - 1) / kTile, pr.bh_count, stream))
+      return rc;
+    return launch_dq_finish_d128(pr, ak.dq_acc, ak.acc_rows, bf16, stream);
   }
   // query-major: dq (+ dbias)
   {

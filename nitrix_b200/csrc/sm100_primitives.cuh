@@ -132,6 +132,20 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
+// Tiled store shared memory -> global (bulk async-group completion): the tile is read from this CTA's shared memory
+// in the layout the tensor map's swizzle mode describes; rows / columns past the tensor's extent are dropped.  The
+// innermost coordinate times the element size must be a multiple of 16 bytes and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All of this thread's committed bulk groups have finished READING their shared-memory sources.
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All of this thread's committed bulk groups are complete (their global writes are done).
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- TMEM -------------------------------------------------------------------
 // One warp allocates `cols` (power of two >= 32) columns; the base address is
 // written to shared memory at `dst_smem`.

@@ -77,7 +77,7 @@ def test_bh_ranges_equal_whole_call(case, dtype, shape, want_dbias):
         ranges = [(0, n // 2 + 1), (n // 2 + 1, n)]
     parts = _run_ranges(q, k, v, bias, mask, causal, want_dbias, ranges)
     names = ("out", "lse", "dq", "dk", "dv", "dbias")
-    merged = q.shape[-1] == 64 and not want_dbias
+    merged = True   # dq of the one-kernel backwards (head dim 64 without dbias, head dim 128) goes through fp32 atomics
     for name, a, b in zip(names, parts, whole):
         if b is None:
             assert a is None
