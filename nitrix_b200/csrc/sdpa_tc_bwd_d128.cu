@@ -35,22 +35,38 @@ constexpr int kThreads = 384;
 constexpr int kStep = 64;                     // streamed queries per step
 constexpr int kYBoxBytes = kStep * 128;       // one 64-row x 128-byte box
 constexpr int kD = 128;
-constexpr int kProducerRegs = 72;
+constexpr int kProducerRegs = 88;
 constexpr int kWorkerRegs = 208;
 constexpr int kLaunchRegs = 168;              // what __launch_bounds__(384, 1) gives
 static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kWorkerRegs - kLaunchRegs) * 256,
               "worker warps would wait forever for registers the producer warps never release");
 
+#ifdef NB200_PROBE
+// Development aid (not compiled into the library): cycles one element-wise warp spends in each phase of its steps.
+__device__ long long g_probe[32];
+#define PROBE_DECL long long pt_ = clock64(); const bool probe_ = blockIdx.x == 3 && blockIdx.y == 1 && warp == 4 && lane == 0
+#define IPROBE_DECL long long ipt_ = clock64(); const bool iprobe_ = blockIdx.x == 3 && blockIdx.y == 1
+#define IPROBE(i) do { const long long now_ = clock64(); if (iprobe_) g_probe[i] += now_ - ipt_; ipt_ = now_; } while (0)
+#define PROBE(i) do { const long long now_ = clock64(); if (probe_) g_probe[i] += now_ - pt_; pt_ = now_; } while (0)
+#else
+#define PROBE_DECL
+#define PROBE(i)
+#define IPROBE_DECL
+#define IPROBE(i)
+#endif
+
 template <bool kTileBias>
 struct Smem {
   static constexpr int kXBytes = kTile * kD * 2;                // K or V tile
   static constexpr int kYBytes = kStep * kD * 2;                // Q or dO step
-  static constexpr int kYStages = 3;
+  // Q / dO ring: a stage is held from its products until its dV / dK, two steps later, and a refill takes about a
+  // step to arrive; without bias tiles there is room for a fourth stage
+  static constexpr int kYStages = kTileBias ? 3 : 4;
   static constexpr int kYStageBytes = 2 * kYBytes + 1024;       // Q, dO, then lse[64] + delta[64]
   static constexpr int kBiasSlots = kTileBias ? 2 : 0;          // [64 queries x 128 keys] = two 64 x 64 boxes, 16 KB
-  // ds^T tiles.  With bias tiles only one fits: the writer of step n + 1 then waits for the MMAs (and the dbias
-  // store) of step n, which are issued half a step earlier.
-  static constexpr int kDsBufs = kTileBias ? 1 : 2;
+  // One ds^T tile: the writer of step n + 1 waits for the MMAs (and the dbias store) of step n, which are issued
+  // half a step earlier.
+  static constexpr int kDsBufs = 1;
   static constexpr int kX = 0;
   static constexpr int kY = kX + 2 * kXBytes;
   static constexpr int kBias = kY + kYStages * kYStageBytes;
@@ -102,6 +118,15 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   const int kept = kept_key_length(a.mask, b, h, a.T);
   if (o0 >= kept) s_end = s_begin;
   const int n_steps = s_end - s_begin;
+  // The CTAs of one (batch, head) run side by side and all add into the same dq accumulator; were they to walk the
+  // queries in the same order they would hit the same lines with their reductions at the same moment.  Each key tile
+  // therefore starts its walk at a different query step and wraps around.
+  const int rot = n_steps > 0 ? int((blockIdx.x * 2u) % uint32_t(n_steps)) : 0;
+  auto step_row = [&](int n) {   // first query row of the n-th step this CTA visits
+    int j = n + rot;
+    if (j >= n_steps) j -= n_steps;
+    return (s_begin + j) * kStep;
+  };
   const bool store_dbias = a.dbias != nullptr;
 
   if (threadIdx.x < L::kNumBars) {
@@ -128,7 +153,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     }
     const int n_first = n_steps < NY ? n_steps : NY;
     for (int n = 0; n < n_first; ++n) {
-      const int r0 = (s_begin + n) * kStep;
+      const int r0 = step_row(n);
       const uint32_t ybase = sbase + L::kY + n * L::kYStageBytes;
       const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
       mbar_expect_tx(bar(Y_FULL + n), 2 * L::kYBytes + 2 * row_bytes);
@@ -188,39 +213,40 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
 
   if (warp < 4) {
   reg_dealloc<kProducerRegs>();
-  if (warp == 0) {
-    // ---------------- Q / dO ring producer (owner tiles and the first NY stages were issued during start-up) ----
-    if (elect_one() && n_steps > NY) {
-      for (int n = NY; n < n_steps; ++n) {
-        const int st = n % NY;
-        if (!wait_or_abort(bar(Y_EMPTY + st), ((n / NY) & 1) ^ 1, abort_flag, a.status, 301)) break;
-        const int r0 = (s_begin + n) * kStep;
-        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-        const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
-        mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + 2 * row_bytes);
-#pragma unroll
-        for (int x = 0; x < kD / 64; ++x) {
-          tma_load_4d(ybase + x * kYBoxBytes, &tm_q, bar(Y_FULL + st), x * 64, r0, h, b);
-          tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_do, bar(Y_FULL + st), x * 64, r0, h, b);
-        }
-        const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
-        bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
-        bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- bias tiles in, dbias tiles out: ONE thread polls both duties ----------------
-    // (two blocking loops in two lanes of a warp would depend on how divergent lanes are scheduled; one thread that
-    // tests both conditions without blocking does not)
-    if (lane == 0 && (kTileBias || store_dbias)) {
-      int bn = kTileBias ? min(n_steps, 2) : n_steps;   // next bias tile to fetch (the first two went out at start-up)
-      int sn = store_dbias ? 0 : n_steps;               // next dbias tile to store
+  if (warp == 1) {
+    // ---------------- every TMA duty of the step loop: ONE thread probes the three barriers ----------------
+    // Q / dO ring refills, bias tiles in, dbias tiles out.  (Blocking loops in several lanes of a warp would depend on
+    // how divergent lanes are scheduled; one thread that waits on each barrier in turn, suspended in hardware for at
+    // most a short time hint, does not, and it serves whichever duty completes first.)
+    if (lane == 0 && n_steps > 0) {
+      int yn = min(n_steps, NY);                         // next ring stage to refill (the first NY went out at start-up)
+      int bn = kTileBias ? min(n_steps, 2) : n_steps;    // next bias tile to fetch (the first two went out at start-up)
+      int sn = store_dbias ? 0 : n_steps;                // next dbias tile to store
       const long long t0 = clock64();
       uint32_t idle = 0;
-      while (bn < n_steps || sn < n_steps) {
+      while (yn < n_steps || bn < n_steps || sn < n_steps) {
+        const int pending = (yn < n_steps) + (bn < n_steps) + (sn < n_steps);
+        const uint32_t hint = pending > 1 ? 64u : 4096u;
         bool progressed = false;
-        if (bn < n_steps && mbar_test_wait(bar(B_EMPTY + (bn & 1)), ((bn >> 1) & 1) ^ 1)) {
-          const int slot = bn & 1, r0 = (s_begin + bn) * kStep;
+        if (yn < n_steps && mbar_try_wait_hint(bar(Y_EMPTY + yn % NY), ((yn / NY) & 1) ^ 1, hint)) {
+          const int st = yn % NY, r0 = step_row(yn);
+          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+          // lse / delta rows of the step that exist (S is a multiple of 8, so the copy stays a multiple of 16 bytes)
+          const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+          mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + 2 * row_bytes);
+#pragma unroll
+          for (int x = 0; x < kD / 64; ++x) {
+            tma_load_4d(ybase + x * kYBoxBytes, &tm_q, bar(Y_FULL + st), x * 64, r0, h, b);
+            tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_do, bar(Y_FULL + st), x * 64, r0, h, b);
+          }
+          const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+          bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
+          bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
+          ++yn;
+          progressed = true;
+        }
+        if (bn < n_steps && mbar_try_wait_hint(bar(B_EMPTY + (bn & 1)), ((bn >> 1) & 1) ^ 1, hint)) {
+          const int slot = bn & 1, r0 = step_row(bn);
           mbar_expect_tx(bar(B_FULL + slot), kBoxBytes);
           const uint32_t dst = sbase + L::kBias + slot * kBoxBytes;
           tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), o0, r0, h * a.bias_h_mul, b * a.bias_b_mul);
@@ -228,10 +254,10 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           ++bn;
           progressed = true;
         }
-        if (sn < n_steps && mbar_test_wait(bar(E_READY + (sn & 1)), (sn >> 1) & 1)) {
+        if (sn < n_steps && mbar_try_wait_hint(bar(E_READY + (sn & 1)), (sn >> 1) & 1, hint)) {
           // the group's writes were fenced towards the async proxy before it arrived on E_READY
           const uint32_t src = sbase + L::kDs + (sn % NDS) * kBoxBytes;
-          const int r0 = (s_begin + sn) * kStep;
+          const int r0 = step_row(sn);
           tma_store_4d(&tm_dbias, src, o0, r0, h, b);
           if (o0 + 64 < a.T) tma_store_4d(&tm_dbias, src + kYBoxBytes, o0 + 64, r0, h, b);
           bulk_commit_group();
@@ -240,118 +266,123 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           ++sn;
           progressed = true;
         }
-        if (!progressed) {
-          __nanosleep(64);
-          if ((++idle & 0x3FF) == 0) {
-            if (*abort_flag) break;
-            if (clock64() - t0 > 20 * kWaitCycles) {   // the whole CTA's life is bounded as well
-              *abort_flag = 1;
-              atomicExch(a.status, 302);
-              break;
-            }
+        if (!progressed && (++idle & 0x3F) == 0) {
+          if (*abort_flag) break;
+          if (*reinterpret_cast<volatile int*>(a.status) != 0) { *abort_flag = 1; break; }
+          if (clock64() - t0 > 20 * kWaitCycles) {   // the whole CTA's life is bounded as well
+            *abort_flag = 1;
+            atomicExch(a.status, 302);
+            break;
           }
         }
       }
       if (store_dbias) bulk_wait_group0();         // every dbias tile has reached global memory
     }
   } else if (warp == 2) {
-    // ---------------- MMA issuer ----------------
+    // ---------------- MMA issuer 1: the products of every step ----------------
+    // Two threads issue MMAs, this one the products and warp 0 the accumulating ones.  A single issuing thread
+    // needs ~2000 cycles of instruction issue per step for the 40-odd MMAs, as much as the element-wise warps need
+    // for their step, and in one instruction stream the products of step n + 2 queue behind the accumulating MMAs of
+    // step n, which wait for the element-wise warps -- the very warps that then wait for those products.
     if (elect_one() && n_steps > 0) {
       constexpr uint32_t idesc_prod = make_idesc(kBf16, kTile, kStep, false, false);
-      constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, kD, false, true);     // dV: A from TMEM, B = dO MN-major
-      constexpr uint32_t idesc_dk = make_idesc(kBf16, kTile, kD, true, true);       // dK: A = ds^T MN-major, B = Q MN-major
-      constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, kStep, true, false);   // dQ^T: A = K MN-major, B = ds^T K-major
       constexpr uint32_t idesc_bias = make_idesc(kBf16, kTile, 16, true, false);    // bias^T (MN-major) x 16 x 16 identity
       bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 303);
       const uint64_t kdesc = make_smem_desc(sbase + L::kX, 16, 1024);
       const uint64_t vdesc = make_smem_desc(sbase + L::kX + L::kXBytes, 16, 1024);
+      const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
+      IPROBE_DECL;
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int st = n % NY, s = n & 1;
+        IPROBE(16);
+        ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 304);
+        IPROBE(17);
+        // one product stage: it may be overwritten once the warps of step n - 1 hold it in registers
+        if (ok && n >= 1) ok = wait_or_abort(bar(P_FREE + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, a.status, 309);
+        IPROBE(18);
+        if (ok) ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 312);
+        IPROBE(19);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+        const uint64_t qdesc = make_smem_desc(ybase, 16, 1024), gdesc = make_smem_desc(ybase + L::kYBytes, 16, 1024);
+        const uint32_t aslot = sbase + L::kAug + s * L::kAugSlotBytes;
+        // the two products are independent accumulation chains: their K steps are issued alternately
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+          const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
+          mma_ss(tm_p1, kdesc + xo, qdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
+          mma_ss(tm_p2, vdesc + xo, gdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
+        }
+        // P1 += W C1^T (C1: -lse / (scale log2e)), P2 += W C2^T (C2: -delta)
+        mma_ss(tm_p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
+        mma_ss(tm_p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
+        mma_commit(bar(AUG_FREE + s));
+        if constexpr (kTileBias) {
+          // P1[key, q] += bias^T[key, q'] (hi I + lo I)[q', q], 16 queries at a time: A = 16 rows of the slot read
+          // MN-major (two 64-key boxes), B = the 16 x 16 scaled identity, D = 16 columns of P1
+          IPROBE(16);
+          ok = wait_or_abort(bar(B_FULL + s), (n >> 1) & 1, abort_flag, a.status, 311);
+          IPROBE(20);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t adesc = make_smem_desc(sbase + L::kBias + s * kBoxBytes, kYBoxBytes, 1024);
+          const int n_ident = a.inv_scale_lo != 0.f ? 2 : 1;
+          for (int tile = 0; tile < n_ident; ++tile) {
+            const uint64_t bdesc = make_smem_desc_noswizzle(sbase + L::kIdent + tile * 512, 128, 256);
+#pragma unroll
+            for (int kk = 0; kk < kStep / 16; ++kk)
+              mma_ss(tm_p1 + kk * 16, adesc + uint64_t((kk * 2048) >> 4), bdesc, idesc_bias, 1u);
+          }
+          mma_commit(bar(B_EMPTY + s));
+        }
+        mma_commit(bar(PROD_FULL + s));
+      }
+    }
+  } else if (warp == 0) {
+    // ---------------- MMA issuer 2: dV, dK and dQ^T of every step ----------------
+    if (elect_one() && n_steps > 0) {
+      constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, kD, false, true);     // dV: A from TMEM, B = dO MN-major
+      constexpr uint32_t idesc_dk = make_idesc(kBf16, kTile, kD, true, true);       // dK: A = ds^T MN-major, B = Q MN-major
+      constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, kStep, true, false);   // dQ^T: A = K MN-major, B = ds^T K-major
+      bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 303);
       const uint64_t kmn = make_smem_desc(sbase + L::kX, kBoxBytes, 1024);          // K as [d x key], d contiguous
-      for (int n = 0; n <= n_steps && ok; ++n) {
-        if (n < n_steps) {
-          const int st = n % NY, s = n & 1;
-          ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 304);
-          // one product stage: it may be overwritten once the warps of step n - 1 hold it in registers
-          if (ok && n >= 1) ok = wait_or_abort(bar(P_FREE + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, a.status, 309);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          const uint64_t qdesc = make_smem_desc(ybase, 16, 1024), gdesc = make_smem_desc(ybase + L::kYBytes, 16, 1024);
+      for (int m = 0; m < n_steps && ok; ++m) {
+        const int st = m % NY, s = m & 1;
+        ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 305);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+        const uint64_t qmn = make_smem_desc(ybase, kYBoxBytes, 1024);                    // Q as [query x d], d contiguous
+        const uint64_t gmn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);      // dO likewise
+        const uint32_t dsbuf = sbase + L::kDs + (m % NDS) * kBoxBytes;
+        const uint64_t ds_mn = make_smem_desc(dsbuf, kYBoxBytes, 1024);                  // ds^T as [key x query] A operand
+        const uint32_t e1 = tm_e + s * 32;
+        // dV += p^T dO (p from TMEM) and dK += ds^T Q: two independent chains, issued alternately
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) {
-            const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
-            const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
-            mma_ss(tm_p1, kdesc + xo, qdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
-          }
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) {
-            const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
-            const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
-            mma_ss(tm_p2, vdesc + xo, gdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
-          }
-          if constexpr (kTileBias) {
-            // P1[key, q] += bias^T[key, q'] (hi I + lo I)[q', q], 16 queries at a time: A = 16 rows of the slot read
-            // MN-major (two 64-key boxes), B = the 16 x 16 scaled identity, D = 16 columns of P1
-            const int slot = n & 1;
-            ok = wait_or_abort(bar(B_FULL + slot), (n >> 1) & 1, abort_flag, a.status, 311);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint64_t adesc = make_smem_desc(sbase + L::kBias + slot * kBoxBytes, kYBoxBytes, 1024);
-            const int n_ident = a.inv_scale_lo != 0.f ? 2 : 1;
-            for (int tile = 0; tile < n_ident; ++tile) {
-              const uint64_t bdesc = make_smem_desc_noswizzle(sbase + L::kIdent + tile * 512, 128, 256);
-#pragma unroll
-              for (int kk = 0; kk < kStep / 16; ++kk)
-                mma_ss(tm_p1 + kk * 16, adesc + uint64_t((kk * 2048) >> 4), bdesc, idesc_bias, 1u);
-            }
-          }
-          // P1 += W C1^T (C1: -lse / (scale log2e)), P2 += W C2^T (C2: -delta)
-          ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 312);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
-          const uint32_t aslot = sbase + L::kAug + s * L::kAugSlotBytes;
-          mma_ss(tm_p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
-          mma_ss(tm_p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
-          mma_commit(bar(PROD_FULL + s));
-          mma_commit(bar(AUG_FREE + s));
-          if (kTileBias) mma_commit(bar(B_EMPTY + (n & 1)));
+        for (int kk = 0; kk < kStep / 16; ++kk) {
+          mma_ts(tm_dv, e1 + kk * 8, gmn + uint64_t((kk * 2048) >> 4), idesc_acc, (m > 0 || kk > 0) ? 1u : 0u);
+          mma_ss(tm_dk, ds_mn + uint64_t((kk * 2048) >> 4), qmn + uint64_t((kk * 2048) >> 4), idesc_dk,
+                 (m > 0 || kk > 0) ? 1u : 0u);
         }
-        if (n >= 1) {
-          const int m = n - 1, st = m % NY, s = m & 1;
-          ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 305);
+        mma_commit(bar(E_FREE + s));             // p of this stage may be rewritten
+        mma_commit(bar(Y_EMPTY + st));           // the last readers of this Q / dO stage
+        // dQ^T[d, query] = sum_key K[key, d] ds[key, query]; the previous tile must have been drained
+        if (m >= 1) {
+          ok = wait_or_abort(bar(DQ_FREE + ((m - 1) & 1)), ((m - 1) >> 1) & 1, abort_flag, a.status, 315);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          const uint64_t qmn = make_smem_desc(ybase, kYBoxBytes, 1024);                    // Q as [query x d], d contiguous
-          const uint64_t gmn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);      // dO likewise
-          const uint32_t dsbuf = sbase + L::kDs + (m % NDS) * kBoxBytes;
-          const uint64_t ds_mn = make_smem_desc(dsbuf, kYBoxBytes, 1024);                  // ds^T as [key x query] A operand
-          const uint32_t e1 = tm_e + s * 32;
-          // dV += p^T dO (p from TMEM), dK += ds^T Q
-#pragma unroll
-          for (int kk = 0; kk < kStep / 16; ++kk)
-            mma_ts(tm_dv, e1 + kk * 8, gmn + uint64_t((kk * 2048) >> 4), idesc_acc, (m > 0 || kk > 0) ? 1u : 0u);
-          mma_commit(bar(E_FREE + s));             // p of this stage may be rewritten once dV has read it
-#pragma unroll
-          for (int kk = 0; kk < kStep / 16; ++kk)
-            mma_ss(tm_dk, ds_mn + uint64_t((kk * 2048) >> 4), qmn + uint64_t((kk * 2048) >> 4), idesc_dk,
-                   (m > 0 || kk > 0) ? 1u : 0u);
-          // dQ^T[d, query] = sum_key K[key, d] ds[key, query]; the previous tile must have been drained
-          if (m >= 1) {
-            ok = wait_or_abort(bar(DQ_FREE + ((m - 1) & 1)), ((m - 1) >> 1) & 1, abort_flag, a.status, 315);
-            if (!ok) break;
-            tc_fence_after_sync();
-          }
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk) {
-            const uint64_t bo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);    // 16 keys of a query row
-            mma_ss(tm_dq, kmn + uint64_t((kk * 2048) >> 4), make_smem_desc(dsbuf, 16, 1024) + bo, idesc_dq, kk > 0 ? 1u : 0u);
-          }
-          mma_commit(bar(DQ_FULL + (m & 1)));
-          mma_commit(bar(DS_FREE + (m & 1)));      // the ds^T tile has been read by dK and dQ^T
-          mma_commit(bar(Y_EMPTY + st));
-          if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
         }
+        const uint64_t ds_k = make_smem_desc(dsbuf, 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          const uint64_t bo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);    // 16 keys of a query row
+          mma_ss(tm_dq, kmn + uint64_t((kk * 2048) >> 4), ds_k + bo, idesc_dq, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(DQ_FULL + (m & 1)));
+        mma_commit(bar(DS_FREE + (m & 1)));      // the ds^T tile has been read by dK and dQ^T
+        if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
       }
     }
   } else {
@@ -368,7 +399,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int q = lane + 32 * e;
-        const bool live = (s_begin + n) * kStep + q < a.S;   // rows past S were not copied; the addend must be finite
+        const bool live = step_row(n) + q < a.S;   // rows past S were not copied; the addend must be finite
         const float c[2] = {live ? -ld[q] * inv_mul : 0.f, live ? -ld[kStep + q] : 0.f};
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile) {
@@ -434,8 +465,11 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     // dq accumulator of this (batch, head): [query / 4][d][query % 4] floats, so that one warp-wide reduction of
     // four queries covers 512 contiguous bytes (lanes = 32 consecutive d)
 
+    PROBE_DECL;
     auto drain = [&](int j) -> bool {
+      PROBE(0);
       if (!wait_or_abort(bar(DQ_FULL + (j & 1)), (j >> 1) & 1, abort_flag, a.status, 316)) return false;
+      PROBE(10);
       tc_fence_after_sync();
       uint32_t v[kStep];
       tmem_ld32(tm_dq + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
@@ -444,15 +478,17 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_FREE + (j & 1)));
-      float* dst = a.dq_acc + int64_t(blockIdx.y) * a.acc_rows * kD + r * 4 + int64_t((s_begin + j) * (kStep / 4)) * (kD * 4);
+      PROBE(11);
+      float* dst = a.dq_acc + int64_t(blockIdx.y) * a.acc_rows * kD + r * 4 + int64_t(step_row(j) / 4) * (kD * 4);
 #pragma unroll
       for (int c = 0; c < kStep / 4; ++c) red_add_v4(dst + c * (kD * 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      PROBE(12);
       return true;
     };
 
     for (int n = grp; n < n_steps && ok; n += 2) {
       const int s = n & 1;
-      const int r0 = (s_begin + n) * kStep;
+      const int r0 = step_row(n);
       // keep bits over the step's 64 queries: query r0 + c needs c < S - r0 and (causal) r0 + c >= key
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
       if (mbits) {
@@ -472,8 +508,10 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         if (key_dropped) keep[0] = keep[1] = 0u;
       }
 
+      PROBE(1);
       ok = wait_or_abort(bar(PROD_FULL + s), (n >> 1) & 1, abort_flag, a.status, 306);
       if (!ok) break;
+      PROBE(2);
       tc_fence_after_sync();
       float2 t[kStep / 2], dp[kStep / 2];
       {
@@ -488,6 +526,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_FREE + s));
+        PROBE(3);
 #pragma unroll
         for (int i = 0; i < kStep / 2; ++i) {
           t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
@@ -514,12 +553,14 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         e1[c] = pack2<kBf16>(p.x, p.y);
         e2[c] = pack2<kBf16>(ds.x, ds.y);
       }
+      PROBE(4);
       // p of this stage is still being read by dV of step n - 2
       if (n >= 2) {
         ok = wait_or_abort(bar(E_FREE + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 310);
         if (!ok) break;
         tc_fence_after_sync();
       }
+      PROBE(5);
       tmem_st32(tm_e + s * 32 + lane_addr, e1);
       // the ds^T buffer was last read by the MMAs (and the dbias store) of step n - NDS
       if (n >= NDS) {
@@ -527,6 +568,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         ok = wait_or_abort(bar(DS_FREE + (m & 1)), (m >> 1) & 1, abort_flag, a.status, 317);
         if (!ok) break;
       }
+      PROBE(6);
       {
         const uint32_t tile = sbase + L::kDs + (n % NDS) * kBoxBytes + ds_thread;
 #pragma unroll
@@ -537,10 +579,12 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         }
         fence_proxy_async_smem();
       }
+      PROBE(7);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(E_READY + s));
+      PROBE(8);
       // dQ^T of the previous step (the other group's) is complete by now: add it to the accumulator
       if (n >= 1) ok = drain(n - 1);
     }
@@ -698,3 +742,12 @@ int launch_dq_finish_d128(const Problem& pr, const float* acc, int acc_rows, boo
 
 }  // namespace tc
 }  // namespace nb200
+
+#ifdef NB200_PROBE
+extern "C" NB200_API int nb200_debug_probe(long long* out32, int reset) {
+  long long zero[32] = {};
+  if (out32) cudaMemcpyFromSymbol(out32, nb200::tc::g_probe, sizeof(zero));
+  if (reset) cudaMemcpyToSymbol(nb200::tc::g_probe, zero, sizeof(zero));
+  return 0;
+}
+#endif
