@@ -80,7 +80,7 @@ struct Smem {
   static constexpr int kWeights = kIdent + 1024;
   static constexpr int kAug = kWeights + kWeightBytes;          // two slots
   static constexpr int kBars = kAug + 2 * kAugSlotBytes;
-  static constexpr int kNumBars = 1 + 2 * kYStages + 2 * 11 + 1;
+  static constexpr int kNumBars = 1 + 2 * kYStages + 2 * 13 + 1;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
   static_assert(kY % 1024 == 0 && kBias % 1024 == 0 && kDs % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -102,8 +102,8 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
   auto bar = [&](int i) { return smem_u32(bars + i); };
-  constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, P_FREE = PROD_FULL + 2,
-                E_READY = P_FREE + 2, E_FREE = E_READY + 2, DS_FREE = E_FREE + 2, DQ_FULL = DS_FREE + 2,
+  constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, P_FREE = PROD_FULL + 4,
+                E_READY = P_FREE + 4, E_FREE = E_READY + 2, DS_FREE = E_FREE + 2, DQ_FULL = DS_FREE + 2,
                 DQ_FREE = DQ_FULL + 2, B_FULL = DQ_FREE + 2, B_EMPTY = B_FULL + 2, AUG_FULL = B_EMPTY + 2,
                 AUG_FREE = AUG_FULL + 2, ACC_DONE = AUG_FREE + 2;
   static_assert(ACC_DONE + 1 == L::kNumBars, "barrier count");
@@ -132,7 +132,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   if (threadIdx.x < L::kNumBars) {
     const int i = threadIdx.x;
     uint32_t count = 1;
-    if (i >= P_FREE && i < P_FREE + 2) count = 4;      // one lane per warp of the group
+    if (i >= P_FREE && i < P_FREE + 4) count = 4;      // one lane per warp of the group
     if (i >= E_READY && i < E_READY + 2) count = 4;
     if (i >= DQ_FREE && i < DQ_FREE + 2) count = 4;
     if (i >= DS_FREE && i < DS_FREE + 2) count = store_dbias ? 2 : 1;   // the MMAs, and the dbias store
@@ -297,7 +297,9 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         IPROBE(16);
         ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 304);
         IPROBE(17);
-        // one product stage: it may be overwritten once the warps of step n - 1 hold it in registers
+        // One stage per product, each with its own pair of barriers (PROD_FULL / P_FREE + 0, 1: scores; + 2, 3: dP):
+        // a product may be overwritten once the warps of step n - 1 hold it in registers, and the warps take the
+        // scores of step n -- and start on their exponentials -- while the tensor core still computes its dP.
         if (ok && n >= 1) ok = wait_or_abort(bar(P_FREE + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, a.status, 309);
         IPROBE(18);
         if (ok) ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 312);
@@ -307,18 +309,14 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
         const uint64_t qdesc = make_smem_desc(ybase, 16, 1024), gdesc = make_smem_desc(ybase + L::kYBytes, 16, 1024);
         const uint32_t aslot = sbase + L::kAug + s * L::kAugSlotBytes;
-        // the two products are independent accumulation chains: their K steps are issued alternately
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
           const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
           const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
           mma_ss(tm_p1, kdesc + xo, qdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
-          mma_ss(tm_p2, vdesc + xo, gdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
         }
-        // P1 += W C1^T (C1: -lse / (scale log2e)), P2 += W C2^T (C2: -delta)
+        // P1 += W C1^T (C1: -lse / (scale log2e))
         mma_ss(tm_p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
-        mma_ss(tm_p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
-        mma_commit(bar(AUG_FREE + s));
         if constexpr (kTileBias) {
           // P1[key, q] += bias^T[key, q'] (hi I + lo I)[q', q], 16 queries at a time: A = 16 rows of the slot read
           // MN-major (two 64-key boxes), B = the 16 x 16 scaled identity, D = 16 columns of P1
@@ -338,6 +336,21 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           mma_commit(bar(B_EMPTY + s));
         }
         mma_commit(bar(PROD_FULL + s));
+        IPROBE(16);
+        if (n >= 1) ok = wait_or_abort(bar(P_FREE + 2 + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, a.status, 319);
+        IPROBE(23);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+          const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
+          mma_ss(tm_p2, vdesc + xo, gdesc + yo, idesc_prod, kk > 0 ? 1u : 0u);
+        }
+        // P2 += W C2^T (C2: -delta)
+        mma_ss(tm_p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
+        mma_commit(bar(AUG_FREE + s));
+        mma_commit(bar(PROD_FULL + 2 + s));
       }
     }
   } else if (warp == 0) {
@@ -513,32 +526,26 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       if (!ok) break;
       PROBE(2);
       tc_fence_after_sync();
-      float2 t[kStep / 2], dp[kStep / 2];
+      // the scores first: p = exp2(t log2e) (they arrive with -lse already added) while dP is still being computed
+      float2 t[kStep / 2];
       {
-        uint32_t raw[2 * kStep];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld32(tm_p1 + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
-          tmem_ld32(tm_p2 + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[kStep + c * 32]));
-        }
+        uint32_t raw[kStep];
+        tmem_ld32(tm_p1 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+        tmem_ld32(tm_p1 + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
         tmem_wait_ld();
-        // both products are in registers: the MMA issuer may compute the next step's
+        // the scores are in registers: the MMA issuer may compute the next step's
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_FREE + s));
         PROBE(3);
 #pragma unroll
-        for (int i = 0; i < kStep / 2; ++i) {
-          t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
-          dp[i] = make_float2(__uint_as_float(raw[kStep + 2 * i]), __uint_as_float(raw[kStep + 2 * i + 1]));
-        }
+        for (int i = 0; i < kStep / 2; ++i) t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
       }
       if (!fold_scale) {
         const float2 own2 = make_float2(bias_own, bias_own);
 #pragma unroll
         for (int c = 0; c < kStep / 2; ++c) t[c] = __ffma2_rn(t[c], scale2, own2);
       }
-      // p = exp2(t log2e) and ds = p dp: the products arrive with -lse and -delta already added
       uint32_t e1[kStep / 2], e2[kStep / 2];
       const bool need_mask = __any_sync(0xffffffffu, (keep[0] & keep[1]) != 0xffffffffu);
 #pragma unroll
@@ -548,10 +555,8 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           if (!((keep[c >> 4] >> ((2 * c) & 31)) & 1u)) x.x = -INFINITY;
           if (!((keep[c >> 4] >> ((2 * c + 1) & 31)) & 1u)) x.y = -INFINITY;
         }
-        const float2 p = make_float2(ex2(x.x), ex2(x.y));
-        const float2 ds = __fmul2_rn(p, dp[c]);
-        e1[c] = pack2<kBf16>(p.x, p.y);
-        e2[c] = pack2<kBf16>(ds.x, ds.y);
+        t[c] = make_float2(ex2(x.x), ex2(x.y));
+        e1[c] = pack2<kBf16>(t[c].x, t[c].y);
       }
       PROBE(4);
       // p of this stage is still being read by dV of step n - 2
@@ -562,6 +567,26 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       }
       PROBE(5);
       tmem_st32(tm_e + s * 32 + lane_addr, e1);
+      // ds = p dP (dP arrives with -delta already added)
+      ok = wait_or_abort(bar(PROD_FULL + 2 + s), (n >> 1) & 1, abort_flag, a.status, 318);
+      if (!ok) break;
+      PROBE(9);
+      tc_fence_after_sync();
+      {
+        uint32_t raw[kStep];
+        tmem_ld32(tm_p2 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+        tmem_ld32(tm_p2 + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_FREE + 2 + s));
+#pragma unroll
+        for (int c = 0; c < kStep / 2; ++c) {
+          const float2 ds = __fmul2_rn(t[c], make_float2(__uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1])));
+          e2[c] = pack2<kBf16>(ds.x, ds.y);
+        }
+      }
+      PROBE(13);
       // the ds^T buffer was last read by the MMAs (and the dbias store) of step n - NDS
       if (n >= NDS) {
         const int m = n - NDS;
