@@ -62,6 +62,7 @@ KERNEL_FLOP_SHARE = {
     "sdpa_bwd_tc_kernel<key-major>": 8 / 14,
     "sdpa_bwd_tc_kernel<query-major>": 2 / 14,
     "sdpa_bwd_tc_kernel<merged>": 10 / 14,      # one kernel for dq, dk, dv
+    "sdpa_bwd_tc_kernel<one-pass d128>": 10 / 14,
     "fwd_tf32x3_kernel": 4 / 14,
     "bwd_dkv_tf32x3_kernel": 8 / 14,
     "bwd_dq_tf32x3_kernel": 2 / 14,
@@ -240,6 +241,32 @@ class ClockSampler:
         reasons = sorted(name for name, bit in self.REASONS if bits & bit)
         return {"sm_mhz": statistics.median(s[0] for s in loaded), "sm_max_mhz": self.max_mhz, "reasons": reasons,
                 "samples": len(loaded)}
+
+
+def bind_near_gpu(index):
+    """Pins this process to the host cores of the NUMA node its GPU hangs off (read from sysfs), so that the pinned
+    staging buffers it allocates afterwards are placed in that node's memory and the ranks of a multi-GPU run do not
+    all stream through one node.  Returns the node number, or None when the topology is not exposed."""
+    try:
+        prop = torch.cuda.get_device_properties(index)
+        bus = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:  # noqa: BLE001 - no sysfs topology, or not permitted: keep the inherited affinity
+        return None
 
 
 def load_peaks():
@@ -524,6 +551,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         try:
+            numa = bind_near_gpu(local_rank) if world > 1 else None
             host_in = {n: t.detach().cpu().pin_memory() for n, t in (("q", runner.q), ("k", runner.k), ("v", runner.v),
                                                                     ("dout", runner.dout))}
             if runner.bias is not None:
@@ -552,7 +580,7 @@ def main():
             e2e = {"value": world * wl["flops"] / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                    "h2d_gbs_per_rank": h2d / (my_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (my_ms * 1e-3) / 1e9,
-                   "kernel_ms_per_step": step_ms,
+                   "kernel_ms_per_step": step_ms, "numa_node_of_staging": numa,
                    "limiter": "host<->device copies (PCIe): copy-in, kernels and copy-out of batch chunks overlap on "
                               "three streams, so a step lasts as long as its larger copy direction",
                    "how": f"{len(pipe.slices)} batch chunks pipelined over copy-in / kernel / copy-out streams"}
