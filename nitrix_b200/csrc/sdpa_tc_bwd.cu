@@ -41,7 +41,7 @@ constexpr int kThreads = 384;
 constexpr int kStep = 64;                     // streamed rows per step
 constexpr int kYBoxBytes = kStep * 128;       // one 64-row x 128-byte TMA box
 // register split after start-up (setmaxnreg): 128 * kProducerRegs + 256 * kWorkerRegs <= 65536
-constexpr int kProducerRegs = 72;
+constexpr int kProducerRegs = 88;
 constexpr int kWorkerRegs = 208;
 // setmaxnreg.inc blocks (without bound) until the CTA's OWN pool -- the registers it was launched with, here
 // kLaunchRegs per thread -- holds enough released registers, so the hand-over must balance at compile time.
@@ -233,172 +233,201 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 
   if (warp < 4) {
   reg_dealloc<kProducerRegs>();
-  if (warp == 0) {
-    // ---------------- X / Y producer ----------------
-    // (the owner tiles and the first NY stages were issued during start-up)
-    if (elect_one() && n_steps > NY) {
-      for (int n = NY; n < n_steps; ++n) {
-        const int st = n % NY;
-        if (!wait_or_abort(bar(Y_EMPTY + st), ((n / NY) & 1) ^ 1, abort_flag, a.status, 201)) break;
-        const int r0 = (s_begin + n) * kStep;
-        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-        // lse / delta rows of the step that exist (S is a multiple of 8, so the copy stays a multiple of 16 bytes)
-        const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
-        mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + (kKeyMajor ? 2 * row_bytes : 0));
+  if (warp == 1) {
+    // ---------------- TMA duties of the step loop: ring refills and bias tiles, ONE thread ----------------
+    // (the owner tiles, the first NY stages and the first two bias slots were issued during start-up).  The thread
+    // waits on each duty's barrier in turn, suspended in hardware for at most a short time hint while both are
+    // pending, so whichever completes first is served at once.
+    if (lane == 0 && n_steps > 0) {
+      int yn = min(n_steps, NY);
+      int bn = a.bias_mode == kBiasTile ? min(n_steps, 2) : n_steps;
+      const long long t0 = clock64();
+      uint32_t idle = 0;
+      while (yn < n_steps || bn < n_steps) {
+        const uint32_t hint = (yn < n_steps && bn < n_steps) ? 64u : 4096u;
+        bool progressed = false;
+        if (yn < n_steps && mbar_try_wait_hint(bar(Y_EMPTY + yn % NY), ((yn / NY) & 1) ^ 1, hint)) {
+          const int st = yn % NY;
+          const int r0 = (s_begin + yn) * kStep;
+          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+          // lse / delta rows of the step that exist (S is a multiple of 8, so the copy stays a multiple of 16 bytes)
+          const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+          mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + (kKeyMajor ? 2 * row_bytes : 0));
 #pragma unroll
-        for (int x = 0; x < D / 64; ++x) {
-          tma_load_4d(ybase + x * kYBoxBytes, &tm_y1, bar(Y_FULL + st), x * 64, r0, h, b);
-          tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_y2, bar(Y_FULL + st), x * 64, r0, h, b);
+          for (int x = 0; x < D / 64; ++x) {
+            tma_load_4d(ybase + x * kYBoxBytes, &tm_y1, bar(Y_FULL + st), x * 64, r0, h, b);
+            tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_y2, bar(Y_FULL + st), x * 64, r0, h, b);
+          }
+          if (kKeyMajor) {
+            // lse and delta of the step's 64 queries: two 256-byte bulk copies on the same barrier
+            const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+            bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
+            bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
+          }
+          ++yn;
+          progressed = true;
         }
-        if (kKeyMajor) {
-          // lse and delta of the step's 64 queries: two 256-byte bulk copies on the same barrier
-          const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
-          bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
-          bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
+        if (bn < n_steps && mbar_try_wait_hint(bar(B_EMPTY + (bn & 1)), ((bn >> 1) & 1) ^ 1, hint)) {
+          const int slot = bn & 1;
+          const int r0 = (s_begin + bn) * kStep;
+          mbar_expect_tx(bar(B_FULL + slot), kBoxBytes);
+          const uint32_t dst = sbase + L::kBias + slot * kBoxBytes;
+          if (kKeyMajor) {  // 64 query rows x 128 keys: two 64 x 64 boxes
+            tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), o0, r0, h * a.bias_h_mul, b * a.bias_b_mul);
+            tma_load_4d(dst + kYBoxBytes, &tm_bias, bar(B_FULL + slot), o0 + 64, r0, h * a.bias_h_mul, b * a.bias_b_mul);
+          } else {          // 128 query rows x 64 keys: one 64 x 128 box
+            tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), r0, o0, h * a.bias_h_mul, b * a.bias_b_mul);
+          }
+          ++bn;
+          progressed = true;
         }
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- bias producer ----------------
-    // (the first two slots were issued during start-up)
-    if (a.bias_mode == kBiasTile && elect_one()) {
-      for (int n = 2; n < n_steps; ++n) {
-        const int slot = n & 1;
-        if (!wait_or_abort(bar(B_EMPTY + slot), ((n >> 1) & 1) ^ 1, abort_flag, a.status, 202)) break;
-        const int r0 = (s_begin + n) * kStep;
-        mbar_expect_tx(bar(B_FULL + slot), kBoxBytes);
-        const uint32_t dst = sbase + L::kBias + slot * kBoxBytes;
-        if (kKeyMajor) {  // 64 query rows x 128 keys: two 64 x 64 boxes
-          tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), o0, r0, h * a.bias_h_mul, b * a.bias_b_mul);
-          tma_load_4d(dst + kYBoxBytes, &tm_bias, bar(B_FULL + slot), o0 + 64, r0, h * a.bias_h_mul, b * a.bias_b_mul);
-        } else {          // 128 query rows x 64 keys: one 64 x 128 box
-          tma_load_4d(dst, &tm_bias, bar(B_FULL + slot), r0, o0, h * a.bias_h_mul, b * a.bias_b_mul);
+        if (!progressed && (++idle & 0x3F) == 0) {
+          if (*abort_flag) break;
+          if (*reinterpret_cast<volatile int*>(a.status) != 0) { *abort_flag = 1; break; }
+          if (clock64() - t0 > 20 * kWaitCycles) {   // the whole CTA's life is bounded as well
+            *abort_flag = 1;
+            atomicExch(a.status, 201);
+            break;
+          }
         }
       }
     }
   } else if (warp == 2) {
-    // ---------------- MMA issuer ----------------
+    // ---------------- MMA issuer 1: the two products of every step ----------------
+    // Two threads issue MMAs: this one the products, warp 0 the accumulating ones.  One issuing thread needs about
+    // as long for a step's 30 to 40 MMA instructions as the element-wise warps need for the step, and in a single
+    // instruction stream the products of a later step queue behind accumulating MMAs that wait for those warps.
     if (elect_one() && n_steps > 0) {
       constexpr uint32_t idesc_prod = make_idesc(kBf16, kTile, kStep, false, false);
-      constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, D, false, true);
       bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 203);
       // descriptors are built once; an offset only moves the 16-byte start-address field
       const uint64_t x1desc = make_smem_desc(sbase + L::kX, 16, 1024);
       const uint64_t x2desc = make_smem_desc(sbase + L::kX + L::kXBytes, 16, 1024);
-      // round n: the two products of step n, then the accumulating MMAs of step n - kLag
-      for (int n = 0; n < n_steps + kLag && ok; ++n) {
-        if (n < n_steps) {
-          const int st = n % NY, s = n & 1;
-          ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 204);
-          // separate E tiles: the stage's products may be overwritten once step n - 2 has read them out
-          if (ok && kDeep && n >= 2) ok = wait_or_abort(bar(P_FREE + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 209);
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int st = n % NY, s = n & 1;
+        ok = wait_or_abort(bar(Y_FULL + st), (n / NY) & 1, abort_flag, a.status, 204);
+        if (ok && n >= 2) {
+          // the stage is rewritten: with E tiles of their own (D = 64) once step n - 2 has read the products out,
+          // otherwise (the E tiles lie over the products) once the accumulating MMAs of step n - 2 have read them
+          ok = wait_or_abort(bar((kDeep ? P_FREE : E_FREE) + s), ((n - 2) >> 1) & 1, abort_flag, a.status, 209);
+        }
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+        const uint64_t y1desc = make_smem_desc(ybase, 16, 1024), y2desc = make_smem_desc(ybase + L::kYBytes, 16, 1024);
+        const uint32_t p1 = tmem + s * 128, p2 = p1 + 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+          const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
+          mma_ss(p1, x1desc + xo, y1desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+          const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
+          mma_ss(p2, x2desc + xo, y2desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
+        }
+        if (a.bias_mma) {
+          // scores += bias * (I / scale): the bias slot is consumed straight from shared memory by the tensor core
+          const int slot = n & 1;
+          ok = wait_or_abort(bar(B_FULL + slot), (n >> 1) & 1, abort_flag, a.status, 211);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          const uint64_t y1desc = make_smem_desc(ybase, 16, 1024), y2desc = make_smem_desc(ybase + L::kYBytes, 16, 1024);
-          const uint32_t p1 = tmem + s * 128, p2 = p1 + 64;
+          const uint32_t bslot = sbase + L::kBias + slot * kBoxBytes;
+          // P1[key, q] += bias^T[key, q'] (hi I + lo I)[q', q]: A = the slot (64 q' rows, two 64-key boxes) read
+          // MN-major, B = the identity tiles, K-major
+          constexpr uint32_t idesc_bias = make_idesc(kBf16, kTile, kStep, true, false);
+          const uint64_t adesc = make_smem_desc(bslot, kYBoxBytes, 1024);
+          const int n_tiles = a.inv_scale_lo != 0.f ? 2 : 1;
+          for (int tile = 0; tile < n_tiles; ++tile) {
+            const uint64_t bdesc = make_smem_desc(sbase + L::kIdent + tile * kYBoxBytes, 16, 1024);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
-            const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
-            mma_ss(p1, x1desc + xo, y1desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < kStep / 16; ++kk)
+              mma_ss(p1, adesc + uint64_t((kk * 2048) >> 4), bdesc + uint64_t((kk * 32) >> 4), idesc_bias, 1u);
           }
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t xo = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
-            const uint64_t yo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);
-            mma_ss(p2, x2desc + xo, y2desc + yo, idesc_prod, kk > 0 ? 1u : 0u);
-          }
-          if (a.bias_mma) {
-            // scores += bias * (I / scale): the bias slot is consumed straight from shared memory by the tensor core
-            const int slot = n & 1;
-            ok = wait_or_abort(bar(B_FULL + slot), (n >> 1) & 1, abort_flag, a.status, 211);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t bslot = sbase + L::kBias + slot * kBoxBytes;
-            // P1[key, q] += bias^T[key, q'] (hi I + lo I)[q', q]: A = the slot (64 q' rows, two 64-key boxes) read
-            // MN-major, B = the identity tiles, K-major
-            constexpr uint32_t idesc_bias = make_idesc(kBf16, kTile, kStep, true, false);
-            const uint64_t adesc = make_smem_desc(bslot, kYBoxBytes, 1024);
-            const int n_tiles = a.inv_scale_lo != 0.f ? 2 : 1;
-            for (int tile = 0; tile < n_tiles; ++tile) {
-              const uint64_t bdesc = make_smem_desc(sbase + L::kIdent + tile * kYBoxBytes, 16, 1024);
-#pragma unroll
-              for (int kk = 0; kk < kStep / 16; ++kk)
-                mma_ss(p1, adesc + uint64_t((kk * 2048) >> 4), bdesc + uint64_t((kk * 32) >> 4), idesc_bias, 1u);
-            }
-          }
-          if constexpr (kKeyMajor) {
-            // P1 += W C1^T (C1: -lse / (scale log2e)), P2 += W C2^T (C2: -delta)
+        }
+        if constexpr (kKeyMajor) {
+          // P1 += W C1^T (C1: -lse / (scale log2e)), P2 += W C2^T (C2: -delta)
+          ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 212);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
+          const uint32_t aslot = sbase + L::kAug + s * L::kAugSlotBytes;
+          mma_ss(p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
+          mma_ss(p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
+        }
+        if constexpr (!kKeyMajor) {
+          if (a.key_aug) {
+            // P1 += W C^T: the per-key addends land on every query row
             ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 212);
             if (!ok) break;
             tc_fence_after_sync();
             const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
-            const uint32_t aslot = sbase + L::kAug + s * L::kAugSlotBytes;
-            mma_ss(p1, wdesc, make_smem_desc_noswizzle(aslot, 128, 256), idesc_prod, 1u);
-            mma_ss(p2, wdesc, make_smem_desc_noswizzle(aslot + L::kAugTileBytes, 128, 256), idesc_prod, 1u);
+            mma_ss(p1, wdesc, make_smem_desc_noswizzle(sbase + L::kAug + s * L::kAugSlotBytes, 128, 256), idesc_prod, 1u);
           }
-          if constexpr (!kKeyMajor) {
-            if (a.key_aug) {
-              // P1 += W C^T: the per-key addends land on every query row
-              ok = wait_or_abort(bar(AUG_FULL + s), (n >> 1) & 1, abort_flag, a.status, 212);
+        }
+        mma_commit(bar(PROD_FULL + s));
+        if (kKeyMajor || a.key_aug) mma_commit(bar(AUG_FREE + s));
+        if (a.bias_mma) mma_commit(bar(B_EMPTY + (n & 1)));   // the slot may be refilled once these MMAs are done
+      }
+    }
+  } else if (warp == 0) {
+    // ---------------- MMA issuer 2: the accumulating MMAs of every step ----------------
+    // (every commit below covers all MMAs this thread issued before it: a stage's E_FREE therefore also tells that
+    // the ds tiles of the steps before it have been read)
+    if (elect_one() && n_steps > 0) {
+      constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, D, false, true);
+      bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 203);
+      for (int m = 0; m < n_steps && ok; ++m) {
+        const int st = m % NY, s = m & 1;
+        ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 205);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
+        const uint64_t y1mn = make_smem_desc(ybase, kYBoxBytes, 1024);
+        const uint64_t y2mn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);
+        const uint32_t e1 = tm_e + s * kEStage, e2 = e1 + kE2Off;
+        if constexpr (kMerged) {
+          // dV += p^T dO (p from TMEM), dK += ds^T Q (ds from its shared-memory tile, K-major)
+          const uint64_t dsk = make_smem_desc(sbase + L::kDs + (m % L::kDsSlots) * kBoxBytes, 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < kStep / 16; ++kk) {
+            const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
+            mma_ts(tm_acc1, e1 + kk * 8, y2mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
+            mma_ss(tm_acc2, dsk + uint64_t((kk * 32) >> 4), y1mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
+          }
+          mma_commit(bar(Y_EMPTY + st));          // the last readers of this ring stage
+          if (m & 1) {
+            // dq tile of the pair (m - 1, m): (128 queries x 128 keys) (128 keys x 64) = ds K; A = the two ds tiles
+            // read MN-major (queries contiguous, tiles 16 KB apart), B = the K tile read MN-major
+            const int j = m >> 1;
+            if (j >= 1) {
+              ok = wait_or_abort(bar(DQ_FREE), (j - 1) & 1, abort_flag, a.status, 215);
               if (!ok) break;
               tc_fence_after_sync();
-              const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kWeights, 128, 256);
-              mma_ss(p1, wdesc, make_smem_desc_noswizzle(sbase + L::kAug + s * L::kAugSlotBytes, 128, 256), idesc_prod, 1u);
             }
+            constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, D, true, true);
+            const uint64_t dsm = make_smem_desc(sbase + L::kDs + ((m - 1) % L::kDsSlots) * kBoxBytes, kBoxBytes, 1024);
+            const uint64_t kmn = make_smem_desc(sbase + L::kX, kBoxBytes, 1024);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              mma_ss(tm_dq, dsm + uint64_t((kk * 2048) >> 4), kmn + uint64_t((kk * 2048) >> 4), idesc_dq, kk > 0 ? 1u : 0u);
+            mma_commit(bar(DQ_FULL));
           }
-          mma_commit(bar(PROD_FULL + s));
-          if (kKeyMajor || a.key_aug) mma_commit(bar(AUG_FREE + s));
-          if (a.bias_mma) mma_commit(bar(B_EMPTY + (n & 1)));   // the slot may be refilled once these MMAs are done
-        }
-        if (n >= kLag) {
-          const int m = n - kLag, st = m % NY, s = m & 1;
-          ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 205);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          const uint64_t y1mn = make_smem_desc(ybase, kYBoxBytes, 1024);
-          const uint64_t y2mn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);
-          const uint32_t e1 = tm_e + s * kEStage, e2 = e1 + kE2Off;
-          if constexpr (kMerged) {
-            // dV += p^T dO (p from TMEM), dK += ds^T Q (ds from its shared-memory tile, K-major)
-            const uint64_t dsk = make_smem_desc(sbase + L::kDs + (m % L::kDsSlots) * kBoxBytes, 16, 1024);
-#pragma unroll
-            for (int kk = 0; kk < kStep / 16; ++kk) {
-              const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
-              mma_ts(tm_acc1, e1 + kk * 8, y2mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
-              mma_ss(tm_acc2, dsk + uint64_t((kk * 32) >> 4), y1mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
-            }
-            if (m & 1) {
-              // dq tile of the pair (m - 1, m): (128 queries x 128 keys) (128 keys x 64) = ds K; A = the two ds tiles
-              // read MN-major (queries contiguous, tiles 16 KB apart), B = the K tile read MN-major
-              const int j = m >> 1;
-              if (j >= 1) {
-                ok = wait_or_abort(bar(DQ_FREE), (j - 1) & 1, abort_flag, a.status, 215);
-                if (!ok) break;
-                tc_fence_after_sync();
-              }
-              constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, D, true, true);
-              const uint64_t dsm = make_smem_desc(sbase + L::kDs + ((m - 1) % L::kDsSlots) * kBoxBytes, kBoxBytes, 1024);
-              const uint64_t kmn = make_smem_desc(sbase + L::kX, kBoxBytes, 1024);
-#pragma unroll
-              for (int kk = 0; kk < kTile / 16; ++kk)
-                mma_ss(tm_dq, dsm + uint64_t((kk * 2048) >> 4), kmn + uint64_t((kk * 2048) >> 4), idesc_dq, kk > 0 ? 1u : 0u);
-              mma_commit(bar(DQ_FULL));
-            }
-          } else {
+        } else {
 #pragma unroll
           for (int kk = 0; kk < kStep / 16; ++kk) {
             const uint32_t acc = (m > 0 || kk > 0) ? 1u : 0u;
             if (kKeyMajor) mma_ts(tm_acc1, e1 + kk * 8, y2mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
             mma_ts(tm_acc2, e2 + kk * 8, y1mn + uint64_t((kk * 2048) >> 4), idesc_acc, acc);
           }
-          }
-          if (kDeep) mma_commit(bar(E_FREE + s));   // the E tiles of this stage may be rewritten once these are done
           mma_commit(bar(Y_EMPTY + st));
-          if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
         }
+        // D = 64: the E tiles of this stage may be rewritten; D = 128 (E tiles over the products): the stage's
+        // products may be recomputed
+        mma_commit(bar(E_FREE + s));
+        if (m == n_steps - 1) mma_commit(bar(ACC_DONE));
       }
     }
   } else if (!kKeyMajor) {
