@@ -153,7 +153,8 @@ NB200_API int nb200_sdpa_plan(const nb200_sdpa_params* p, int pass, int* kernel)
 /* Scratch bytes `pass` needs for this problem: packed mask bits (forward and backward), and for the backward
  * the delta rows (B*H*S floats), an fp32 copy of a broadcast bias' gradient, and -- bf16/fp16 at head dim 64
  * without a bias gradient, where one kernel produces dq, dk and dv -- an fp32 copy of dq (B*H*S*64 floats).
- * The tensor-core kernels take bf16/fp16 with D == Dv in {64, 128} and S, T multiples of 8; everything else runs
+ * plus padded copies of bias / dbias / lse / delta when their rows are not 16-byte addressable (lengths that are not
+ * multiples of 8, strided keys).  The tensor-core kernels take bf16/fp16 with D == Dv in {64, 128}; everything else runs
  * on the fp32 CUDA-core family (nb200_sdpa_plan tells which). */
 NB200_API int nb200_sdpa_workspace_bytes(const nb200_sdpa_params* p, int pass, size_t* bytes);
 

@@ -160,7 +160,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     for (int n = 0; n < n_first; ++n) {
       const int r0 = (s_begin + n) * kStep;
       const uint32_t ybase = sbase + L::kY + n * L::kYStageBytes;
-      const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+      const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.ld_rows - r0));
       mbar_expect_tx(bar(Y_FULL + n), 2 * L::kYBytes + (kKeyMajor ? 2 * row_bytes : 0));
 #pragma unroll
       for (int x = 0; x < D / 64; ++x) {
@@ -168,7 +168,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_y2, bar(Y_FULL + n), x * 64, r0, h, b);
       }
       if (kKeyMajor) {
-        const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+        const int64_t ro = (int64_t(b) * a.H + h) * a.ld_rows + r0;
         bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + n));
         bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + n));
       }
@@ -250,8 +250,8 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           const int st = yn % NY;
           const int r0 = (s_begin + yn) * kStep;
           const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          // lse / delta rows of the step that exist (S is a multiple of 8, so the copy stays a multiple of 16 bytes)
-          const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+          // lse / delta rows of the step that exist (a multiple of 4 rows, so the copy stays a multiple of 16 bytes)
+          const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.ld_rows - r0));
           mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + (kKeyMajor ? 2 * row_bytes : 0));
 #pragma unroll
           for (int x = 0; x < D / 64; ++x) {
@@ -260,7 +260,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
           }
           if (kKeyMajor) {
             // lse and delta of the step's 64 queries: two 256-byte bulk copies on the same barrier
-            const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+            const int64_t ro = (int64_t(b) * a.H + h) * a.ld_rows + r0;
             bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
             bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
           }
@@ -547,7 +547,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     const float2 mul2 = make_float2(mul, mul), scale2 = make_float2(a.scale, a.scale);
     float lse_row = 0.f, delta_row = 0.f;
     if (!kKeyMajor && orow < a.S) {
-      const int64_t ro = (int64_t(b) * a.H + h) * a.S + orow;
+      const int64_t ro = (int64_t(b) * a.H + h) * a.ld_rows + orow;
       lse_row = a.lse[ro];
       delta_row = a.delta[ro];
     }
@@ -581,6 +581,7 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     float* acc_row = nullptr;                    // query-major, broadcast tile bias: this query's accumulator row
     if (!kKeyMajor && a.dbias_acc && orow < a.S)
       acc_row = a.dbias_acc + b * a.acc_s[0] + h * a.acc_s[1] + int64_t(orow) * a.acc_s[2];
+    const bool acc_vec = (a.T & 3) == 0;
     // merged: pair j of steps (2j, 2j + 1) leaves a 128-query x 64 dq tile in TMEM; this group adds its 32 columns
     // of it to the fp32 accumulator in global memory (thread = query row)
     int next_pair = 0;
@@ -735,9 +736,17 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
         if constexpr (!kKeyMajor) {
           // broadcast bias: this row's ds of four consecutive keys joins the fp32 sums over the broadcast axes
-          if (acc_row && r0 + 4 * c4 < a.T)
-            red_add_v4(acc_row + r0 + 4 * c4, __float_as_uint(ds4[0].x), __float_as_uint(ds4[0].y),
-                       __float_as_uint(ds4[1].x), __float_as_uint(ds4[1].y));
+          if (acc_row && r0 + 4 * c4 < a.T) {
+            if (acc_vec) {
+              red_add_v4(acc_row + r0 + 4 * c4, __float_as_uint(ds4[0].x), __float_as_uint(ds4[0].y),
+                         __float_as_uint(ds4[1].x), __float_as_uint(ds4[1].y));
+            } else {   // key count not a multiple of 4: rows of the accumulator are not 16-byte aligned
+              const float d4[4] = {ds4[0].x, ds4[0].y, ds4[1].x, ds4[1].y};
+#pragma unroll
+              for (int e4 = 0; e4 < 4; ++e4)
+                if (r0 + 4 * c4 + e4 < a.T) atomicAdd(acc_row + r0 + 4 * c4 + e4, d4[e4]);
+            }
+          }
         }
       }
       if constexpr (kKeyMajor && !kMerged) {
@@ -949,7 +958,6 @@ bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** wh
     *why = "scale is zero or not finite";   // the key-major kernel divides lse by scale
     return false;
   }
-  if (pr.lse && reinterpret_cast<uintptr_t>(pr.lse) % 16) { *why = "lse is not 16-byte aligned"; return false; }
   if (pr.mask_packed == 1 && !mask_key_only(pr)) {
     *why = "the mask was packed without the transposed copy the backward needs (nb200_mask_pack with_transpose = 1)";
     return false;
@@ -1015,7 +1023,7 @@ size_t bwd_workspace_bytes(const Problem& pr, int dtype, int) {
   return bytes;
 }
 
-int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, int ld_rows, cudaStream_t stream) {
   (void)bias_dtype;
   const char* why = "";
   const bool key_only = mask_key_only(pr);
@@ -1042,7 +1050,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
   a.bias_b_mul = (pr.B > 1 && pr.bs[0] != 0) ? 1 : 0;
   a.bias_h_mul = (pr.H > 1 && pr.bs[1] != 0) ? 1 : 0;
   a.bias = pr.bias; a.bias_bs = pr.bs[0]; a.bias_hs = pr.bs[1];
-  a.lse = pr.lse; a.delta = pr.delta;
+  a.lse = pr.lse; a.delta = pr.delta; a.ld_rows = ld_rows;
   a.status = device_status_word();
   if (!a.status) { set_error("device status word is unavailable"); return NB200_ERR_LAUNCH; }
 
@@ -1106,7 +1114,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
       }
       if (pr.causal || key_only) {
         // query / key ranges the kernel never visits (above the diagonal, past the last kept key) get exact zeros
-        e = cudaMemsetAsync(pr.dbias, 0, size_t(pr.B) * pr.H * pr.S * pr.T * 2, stream);
+        e = cudaMemsetAsync(pr.dbias, 0, size_t(pr.B) * pr.H * pr.S * size_t(pr.dbs[2]) * 2, stream);
         if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return NB200_ERR_LAUNCH; }
       }
     }

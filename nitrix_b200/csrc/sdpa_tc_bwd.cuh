@@ -29,6 +29,10 @@ struct BwdArgs {
   int mask_key_only;            // key-major: the mask has no query axis (use mask.rows per key)
   const float* lse;
   const float* delta;
+  // Rows per (batch, head) of the lse / delta arrays handed to the kernels: S, or -- when S is not a multiple of 4, so
+  // that 16-byte copies of 64-row blocks would start off their alignment -- S rounded up to 64 (padded copies in the
+  // workspace, made by launch_bwd).
+  int ld_rows;
   void* out1; int64_t o1s[3];   // key-major: dv
   void* out2; int64_t o2s[3];   // dq | dk
   void* dbias; int64_t dbs[4];  // query-major only; null when not requested
@@ -54,7 +58,8 @@ int launch_dq_finish_d128(const Problem& pr, const float* acc, int acc_rows, boo
 
 bool bwd_supported(const Problem& pr, int dtype, int bias_dtype, const char** why);
 size_t bwd_workspace_bytes(const Problem& pr, int dtype, int bias_dtype);
-int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream);
+// ld_rows: rows per (batch, head) of pr.lse / pr.delta as passed (S, or the padded count of staged copies)
+int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, int ld_rows, cudaStream_t stream);
 
 }  // namespace tc
 }  // namespace nb200

@@ -155,14 +155,14 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     for (int n = 0; n < n_first; ++n) {
       const int r0 = step_row(n);
       const uint32_t ybase = sbase + L::kY + n * L::kYStageBytes;
-      const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+      const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.ld_rows - r0));
       mbar_expect_tx(bar(Y_FULL + n), 2 * L::kYBytes + 2 * row_bytes);
 #pragma unroll
       for (int x = 0; x < kD / 64; ++x) {
         tma_load_4d(ybase + x * kYBoxBytes, &tm_q, bar(Y_FULL + n), x * 64, r0, h, b);
         tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_do, bar(Y_FULL + n), x * 64, r0, h, b);
       }
-      const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+      const int64_t ro = (int64_t(b) * a.H + h) * a.ld_rows + r0;
       bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + n));
       bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + n));
       if (kTileBias && n < 2) {
@@ -231,15 +231,15 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         if (yn < n_steps && mbar_try_wait_hint(bar(Y_EMPTY + yn % NY), ((yn / NY) & 1) ^ 1, hint)) {
           const int st = yn % NY, r0 = step_row(yn);
           const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
-          // lse / delta rows of the step that exist (S is a multiple of 8, so the copy stays a multiple of 16 bytes)
-          const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.S - r0));
+          // lse / delta rows of the step that exist (a multiple of 4 rows, so the copy stays a multiple of 16 bytes)
+          const uint32_t row_bytes = 4u * uint32_t(min(kStep, a.ld_rows - r0));
           mbar_expect_tx(bar(Y_FULL + st), 2 * L::kYBytes + 2 * row_bytes);
 #pragma unroll
           for (int x = 0; x < kD / 64; ++x) {
             tma_load_4d(ybase + x * kYBoxBytes, &tm_q, bar(Y_FULL + st), x * 64, r0, h, b);
             tma_load_4d(ybase + L::kYBytes + x * kYBoxBytes, &tm_do, bar(Y_FULL + st), x * 64, r0, h, b);
           }
-          const int64_t ro = (int64_t(b) * a.H + h) * a.S + r0;
+          const int64_t ro = (int64_t(b) * a.H + h) * a.ld_rows + r0;
           bulk_load(ybase + 2 * L::kYBytes, a.lse + ro, row_bytes, bar(Y_FULL + st));
           bulk_load(ybase + 2 * L::kYBytes + 256, a.delta + ro, row_bytes, bar(Y_FULL + st));
           ++yn;
@@ -735,7 +735,7 @@ bool d128_merged_supported(const Problem& pr, int bias_mode, bool bias_mma) {
     if (!pr.dbias) return true;                            // planning: no buffer yet
     if (!tile_map_ok(pr.dbias, pr.dbs[2], pr.dbs[1], pr.dbs[0], pr.H, pr.B, false)) return false;
     const bool needs_zero_fill = pr.causal || mask_key_only(pr);
-    const bool dense = pr.dbs[2] == pr.T && pr.dbs[1] == int64_t(pr.S) * pr.T && pr.dbs[0] == int64_t(pr.H) * pr.S * pr.T;
+    const bool dense = pr.dbs[1] == int64_t(pr.S) * pr.dbs[2] && pr.dbs[0] == int64_t(pr.H) * pr.S * pr.dbs[2];
     if (needs_zero_fill && !dense) return false;
   }
   return true;

@@ -83,6 +83,29 @@ bool mask_key_only(const Problem& pr);
 MaskPackPlan mask_plan_for_pass(const Problem& pr, bool backward, size_t* ws_bytes);
 int launch_mask_pack(const Problem& pr, const MaskPackPlan& plan, void* ws, MaskBits* out, cudaStream_t stream);
 
+// ---- staging of operands whose layout the kernels cannot address directly --------
+// TMA needs 16-byte aligned bases and row strides, and the backward copies 64-row blocks of lse / delta with 16-byte
+// granularity.  A bias (or dbias) whose key count is not a multiple of 8, whose rows are strided oddly or whose key
+// axis is not contiguous, and lse / delta with a query count that is not a multiple of 4, therefore go through
+// padded copies in the workspace: bias is copied in before the kernels, dbias is written padded and copied out after
+// them, lse / delta are copied into rows padded to 64.  Lengths that are multiples of 8 with dense operands need
+// none of this.
+struct Staging {
+  bool bias, dbias, rows;        // which operands are staged
+  int Tp, Sp;                    // padded key count (multiple of 8) and query count (multiple of 64)
+  int64_t extent[4];             // bias' own extent (1 on broadcast axes)
+  size_t bias_bytes, dbias_bytes, rows_bytes;   // each a multiple of 256; rows_bytes is for ONE of lse / delta
+  size_t total() const { return bias_bytes + dbias_bytes + 2 * rows_bytes; }
+};
+Staging plan_staging(const Problem& pr, int pass);
+// The problem as the kernels see it: staged operands replaced by their padded copies at `base` (bias, then dbias,
+// then lse, then delta).  With base == nullptr (planning) the staged pointers are aligned placeholders.
+Problem staged_view(const Problem& pr, const Staging& sg, void* base);
+// Copies before the kernels (bias in; lse / delta into padded rows -- delta must have been computed already) and
+// after them (dbias out).
+int stage_in(const Problem& pr, const Problem& staged, const Staging& sg, int pass, cudaStream_t stream);
+int stage_out(const Problem& pr, const Problem& staged, const Staging& sg, cudaStream_t stream);
+
 // ---- device helpers -----------------------------------------------------------
 #ifdef __CUDACC__
 

@@ -167,6 +167,128 @@ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 }  // namespace
 
+// ---- staging ---------------------------------------------------------------------
+namespace {
+
+// dst[i0][i1][i2][i3] = src[...] for 16-bit elements, both sides described by element strides
+__global__ void copy16_4d_kernel(const uint16_t* __restrict__ src, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
+                                 uint16_t* __restrict__ dst, int64_t d0, int64_t d1, int64_t d2, int64_t d3, int64_t e1,
+                                 int64_t e2, int64_t e3, int64_t n) {
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t i3 = i % e3, r = i / e3;
+    const int64_t i2 = r % e2, r2 = r / e2;
+    const int64_t i1 = r2 % e1, i0 = r2 / e1;
+    dst[i0 * d0 + i1 * d1 + i2 * d2 + i3 * d3] = src[i0 * s0 + i1 * s1 + i2 * s2 + i3 * s3];
+  }
+}
+
+// (BH, S) fp32 rows -> (BH, Sp) rows, zero beyond S
+__global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int S, int Sp, int64_t n) {
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t bh = i / Sp;
+    const int r = int(i - bh * Sp);
+    dst[i] = r < S ? src[bh * S + r] : 0.f;
+  }
+}
+
+inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+int launch_copy16(const void* src, const int64_t ss[4], void* dst, const int64_t ds[4], const int64_t e[4], cudaStream_t st,
+                  const char* what) {
+  const int64_t n = e[0] * e[1] * e[2] * e[3];
+  if (n <= 0) return NB200_OK;
+  const int64_t want = (n + 255) / 256;
+  const int blocks = int(want < 148 * 16 ? want : 148 * 16);
+  copy16_4d_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(src), ss[0], ss[1], ss[2], ss[3],
+                                           static_cast<uint16_t*>(dst), ds[0], ds[1], ds[2], ds[3], e[1], e[2], e[3], n);
+  count_launch();
+  return check_launch(what);
+}
+
+}  // namespace
+
+Staging plan_staging(const Problem& pr, int pass) {
+  Staging sg{};
+  sg.Tp = (pr.T + 7) / 8 * 8;
+  sg.Sp = (pr.S + kTile / 2 - 1) / (kTile / 2) * (kTile / 2);
+  const int64_t full[4] = {pr.B, pr.H, pr.S, pr.T};
+  for (int a = 0; a < 4; ++a) sg.extent[a] = (!pr.bias || pr.bs[a] == 0 || full[a] == 1) ? 1 : full[a];
+  const bool tile_bias = pr.bias && !(pr.bs[2] == 0 || pr.S == 1);
+  if (tile_bias) {
+    const bool direct = (pr.T == 1 || pr.bs[3] == 1) && tile_map_ok(pr.bias, pr.bs[2], pr.bs[1], pr.bs[0], pr.H, pr.B, true);
+    if (!direct) {
+      sg.bias = true;
+      sg.bias_bytes = up256(size_t(sg.extent[0] * sg.extent[1] * pr.S) * sg.Tp * 2);
+    }
+  }
+  // a gradient of full extent (no axis of the bias is broadcast) is written by the kernels in 16-byte row segments
+  // or by TMA: same layout rules as the bias tiles
+  const bool broadcast = (pr.B > 1 && pr.bs[0] == 0) || (pr.H > 1 && pr.bs[1] == 0) || (pr.S > 1 && pr.bs[2] == 0);
+  if (pr.bias && pass == NB200_PASS_BWD && pr.want_dbias && !broadcast) {
+    const bool direct = pr.T % 8 == 0 && (!pr.dbias || (pr.dbs[3] == 1 && aligned16(pr.dbias) && pr.dbs[0] % 8 == 0 &&
+                                                        pr.dbs[1] % 8 == 0 && pr.dbs[2] % 8 == 0));
+    if (!direct) {
+      sg.dbias = true;
+      sg.dbias_bytes = up256(size_t(pr.B) * pr.H * pr.S * sg.Tp * 2);
+    }
+  }
+  if (pass == NB200_PASS_BWD && (pr.S % 4 != 0 || (pr.lse && !aligned16(pr.lse)))) {
+    sg.rows = true;
+    sg.rows_bytes = up256(sizeof(float) * size_t(pr.B) * pr.H * sg.Sp);
+  }
+  return sg;
+}
+
+Problem staged_view(const Problem& pr, const Staging& sg, void* base) {
+  Problem v = pr;
+  char* p = base ? static_cast<char*>(base) : reinterpret_cast<char*>(uintptr_t(1) << 20);
+  if (sg.bias) {
+    v.bias = p;
+    // dense over the bias' own extent with rows of Tp keys; broadcast axes keep stride 0
+    v.bs[3] = 1;
+    v.bs[2] = sg.Tp;
+    v.bs[1] = sg.extent[1] == 1 ? 0 : int64_t(pr.S) * sg.Tp;
+    v.bs[0] = sg.extent[0] == 1 ? 0 : sg.extent[1] * int64_t(pr.S) * sg.Tp;
+    p += sg.bias_bytes;
+  }
+  if (sg.dbias) {
+    v.dbias = p;
+    v.dbs[3] = 1;
+    v.dbs[2] = sg.Tp;
+    v.dbs[1] = int64_t(pr.S) * sg.Tp;
+    v.dbs[0] = int64_t(pr.H) * pr.S * sg.Tp;
+    p += sg.dbias_bytes;
+  }
+  if (sg.rows) {
+    v.lse = reinterpret_cast<float*>(p);
+    v.delta = reinterpret_cast<float*>(p + sg.rows_bytes);
+  }
+  return v;
+}
+
+int stage_in(const Problem& pr, const Problem& v, const Staging& sg, int pass, cudaStream_t stream) {
+  if (sg.bias) {
+    const int64_t e[4] = {sg.extent[0], sg.extent[1], pr.S, pr.T};
+    if (int rc = launch_copy16(pr.bias, pr.bs, const_cast<void*>(v.bias), v.bs, e, stream, "bias_pad_kernel")) return rc;
+  }
+  if (sg.rows && pass == NB200_PASS_BWD) {
+    const int64_t n = int64_t(pr.B) * pr.H * sg.Sp;
+    const int blocks = int(((n + 255) / 256) < 148 * 16 ? ((n + 255) / 256) : 148 * 16);
+    pad_rows_kernel<<<blocks, 256, 0, stream>>>(pr.lse, v.lse, pr.S, sg.Sp, n);
+    pad_rows_kernel<<<blocks, 256, 0, stream>>>(pr.delta, v.delta, pr.S, sg.Sp, n);
+    count_launch(2);
+    if (int rc = check_launch("pad_rows_kernel")) return rc;
+  }
+  return NB200_OK;
+}
+
+int stage_out(const Problem& pr, const Problem& v, const Staging& sg, cudaStream_t stream) {
+  if (!sg.dbias || !pr.dbias) return NB200_OK;
+  const int64_t e[4] = {pr.B, pr.H, pr.S, pr.T};
+  return launch_copy16(v.dbias, v.dbs, pr.dbias, pr.dbs, e, stream, "dbias_unpad_kernel");
+}
+
 bool split_inv_scale(float scale, bool bf16, float* hi, float* lo) {
   *hi = *lo = 0.f;
   if (scale == 0.f || !isfinite(scale) || !isfinite(1.f / scale)) return false;
@@ -274,7 +396,10 @@ bool bias_plan(const Problem& pr, int dtype, int bias_dtype, BiasPlan* bp, const
   const bool row_bc = pr.bs[2] == 0 || pr.S == 1;
   if (pr.T > 1 && pr.bs[3] != 1) { *why = "bias needs a unit stride over keys"; return false; }
   if (row_bc) {
-    if (reinterpret_cast<uintptr_t>(pr.bias) % 16 || pr.bs[0] % 8 || pr.bs[1] % 8) {
+    // with a positive scale the per-key bias is read element by element (and added by the tensor core); only the
+    // path for other scales reads it in 16-byte vectors
+    const bool scalar_reads = pr.scale > 0.f && isfinite(1.f / pr.scale);
+    if (!scalar_reads && (reinterpret_cast<uintptr_t>(pr.bias) % 16 || pr.bs[0] % 8 || pr.bs[1] % 8 || pr.T % 8)) {
       *why = "per-key bias is not 16-byte aligned";
       return false;
     }
@@ -291,19 +416,23 @@ bool bias_plan(const Problem& pr, int dtype, int bias_dtype, BiasPlan* bp, const
 
 }  // namespace
 
-bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const char** why) {
+bool tc_supported(const Problem& original, int dtype, int bias_dtype, int pass, const char** why) {
   const char* dummy;
   if (!why) why = &dummy;
+  // judged on the problem as the kernels will see it (operands with awkward layouts go through padded copies)
+  const tc::Staging sg = tc::plan_staging(original, pass);
+  const Problem pr = tc::staged_view(original, sg, nullptr);
   if (dtype != NB200_BF16 && dtype != NB200_F16) { *why = "dtype is not bf16/fp16"; return false; }
   if (pr.D != pr.Dv || (pr.D != 64 && pr.D != 128)) { *why = "head dims must be equal and 64 or 128"; return false; }
-  // Lengths need not fill whole 128-row tiles: TMA zero-fills rows past the end, the kernels mask keys past T and
-  // store only rows below S.  Multiples of 8 keep every 16-byte row segment (bias, dbias, lse, packed rows) whole.
+  // Lengths need not fill whole 128-row tiles, nor be multiples of anything: TMA zero-fills rows past the end, the
+  // kernels mask keys past T and store only rows below S, and the operands with 16-byte row segments (bias, dbias,
+  // lse, delta) are staged through padded copies when the lengths leave those segments ragged.
   if (pr.bh_count > 65535 || int64_t(pr.B) * pr.H > 65535) {
     *why = "more than 65535 (batch, head) pairs (grid limit of the backward and mask-packing launches)";
     return false;
   }
-  if (pr.S <= 0 || pr.T <= 0 || pr.S % 8 || pr.T % 8) {
-    *why = "query and key lengths must be positive multiples of 8";
+  if (pr.S <= 0 || pr.T <= 0) {
+    *why = "query and key lengths must be positive";
     return false;
   }
   if (!tc::tile_map_ok(pr.q, pr.qs[2], pr.qs[1], pr.qs[0], pr.H, pr.B, false) ||
@@ -323,22 +452,28 @@ bool tc_supported(const Problem& pr, int dtype, int bias_dtype, int pass, const 
 }
 
 size_t tc_workspace_bytes(const Problem& pr, int dtype, int bias_dtype, int pass) {
-  if (pass == NB200_PASS_BWD) return tc::bwd_workspace_bytes(pr, dtype, bias_dtype);
+  const tc::Staging sg = tc::plan_staging(pr, pass);
+  if (pass == NB200_PASS_BWD)
+    return (tc::bwd_workspace_bytes(tc::staged_view(pr, sg, nullptr), dtype, bias_dtype) + 255) / 256 * 256 + sg.total();
   size_t bytes = 0;
   tc::mask_plan_for_pass(pr, false, &bytes);
-  return bytes;
+  return (bytes + 255) / 256 * 256 + sg.total();
 }
 
-int tc_forward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+int tc_forward(const Problem& original, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
   const char* why = "";
-  BiasPlan bp;
-  if (!bias_plan(pr, dtype, bias_dtype, &bp, &why)) { set_error("%s", why); return NB200_ERR_UNSUPPORTED; }
   size_t mask_ws = 0;
-  const tc::MaskPackPlan mp = tc::mask_plan_for_pass(pr, false, &mask_ws);
-  if (mask_ws > ws_bytes || (mask_ws && !ws)) {
-    set_error("forward mask bits need %zu workspace bytes", mask_ws);
+  const tc::MaskPackPlan mp = tc::mask_plan_for_pass(original, false, &mask_ws);
+  const tc::Staging sg = tc::plan_staging(original, NB200_PASS_FWD);
+  const size_t staging_off = (mask_ws + 255) / 256 * 256;
+  if (staging_off + sg.total() > ws_bytes || ((mask_ws || sg.total()) && !ws)) {
+    set_error("forward needs %zu workspace bytes (mask bits, padded bias)", staging_off + sg.total());
     return NB200_ERR_WORKSPACE;
   }
+  const Problem pr = tc::staged_view(original, sg, static_cast<char*>(ws) + staging_off);
+  if (int rc = tc::stage_in(original, pr, sg, NB200_PASS_FWD, stream)) return rc;
+  BiasPlan bp;
+  if (!bias_plan(pr, dtype, bias_dtype, &bp, &why)) { set_error("%s", why); return NB200_ERR_UNSUPPORTED; }
   tc::FwdArgs a{};
   if (int rc = tc::launch_mask_pack(pr, mp, ws, &a.mask, stream)) return rc;
   CUtensorMap tq, tk, tv, tb;
@@ -410,8 +545,18 @@ int tc_mask_pack(const Problem& pr, bool with_transpose, void* packed, size_t pa
   return tc::launch_mask_pack(pr, mp, packed, &unused, stream);
 }
 
-int tc_backward(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
-  return tc::launch_bwd(pr, dtype, bias_dtype, ws, ws_bytes, stream);
+int tc_backward(const Problem& original, int dtype, int bias_dtype, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  // padded copies (bias in; lse / delta rows; dbias out) sit behind the kernels' own scratch
+  const tc::Staging sg = tc::plan_staging(original, NB200_PASS_BWD);
+  const size_t inner = (tc::bwd_workspace_bytes(tc::staged_view(original, sg, nullptr), dtype, bias_dtype) + 255) / 256 * 256;
+  if (inner + sg.total() > ws_bytes) {
+    set_error("tensor-core backward needs %zu workspace bytes", inner + sg.total());
+    return NB200_ERR_WORKSPACE;
+  }
+  const Problem pr = tc::staged_view(original, sg, static_cast<char*>(ws) + inner);
+  if (int rc = tc::stage_in(original, pr, sg, NB200_PASS_BWD, stream)) return rc;
+  if (int rc = tc::launch_bwd(pr, dtype, bias_dtype, ws, inner, sg.rows ? sg.Sp : original.S, stream)) return rc;
+  return tc::stage_out(original, pr, sg, stream);
 }
 
 }  // namespace nb200

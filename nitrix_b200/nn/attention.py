@@ -419,8 +419,8 @@ def scaled_dot_product_attention(
                 requested="cuda-sm100",
                 resolved="cuda-simt",
                 reason=(
-                    "the fused tcgen05 kernels take bf16/fp16 with d == d_v in {64, 128} and query/key lengths "
-                    "that are multiples of 8; the fused 3xTF32 kernels take fp32 with d, d_v in {32, 64, 128}"
+                    "the fused tcgen05 kernels take bf16/fp16 with d == d_v in {64, 128} (any query/key lengths); "
+                    "the fused 3xTF32 kernels take fp32 with d, d_v in {32, 64, 128}"
                 ),
                 shapes=(tuple(q.shape), tuple(k.shape), tuple(v.shape)),
                 dtype=out_dtype,

@@ -178,20 +178,25 @@ def test_bh_partition_covers_everything_once():
 def test_plan_reports_the_family_that_runs():
     """The planner's three answers (no launch, no GPU needed): bf16 at head dim 64 -> tcgen05; fp32 at a head dim
     the 3 x TF32 kernels take -> the TF32 tensor path (what decides that an fp32 caller gets no fallback warning,
-    as on the reference's fused path, attention.py:736-765); a length that is not a multiple of 8 in bf16, or an
-    fp32 head dim of 40 -> plain CUDA cores."""
+    as on the reference's fused path, attention.py:736-765); a head dim of 40 -> plain CUDA cores."""
     from nitrix_b200 import _cabi
 
     assert _plan()[:2] == (_cabi.OK, _cabi.KERNEL_TCGEN05)
     assert _plan(dtype=_cabi.F32)[:2] == (_cabi.OK, _cabi.KERNEL_MMA_TF32X3)
-    assert _plan(S=100, T=100)[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
+    # lengths need not be multiples of anything on the tensor-core family (the caller shapes the reference's docs
+    # name: 217, 28, 197, 111 tokens)
+    for n in (100, 217, 28, 197, 111):
+        assert _plan(S=n, T=n)[:2] == (_cabi.OK, _cabi.KERNEL_TCGEN05), n
+    d40 = dict(D=40, Dv=40, q_stride=[4 * 256 * 40, 256 * 40, 40, 1], k_stride=[4 * 256 * 40, 256 * 40, 40, 1],
+               v_stride=[4 * 256 * 40, 256 * 40, 40, 1], out_stride=[4 * 256 * 40, 256 * 40, 40, 1])
+    assert _plan(**d40)[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
     assert _plan(dtype=_cabi.F32, D=40, Dv=40, q_stride=[4 * 256 * 40, 256 * 40, 40, 1], k_stride=[4 * 256 * 40, 256 * 40, 40, 1],
                  v_stride=[4 * 256 * 40, 256 * 40, 40, 1], out_stride=[4 * 256 * 40, 256 * 40, 40, 1])[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
     # an expanded (stride 0) head axis on k is declined by the tensor-core family
     assert _plan(k_stride=[4 * 256 * 64, 0, 64, 1])[:2] == (_cabi.OK, _cabi.KERNEL_SIMT)
     # the forced family reports why it cannot take a problem
-    rc, _, msg = _plan(S=100, T=100, kernel=_cabi.KERNEL_TCGEN05)
-    assert rc == _cabi.ERR_UNSUPPORTED and "multiples of 8" in msg
+    rc, _, msg = _plan(kernel=_cabi.KERNEL_TCGEN05, **d40)
+    assert rc == _cabi.ERR_UNSUPPORTED and "head dims" in msg
 
 
 def test_packed_mask_and_peer_fields_are_validated():

@@ -314,18 +314,52 @@ def test_tc_ragged_lengths(name, shape, d):
     check(got, ref, dtype)
 
 
-def test_tc_ragged_fp16_and_odd_multiple_falls_back():
-    from nitrix_b200 import _cabi
-    _, att = _nb()
+def test_tc_ragged_fp16():
     q, k, v, kw = _cases.kernel_case("bias_mask", s=264, t=136, d=64)
     _assert_plans_tc(q, k, v, kw, torch.float16)
     got, ref = run_both(q, k, v, kw, torch.float16, "cuda-sm100", want_dbias=False)
     _device_ok()
     check(got, ref, torch.float16)
-    # a length that is not a multiple of 8 is declined (CUDA-core kernels take it)
-    q, k, v, kw = _cases.kernel_case("dense", s=100, t=100, d=64)
-    chosen = att.planned_kernel(q.bfloat16().cuda(), k.bfloat16().cuda(), v.bfloat16().cuda(), None, None, causal=False)
-    assert chosen == _cabi.KERNEL_SIMT
+
+
+# the token counts the reference's documents name as what its callers have (6^3 patches + CLS = 217, 28, ViT's 197,
+# 111, 344): none but the last is a multiple of 8, and all must stay on the tensor-core kernels -- bias and dbias rows
+# of such lengths go through padded copies, lse / delta through padded rows
+ODD = [dict(s=217, t=217), dict(s=28, t=28), dict(s=197, t=197), dict(s=111, t=344), dict(s=344, t=111), dict(s=1, t=77),
+       dict(s=130, t=5)]
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("shape", ODD)
+@pytest.mark.parametrize("name", ["dense", "bias", "bias_causal", "full_bias_mask", "key_padding", "key_bias", "mask_b1st"])
+def test_tc_any_lengths(name, shape, d):
+    q, k, v, kw = _cases.kernel_case(name, d=d, **shape)
+    dtype = torch.bfloat16
+    want_dbias = kw.get("bias") is not None
+    _assert_plans_tc(q, k, v, kw, dtype)
+    _assert_plans_tc(q, k, v, kw, dtype, which=1, want_dbias=want_dbias)
+    got, ref = run_both(q, k, v, kw, dtype, "cuda-sm100", want_dbias=want_dbias)
+    _device_ok()
+    check(got, ref, dtype)
+
+
+def test_tc_bias_with_strided_keys_and_odd_row_stride():
+    """A bias whose key axis is not contiguous (a transposed view) and one whose rows are an odd number of elements
+    apart: both reach the kernels through the padded copy instead of falling off the tensor-core path."""
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    q, k, v, _ = _cases.kernel_case("dense", s=256, t=256, d=64)
+    base = _cases._randn((2, 2, 256, 256), 3).to(torch.bfloat16)
+    dt = torch.bfloat16
+    qd, kd, vd = (x.to(dt).cuda() for x in (q, k, v))
+    wide = torch.zeros(2, 2, 256, 261, dtype=dt)
+    wide[..., :256] = base
+    for bias_cpu, bias_gpu in ((base.transpose(-1, -2), base.cuda().transpose(-1, -2)), (base, wide.cuda()[..., :256])):
+        assert att.planned_kernel(qd, kd, vd, bias_gpu, None, scale=0.125) == _cabi.KERNEL_TCGEN05
+        ref = O.reference_sdpa_torch(qd.cpu().float(), kd.cpu().float(), vd.cpu().float(), bias=bias_cpu.float())
+        got = att.scaled_dot_product_attention(qd, kd, vd, bias=bias_gpu, backend="cuda-sm100")
+        _device_ok()
+        assert abserr(got, ref) < LOWP_ABS
 
 
 def test_tc_backward_full_bias_causal_dbias_zero_past_diagonal():
