@@ -47,6 +47,20 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) gives: 65536
 static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) * 256,
               "softmax warps would wait forever for registers the producer warps never release");
 
+#ifdef NB200_PROBE
+// Development aid (not compiled into the library): cycles one softmax warp spends in each phase of its tiles.
+__device__ unsigned long long g_fprobe[16];
+#define FPROBE_DECL long long fpt_ = clock64(); const bool fprobe_ = blockIdx.x == 5 && warp == 4 && lane == 0; unsigned fp_[12] = {}
+#define FPROBE(i) do { const long long now_ = clock64(); fp_[i] += unsigned(now_ - fpt_); fpt_ = now_; } while (0)
+#define FPROBE_FLUSH do { if (fprobe_) for (int i_ = 0; i_ < 12; ++i_) g_fprobe[i_] += fp_[i_]; } while (0)
+#define FPROBE_TILES(n) do { fp_[11] += unsigned(n); } while (0)
+#else
+#define FPROBE_DECL
+#define FPROBE(i)
+#define FPROBE_FLUSH
+#define FPROBE_TILES(n)
+#endif
+
 template <int D, bool kTileBias>
 struct FwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;        // one Q / K / V tile
@@ -492,6 +506,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float2 scale2 = make_float2(a.scale, a.scale), mul2 = make_float2(mul, mul);
     uint32_t bias_phase = 0;  // bit s = parity of this tile's next wait on its "full" barrier of slot s
     int tc = 0, oc = 0, seq_base = 0;
+    FPROBE_DECL;
 
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const Item it = decode_item(a, item);
@@ -527,7 +542,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         need_mask = __any_sync(0xffffffffu, need_mask);
 
+        FPROBE(0);
         ok = wait_or_abort(bar(S_FULL + g), gt & 1, abort_flag, a.status, 108);
+        FPROBE(1);
         if (!ok) break;
         tc_fence_after_sync();
 
@@ -549,6 +566,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
         }
         // logits: t = s * scale + bias (natural units); without a bias the scale is folded into the exponent
+        FPROBE(2);
         if (a.bias_mode == kBiasTile && !a.bias_mma) {
           // slots filled before this (tile, query tile): every live query tile of the earlier key tiles, and
           // query tile 0 of this one when this is query tile 1
@@ -586,6 +604,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int i = 0; i < kTile / 2; ++i) t[i] = __fmul2_rn(t[i], scale2);
         }
+        FPROBE(3);
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < kTile / 2; ++i) {
@@ -593,6 +612,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (!((keep[i >> 4] >> ((2 * i + 1) & 31)) & 1u)) t[i].y = -INFINITY;
           }
         }
+        FPROBE(4);
         // row max: four independent chains of three-input max
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -624,6 +644,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tc_fence_after_sync();
           }
         }
+        FPROBE(6);
         // rescale the running output when some row of this warp moved its reference max
         if (j > 0 && __any_sync(0xffffffffu, bump)) {
 #pragma unroll
@@ -637,6 +658,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
         m = m_use;
+        FPROBE(7);
         // P as 16-bit pairs: 64 columns (over the S tile when aliased)
 #pragma unroll
         for (int c = 0; c < 2; ++c) tmem_st32(tP + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
@@ -644,8 +666,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY + g));
+        FPROBE(8);
       }
 
+      FPROBE(9);
       // ---------------- epilogue: out = O / l, lse = m * mul + log2 l ----------------
       if (ok && my_nt > 0) ok = wait_or_abort(bar(O_DONE + g), oc & 1, abort_flag, a.status, 110);
       if (ok && my_nt > 0) {
@@ -688,7 +712,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc += my_nt;
       oc += my_nt > 0 ? 1 : 0;
       seq_base += 2 * (it.nt[0] + it.nt[1]);
+      FPROBE(10);
+      FPROBE_TILES(my_nt);
     }
+    FPROBE_FLUSH;
   }
 
   // ---------------- teardown ----------------
@@ -753,3 +780,12 @@ int launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, c
 
 }  // namespace tc
 }  // namespace nb200
+
+#ifdef NB200_PROBE
+extern "C" NB200_API int nb200_debug_fprobe(unsigned long long* out16, int reset) {
+  unsigned long long zero[16] = {};
+  if (out16) cudaMemcpyFromSymbol(out16, nb200::tc::g_fprobe, sizeof(zero));
+  if (reset) cudaMemcpyToSymbol(nb200::tc::g_fprobe, zero, sizeof(zero));
+  return 0;
+}
+#endif

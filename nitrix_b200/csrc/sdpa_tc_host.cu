@@ -1,6 +1,7 @@
 // Host side of the tensor-core kernels: coverage gate, workspace plan, tensor
 // maps, the mask bit-packing kernel and the launches.
 #include <mutex>
+#include <stdlib.h>
 
 #include "sdpa_tc_bwd.cuh"
 #include "sdpa_tc_common.cuh"
