@@ -170,9 +170,12 @@ NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream);
 /* Backward pass for callers that cannot allocate device memory (no counterpart
  * in the reference, whose runtime allocates scratch for its kernels itself).
  * Same operands, results and status codes as nb200_sdpa_bwd, but the scratch the
- * backward needs (row-wise delta; fp32 accumulator of a broadcast bias gradient)
- * lives in a fixed NB200_STATIC_SCRATCH_BYTES array inside the library image on
- * every GPU that loads it; p->workspace and p->workspace_bytes are ignored.
+ * backward needs (row-wise delta; fp32 accumulator of a broadcast bias gradient;
+ * for the tensor-core kernels also the packed mask words -- row-major, key-major
+ * and per-sequence key counts --, the fp32 dq sums of the one-kernel backwards and
+ * any padded copies of bias / dbias / lse / delta) lives in a fixed
+ * NB200_STATIC_SCRATCH_BYTES array inside the library image on every GPU that
+ * loads it; p->workspace and p->workspace_bytes are ignored.
  *  - Allocates nothing: no cudaMalloc / cudaFree, no allocating library call.
  *  - A problem whose scratch (nb200_sdpa_workspace_bytes, backward pass) exceeds
  *    NB200_STATIC_SCRATCH_BYTES is rejected with NB200_ERR_WORKSPACE.

@@ -18,13 +18,16 @@
 //                                          (TS tcgen05.mma, Y consumed MN-major)
 // TMEM columns (512): D = 128: products of stage s in {0,1} at 128 s (P1) and 128 s + 64 (P2), E tiles written over
 // them, ACC1 at 256, ACC2 at 384.  D = 64: products as above, E tiles of their own at 256 + 64 s, ACC1 at 384,
-// ACC2 at 448, and the accumulating MMAs trail the products by two steps.
+// ACC2 at 448 (a stage's products are recomputed as soon as the element-wise warps hold them in registers).
 // Merged variant (key-major, D = 64, no bias gradient): ds goes to shared memory instead of TMEM and also feeds
 // dQ = ds K per pair of steps (a 128 x 64 tile at TMEM column 320), which the element-wise warps add to an fp32
 // accumulator in global memory; the query-major kernel is then not needed.
-// Twelve warps: 0 TMA producer (X once, Y ring), 1 bias producer, 2 MMA issuer, 3 TMEM owner (key-major: also
-// builds the per-query addends -lse / (scale log2e), -delta as MMA operands), 4-7 / 8-11 two element-wise groups
-// that take alternate steps (one owner row per thread).  All waits are bounded.
+// Twelve warps: 0 issues the accumulating MMAs, 1 the TMA copies of the step loop (ring refills and bias tiles, one
+// thread serving both), 2 issues the products, 3 owns TMEM and builds the per-query (key-major) or per-key
+// (query-major) addends as MMA operands, 4-7 / 8-11 are two element-wise groups that take alternate steps (one
+// owner row per thread).  The owner tiles and the first ring stages are issued by thread 0 during start-up.  All
+// waits are bounded.  At head dim 128 these kernels only serve what the one-kernel backward of
+// sdpa_tc_bwd_d128.cu declines (a bias gradient that needs fp32 sums).
 #include <math.h>
 #include <stdlib.h>
 
@@ -103,10 +106,9 @@ sdpa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                 ACC_DONE = E_READY + 2, B_FULL = ACC_DONE + 1, B_EMPTY = B_FULL + 2, P_FREE = B_EMPTY + 2,
                 E_FREE = P_FREE + 2, AUG_FULL = E_FREE + 2, AUG_FREE = AUG_FULL + 2, DQ_FULL = AUG_FREE + 2, DQ_FREE = DQ_FULL + 1;
   // D = 64 has TMEM room for E tiles of their own.  Then a stage's products can be recomputed as soon as the
-  // element-wise group has read them out, and the accumulating MMAs trail the products by two steps, so
-  // neither group ever waits for the other's MMAs.  D = 128 overwrites the products and trails by one.
+  // element-wise group has read them out (P_FREE).  At D = 128 the E tiles lie over the products, which can be
+  // recomputed only once the accumulating MMAs of two steps earlier have read them (E_FREE).
   constexpr bool kDeep = D == 64;
-  constexpr int kLag = kDeep ? 2 : 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = a.bh_begin + blockIdx.y;
