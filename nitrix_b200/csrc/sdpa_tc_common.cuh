@@ -150,6 +150,26 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for a pair on the FMA and integer pipes instead of the special-function unit (which serves 16 lanes a
+// clock per SM and bounds the soft-max when every exponential goes through it).  x = n + f with n the nearest
+// integer (the magic-constant add leaves n in the low mantissa bits) and f in [-0.5, 0.5]; 2^f by a cubic
+// (relative error 7.5e-5, far below the rounding of the 16-bit P it feeds), then n goes into the exponent
+// field.  Inputs below -127 (masked keys: -inf) are clamped; there the exponent field wraps negative and the
+// signed max returns exactly +0, as ex2 does.  Valid for x <= 100.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -127.f);
+  x.y = fmaxf(x.y, -127.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f), neg_magic = make_float2(-12582912.f, -12582912.f);
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 n = __fadd2_rn(t, neg_magic);
+  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+  float2 p = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+  p = __ffma2_rn(p, f, make_float2(0.6932609677f, 0.6932609677f));
+  p = __ffma2_rn(p, f, make_float2(0.9999280572f, 0.9999280572f));
+  const int bx = max(__float_as_int(p.x) + (__float_as_int(t.x) << 23), 0);
+  const int by = max(__float_as_int(p.y) + (__float_as_int(t.y) << 23), 0);
+  return make_float2(__int_as_float(bx), __int_as_float(by));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));

@@ -15,15 +15,19 @@
 // tiles in L2.  Twelve warps:
 //   warp 0      TMA producer for Q (per item) and the K / V rings
 //   warp 1      TMA producer for the bias ring (128 x 64 slots)
-//   warp 2      issues tcgen05.mma (one elected lane): D = 64 the chain of query tile 0, D = 128 both chains
-//   warp 3      D = 64: the chain of query tile 1; owns the TMEM allocation
+//   warp 2      issues tcgen05.mma for query tile 0 (one elected lane)
+//   warp 3      issues tcgen05.mma for query tile 1; owns the TMEM allocation
 //   warps 4-7   softmax of query tile 0 (one row per thread)
 //   warps 8-11  softmax of query tile 1
-// TMEM (512 columns).  D = 128: [0,128) S0 / P0, [128,256) S1 / P1, then O0, O1;
-// P (16-bit) overwrites the first 64 columns of its S tile, so per query tile the
-// chain QK(j) -> softmax(j) -> PV(j) -> QK(j+1) is serial and the two query tiles
-// interleave.  D = 64 leaves room for separate P tiles ([256,384)), so QK(j+1) is
-// issued as soon as softmax(j) has read S out and runs underneath it.
+// TMEM (512 columns).  D = 128: [0,128) S0, [128,256) S1, then O0, O1.  There is no
+// room for separate P tiles, so a key tile is taken as two halves of 64 keys: each
+// half has its own 64-column S buffer and its P (16-bit, 32 columns) overwrites
+// that buffer.  QK(half u+1) is issued right after PV(half u-1) and runs while the
+// softmax warps work on half u; only a rescale of O waits for the previous PV.
+// Both query tiles' soft-maxes then run at the same time and share the special-
+// function unit, so a quarter of the exponentials are computed on the FMA pipe.
+// D = 64 leaves room for separate P tiles ([256,384)), so QK(j+1) is issued as
+// soon as softmax(j) has read S out and runs underneath it.
 // P feeds the PV MMA as the TMEM A operand; V is consumed from shared memory as
 // an MN-major B operand, so nothing is transposed or staged through shared memory.
 // All waits are bounded (sdpa_tc_common.cuh).
@@ -41,6 +45,12 @@ constexpr int kThreads = 384;
 // register split after start-up (setmaxnreg): the softmax warps hold a whole score row
 constexpr int kProducerRegs = 56;
 constexpr int kSoftmaxRegs = 216;
+#ifndef NB200_POLY_PERIOD
+#define NB200_POLY_PERIOD 4
+#endif
+// D = 128: one pair in this many computes 2^x without the special-function unit (0: none).  There the two query
+// tiles' soft-maxes run at the same time and share the unit; at D = 64 the extra arithmetic costs more than it saves.
+constexpr int kPolyPeriod = NB200_POLY_PERIOD;
 // setmaxnreg.inc blocks (without bound) until the CTA's OWN pool -- the registers it was launched with, here
 // kLaunchRegs per thread -- holds enough released registers, so the hand-over must balance at compile time.
 constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) gives: 65536 / 384 rounded down to a multiple of 8
@@ -83,7 +93,7 @@ struct FwdSmem {
   // no swizzle, 4 KB) and a ring of three 128-key x 16 tiles (4 KB each).
   static constexpr int kAugSlots = 3;
   static constexpr int kAugTileBytes = (kTile / 8) * 256;
-  static constexpr int kNumBars = 4 + 4 * kStages + 12 + 3 * kBiasSlots + 2 * kAugSlots;
+  static constexpr int kNumBars = 4 + 4 * kStages + 16 + 3 * kBiasSlots + 2 * kAugSlots;
   static constexpr int kMisc = kBars + 8 * kNumBars;      // tmem base (4 B) + abort flag (4 B)
   static constexpr int kTotal = kMisc + 16;
 };
@@ -162,10 +172,12 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   auto bar = [&](int i) { return smem_u32(bars + i); };
   constexpr int Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + kStages, V_FULL = K_EMPTY + kStages,
-                V_EMPTY = V_FULL + kStages, S_FULL = V_EMPTY + kStages, P_READY = S_FULL + 2, O_DONE = P_READY + 2,
+                V_EMPTY = V_FULL + kStages, S_FULL = V_EMPTY + kStages, P_READY = S_FULL + 4, O_DONE = P_READY + 4,
                 O_FREE = O_DONE + 2, S_FREE = O_FREE + 2, PV_DONE = S_FREE + 2, B_FULL = PV_DONE + 2,
                 B_EMPTY = B_FULL + 2 * L::kBiasSlots, AUG_FULL = B_EMPTY + L::kBiasSlots, AUG_FREE = AUG_FULL + L::kAugSlots;
-  // D = 128 fills TMEM (2 x 128 S + 2 x 128 O): P must overwrite S and each query tile's chain is serial.
+  // D = 128 fills TMEM (2 x 128 S + 2 x 128 O), so P must overwrite S: a key tile is taken as two halves of 64
+  //   keys, each with its own 64-column S buffer and P written over that buffer, and the scores of the next half
+  //   are computed while the softmax warps work on the current one.
   // D = 64 leaves room for separate P tiles, so the next score MMA can run under the current softmax.
   constexpr bool kAlias = D == 128;
 
@@ -175,13 +187,13 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (threadIdx.x == 0) {
     for (int i = 0; i < L::kNumBars; ++i) {
       uint32_t count = 1;
-      if (i >= P_READY && i < P_READY + 2) count = 4;                       // one lane per softmax warp of the tile
-      if (i >= K_EMPTY && i < K_EMPTY + kStages) count = kAlias ? 1 : 2;    // one arrival per MMA issuer
-      if (i >= V_EMPTY && i < V_EMPTY + kStages) count = kAlias ? 1 : 2;
+      if (i >= P_READY && i < P_READY + 4) count = 4;                       // one lane per softmax warp of the tile
+      if (i >= K_EMPTY && i < K_EMPTY + kStages) count = 2;    // one arrival per MMA issuer
+      if (i >= V_EMPTY && i < V_EMPTY + kStages) count = 2;
       if (i >= O_FREE && i < O_FREE + 2) count = 4;                         // one lane per softmax warp of the tile
       if (i >= S_FREE && i < S_FREE + 2) count = 4;
       if (i >= B_EMPTY && i < B_EMPTY + L::kBiasSlots) count = a.bias_mma ? 1 : 4;   // MMA issuer or the tile's warps
-      if (i >= AUG_FREE && i < AUG_FREE + L::kAugSlots) count = kAlias ? 1 : 2;        // one arrival per MMA issuer
+      if (i >= AUG_FREE && i < AUG_FREE + L::kAugSlots) count = 2;        // one arrival per MMA issuer
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
@@ -360,16 +372,15 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
     }
-  } else if (kAlias ? warp == 2 : true) {
+  } else {
     // ---------------- MMA issuers ----------------
-    // D = 64: warp 2 issues the chain of query tile 0, warp 3 that of query tile 1; a tile's next score MMA
-    //   runs under its own softmax, so the two chains are independent.
-    // D = 128: warp 2 alone issues both chains in a fixed order (tile 0 then tile 1 per round).  The
-    //   serial order staggers the two query tiles, so that one tile's MMAs run under the other's softmax.
+    // Warp 2 issues the chain of query tile 0, warp 3 that of query tile 1; a tile's next score MMA runs under
+    // its own softmax, so the two chains are independent (one thread issuing both was measured slower at both
+    // head sizes: it needs some 50 cycles per instruction and a wait for one tile holds up the other).
     // An issuer observes every key tile of the rings, also those its query tile skips, and commits once per
     // tile to the "empty" barriers (with nothing outstanding the arrival is immediate): one arrival per
     // issuer per phase.
-    const int g_begin = kAlias ? 0 : warp - 2, g_end = kAlias ? 2 : warp - 1;
+    const int g_begin = warp - 2, g_end = warp - 1;
     if (elect_one()) {
       constexpr uint32_t idesc_qk = make_idesc(kBf16, kTile, kTile, false, false);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, kTile, D, false, true);
@@ -388,6 +399,84 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       uint32_t bias_phase = 0;     // bit s = parity of this issuer's next wait on its tile's "full" barrier of slot s
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const Item it = decode_item(a, item);
+        if constexpr (kAlias) {
+          // D = 128: key tiles are taken in two halves of 64 keys.  A query tile's S region holds two 64-column
+          // buffers, one per half, and P (16-bit, 32 columns) is written over its own buffer, so the scores of the
+          // next half are computed while the softmax warps work on the current one.  Round u (half u = 2 j + hf):
+          // the score MMAs of half u of this issuer's query tile, then the output MMAs of half u - 1.  Everything that
+          // touches a query tile's buffers is issued by this one thread and the tensor core runs it in order: the
+          // scores of half u follow the output MMA of half u - 2, which read P out of the same buffer.
+          constexpr uint32_t idesc_qk64 = make_idesc(kBf16, kTile, kTile / 2, false, false);
+          const int n_sub = 2 * it.nt_max;
+          for (int u = 0; u <= n_sub && ok; ++u) {
+            const int j = u >> 1, hf = u & 1;                 // scores: tile j, half hf
+            const int jp = (u - 1) >> 1, hp = (u - 1) & 1;    // outputs: tile jp, half hp
+            const int st = (kv + j) % kStages, stp = (kv + jp) % kStages;
+            const int aslot = (kv + j) % L::kAugSlots;
+            if (u < n_sub && hf == 0) {
+              ok = wait_or_abort(bar(K_FULL + st), ((kv + j) / kStages) & 1, abort_flag, a.status, 105);
+              if (!kTileBias && a.key_mma && ok)
+                ok = wait_or_abort(bar(AUG_FULL + aslot), ((kv + j) / L::kAugSlots) & 1, abort_flag, a.status, 118);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            if (u < n_sub) {
+              for (int g = g_begin; g < g_end && ok; ++g) {
+                if (j >= it.nt[g]) continue;
+                if (u == 0) {
+                  ok = wait_or_abort(bar(Q_FULL + g), oc[g] & 1, abort_flag, a.status, 104);
+                  if (!ok) break;
+                  tc_fence_after_sync();
+                }
+                const uint32_t tS = tm_S[g] + hf * 64;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                  const uint64_t off = uint64_t(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+                  mma_ss(tS, qdesc[g] + off, kdesc[st] + off + uint64_t((hf * 64 * 128) >> 4), idesc_qk64, kk > 0 ? 1u : 0u);
+                }
+                if constexpr (!kTileBias) {
+                  if (a.key_mma) {
+                    // S += W C^T for the 64 keys of this half (8 groups of 8 keys, 256 bytes each, into the tile)
+                    const uint64_t wdesc = make_smem_desc_noswizzle(sbase + L::kBias, 128, 256);
+                    const uint64_t cdesc = make_smem_desc_noswizzle(sbase + L::kBias + L::kAugTileBytes * (1 + aslot) + hf * 2048, 128, 256);
+                    mma_ss(tS, wdesc, cdesc, idesc_qk64, 1u);
+                  }
+                }
+                mma_commit(bar(S_FULL + 2 * g + hf));
+                if (u == 2 * it.nt[g] - 1) mma_commit(bar(Q_EMPTY + g));   // Q_g may be reloaded once these are done
+              }
+              if (!ok) break;
+              if (hf == 1) {
+                mma_commit(bar(K_EMPTY + st));
+                if (!kTileBias && a.key_mma) mma_commit(bar(AUG_FREE + aslot));
+              }
+            }
+            if (u >= 1) {
+              if (hp == 0) {
+                ok = wait_or_abort(bar(V_FULL + stp), ((kv + jp) / kStages) & 1, abort_flag, a.status, 106);
+                if (!ok) break;
+              }
+              for (int g = g_begin; g < g_end && ok; ++g) {
+                if (jp >= it.nt[g]) continue;
+                ok = wait_or_abort(bar(P_READY + 2 * g + hp), (tc[g] + jp) & 1, abort_flag, a.status, 107);
+                // the previous item's epilogue must have read O_g out before the first half overwrites it
+                if (ok && u == 1 && oc[g] > 0)
+                  ok = wait_or_abort(bar(O_FREE + g), (oc[g] - 1) & 1, abort_flag, a.status, 115);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tP = tm_S[g] + hp * 64;
+#pragma unroll
+                for (int kk = 0; kk < kTile / 32; ++kk)
+                  mma_ts(tm_O[g], tP + kk * 8, vdesc[stp] + uint64_t(((hp * 4 + kk) * 2048) >> 4), idesc_pv,
+                         (u > 1 || kk > 0) ? 1u : 0u);
+                mma_commit(bar(PV_DONE + g));
+                if (u == 2 * it.nt[g]) mma_commit(bar(O_DONE + g));
+              }
+              if (!ok) break;
+              if (hp == 1) mma_commit(bar(V_EMPTY + stp));
+            }
+          }
+        } else {
         // round j: score MMA of key tile j and output MMA of key tile j - 1
         for (int j = 0; j <= it.nt_max && ok; ++j) {
           const int st = (kv + j) % kStages, stp = (kv + j + kStages - 1) % kStages;
@@ -413,14 +502,14 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               for (int kk = 0; kk < kTile / 16; ++kk)
                 mma_ts(tm_O[g], tm_P[g] + kk * 8, vdesc[stp] + uint64_t((kk * 2048) >> 4), idesc_pv,
                        (jj > 0 || kk > 0) ? 1u : 0u);
-              if (!kAlias) mma_commit(bar(PV_DONE + g));
+              mma_commit(bar(PV_DONE + g));
               if (jj == nt - 1) mma_commit(bar(O_DONE + g));
             };
             auto round_qk = [&]() {
               if (j >= nt) return;
               const int gt = tc[g] + j;
               if (j == 0) ok = wait_or_abort(bar(Q_FULL + g), oc[g] & 1, abort_flag, a.status, 104);
-              if (ok && !kAlias && gt > 0) ok = wait_or_abort(bar(S_FREE + g), (gt - 1) & 1, abort_flag, a.status, 111);
+              if (ok && gt > 0) ok = wait_or_abort(bar(S_FREE + g), (gt - 1) & 1, abort_flag, a.status, 111);
               if (!ok) return;
               tc_fence_after_sync();
 #pragma unroll
@@ -465,18 +554,14 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               mma_commit(bar(S_FULL + g));
               if (j == nt - 1) mma_commit(bar(Q_EMPTY + g));   // Q_g may be reloaded once these are done
             };
-            if constexpr (kAlias) {
-              round_pv();   // P(j-1) lives in S_g: its output MMA goes first
-              if (ok) round_qk();
-            } else {
-              round_qk();   // S_g was read out early in softmax(j-1): the next scores run underneath it
-              if (ok) round_pv();
-            }
+            round_qk();   // S_g was read out early in softmax(j-1): the next scores run underneath it
+            if (ok) round_pv();
           }
           if (!ok) break;
           if (j < it.nt_max) mma_commit(bar(K_EMPTY + st));
           if (!kTileBias && a.key_mma && j < it.nt_max) mma_commit(bar(AUG_FREE + aslot));
           if (j > 0) mma_commit(bar(V_EMPTY + stp));
+        }
         }
         kv += it.nt_max;
         seq_base += 2 * (it.nt[0] + it.nt[1]);
@@ -523,37 +608,72 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (a.bias_mode == kBiasKey && !key_mma)
         bias_key = reinterpret_cast<const uint8_t*>(a.bias) + 2 * (b * a.bias_bs + h * a.bias_hs);
 
+      // D = 128 takes a key tile as two halves of 64 keys (one S buffer each, P written over its own buffer);
+      // D = 64 takes it whole
+      constexpr int kSub = kAlias ? kTile / 2 : kTile;   // keys per pass
+      constexpr int kSubs = kTile / kSub;
+      uint32_t mnext[kSub / 32];   // keep-bits of this row for the coming pass
+      auto load_mask_words = [](const uint32_t* src, uint32_t (&dst)[kSub / 32]) {
+        if constexpr (kSub == 64) {
+          const uint2 w = __ldg(reinterpret_cast<const uint2*>(src));
+          dst[0] = w.x; dst[1] = w.y;
+        } else {
+          const uint4 w = __ldg(reinterpret_cast<const uint4*>(src));
+          dst[0] = w.x; dst[1] = w.y; dst[2] = w.z; dst[3] = w.w;
+        }
+      };
+#pragma unroll
+      for (int i = 0; i < kSub / 32; ++i) mnext[i] = 0xffffffffu;
+      if (mrow && my_nt > 0) load_mask_words(mrow, mnext);
       for (int j = 0; j < my_nt && ok; ++j) {
-        const int key0 = j * kTile;
         const int gt = tc + j;   // this tile's running index for this query tile
-        // keep-bits of this row for this key tile
-        uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+#pragma unroll 1
+        for (int hf = 0; hf < kSubs && ok; ++hf) {
+        const int key0 = j * kTile + hf * kSub;
+        const bool first = j == 0 && hf == 0;
+        const int sbar = kAlias ? 2 * g + hf : g;
+        const uint32_t tSh = tS + hf * kSub;
+        // keep-bits of this row for these keys
+        uint32_t keep[kSub / 32];
+#pragma unroll
+        for (int i = 0; i < kSub / 32; ++i) keep[i] = 0xffffffffu;
         bool need_mask = false;
         if (mrow) {
-          const uint4 w = __ldg(reinterpret_cast<const uint4*>(mrow + j * 4));
-          keep[0] = w.x; keep[1] = w.y; keep[2] = w.z; keep[3] = w.w;
-          need_mask = (w.x & w.y & w.z & w.w) != 0xffffffffu;   // a tile the mask keeps whole needs no selects
+          // this pass's words were fetched a pass ago; the next pass's fetch runs under this pass's arithmetic
+          uint32_t all = 0xffffffffu;
+#pragma unroll
+          for (int i = 0; i < kSub / 32; ++i) {
+            keep[i] = mnext[i];
+            all &= mnext[i];
+          }
+          need_mask = all != 0xffffffffu;   // keys the mask keeps whole need no selects
+          const int nj = hf + 1 < kSubs ? j : j + 1, nh = hf + 1 < kSubs ? hf + 1 : 0;
+          if (nj < my_nt) load_mask_words(mrow + nj * 4 + nh * (kSub / 32), mnext);
         }
         int n_keep = a.T - key0;
         if (a.causal) n_keep = min(n_keep, row - key0 + 1);
-        if (n_keep < kTile) {
-          limit_bits(keep, n_keep);
+        if (n_keep < kSub) {
+#pragma unroll
+          for (int i = 0; i < kSub / 32; ++i) {
+            const int n = n_keep - 32 * i;
+            keep[i] &= n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u));
+          }
           need_mask = true;
         }
         need_mask = __any_sync(0xffffffffu, need_mask);
 
         FPROBE(0);
-        ok = wait_or_abort(bar(S_FULL + g), gt & 1, abort_flag, a.status, 108);
+        ok = wait_or_abort(bar(S_FULL + sbar), gt & 1, abort_flag, a.status, 108);
         FPROBE(1);
         if (!ok) break;
         tc_fence_after_sync();
 
-        // the whole score row: four TMEM loads in flight, one wait; handled as 64 fp32 pairs
-        float2 t[kTile / 2];
+        // the whole score row of this pass: all TMEM loads in flight, one wait; handled as fp32 pairs
+        float2 t[kSub / 2];
         {
-          uint32_t raw[kTile];
+          uint32_t raw[kSub];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
+          for (int c = 0; c < kSub / 32; ++c) tmem_ld32(tSh + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
           tmem_wait_ld();
           if constexpr (!kAlias) {
             // the scores are in registers: S_g may be overwritten by the next tile's MMA right away
@@ -562,18 +682,18 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (lane == 0) mbar_arrive(bar(S_FREE + g));
           }
 #pragma unroll
-          for (int i = 0; i < kTile / 2; ++i)
+          for (int i = 0; i < kSub / 2; ++i)
             t[i] = make_float2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
         }
         // logits: t = s * scale + bias (natural units); without a bias the scale is folded into the exponent
         FPROBE(2);
         if (a.bias_mode == kBiasTile && !a.bias_mma) {
           // slots filled before this (tile, query tile): every live query tile of the earlier key tiles, and
-          // query tile 0 of this one when this is query tile 1
+          // query tile 0 of this one when this is query tile 1.  One slot per 64 keys.
           const int seq0 = seq_base + 2 * (min(j, it.nt[0]) + min(j, it.nt[1]) + ((g == 1 && j < it.nt[0]) ? 1 : 0));
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int slot = (seq0 + half) % L::kBiasSlots;
+          for (int hh = 0; hh < kSub / 64; ++hh) {
+            const int slot = (seq0 + (kAlias ? hf : hh)) % L::kBiasSlots;
             ok = wait_or_abort(bar(B_FULL + g * L::kBiasSlots + slot), (bias_phase >> slot) & 1u, abort_flag, a.status,
                                109);
             if (!ok) break;
@@ -585,7 +705,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e)
-                t[half * 32 + c * 4 + e] = __ffma2_rn(t[half * 32 + c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
+                t[hh * 32 + c * 4 + e] = __ffma2_rn(t[hh * 32 + c * 4 + e], scale2, unpack2<kBf16>(ww[e]));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_EMPTY + slot));
@@ -594,7 +714,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         } else if (a.bias_mode == kBiasKey && !key_mma) {
           const uint4* bk = reinterpret_cast<const uint4*>(bias_key + 2 * key0);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < kSub / 8; ++c) {
             const uint4 w = key0 + 8 * c < a.T ? __ldg(bk + c) : make_uint4(0, 0, 0, 0);   // T is a multiple of 8
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -602,12 +722,12 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         } else if (!fold_scale) {
 #pragma unroll
-          for (int i = 0; i < kTile / 2; ++i) t[i] = __fmul2_rn(t[i], scale2);
+          for (int i = 0; i < kSub / 2; ++i) t[i] = __fmul2_rn(t[i], scale2);
         }
         FPROBE(3);
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < kTile / 2; ++i) {
+          for (int i = 0; i < kSub / 2; ++i) {
             if (!((keep[i >> 4] >> ((2 * i) & 31)) & 1u)) t[i].x = -INFINITY;
             if (!((keep[i >> 4] >> ((2 * i + 1) & 31)) & 1u)) t[i].y = -INFINITY;
           }
@@ -616,7 +736,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // row max: four independent chains of three-input max
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < kTile / 2; ++i) mx4[i & 3] = max3(mx4[i & 3], t[i].x, t[i].y);
+        for (int i = 0; i < kSub / 2; ++i) mx4[i & 3] = max3(mx4[i & 3], t[i].x, t[i].y);
         const float mx = max3(mx4[0], mx4[1], fmaxf(mx4[2], mx4[3]));
         // the exponentials use a reference max that is only moved when the true max has run more than
         // 2^8 ahead of it (so p <= 256 and the running output is rescaled rarely); l uses the same reference
@@ -626,15 +746,18 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const float neg = m_use == -INFINITY ? 0.f : -m_use * mul;
         const float2 neg2 = make_float2(neg, neg);
         float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-        uint32_t pk[kTile / 2];
+        uint32_t pk[kSub / 2];
 #pragma unroll
-        for (int i = 0; i < kTile / 2; ++i) {
+        for (int i = 0; i < kSub / 2; ++i) {
           const float2 x = __ffma2_rn(t[i], mul2, neg2);
-          const float2 p = make_float2(ex2(x.x), ex2(x.y));
+          // every kPolyPeriod-th pair takes its exponentials on the FMA pipe (see ex2_poly2)
+          const float2 p = (kAlias && kPolyPeriod > 0 && i % (kPolyPeriod > 0 ? kPolyPeriod : 1) == 0) ? ex2_poly2(x)
+                                                                                             : make_float2(ex2(x.x), ex2(x.y));
           sum2[i & 1] = __fadd2_rn(sum2[i & 1], p);
           pk[i] = pack2<kBf16>(p.x, p.y);
         }
         l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+        const bool rescale = !first && __any_sync(0xffffffffu, bump);
         if constexpr (!kAlias) {
           // O_g and P_g are still in use by the previous tile's output MMA until it has completed
           // (the first tile of an item follows the previous item's epilogue, which waited for that)
@@ -643,10 +766,17 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (!ok) break;
             tc_fence_after_sync();
           }
+        } else if (rescale) {
+          // O_g is being accumulated into by the previous half's output MMA until that has completed (its P buffer
+          // is the other one, and this buffer's earlier reader ran before these scores).  Output MMA number
+          // 2 gt + hf - 1 of this query tile: at most one phase of the barrier is outstanding, so parity names it.
+          ok = wait_or_abort(bar(PV_DONE + g), (2 * gt + hf - 1) & 1, abort_flag, a.status, 112);
+          if (!ok) break;
+          tc_fence_after_sync();
         }
         FPROBE(6);
         // rescale the running output when some row of this warp moved its reference max
-        if (j > 0 && __any_sync(0xffffffffu, bump)) {
+        if (rescale) {
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
@@ -659,14 +789,16 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         m = m_use;
         FPROBE(7);
-        // P as 16-bit pairs: 64 columns (over the S tile when aliased)
+        // P as 16-bit pairs: half as many columns as keys (over its own S buffer when aliased)
+        const uint32_t tPh = kAlias ? tSh : tP;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) tmem_st32(tP + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
+        for (int c = 0; c < kSub / 64; ++c) tmem_st32(tPh + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(P_READY + g));
+        if (lane == 0) mbar_arrive(bar(P_READY + sbar));
         FPROBE(8);
+        }
       }
 
       FPROBE(9);
