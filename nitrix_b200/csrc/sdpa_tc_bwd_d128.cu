@@ -499,15 +499,15 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       return true;
     };
 
+    uint2 mnext = make_uint2(0xffffffffu, 0xffffffffu);
+    if (mbits && grp < n_steps) mnext = __ldg(reinterpret_cast<const uint2*>(mbits + (step_row(grp) >> 5)));
     for (int n = grp; n < n_steps && ok; n += 2) {
       const int s = n & 1;
       const int r0 = step_row(n);
       // keep bits over the step's 64 queries: query r0 + c needs c < S - r0 and (causal) r0 + c >= key
-      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
-      if (mbits) {
-        const uint2 w = __ldg(reinterpret_cast<const uint2*>(mbits + (r0 >> 5)));
-        keep[0] = w.x; keep[1] = w.y;
-      }
+      // (the mask words of this step were fetched a step of this group ago; the next fetch runs under this step)
+      uint32_t keep[2] = {mnext.x, mnext.y};
+      if (mbits && n + 2 < n_steps) mnext = __ldg(reinterpret_cast<const uint2*>(mbits + (step_row(n + 2) >> 5)));
       {
         const int hi = a.S - r0;
         const int lo = a.causal ? key - r0 : 0;
