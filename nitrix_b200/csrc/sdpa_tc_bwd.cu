@@ -1110,6 +1110,7 @@ int launch_bwd(const Problem& pr, int dtype, int bias_dtype, void* ws, size_t ws
     D128Maps maps{k128, v128, q64, g64, bias_k, q64};
     if (pr.dbias) {
       ak.dbias = pr.dbias;
+      for (int i = 0; i < 4; ++i) ak.dbs[i] = pr.dbs[i];
       if (!make_tile_map(&maps.dbias, pr.dbias, pr.S, pr.T, pr.H, pr.B, pr.dbs[2], pr.dbs[1], pr.dbs[0], kStep, &why)) {
         set_error("dbias tensor map: %s", why);
         return NB200_ERR_LAUNCH;

@@ -87,7 +87,7 @@ struct Smem {
   static_assert(kTotal + 1024 <= 232448, "shared memory exceeds the per-CTA limit");
 };
 
-template <bool kBf16, bool kTileBias>
+template <bool kBf16, bool kTileBias, bool kDbias>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                         const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
@@ -127,7 +127,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     if (j >= n_steps) j -= n_steps;
     return (s_begin + j) * kStep;
   };
-  const bool store_dbias = a.dbias != nullptr;
+  constexpr bool store_dbias = kDbias;   // the ds tile doubles as the source of the dbias TMA stores
 
   if (threadIdx.x < L::kNumBars) {
     const int i = threadIdx.x;
@@ -357,8 +357,8 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     // ---------------- MMA issuer 2: dV, dK and dQ^T of every step ----------------
     if (elect_one() && n_steps > 0) {
       constexpr uint32_t idesc_acc = make_idesc(kBf16, kTile, kD, false, true);     // dV: A from TMEM, B = dO MN-major
-      constexpr uint32_t idesc_dk = make_idesc(kBf16, kTile, kD, true, true);       // dK: A = ds^T MN-major, B = Q MN-major
-      constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, kStep, true, false);   // dQ^T: A = K MN-major, B = ds^T K-major
+      constexpr uint32_t idesc_dk = make_idesc(kBf16, kTile, kD, kDbias, true);     // dK: A = ds (MN-major when [query x key]), B = Q MN-major
+      constexpr uint32_t idesc_dq = make_idesc(kBf16, kTile, kStep, true, !kDbias); // dQ^T: A = K MN-major, B = ds (K-major when [query x key])
       bool ok = wait_or_abort(bar(X_FULL), 0, abort_flag, a.status, 303);
       const uint64_t kmn = make_smem_desc(sbase + L::kX, kBoxBytes, 1024);          // K as [d x key], d contiguous
       for (int m = 0; m < n_steps && ok; ++m) {
@@ -370,13 +370,16 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const uint64_t qmn = make_smem_desc(ybase, kYBoxBytes, 1024);                    // Q as [query x d], d contiguous
         const uint64_t gmn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);      // dO likewise
         const uint32_t dsbuf = sbase + L::kDs + (m % NDS) * kBoxBytes;
-        const uint64_t ds_mn = make_smem_desc(dsbuf, kYBoxBytes, 1024);                  // ds^T as [key x query] A operand
+        // ds as the A operand of dK (M = key, K = query): [query x key] is MN-major, 16 queries = 16 rows of a box;
+        // [key x query] is K-major, 16 queries = 32 bytes of a row
+        const uint64_t ds_a = kDbias ? make_smem_desc(dsbuf, kYBoxBytes, 1024) : make_smem_desc(dsbuf, 16, 1024);
+        constexpr int ds_a_step = kDbias ? 2048 : 32;
         const uint32_t e1 = tm_e + s * 32;
         // dV += p^T dO (p from TMEM) and dK += ds^T Q: two independent chains, issued alternately
 #pragma unroll
         for (int kk = 0; kk < kStep / 16; ++kk) {
           mma_ts(tm_dv, e1 + kk * 8, gmn + uint64_t((kk * 2048) >> 4), idesc_acc, (m > 0 || kk > 0) ? 1u : 0u);
-          mma_ss(tm_dk, ds_mn + uint64_t((kk * 2048) >> 4), qmn + uint64_t((kk * 2048) >> 4), idesc_dk,
+          mma_ss(tm_dk, ds_a + uint64_t((kk * ds_a_step) >> 4), qmn + uint64_t((kk * 2048) >> 4), idesc_dk,
                  (m > 0 || kk > 0) ? 1u : 0u);
         }
         mma_commit(bar(E_FREE + s));             // p of this stage may be rewritten
@@ -387,11 +390,13 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           if (!ok) break;
           tc_fence_after_sync();
         }
-        const uint64_t ds_k = make_smem_desc(dsbuf, 16, 1024);
+        // ds as the B operand of dQ^T (N = query, K = key): [query x key] is K-major, 16 keys = 32 bytes of a query
+        // row (second box from key 64 on); [key x query] is MN-major, 16 keys = 16 rows
+        const uint64_t ds_b = kDbias ? make_smem_desc(dsbuf, 16, 1024) : make_smem_desc(dsbuf, kBoxBytes, 1024);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint64_t bo = uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4);    // 16 keys of a query row
-          mma_ss(tm_dq, kmn + uint64_t((kk * 2048) >> 4), ds_k + bo, idesc_dq, kk > 0 ? 1u : 0u);
+          const uint64_t bo = kDbias ? uint64_t(((kk / 4) * kYBoxBytes + (kk % 4) * 32) >> 4) : uint64_t((kk * 2048) >> 4);
+          mma_ss(tm_dq, kmn + uint64_t((kk * 2048) >> 4), ds_b + bo, idesc_dq, kk > 0 ? 1u : 0u);
         }
         mma_commit(bar(DQ_FULL + (m & 1)));
         mma_commit(bar(DS_FREE + (m & 1)));      // the ds^T tile has been read by dK and dQ^T
@@ -471,10 +476,16 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       const uint16_t raw = reinterpret_cast<const uint16_t*>(a.bias)[b * a.bias_bs + h * a.bias_hs + key];
       bias_own = kBf16 ? __uint_as_float(uint32_t(raw) << 16) : __half2float(__ushort_as_half(raw));
     }
-    // ds^T tile: element (query c, key r) lives in box r / 64, row c, 16-byte chunk ((r % 64) / 8) ^ (c % 8)
-    // (the tile base is 1024-byte aligned and the other terms leave bits 4-6 clear, so the chunk swizzle is one XOR
-    // of the row's low bits into the address)
-    const uint32_t ds_thread = uint32_t(r >> 6) * kYBoxBytes + uint32_t(r & 7) * 2 + (uint32_t((r & 63) >> 3) << 4);
+    // The ds tile (16 KB, 128-byte swizzle) feeds dK += ds^T Q and dQ^T = K^T ds^T; either orientation serves both
+    // MMAs (operand majors are free), so the layout follows the third use:
+    //  * with a dbias to store it is [64 queries x 128 keys] (two boxes of 64 keys), exactly a dbias tile, which leaves
+    //    by TMA; a thread (one key) then writes 64 separate 16-bit elements: element (query c, key r) lives in box
+    //    r / 64, row c, 16-byte chunk ((r % 64) / 8) ^ (c % 8)
+    //  * without, it is [128 keys x 64 queries]: a thread writes its own 128-byte row as eight 16-byte chunks,
+    //    chunk i at position i ^ (r % 8)
+    // (the tile base is 1024-byte aligned and the other terms leave bits 4-6 clear, so the swizzle is one XOR)
+    const uint32_t ds_thread = kDbias ? uint32_t(r >> 6) * kYBoxBytes + uint32_t(r & 7) * 2 + (uint32_t((r & 63) >> 3) << 4)
+                                      : uint32_t(r) * 128 + (uint32_t(r & 7) << 4);
     // dq accumulator of this (batch, head): [query / 4][d][query % 4] floats, so that one warp-wide reduction of
     // four queries covers 512 contiguous bytes (lanes = 32 consecutive d)
 
@@ -596,11 +607,19 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       PROBE(6);
       {
         const uint32_t tile = sbase + L::kDs + (n % NDS) * kBoxBytes + ds_thread;
+        if constexpr (kDbias) {
+  #pragma unroll
+          for (int c = 0; c < kStep / 2; ++c) {
+            const uint32_t lo16 = e2[c] & 0xffffu, hi16 = e2[c] >> 16;
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"((tile ^ (((2 * c) & 7) << 4)) + (2 * c) * 128), "h"(uint16_t(lo16)) : "memory");
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"((tile ^ (((2 * c + 1) & 7) << 4)) + (2 * c + 1) * 128), "h"(uint16_t(hi16)) : "memory");
+          }
+        } else {
 #pragma unroll
-        for (int c = 0; c < kStep / 2; ++c) {
-          const uint32_t lo16 = e2[c] & 0xffffu, hi16 = e2[c] >> 16;
-          asm volatile("st.shared.u16 [%0], %1;" ::"r"((tile ^ (((2 * c) & 7) << 4)) + (2 * c) * 128), "h"(uint16_t(lo16)) : "memory");
-          asm volatile("st.shared.u16 [%0], %1;" ::"r"((tile ^ (((2 * c + 1) & 7) << 4)) + (2 * c + 1) * 128), "h"(uint16_t(hi16)) : "memory");
+          for (int i = 0; i < 8; ++i)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile ^ (uint32_t(i) << 4)), "r"(e2[4 * i]),
+                         "r"(e2[4 * i + 1]), "r"(e2[4 * i + 2]), "r"(e2[4 * i + 3])
+                         : "memory");
         }
         fence_proxy_async_smem();
       }
@@ -693,9 +712,9 @@ __global__ void dq_finish_d128_kernel(const float* __restrict__ acc, void* dq, i
   }
 }
 
-template <bool kBf16, bool kTileBias>
+template <bool kBf16, bool kTileBias, bool kDbias>
 int launch_one(const D128Maps& m, const BwdArgs& a, int n_tiles, int bh_count, cudaStream_t st) {
-  auto kernel = sdpa_bwd_tc_d128_kernel<kBf16, kTileBias>;
+  auto kernel = sdpa_bwd_tc_d128_kernel<kBf16, kTileBias, kDbias>;
   const int smem = Smem<kTileBias>::kTotal + 1024;
   static bool ready[64] = {};
   int dev = 0;
@@ -748,8 +767,14 @@ size_t d128_acc_bytes(const Problem& pr) {
 
 int launch_bwd_d128(const D128Maps& maps, const BwdArgs& a, bool bf16, bool tile_bias, int n_tiles, int bh_count,
                     cudaStream_t st) {
-  if (tile_bias) return bf16 ? launch_one<true, true>(maps, a, n_tiles, bh_count, st) : launch_one<false, true>(maps, a, n_tiles, bh_count, st);
-  return bf16 ? launch_one<true, false>(maps, a, n_tiles, bh_count, st) : launch_one<false, false>(maps, a, n_tiles, bh_count, st);
+  if (tile_bias && a.dbias)
+    return bf16 ? launch_one<true, true, true>(maps, a, n_tiles, bh_count, st)
+                : launch_one<false, true, true>(maps, a, n_tiles, bh_count, st);
+  if (tile_bias)
+    return bf16 ? launch_one<true, true, false>(maps, a, n_tiles, bh_count, st)
+                : launch_one<false, true, false>(maps, a, n_tiles, bh_count, st);
+  return bf16 ? launch_one<true, false, false>(maps, a, n_tiles, bh_count, st)
+              : launch_one<false, false, false>(maps, a, n_tiles, bh_count, st);
 }
 
 int launch_dq_finish_d128(const Problem& pr, const float* acc, int acc_rows, bool bf16, cudaStream_t st) {
