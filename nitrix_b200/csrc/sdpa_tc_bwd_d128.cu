@@ -80,7 +80,7 @@ struct Smem {
   static constexpr int kWeights = kIdent + 1024;
   static constexpr int kAug = kWeights + kWeightBytes;          // two slots
   static constexpr int kBars = kAug + 2 * kAugSlotBytes;
-  static constexpr int kNumBars = 1 + 2 * kYStages + 2 * 13 + 1;
+  static constexpr int kNumBars = 1 + 2 * kYStages + 2 * 14 + 1;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
   static_assert(kY % 1024 == 0 && kBias % 1024 == 0 && kDs % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -105,8 +105,8 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + NY, PROD_FULL = Y_EMPTY + NY, P_FREE = PROD_FULL + 4,
                 E_READY = P_FREE + 4, E_FREE = E_READY + 2, DS_FREE = E_FREE + 2, DQ_FULL = DS_FREE + 2,
                 DQ_FREE = DQ_FULL + 2, B_FULL = DQ_FREE + 2, B_EMPTY = B_FULL + 2, AUG_FULL = B_EMPTY + 2,
-                AUG_FREE = AUG_FULL + 2, ACC_DONE = AUG_FREE + 2;
-  static_assert(ACC_DONE + 1 == L::kNumBars, "barrier count");
+                AUG_FREE = AUG_FULL + 2, ACC_DONE = AUG_FREE + 2, P_READY = ACC_DONE + 1;
+  static_assert(P_READY + 2 == L::kNumBars, "barrier count");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = a.bh_begin + blockIdx.y;
@@ -134,6 +134,7 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     uint32_t count = 1;
     if (i >= P_FREE && i < P_FREE + 4) count = 4;      // one lane per warp of the group
     if (i >= E_READY && i < E_READY + 2) count = 4;
+    if (i >= P_READY && i < P_READY + 2) count = 4;
     if (i >= DQ_FREE && i < DQ_FREE + 2) count = 4;
     if (i >= DS_FREE && i < DS_FREE + 2) count = store_dbias ? 2 : 1;   // the MMAs, and the dbias store
     mbar_init(bar(i), count);
@@ -363,9 +364,6 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       const uint64_t kmn = make_smem_desc(sbase + L::kX, kBoxBytes, 1024);          // K as [d x key], d contiguous
       for (int m = 0; m < n_steps && ok; ++m) {
         const int st = m % NY, s = m & 1;
-        ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 305);
-        if (!ok) break;
-        tc_fence_after_sync();
         const uint32_t ybase = sbase + L::kY + st * L::kYStageBytes;
         const uint64_t qmn = make_smem_desc(ybase, kYBoxBytes, 1024);                    // Q as [query x d], d contiguous
         const uint64_t gmn = make_smem_desc(ybase + L::kYBytes, kYBoxBytes, 1024);      // dO likewise
@@ -375,14 +373,22 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const uint64_t ds_a = kDbias ? make_smem_desc(dsbuf, kYBoxBytes, 1024) : make_smem_desc(dsbuf, 16, 1024);
         constexpr int ds_a_step = kDbias ? 2048 : 32;
         const uint32_t e1 = tm_e + s * 32;
-        // dV += p^T dO (p from TMEM) and dK += ds^T Q: two independent chains, issued alternately
+        // dV += p^T dO (p from TMEM) as soon as p is there: it runs while the warps still form ds
+        ok = wait_or_abort(bar(P_READY + s), (m >> 1) & 1, abort_flag, a.status, 319);
+        if (!ok) break;
+        tc_fence_after_sync();
 #pragma unroll
-        for (int kk = 0; kk < kStep / 16; ++kk) {
+        for (int kk = 0; kk < kStep / 16; ++kk)
           mma_ts(tm_dv, e1 + kk * 8, gmn + uint64_t((kk * 2048) >> 4), idesc_acc, (m > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(bar(E_FREE + s));             // p of this stage may be rewritten
+        // dK += ds^T Q once the ds tile is in shared memory
+        ok = wait_or_abort(bar(E_READY + s), (m >> 1) & 1, abort_flag, a.status, 305);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kStep / 16; ++kk)
           mma_ss(tm_dk, ds_a + uint64_t((kk * ds_a_step) >> 4), qmn + uint64_t((kk * 2048) >> 4), idesc_dk,
                  (m > 0 || kk > 0) ? 1u : 0u);
-        }
-        mma_commit(bar(E_FREE + s));             // p of this stage may be rewritten
         mma_commit(bar(Y_EMPTY + st));           // the last readers of this Q / dO stage
         // dQ^T[d, query] = sum_key K[key, d] ds[key, query]; the previous tile must have been drained
         if (m >= 1) {
@@ -582,6 +588,11 @@ sdpa_bwd_tc_d128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       ok = wait_or_abort(bar(PROD_FULL + 2 + s), (n >> 1) & 1, abort_flag, a.status, 318);
       if (!ok) break;
       PROBE(9);
+      // p is in TMEM by now (its store was issued before the wait): dV += p^T dO may start while ds is formed
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_READY + s));
       tc_fence_after_sync();
       {
         uint32_t raw[kStep];
