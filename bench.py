@@ -74,7 +74,14 @@ KERNEL_FLOP_SHARE = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (each entry names its summary).  Filled in only for kernels whose capture was taken from the build
 # that is being timed; a workload without an entry reports traffic = null.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/c3_b1_attention_kernels_ncu_full.md: captured at batch 1 (the recipe's size rule), x 4 for the bench's
+    # batch 4 -- every (batch, head) pair has its own bias / dbias, so traffic grows in proportion
+    "c3": {"sdpa_bwd_tc_kernel<one-pass d128>": 4 * (1.350313e9 + 1.179659e9), "sdpa_fwd_tc_kernel": 4 * (1.190932e9 + 0.037818e9)},
+    # profiles/c2_attention_kernels_ncu_full.md, profiles/c4_attention_kernels_ncu_full.md: captured at full size
+    "c2": {"sdpa_bwd_tc_kernel<merged>": 671.107072e6 + 124.168704e6, "sdpa_fwd_tc_kernel": 244.395008e6 + 24.405248e6},
+    "c4": {"sdpa_bwd_tc_kernel<merged>": 176.487936e6 + 83.972608e6, "sdpa_fwd_tc_kernel": 74.777344e6 + 10.518784e6},
+}
 
 METRIC = "fwd+bwd attention TFLOP/s"
 UNIT = "TFLOP/s"
@@ -591,7 +598,7 @@ def main():
             torch.cuda.synchronize()
 
     peaks = load_peaks()
-    roofline = roofline_record(wl_name, wl, step_ms, kernels, peaks) if rank == 0 else None
+    roofline = roofline_record(wl_name, wl, step_ms, kernels, peaks, with_traffic=not args.batch) if rank == 0 else None
     headline_clocks = m["clocks"]
     headline_launches = m["launches_per_step"]
     del runner
