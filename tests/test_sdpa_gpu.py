@@ -384,6 +384,43 @@ def test_tc_many_tiles_full_bias_mask(d):
     check(got, ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tc_fully_masked_rows_are_nan_and_the_rest_matches(d, dtype):
+    """Rows whose mask drops every key come out NaN (0 * inf, as the reference's softmax gives) on the tensor-core
+    kernels too; every masked key contributes exactly zero (also where 2^x is computed on the FMA pipe, which clamps
+    its argument instead of seeing -inf), and widely spread logits (bias of +-60) stay inside the budget."""
+    _, att = _nb()
+    g = torch.Generator().manual_seed(11)
+    b, h, s, t = 1, 2, 256, 384
+    q = torch.randn(b, h, s, d, generator=g)
+    k = torch.randn(b, h, t, d, generator=g)
+    v = torch.randn(b, h, t, d, generator=g)
+    bias = (torch.randn(b, h, s, t, generator=g) * 20).clamp(-60, 60)
+    mask = torch.rand(b, 1, s, t, generator=g) >= 0.3
+    dead = torch.tensor([0, 5, 127, 128, 255])
+    mask[:, :, dead, :] = False
+    mask[:, :, 7, :] = False
+    mask[:, :, 7, 300] = True            # a row with one kept key, in the last key tile
+    kw = dict(bias=bias, mask=mask)
+    _assert_plans_tc(q, k, v, kw, dtype)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = att.scaled_dot_product_attention(q.to(dtype).cuda(), k.to(dtype).cuda(), v.to(dtype).cuda(),
+                                               bias=bias.to(dtype).cuda(), mask=mask.cuda())
+    _device_ok()
+    out = out.float().cpu()
+    assert torch.isnan(out[:, :, dead]).all()
+    live = torch.ones(s, dtype=torch.bool)
+    live[dead] = False
+    assert torch.isfinite(out[:, :, live]).all()
+    ref = O.reference_sdpa_torch(q.to(dtype).float(), k.to(dtype).float(), v.to(dtype).float(),
+                                 bias=bias.to(dtype).float(), mask=mask)
+    assert relerr(out[:, :, live], ref[:, :, live]) <= (2e-2 if dtype == torch.bfloat16 else 4e-3)
+    # the row with a single kept key is that key's value row
+    assert abserr(out[:, :, 7], v.to(dtype).float()[:, :, 300]) <= 1e-6
+
+
 def test_tc_single_tile_and_odd_tile_count():
     for s, t in ((128, 128), (384, 128), (128, 640)):
         q, k, v, kw = _cases.kernel_case("bias_mask", s=s, t=t, d=64, b=1, h=3)
