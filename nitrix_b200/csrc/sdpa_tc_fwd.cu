@@ -95,7 +95,8 @@ struct FwdSmem {
   static constexpr int kAugTileBytes = (kTile / 8) * 256;
   static constexpr int kNumBars = 4 + 4 * kStages + 16 + 3 * kBiasSlots + 2 * kAugSlots;
   static constexpr int kMisc = kBars + 8 * kNumBars;      // tmem base (4 B) + abort flag (4 B)
-  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kOrder = kMisc + 16;               // batch indices by kept length (item order 3), 16-bit each
+  static constexpr int kTotal = kOrder + 2 * kThreads;
 };
 
 // One work item: two query tiles of one (batch, head).
@@ -104,7 +105,7 @@ struct Item {
   int nt[2], nt_max;
 };
 
-__device__ __forceinline__ Item decode_item(const FwdArgs& a, int item) {
+__device__ __forceinline__ Item decode_item(const FwdArgs& a, int item, const uint16_t* order) {
   Item it;
   // CTAs that run side by side take consecutive items, so the order decides what they share in L2 and how evenly
   // the work is spread.
@@ -130,6 +131,20 @@ __device__ __forceinline__ Item decode_item(const FwdArgs& a, int item) {
     const int rem = pos - rank * per_rank;
     it.h = rem / a.B;
     it.b = rem - it.h * a.B;
+  } else if (a.head_major == 3) {
+    // Key-padding masks: an item's work is proportional to its batch element's kept length.  Items sorted by that
+    // length (longest first; `order` = batch indices by descending length), then head, then query block, and dealt
+    // in rows of alternating direction as above.  Neighbours share one (batch, head) pair's K / V.
+    const int G = int(gridDim.x), n_items = a.n_qblocks * a.bh_count;
+    const int row = item / G, col = item - row * G;
+    const bool full_row = (row + 1) * G <= n_items;
+    const int pos = row * G + ((row & 1) && full_row ? G - 1 - col : col);
+    const int per_batch = a.H * a.n_qblocks;
+    const int rb = pos / per_batch;
+    const int rem = pos - rb * per_batch;
+    it.b = order[rb];
+    it.h = rem / a.n_qblocks;
+    rank = rem - it.h * a.n_qblocks;
   } else {  // a partial (batch, head) range: keep each pair's query blocks together
     const int bh = a.bh_begin + item / a.n_qblocks;
     rank = item % a.n_qblocks;
@@ -229,6 +244,17 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       fence_proxy_async_smem();
     }
   }
+  const uint16_t* const order = reinterpret_cast<const uint16_t*>(smem + L::kOrder);
+  if (a.head_major == 3 && int(threadIdx.x) < a.B) {
+    // rank of this batch element among the kept lengths (ties by index): B <= kThreads loads per thread, once per CTA
+    const int mine = a.mask.kv_len[threadIdx.x * a.mask.len_b_stride];
+    int r = 0;
+    for (int j = 0; j < a.B; ++j) {
+      const int other = __ldg(a.mask.kv_len + j * a.mask.len_b_stride);
+      r += (other > mine || (other == mine && j < int(threadIdx.x))) ? 1 : 0;
+    }
+    reinterpret_cast<uint16_t*>(smem + L::kOrder)[r] = uint16_t(threadIdx.x);
+  }
   if (warp == 3) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -256,7 +282,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       int kv = 0, oc[2] = {0, 0};
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const Item it = decode_item(a, item);
+        const Item it = decode_item(a, item, order);
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           if (it.nt[g] == 0) continue;
@@ -297,7 +323,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         int kv = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-          const Item it = decode_item(a, item);
+          const Item it = decode_item(a, item, order);
           const uint16_t* bk = a.bias_mode == kBiasKey
                                    ? reinterpret_cast<const uint16_t*>(a.bias) + (it.b * a.bias_bs + it.h * a.bias_hs)
                                    : nullptr;
@@ -352,7 +378,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       int seq = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const Item it = decode_item(a, item);
+        const Item it = decode_item(a, item, order);
         // slots are filled in the order: for each key tile, for each live query tile, column half 0 then 1
         for (int j = 0; j < it.nt_max && ok; ++j) {
           for (int g = 0; g < 2 && ok; ++g) {
@@ -398,7 +424,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       int seq_base = 0;            // bias slots filled before this item
       uint32_t bias_phase = 0;     // bit s = parity of this issuer's next wait on its tile's "full" barrier of slot s
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const Item it = decode_item(a, item);
+        const Item it = decode_item(a, item, order);
         if constexpr (kAlias) {
           // D = 128: key tiles are taken in two halves of 64 keys.  A query tile's S region holds two 64-column
           // buffers, one per half, and P (16-bit, 32 columns) is written over its own buffer, so the scores of the
@@ -594,7 +620,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     FPROBE_DECL;
 
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const Item it = decode_item(a, item);
+      const Item it = decode_item(a, item, order);
       const int my_nt = it.nt[g];
       const int row = it.q0 + g * kTile + r;
       const int b = it.b, h = it.h;

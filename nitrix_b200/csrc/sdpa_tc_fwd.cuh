@@ -14,6 +14,7 @@ struct FwdArgs {
   //   1: head, query block, batch fastest -- neighbours share a head's K / V and bias in L2;
   //   2: query block (heaviest first), head, batch, dealt in rows of alternating direction -- evens out causal
   //      work when a CTA gets only a few items, at the price of K / V locality.
+  //   3: batch element (longest kept length first, key-padding masks), head, query block, dealt the same way.
   int head_major;
   int causal;
   float scale;

@@ -525,6 +525,9 @@ int tc_forward(const Problem& original, int dtype, int bias_dtype, void* ws, siz
   // causal items differ in length by up to the number of key tiles; with few items per CTA that imbalance costs
   // more than the K / V locality of the head-major order
   if (a.head_major && pr.causal && int64_t(a.n_qblocks) * pr.bh_count <= 16 * int64_t(tc::sm_count())) a.head_major = 2;
+  // key padding: items by kept length, longest first (the kernel ranks the batch elements itself)
+  if (a.head_major && !pr.causal && a.mask.kv_len && a.mask.len_h_stride == 0 && a.mask.len_b_stride != 0 && pr.B > 1 && pr.B <= 384)
+    a.head_major = 3;
   return tc::launch_fwd(pr.D, dtype == NB200_BF16, tq, tk, tv, tb, a, stream);
 }
 
