@@ -77,10 +77,10 @@ KERNEL_FLOP_SHARE = {
 NCU_TRAFFIC_BYTES = {
     # profiles/c3_b1_attention_kernels_ncu_full.md: captured at batch 1 (the recipe's size rule), x 4 for the bench's
     # batch 4 -- every (batch, head) pair has its own bias / dbias, so traffic grows in proportion
-    "c3": {"sdpa_bwd_tc_kernel<one-pass d128>": 4 * (1.350313e9 + 1.179659e9), "sdpa_fwd_tc_kernel": 4 * (1.190932e9 + 0.037818e9)},
+    "c3": {"sdpa_bwd_tc_kernel<one-pass d128>": 4 * (1.355364e9 + 1.181375e9), "sdpa_fwd_tc_kernel": 4 * (1.191293e9 + 0.039252e9)},
     # profiles/c2_attention_kernels_ncu_full.md, profiles/c4_attention_kernels_ncu_full.md: captured at full size
-    "c2": {"sdpa_bwd_tc_kernel<merged>": 671.107072e6 + 124.168704e6, "sdpa_fwd_tc_kernel": 244.395008e6 + 24.405248e6},
-    "c4": {"sdpa_bwd_tc_kernel<merged>": 176.487936e6 + 83.972608e6, "sdpa_fwd_tc_kernel": 74.777344e6 + 10.518784e6},
+    "c2": {"sdpa_bwd_tc_kernel<merged>": 671.002368e6 + 123.455744e6, "sdpa_fwd_tc_kernel": 250.225664e6 + 25.214464e6},
+    "c4": {"sdpa_bwd_tc_kernel<merged>": 176.488704e6 + 84.309760e6, "sdpa_fwd_tc_kernel": 74.746368e6 + 6.363136e6},
 }
 
 METRIC = "fwd+bwd attention TFLOP/s"
