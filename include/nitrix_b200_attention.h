@@ -224,6 +224,29 @@ NB200_API int nb200_ipc_export(const void* device_ptr, nb200_ipc_handle* handle)
 NB200_API int nb200_ipc_open(const nb200_ipc_handle* handle, void** device_ptr);
 NB200_API int nb200_ipc_close(void* device_ptr);
 
+/* RMS normalisation of q and k over the head dim -- the `qk_norm=True` pre-op -- and its gradient, each as one launch
+ * for both tensors.  Replaces the element-wise ops the reference runs outside its fused kernels
+ * (src/nitrix/nn/attention/__init__.py:184-197 `qk_rms_norm(q)`, `qk_rms_norm(k)`; the op:
+ * src/nitrix/nn/attention/_reference.py:52-77): y = x * rsqrt(mean(x^2 over the head dim) + 1e-6), fp32 arithmetic,
+ * no learnable scale.  It stays a pre-op, as in the reference: the attention entry points then take y.
+ * A tensor is [B][H][N][head_dim] with element strides xs over (b, h, n) and a contiguous head dim; y (and, for the
+ * gradient, g = dL/dy in, y = dL/dx out) are dense [B*H*N][head_dim].  Pointers and row starts 16-byte aligned; head_dim
+ * a multiple of 16 bytes and at most 256; B * H * N may be 0.
+ *   nb200_qk_rms_norm        y  = x r,                  r = rsqrt(mean(x^2) + eps)
+ *   nb200_qk_rms_norm_grad   dx = r (g - (x r) mean(g x r))   (x is the un-normalised input again) */
+typedef struct nb200_qk_norm_tensor {
+  const void* x;
+  const void* g;      /* gradient pass only */
+  void* y;
+  int64_t xs[3];
+  int32_t B, H, N;
+  int32_t reserved;
+} nb200_qk_norm_tensor;
+NB200_API int nb200_qk_rms_norm(const nb200_qk_norm_tensor* q, const nb200_qk_norm_tensor* k, int head_dim, int dtype,
+                                void* cuda_stream);
+NB200_API int nb200_qk_rms_norm_grad(const nb200_qk_norm_tensor* q, const nb200_qk_norm_tensor* k, int head_dim,
+                                     int dtype, void* cuda_stream);
+
 /* Diagnostic: runs the give-up branch of the bounded mbarrier wait all tensor-core kernels use (no counterpart in
  * the reference).  One warp waits, with a budget of a few thousand cycles, on a barrier nothing completes; the wait
  * expires within a few milliseconds, the kernel exits normally and the device status word holds a time-out code.

@@ -57,6 +57,13 @@ class IpcHandle(C.Structure):
     _fields_ = [("bytes", C.c_ubyte * 128)]
 
 
+class QkNormTensor(C.Structure):
+    """``nb200_qk_norm_tensor``: one operand of the fused QK-norm pre-op (include/nitrix_b200_attention.h)."""
+
+    _fields_ = [("x", C.c_void_p), ("g", C.c_void_p), ("y", C.c_void_p), ("xs", C.c_int64 * 3),
+                ("B", C.c_int32), ("H", C.c_int32), ("N", C.c_int32), ("reserved", C.c_int32)]
+
+
 EXPORTS = (
     "nb200_version",
     "nb200_last_error",
@@ -75,6 +82,8 @@ EXPORTS = (
     "nb200_ipc_export",
     "nb200_ipc_open",
     "nb200_ipc_close",
+    "nb200_qk_rms_norm",
+    "nb200_qk_rms_norm_grad",
 )
 
 
@@ -112,6 +121,8 @@ def lib() -> C.CDLL:
     L.nb200_ipc_export.argtypes = [C.c_void_p, C.POINTER(IpcHandle)]
     L.nb200_ipc_open.argtypes = [C.POINTER(IpcHandle), C.POINTER(C.c_void_p)]
     L.nb200_ipc_close.argtypes = [C.c_void_p]
+    L.nb200_qk_rms_norm.argtypes = [C.POINTER(QkNormTensor), C.POINTER(QkNormTensor), C.c_int, C.c_int, C.c_void_p]
+    L.nb200_qk_rms_norm_grad.argtypes = [C.POINTER(QkNormTensor), C.POINTER(QkNormTensor), C.c_int, C.c_int, C.c_void_p]
     if L.nb200_version() != ABI_VERSION:
         raise NativeLibraryError(f"{path}: ABI {L.nb200_version()} != expected {ABI_VERSION}")
     return L

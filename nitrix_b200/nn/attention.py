@@ -57,6 +57,71 @@ def qk_rms_norm(z: torch.Tensor) -> torch.Tensor:
     return (zf * torch.rsqrt(zf.square().mean(-1, keepdim=True) + _QK_RMS_EPS)).to(z.dtype)
 
 
+def _norm_desc(x: torch.Tensor, y: torch.Tensor, g: Optional[torch.Tensor] = None) -> "_cabi.QkNormTensor":
+    """Describes ``x`` viewed as (B, H, N, D) -- leading dims flattened -- for the fused pre-op."""
+    t = _cabi.QkNormTensor()
+    h, n = x.shape[-3], x.shape[-2]
+    x4 = x.reshape((-1, h, n, x.shape[-1])) if x.dim() != 4 else x
+    t.x, t.y, t.g = x4.data_ptr(), y.data_ptr(), (g.data_ptr() if g is not None else None)
+    t.xs[0], t.xs[1], t.xs[2] = x4.stride(0), x4.stride(1), x4.stride(2)
+    t.B, t.H, t.N = x4.shape[0], h, n
+    return t
+
+
+def _qk_norm_fusable(q: torch.Tensor, k: torch.Tensor) -> bool:
+    """Both on one CUDA device, same supported dtype and head dim, rows the kernel can read with 16-byte loads."""
+    if not (q.is_cuda and k.is_cuda and q.device == k.device and q.dtype == k.dtype and q.dtype in _DTYPES):
+        return False
+    d = q.shape[-1]
+    vec = 16 // q.element_size()
+    if q.dim() < 3 or k.dim() < 3 or k.shape[-1] != d or d % vec or d > 256:
+        return False
+    for z in (q, k):
+        if z.stride(-1) != 1 or z.data_ptr() % 16:
+            return False
+        z4 = z if z.dim() == 4 else (z.reshape((-1,) + tuple(z.shape[-3:])) if z.is_contiguous() else None)
+        if z4 is None or any(st % vec for st in z4.stride()[:3]):
+            return False
+    return True
+
+
+class _QkRmsNorm(torch.autograd.Function):
+    """``(q, k) -> (qk_rms_norm(q), qk_rms_norm(k))`` as one kernel launch each way (``nb200_qk_rms_norm`` /
+    ``nb200_qk_rms_norm_grad``) instead of a chain of element-wise passes.  Same place in the call sequence as the
+    reference's pre-op (``nn/attention/__init__.py:193-197``): outside the attention kernels' own differentiation
+    rule, so autograd chains the two."""
+
+    @staticmethod
+    def forward(ctx, q, k):
+        qn, kn = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        with torch.cuda.device(q.device):
+            rc = _cabi.lib().nb200_qk_rms_norm(_norm_desc(q, qn), _norm_desc(k, kn), q.shape[-1], _DTYPES[q.dtype],
+                                                torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError("nb200_qk_rms_norm: " + _cabi.last_error())
+        ctx.save_for_backward(q, k)
+        return qn, kn
+
+    @staticmethod
+    def backward(ctx, gq, gk):
+        q, k = ctx.saved_tensors
+        gq, gk = gq.contiguous().to(q.dtype), gk.contiguous().to(k.dtype)
+        dq, dk = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        with torch.cuda.device(q.device):
+            rc = _cabi.lib().nb200_qk_rms_norm_grad(_norm_desc(q, dq, gq), _norm_desc(k, dk, gk), q.shape[-1],
+                                                     _DTYPES[q.dtype], torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError("nb200_qk_rms_norm_grad: " + _cabi.last_error())
+        return dq, dk
+
+
+def qk_rms_norm_pair(q: torch.Tensor, k: torch.Tensor):
+    """``qk_rms_norm`` of q and k: the fused CUDA pre-op where its layout rules hold, else the element-wise form."""
+    if _qk_norm_fusable(q, k):
+        return _QkRmsNorm.apply(q, k)
+    return qk_rms_norm(q), qk_rms_norm(k)
+
+
 def _validate(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
     # reference nn/attention/__init__.py:40-60
     if q.ndim < 3 or k.ndim < 3 or v.ndim < 3:
@@ -390,7 +455,7 @@ def scaled_dot_product_attention(
         raise ValueError(f"scaled_dot_product_attention: dtype {out_dtype} is not supported (fp32, bf16, fp16)")
     q, k, v = q.to(out_dtype), k.to(out_dtype), v.to(out_dtype)
     if qk_norm:
-        q, k = qk_rms_norm(q), qk_rms_norm(k)
+        q, k = qk_rms_norm_pair(q, k)
 
     h, s, d = q.shape[-3:]
     t, dv = k.shape[-2], v.shape[-1]

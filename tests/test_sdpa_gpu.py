@@ -553,6 +553,48 @@ def test_qk_norm_gradients(dtype, backend):
     check([out.detach(), *grads], list(ref), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [32, 64, 128, 256])
+def test_fused_qk_norm_pre_op_matches_the_reference_op(dtype, d):
+    """The one-launch pre-op (nb200_qk_rms_norm / _grad) against the reference's formula in fp64 (reference
+    nn/attention/_reference.py:52-77), forward and gradient, on a dense layout, a (batch, seq, head) memory order and a
+    3-D input; the launch counter shows that the fused kernels ran (one launch each way for q and k together)."""
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    g = torch.Generator().manual_seed(3)
+    b, h, s, t = 2, 3, 37, 21
+    q = (torch.randn(b, h, s, d, generator=g) * 3).to(dtype).cuda()
+    k = (torch.randn(b, t, h, d, generator=g) * 0.01).to(dtype).cuda().permute(0, 2, 1, 3)   # heads strided
+    gq = torch.randn(b, h, s, d, generator=g).to(dtype).cuda()
+    gk = torch.randn(b, h, t, d, generator=g).to(dtype).cuda()
+
+    def ref(x, gx):
+        x64 = x.double().requires_grad_(True)
+        y = x64 * torch.rsqrt(x64.square().mean(-1, keepdim=True) + 1e-6)
+        (dx,) = torch.autograd.grad(y, x64, grad_outputs=gx.double())
+        return y.detach(), dx
+
+    assert att._qk_norm_fusable(q, k)
+    ql, kl = q.clone().requires_grad_(True), k.clone().requires_grad_(True)
+    before = _cabi.lib().nb200_launch_count()
+    qn, kn = att.qk_rms_norm_pair(ql, kl)
+    dq, dk = torch.autograd.grad([qn, kn], [ql, kl], grad_outputs=[gq, gk])
+    torch.cuda.synchronize()
+    assert _cabi.lib().nb200_launch_count() - before == 2
+    tol = 2e-6 if dtype == torch.float32 else (1e-2 if dtype == torch.bfloat16 else 1.5e-3)
+    for got, (want_y, want_dx), gy in ((qn, ref(q, gq), dq), (kn, ref(k, gk), dk)):
+        assert relerr(got.detach(), want_y) <= tol
+        assert relerr(gy, want_dx) <= tol
+    # a 3-D (h, s, d) operand pair
+    q3, k3 = q[0].contiguous(), k[0].contiguous()
+    a3, b3 = att.qk_rms_norm_pair(q3, k3)
+    assert relerr(a3, ref(q3, gq[0])[0]) <= tol and relerr(b3, ref(k3, gk[0])[0]) <= tol
+    # layouts the kernel cannot read with 16-byte loads fall back to the element-wise form
+    odd = q[..., : d - 1]
+    assert not att._qk_norm_fusable(odd, odd)
+    assert relerr(att.qk_rms_norm_pair(odd, odd)[0], ref(odd, gq[..., : d - 1])[0]) <= tol
+
+
 def test_fp32_on_the_fused_tf32_path_does_not_warn_or_raise(monkeypatch):
     """fp32 is what the reference's fused path accepts silently (attention.py:736-744): with backend='auto' an fp32
     call that lands on the 3 x TF32 tensor kernels must neither warn nor, under NITRIX_STRICT_BACKEND=1, raise."""
