@@ -61,6 +61,36 @@ int check_launch(const char* what) {
   return NB200_OK;
 }
 
+namespace {
+thread_local bool g_no_side_stream = false;
+}
+void forbid_side_stream(bool on) { g_no_side_stream = on; }
+
+const SideStream* side_stream(cudaStream_t main) {
+  if (g_no_side_stream || g_prof_on.load(std::memory_order_relaxed)) return nullptr;
+  static thread_local SideStream cache[64] = {};
+  static thread_local bool made[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!made[dev]) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(main, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    SideStream ss{};
+    if (cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cache[dev] = ss;
+    made[dev] = true;
+  }
+  return &cache[dev];
+}
+
 int* device_status_word() {
   // the symbol's address is fixed per device: looked up once and remembered (host threads may race here)
   static std::atomic<int*> known[64] = {};

@@ -81,6 +81,14 @@ void count_launch(int n = 1);
 int check_launch(const char* what);
 // Address (on the current device) of the status word bounded waits report to.
 int* device_status_word();
+// A second stream of the calling thread on the current device, with the two events of a fork / join: small problems
+// run their two independent backward kernels side by side on it.  Created at first use; null when per-kernel timing
+// is on (its events bracket kernels on ONE in-order stream), inside nb200_sdpa_bwd_static_scratch (which creates
+// nothing), when `main` is being captured into a graph before the stream exists (nothing is created during a
+// capture), or when creation fails -- callers then launch on their own stream.
+struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; };
+const SideStream* side_stream(cudaStream_t main);
+void forbid_side_stream(bool on);
 
 // ---- SIMT kernels (sdpa_simt.cu) -------------------------------------------
 int simt_forward(const Problem& pr, int dtype, int bias_dtype, cudaStream_t stream);

@@ -1165,6 +1165,32 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   const size_t smem = bwd_smem(pr);
   if (int rc = prepare(simt_bwd_dq_kernel<T>, smem)) return rc;
   if (int rc = prepare(simt_bwd_dkv_kernel<T>, smem)) return rc;
+  // The dq (+ dbias) kernel and the dk / dv kernel are independent.  On a small problem neither fills the GPU (C1:
+  // 256 CTAs of 8 warps each, 80 to 90 us apiece, bound by the latency of one row's pass over the keys), so the
+  // second one runs on a side stream between a fork and a join event and the pair takes as long as the slower one.
+  cudaStream_t st_kv = st;
+  const SideStream* side = nullptr;
+  {
+    const int64_t ctas_q = int64_t((pr.S + kWarps - 1) / kWarps) * pr.bh_count;
+    const int64_t ctas_k = int64_t((pr.T + kWarps - 1) / kWarps) * pr.bh_count;
+    if (pr.S > 0 && pr.T > 0 && ctas_q + ctas_k <= 4 * 148) side = side_stream(st);
+    if (side) {
+      if (cudaEventRecord(side->fork, st) == cudaSuccess && cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess) {
+        st_kv = side->stream;
+      } else {
+        cudaGetLastError();
+        side = nullptr;
+      }
+    }
+  }
+  auto join = [&](int rc) -> int {
+    if (side && (cudaEventRecord(side->join, side->stream) != cudaSuccess ||
+                 cudaStreamWaitEvent(st, side->join, 0) != cudaSuccess)) {
+      set_error("joining the side stream: %s", cudaGetErrorString(cudaGetLastError()));
+      return rc ? rc : NB200_ERR_LAUNCH;
+    }
+    return rc;
+  };
   bool dq_done = false;
   if constexpr (sizeof(T) == 4) {
     // fp32 operands with head dims in whole 8-column MMA blocks: 3 x TF32 on the warp-level tensor-core path
@@ -1181,9 +1207,9 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       } else {
         if ((rc = prepare(bwd_dq_tf32x3_kernel<16>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<16><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
       }
-      if (rc) return rc;
+      if (rc) return join(rc);
       count_launch();
-      if (int rc2 = check_launch("bwd_dq_tf32x3_kernel")) return rc2;
+      if (int rc2 = check_launch("bwd_dq_tf32x3_kernel")) return join(rc2);
       dq_done = true;
     }
   }
@@ -1191,7 +1217,7 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
     dim3 gq((pr.S + kWarps - 1) / kWarps, pr.bh_count);
     simt_bwd_dq_kernel<T><<<gq, kWarps * 32, smem, st>>>(pr, bias_dtype);
     count_launch();
-    if (int rc = check_launch("simt_bwd_dq_kernel")) return rc;
+    if (int rc = check_launch("simt_bwd_dq_kernel")) return join(rc);
   }
   if constexpr (sizeof(T) == 4) {
     if (pr.T > 0 && pr.D == pr.Dv && (pr.D == 32 || pr.D == 64 || pr.D == 128) &&
@@ -1200,24 +1226,24 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       dim3 gk((pr.T + 63) / 64, pr.bh_count);
       int rc = NB200_OK;
       if (pr.D == 32) {
-        if ((rc = prepare(bwd_dkv_tf32x3_kernel<4>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<4><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
+        if ((rc = prepare(bwd_dkv_tf32x3_kernel<4>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<4><<<gk, kTiledThreads, sm, st_kv>>>(pr, bias_dtype);
       } else if (pr.D == 64) {
-        if ((rc = prepare(bwd_dkv_tf32x3_kernel<8>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<8><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
+        if ((rc = prepare(bwd_dkv_tf32x3_kernel<8>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<8><<<gk, kTiledThreads, sm, st_kv>>>(pr, bias_dtype);
       } else {
-        if ((rc = prepare(bwd_dkv_tf32x3_kernel<16>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<16><<<gk, kTiledThreads, sm, st>>>(pr, bias_dtype);
+        if ((rc = prepare(bwd_dkv_tf32x3_kernel<16>, sm)) == NB200_OK) bwd_dkv_tf32x3_kernel<16><<<gk, kTiledThreads, sm, st_kv>>>(pr, bias_dtype);
       }
-      if (rc) return rc;
+      if (rc) return join(rc);
       count_launch();
-      return check_launch("bwd_dkv_tf32x3_kernel");
+      return join(check_launch("bwd_dkv_tf32x3_kernel"));
     }
   }
   if (pr.T > 0) {
     dim3 gk((pr.T + kWarps - 1) / kWarps, pr.bh_count);
-    simt_bwd_dkv_kernel<T><<<gk, kWarps * 32, smem, st>>>(pr, bias_dtype);
+    simt_bwd_dkv_kernel<T><<<gk, kWarps * 32, smem, st_kv>>>(pr, bias_dtype);
     count_launch();
-    return check_launch("simt_bwd_dkv_kernel");
+    return join(check_launch("simt_bwd_dkv_kernel"));
   }
-  return NB200_OK;
+  return join(NB200_OK);
 }
 
 }  // namespace

@@ -63,5 +63,8 @@ extern "C" NB200_API int nb200_sdpa_bwd_static_scratch(const nb200_sdpa_params* 
   nb200_sdpa_params local = *p;  // the caller's workspace fields are ignored
   local.workspace = scratch;
   local.workspace_bytes = size_t(NB200_STATIC_SCRATCH_BYTES);
-  return nb200_sdpa_bwd(&local, cuda_stream);
+  nb200::forbid_side_stream(true);   // this entry point creates nothing, streams and events included
+  const int rc = nb200_sdpa_bwd(&local, cuda_stream);
+  nb200::forbid_side_stream(false);
+  return rc;
 }

@@ -595,6 +595,68 @@ def test_fused_qk_norm_pre_op_matches_the_reference_op(dtype, d):
     assert relerr(att.qk_rms_norm_pair(odd, odd)[0], ref(odd, gq[..., : d - 1])[0]) <= tol
 
 
+def _small_fp32_backward(att):
+    g = torch.Generator().manual_seed(21)
+    b, h, s, t, d = 2, 2, 96, 80, 32
+    q, k, v, dout = (torch.randn(b, h, n, d, generator=g).cuda() for n in (s, t, t, s))
+    bias = torch.randn(b, h, s, t, generator=g).cuda()
+    out, lse = att.sdpa_forward(q, k, v, bias, None, scale=d ** -0.5)
+    return (q, k, v, bias, None, out, lse, dout), dict(scale=d ** -0.5, want_dbias=True)
+
+
+def test_small_backward_side_stream_equals_one_stream():
+    """A small problem's dq and dk / dv kernels run side by side on a second stream (fork / join events).  With
+    per-kernel timing on the library keeps to one stream: both ways must give the same bits."""
+    from nitrix_b200 import _cabi
+    _, att = _nb()
+    args, kw = _small_fp32_backward(att)
+    forked = att.sdpa_backward(*args, **kw)
+    torch.cuda.synchronize()
+    _cabi.lib().nb200_profile(1)
+    try:
+        serial = att.sdpa_backward(*args, **kw)
+        torch.cuda.synchronize()
+    finally:
+        _cabi.lib().nb200_profile(0)
+    _device_ok()
+    for a, b in zip(forked, serial):
+        assert torch.equal(a, b)
+
+
+def test_small_backward_first_called_inside_a_graph_capture():
+    """A host thread whose first backward call happens while its stream is being captured: the library must not
+    create its side stream then (nothing is created during a capture); the captured graph replays correctly."""
+    import threading
+    _, att = _nb()
+    args, kw = _small_fp32_backward(att)
+    want = att.sdpa_backward(*args, **kw)
+    torch.cuda.synchronize()
+    box = {}
+
+    def work():
+        try:
+            torch.cuda.set_device(0)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    got = att.sdpa_backward(*args, **kw)
+            graph.replay()
+            torch.cuda.synchronize()
+            box["got"] = [x.clone() for x in got]
+        except Exception as e:   # surfaced in the main thread below
+            box["err"] = e
+
+    th = threading.Thread(target=work)
+    th.start()
+    th.join()
+    assert "err" not in box, box.get("err")
+    _device_ok()
+    for a, b in zip(box["got"], want):
+        assert torch.equal(a, b)
+
+
 def test_fp32_on_the_fused_tf32_path_does_not_warn_or_raise(monkeypatch):
     """fp32 is what the reference's fused path accepts silently (attention.py:736-744): with backend='auto' an fp32
     call that lands on the 3 x TF32 tensor kernels must neither warn nor, under NITRIX_STRICT_BACKEND=1, raise."""
