@@ -164,7 +164,11 @@ NB200_API int nb200_sdpa_fwd(const nb200_sdpa_params* p, void* cuda_stream);
 
 /* Backward: dq, dk, dv and, when dbias != NULL, dbias (reduced over the
  * broadcast axes of bias, in bias dtype) from (q, k, v, bias, mask, out, lse,
- * dout).  Replaces reference attention.py:600-653 and :390-499. */
+ * dout).  Replaces reference attention.py:600-653 and :390-499.
+ * All work is ordered on cuda_stream as seen by the caller.  For a small problem on the CUDA-core kernels two
+ * independent kernels may run side by side: the second on a stream the library owns (one per host thread and
+ * device, created at the first such call outside a graph capture), forked from and joined back into cuda_stream by
+ * events, so the call can be captured into a CUDA graph like any other. */
 NB200_API int nb200_sdpa_bwd(const nb200_sdpa_params* p, void* cuda_stream);
 
 /* Backward pass for callers that cannot allocate device memory (no counterpart
