@@ -189,9 +189,10 @@ __device__ __forceinline__ void stage_rows(float* dst, int ld, const T* src, int
 // in flight at once (a load-then-store loop pays the global latency once per iteration); rows past `limit` are
 // zero-filled by a copy of source size 0.  The caller's __syncthreads() follows the wait below.
 __device__ __forceinline__ void stage_rows_f4(float* dst, int ld, const float* src, int64_t row_stride, int row0,
-                                              int n_rows, int limit, int dim) {
+                                              int n_rows, int limit, int dim, int tid = threadIdx.x,
+                                              int n_threads = blockDim.x) {
   const int per_row = dim >> 2;
-  for (int idx = threadIdx.x; idx < n_rows * per_row; idx += blockDim.x) {
+  for (int idx = tid; idx < n_rows * per_row; idx += n_threads) {
     const int r = idx / per_row, c4 = idx - r * per_row;
     const int row = row0 + r;
     const bool in = row < limit;
@@ -405,6 +406,99 @@ __device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4
   mma_tf32(c, ah, bh);
 }
 
+// One 64-key tile of the 3 x TF32 forward for this warp's 16 query rows: scores, logits and masks, online softmax,
+// out += P V.  Ks / Vs: the tile in shared memory (rows past T zero-filled); kt: its first key.
+template <int kDvBlocks>
+__device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtype, const float* Qs, const float* Ks,
+                                                const float* Vs, int LDQ, int LDV, int D, int kt, int row0,
+                                                const int (&lr)[2], const int64_t (&boff)[2], const int64_t (&moff)[2],
+                                                float s2scale, int g, int t, float (&o)[kDvBlocks][4], float (&m)[2],
+                                                float (&l)[2]) {
+  // ---- scores: 8 blocks of 8 keys ----
+  float sc[8][4];
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sc[nb][e] = 0.f;
+  for (int kk = 0; kk < D; kk += 8) {
+    uint32_t ah[4], al[4];
+    split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
+    split_tf32(Qs[lr[1] * LDQ + kk + t], ah[1], al[1]);
+    split_tf32(Qs[lr[0] * LDQ + kk + t + 4], ah[2], al[2]);
+    split_tf32(Qs[lr[1] * LDQ + kk + t + 4], ah[3], al[3]);
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+      uint32_t bh2[2], bl2[2];
+      split_tf32(Ks[(8 * nb + g) * LDQ + kk + t], bh2[0], bl2[0]);
+      split_tf32(Ks[(8 * nb + g) * LDQ + kk + t + 4], bh2[1], bl2[1]);
+      mma_3xtf32(sc[nb], ah, al, bh2, bl2);
+    }
+  }
+  // ---- logits in base 2, masks, online softmax (rows g and g + 8 of the warp's 16) ----
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
+      bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
+      if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
+      const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
+      sc[nb][e] = keep ? fmaf(sc[nb][e], s2scale, bias) : -INFINITY;
+      mx[i] = fmaxf(mx[i], sc[nb][e]);
+    }
+  float alpha[2], m_ref[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    const float m_new = fmaxf(m[i], mx[i]);
+    m_ref[i] = m_new == -INFINITY ? 0.f : m_new;   // nothing kept so far: every p is 0
+    alpha[i] = exp2f(m[i] - m_ref[i]);
+    m[i] = m_new;
+  }
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = exp2f(sc[nb][e] - m_ref[e >> 1]);
+      sc[nb][e] = p;
+      sum[e >> 1] += p;
+    }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+    sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+    l[i] = l[i] * alpha[i] + sum[i];
+  }
+#pragma unroll
+  for (int nb = 0; nb < kDvBlocks; ++nb) {
+    o[nb][0] *= alpha[0];
+    o[nb][1] *= alpha[0];
+    o[nb][2] *= alpha[1];
+    o[nb][3] *= alpha[1];
+  }
+  // ---- out += P V: key block kb supplies operand columns (t -> key 2 t, t + 4 -> key 2 t + 1) ----
+#pragma unroll
+  for (int kb = 0; kb < 8; ++kb) {
+    uint32_t ah[4], al[4];
+    split_tf32(sc[kb][0], ah[0], al[0]);   // row g,     key 2 t
+    split_tf32(sc[kb][2], ah[1], al[1]);   // row g + 8, key 2 t
+    split_tf32(sc[kb][1], ah[2], al[2]);   // row g,     key 2 t + 1
+    split_tf32(sc[kb][3], ah[3], al[3]);   // row g + 8, key 2 t + 1
+    const float* v0 = Vs + (8 * kb + 2 * t) * LDV + g;
+    const float* v1 = v0 + LDV;
+#pragma unroll
+    for (int nb = 0; nb < kDvBlocks; ++nb) {
+      uint32_t bh2[2], bl2[2];
+      split_tf32(v0[8 * nb], bh2[0], bl2[0]);
+      split_tf32(v1[8 * nb], bh2[1], bl2[1]);
+      mma_3xtf32(o[nb], ah, al, bh2, bl2);
+    }
+  }
+}
+
 template <int kDvBlocks>   // Dv / 8
 __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
@@ -456,93 +550,115 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
       stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
       stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
     }
-    // ---- scores: 8 blocks of 8 keys ----
-    float sc[8][4];
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sc[nb][e] = 0.f;
-    for (int kk = 0; kk < D; kk += 8) {
-      uint32_t ah[4], al[4];
-      split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
-      split_tf32(Qs[lr[1] * LDQ + kk + t], ah[1], al[1]);
-      split_tf32(Qs[lr[0] * LDQ + kk + t + 4], ah[2], al[2]);
-      split_tf32(Qs[lr[1] * LDQ + kk + t + 4], ah[3], al[3]);
-#pragma unroll
-      for (int nb = 0; nb < 8; ++nb) {
-        uint32_t bh2[2], bl2[2];
-        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t], bh2[0], bl2[0]);
-        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t + 4], bh2[1], bl2[1]);
-        mma_3xtf32(sc[nb], ah, al, bh2, bl2);
-      }
-    }
-    // ---- logits in base 2, masks, online softmax (rows g and g + 8 of the warp's 16) ----
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
-        bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
-        if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
-        const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
-        sc[nb][e] = keep ? fmaf(sc[nb][e], s2scale, bias) : -INFINITY;
-        mx[i] = fmaxf(mx[i], sc[nb][e]);
-      }
-    float alpha[2], m_ref[2], sum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      const float m_new = fmaxf(m[i], mx[i]);
-      m_ref[i] = m_new == -INFINITY ? 0.f : m_new;   // nothing kept so far: every p is 0
-      alpha[i] = exp2f(m[i] - m_ref[i]);
-      m[i] = m_new;
-    }
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = exp2f(sc[nb][e] - m_ref[e >> 1]);
-        sc[nb][e] = p;
-        sum[e >> 1] += p;
-      }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
-      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
-      l[i] = l[i] * alpha[i] + sum[i];
-    }
-#pragma unroll
-    for (int nb = 0; nb < kDvBlocks; ++nb) {
-      o[nb][0] *= alpha[0];
-      o[nb][1] *= alpha[0];
-      o[nb][2] *= alpha[1];
-      o[nb][3] *= alpha[1];
-    }
-    // ---- out += P V: key block kb supplies operand columns (t -> key 2 t, t + 4 -> key 2 t + 1) ----
-#pragma unroll
-    for (int kb = 0; kb < 8; ++kb) {
-      uint32_t ah[4], al[4];
-      split_tf32(sc[kb][0], ah[0], al[0]);   // row g,     key 2 t
-      split_tf32(sc[kb][2], ah[1], al[1]);   // row g + 8, key 2 t
-      split_tf32(sc[kb][1], ah[2], al[2]);   // row g,     key 2 t + 1
-      split_tf32(sc[kb][3], ah[3], al[3]);   // row g + 8, key 2 t + 1
-      const float* v0 = Vs + (8 * kb + 2 * t) * LDV + g;
-      const float* v1 = v0 + LDV;
-#pragma unroll
-      for (int nb = 0; nb < kDvBlocks; ++nb) {
-        uint32_t bh2[2], bl2[2];
-        split_tf32(v0[8 * nb], bh2[0], bl2[0]);
-        split_tf32(v1[8 * nb], bh2[1], bl2[1]);
-        mma_3xtf32(o[nb], ah, al, bh2, bl2);
-      }
-    }
+    fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
   }
   // ---- out = o / l (NaN for a row with no kept key, as the reference's softmax gives), lse ----
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
+    const int row = row0 + lr[i];
+    if (row >= pr.S) continue;
+    const float inv = 1.f / l[i];
+    float* op = reinterpret_cast<float*>(pr.out) + b * pr.os[0] + h * pr.os[1] + row * pr.os[2];
+#pragma unroll
+    for (int nb = 0; nb < kDvBlocks; ++nb) {
+      op[8 * nb + 2 * t] = l[i] == 0.f ? NAN : o[nb][2 * i] * inv;
+      op[8 * nb + 2 * t + 1] = l[i] == 0.f ? NAN : o[nb][2 * i + 1] * inv;
+    }
+    if (t == 0) pr.lse[(int64_t(b) * pr.H + h) * pr.S + row] = m[i] + log2f(l[i]);
+  }
+}
+
+// The same forward for SMALL problems: kG groups of four warps share a CTA's 64 query rows and take the key tiles in
+// turn (group j tiles j, j + kG, ...), each with a K / V stage of its own and its own named barrier; at the end the
+// groups' partial (m, l, out) are merged through shared memory by group 0.  The 3 x TF32 loop is bound by the
+// latency of its mma.sync chain, not by the tensor pipe (one warp per scheduler keeps it about a tenth busy), and a
+// problem of a hundred-odd CTAs cannot put more than four warps on an SM otherwise.
+template <int kDvBlocks, int kG>
+__global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Problem pr, int bias_dtype) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kBM = 64;
+  const int D = pr.D, Dv = pr.Dv;
+  const int LDQ = D + 4, LDV = Dv + 4;
+  float* Qs = smem;                          // [kBM][LDQ]
+  float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV]); afterwards the partial results
+  const int kg = threadIdx.x >> 7, tg = threadIdx.x & 127;
+  const int warp = tg >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV);
+  float* Vs = Ks + kBN * LDQ;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  const int row0 = blockIdx.x * kBM;
+  const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
+  const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
+  const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
+  stage_rows_f4(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D);   // (the launcher checked the 16-byte alignment)
+  stage_wait();
+  __syncthreads();
+
+  const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = min(row0 + lr[i], pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+  }
+  float o[kDvBlocks][4];
+#pragma unroll
+  for (int nb = 0; nb < kDvBlocks; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nb][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const float s2scale = pr.scale * kLog2e;
+  const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
+  auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + kg) : "memory"); };
+
+  for (int kt = kg * kBN; kt < t_end; kt += kG * kBN) {
+    group_sync();   // the group's previous tile is no longer read
+    stage_rows_f4(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D, tg, kTiledThreads);
+    stage_rows_f4(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv, tg, kTiledThreads);
+    stage_wait();
+    group_sync();
+    fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
+  }
+
+  // ---- merge the groups: partial [kG - 1][64 rows][Dv + 2] = (out, m, l), in the K / V stages ----
+  __syncthreads();
+  const int LDP = Dv + 2;
+  if (kg > 0) {
+    float* part = KV + (kg - 1) * kBM * LDP;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float* prow = part + lr[i] * LDP;
+#pragma unroll
+      for (int nb = 0; nb < kDvBlocks; ++nb) {
+        prow[8 * nb + 2 * t] = o[nb][2 * i];
+        prow[8 * nb + 2 * t + 1] = o[nb][2 * i + 1];
+      }
+      if (t == 0) {
+        prow[Dv] = m[i];
+        prow[Dv + 1] = l[i];
+      }
+    }
+  }
+  __syncthreads();
+  if (kg > 0) return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    for (int j = 0; j < kG - 1; ++j) {
+      const float* prow = KV + j * kBM * LDP + lr[i] * LDP;
+      const float m2 = prow[Dv], l2 = prow[Dv + 1];
+      const float m_new = fmaxf(m[i], m2);
+      const float m_ref = m_new == -INFINITY ? 0.f : m_new;   // nothing kept on either side: both weights are 0
+      const float wa = exp2f(m[i] - m_ref), wb = exp2f(m2 - m_ref);
+      l[i] = l[i] * wa + l2 * wb;
+      m[i] = m_new;
+#pragma unroll
+      for (int nb = 0; nb < kDvBlocks; ++nb) {
+        o[nb][2 * i] = o[nb][2 * i] * wa + prow[8 * nb + 2 * t] * wb;
+        o[nb][2 * i + 1] = o[nb][2 * i + 1] * wa + prow[8 * nb + 2 * t + 1] * wb;
+      }
+    }
     const int row = row0 + lr[i];
     if (row >= pr.S) continue;
     const float inv = 1.f / l[i];
@@ -1120,8 +1236,37 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   return fwd_tiled_r<T, kVChunks, 4>(pr, bias_dtype, st);
 }
 
+template <int kDvBlocks, int kG>
+int fwd_tf32x3_split_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) + size_t(kG) * kBN * (pr.D + 4 + pr.Dv + 4));
+  if (int rc = prepare(fwd_tf32x3_split_kernel<kDvBlocks, kG>, smem)) return rc;
+  dim3 grid((pr.S + 63) / 64, pr.bh_count);
+  fwd_tf32x3_split_kernel<kDvBlocks, kG><<<grid, kTiledThreads * kG, smem, st>>>(pr, bias_dtype);
+  count_launch();
+  return check_launch("fwd_tf32x3_kernel");
+}
+
 template <int kDvBlocks>
 int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
+  // A small problem (fewer 64-row CTAs than two per SM would hold) with several key tiles: groups of warps split the
+  // keys inside each CTA (see fwd_tf32x3_split_kernel).  Needs 16-byte aligned fp32 rows for the asynchronous copies.
+  {
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t ctas = int64_t((pr.S + 63) / 64) * pr.bh_count;
+    const int tiles = (pr.T + kBN - 1) / kBN;
+    auto rows16 = [](const void* p, const int64_t* st3) {
+      return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && st3[0] % 4 == 0 && st3[1] % 4 == 0 && st3[2] % 4 == 0;
+    };
+    const bool aligned = rows16(pr.q, pr.qs) && rows16(pr.k, pr.ks) && rows16(pr.v, pr.vs);
+    if constexpr (kDvBlocks <= 8)
+    if (aligned && ctas <= 2 * int64_t(sms > 0 ? sms : 148) && tiles >= 2 && pr.D <= 64 && pr.Dv <= 64) {
+      if (tiles >= 4) return fwd_tf32x3_split_t<kDvBlocks, 4>(pr, bias_dtype, st);
+      if (tiles == 3) return fwd_tf32x3_split_t<kDvBlocks, 3>(pr, bias_dtype, st);
+      return fwd_tf32x3_split_t<kDvBlocks, 2>(pr, bias_dtype, st);
+    }
+  }
   const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4));
   if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
