@@ -130,6 +130,35 @@ def test_fp32_3xtf32_parity(name, d):
     check(got, ref, torch.float32)
 
 
+@pytest.mark.parametrize("t", [100, 130, 200, 344, 520])
+@pytest.mark.parametrize("name", ["dense", "bias_causal", "full_bias_mask", "key_padding"])
+def test_fp32_small_forward_splits_keys_over_warp_groups(name, t):
+    """Small fp32 problems: a CTA's groups of warps take the key tiles in turn and merge (m, l, out) at the end -- two,
+    three and four groups (2, 3, 4+ key tiles; 100 keys is two tiles of which the second is partial), with causal rows
+    whose later groups see no key at all, a random mask, key padding, and a row the mask empties."""
+    _, att = _nb()
+    s_len = t if name == "bias_causal" else 150
+    q, k, v, kw = _cases.kernel_case(name, b=2, h=3, s=s_len, t=t, d=64)
+    mask = kw.get("mask")
+    if name == "full_bias_mask":
+        mask = mask.clone()
+        mask[0, 1, 7, :] = False           # one row with no kept key: NaN, as the reference's softmax gives
+        kw = dict(kw, mask=mask)
+    ref = O.reference_sdpa_torch(q, k, v, bias=kw.get("bias"), mask=kw.get("mask"), causal=kw.get("causal", False),
+                                 acc_dtype=torch.float64)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out, lse = att.scaled_dot_product_attention(q.cuda(), k.cuda(), v.cuda(),
+                                                    bias=None if kw.get("bias") is None else kw["bias"].cuda(),
+                                                    mask=None if mask is None else mask.cuda(),
+                                                    causal=kw.get("causal", False), return_lse=True)
+    _device_ok()
+    out = out.cpu().double()
+    dead = torch.isnan(ref)
+    assert torch.equal(torch.isnan(out), dead)
+    assert float((out[~dead] - ref[~dead]).abs().max()) <= FP32_REL * float(ref[~dead].abs().max())
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", ["bias_mask", "causal", "key_padding"])
 def test_simt_low_precision_parity(name, dtype):
