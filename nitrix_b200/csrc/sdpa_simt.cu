@@ -803,6 +803,90 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_dq_kernel(Problem pr, in
 // A warp owns 16 query rows against a 64-key tile: S = Q K^T and dP = dO V^T in accumulator fragments,
 // p = exp2(s - lse), ds = p (dP - delta) in place, then dQ += ds K with the ds fragment as the A operand (key 2 t /
 // 2 t + 1 of a block stand in operand columns t / t + 4; the K rows are fetched in that order).
+// One 64-key tile of the 3 x TF32 dq backward for this warp's 16 query rows: S and dP, p and ds (dbias on the way),
+// dQ += ds K.  Ks / Vs: the tile in shared memory; kt: its first key.
+template <int kDBlocks>
+__device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_dtype, const float* Qs, const float* Gs,
+                                                   const float* Ks, const float* Vs, int LDQ, int LDV, int D, int Dv,
+                                                   int kt, int row0, const int (&lr)[2], const int64_t (&boff)[2],
+                                                   const int64_t (&moff)[2], const int64_t (&dboff)[2],
+                                                   const float (&lse)[2], const float (&delta)[2], float s2scale,
+                                                   bool want_db, int g, int t, float (&dq)[kDBlocks][4]) {
+  float sc[8][4], dp[8][4];
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sc[nb][e] = dp[nb][e] = 0.f;
+  for (int kk = 0; kk < D; kk += 8) {
+    uint32_t ah[4], al[4];
+    split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
+    split_tf32(Qs[lr[1] * LDQ + kk + t], ah[1], al[1]);
+    split_tf32(Qs[lr[0] * LDQ + kk + t + 4], ah[2], al[2]);
+    split_tf32(Qs[lr[1] * LDQ + kk + t + 4], ah[3], al[3]);
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+      uint32_t bh2[2], bl2[2];
+      split_tf32(Ks[(8 * nb + g) * LDQ + kk + t], bh2[0], bl2[0]);
+      split_tf32(Ks[(8 * nb + g) * LDQ + kk + t + 4], bh2[1], bl2[1]);
+      mma_3xtf32(sc[nb], ah, al, bh2, bl2);
+    }
+  }
+  for (int kk = 0; kk < Dv; kk += 8) {
+    uint32_t ah[4], al[4];
+    split_tf32(Gs[lr[0] * LDV + kk + t], ah[0], al[0]);
+    split_tf32(Gs[lr[1] * LDV + kk + t], ah[1], al[1]);
+    split_tf32(Gs[lr[0] * LDV + kk + t + 4], ah[2], al[2]);
+    split_tf32(Gs[lr[1] * LDV + kk + t + 4], ah[3], al[3]);
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+      uint32_t bh2[2], bl2[2];
+      split_tf32(Vs[(8 * nb + g) * LDV + kk + t], bh2[0], bl2[0]);
+      split_tf32(Vs[(8 * nb + g) * LDV + kk + t + 4], bh2[1], bl2[1]);
+      mma_3xtf32(dp[nb], ah, al, bh2, bl2);
+    }
+  }
+  // ---- p = exp2(logit2 - lse), ds = p (dP - delta); ds replaces the score fragment ----
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
+      bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
+      if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
+      const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
+      const float p = keep ? exp2f(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
+      const float ds = p * (dp[nb][e] - delta[i]);
+      sc[nb][e] = ds;
+      if (want_db && key < pr.T && row < pr.S) {
+        const int64_t off = dboff[i] + key * pr.dbs[3];
+        if (pr.dbias_accum) {
+          if (ds != 0.f) atomicAdd(pr.dbias_accum + off, ds);
+        } else {
+          store_from_f32(pr.dbias, off, bias_dtype, ds);
+        }
+      }
+    }
+  // ---- dQ += ds K ----
+#pragma unroll
+  for (int kb = 0; kb < 8; ++kb) {
+    uint32_t ah[4], al[4];
+    split_tf32(sc[kb][0], ah[0], al[0]);   // row g,     key 2 t
+    split_tf32(sc[kb][2], ah[1], al[1]);   // row g + 8, key 2 t
+    split_tf32(sc[kb][1], ah[2], al[2]);   // row g,     key 2 t + 1
+    split_tf32(sc[kb][3], ah[3], al[3]);   // row g + 8, key 2 t + 1
+    const float* k0 = Ks + (8 * kb + 2 * t) * LDQ + g;
+    const float* k1 = k0 + LDQ;
+#pragma unroll
+    for (int nb = 0; nb < kDBlocks; ++nb) {
+      uint32_t bh2[2], bl2[2];
+      split_tf32(k0[8 * nb], bh2[0], bl2[0]);
+      split_tf32(k1[8 * nb], bh2[1], bl2[1]);
+      mma_3xtf32(dq[nb], ah, al, bh2, bl2);
+    }
+  }
+}
+
 template <int kDBlocks>   // D / 8
 __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
@@ -860,79 +944,8 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr
       stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
       stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
     }
-    float sc[8][4], dp[8][4];
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sc[nb][e] = dp[nb][e] = 0.f;
-    for (int kk = 0; kk < D; kk += 8) {
-      uint32_t ah[4], al[4];
-      split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
-      split_tf32(Qs[lr[1] * LDQ + kk + t], ah[1], al[1]);
-      split_tf32(Qs[lr[0] * LDQ + kk + t + 4], ah[2], al[2]);
-      split_tf32(Qs[lr[1] * LDQ + kk + t + 4], ah[3], al[3]);
-#pragma unroll
-      for (int nb = 0; nb < 8; ++nb) {
-        uint32_t bh2[2], bl2[2];
-        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t], bh2[0], bl2[0]);
-        split_tf32(Ks[(8 * nb + g) * LDQ + kk + t + 4], bh2[1], bl2[1]);
-        mma_3xtf32(sc[nb], ah, al, bh2, bl2);
-      }
-    }
-    for (int kk = 0; kk < Dv; kk += 8) {
-      uint32_t ah[4], al[4];
-      split_tf32(Gs[lr[0] * LDV + kk + t], ah[0], al[0]);
-      split_tf32(Gs[lr[1] * LDV + kk + t], ah[1], al[1]);
-      split_tf32(Gs[lr[0] * LDV + kk + t + 4], ah[2], al[2]);
-      split_tf32(Gs[lr[1] * LDV + kk + t + 4], ah[3], al[3]);
-#pragma unroll
-      for (int nb = 0; nb < 8; ++nb) {
-        uint32_t bh2[2], bl2[2];
-        split_tf32(Vs[(8 * nb + g) * LDV + kk + t], bh2[0], bl2[0]);
-        split_tf32(Vs[(8 * nb + g) * LDV + kk + t + 4], bh2[1], bl2[1]);
-        mma_3xtf32(dp[nb], ah, al, bh2, bl2);
-      }
-    }
-    // ---- p = exp2(logit2 - lse), ds = p (dP - delta); ds replaces the score fragment ----
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
-        bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
-        if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
-        const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
-        const float p = keep ? exp2f(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
-        const float ds = p * (dp[nb][e] - delta[i]);
-        sc[nb][e] = ds;
-        if (want_db && key < pr.T && row < pr.S) {
-          const int64_t off = dboff[i] + key * pr.dbs[3];
-          if (pr.dbias_accum) {
-            if (ds != 0.f) atomicAdd(pr.dbias_accum + off, ds);
-          } else {
-            store_from_f32(pr.dbias, off, bias_dtype, ds);
-          }
-        }
-      }
-    // ---- dQ += ds K ----
-#pragma unroll
-    for (int kb = 0; kb < 8; ++kb) {
-      uint32_t ah[4], al[4];
-      split_tf32(sc[kb][0], ah[0], al[0]);   // row g,     key 2 t
-      split_tf32(sc[kb][2], ah[1], al[1]);   // row g + 8, key 2 t
-      split_tf32(sc[kb][1], ah[2], al[2]);   // row g,     key 2 t + 1
-      split_tf32(sc[kb][3], ah[3], al[3]);   // row g + 8, key 2 t + 1
-      const float* k0 = Ks + (8 * kb + 2 * t) * LDQ + g;
-      const float* k1 = k0 + LDQ;
-#pragma unroll
-      for (int nb = 0; nb < kDBlocks; ++nb) {
-        uint32_t bh2[2], bl2[2];
-        split_tf32(k0[8 * nb], bh2[0], bl2[0]);
-        split_tf32(k1[8 * nb], bh2[1], bl2[1]);
-        mma_3xtf32(dq[nb], ah, al, bh2, bl2);
-      }
-    }
+    bwd_dq_tf32x3_tile<kDBlocks>(pr, bias_dtype, Qs, Gs, Ks, Vs, LDQ, LDV, D, Dv, kt, row0, lr, boff, moff, dboff, lse,
+                                 delta, s2scale, want_db, g, t, dq);
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -948,6 +961,104 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr
     for (int nb = 0; nb < kDBlocks; ++nb) {
       dqp[8 * nb + 2 * t] = dq[nb][2 * i] * pr.scale;
       dqp[8 * nb + 2 * t + 1] = dq[nb][2 * i + 1] * pr.scale;
+    }
+  }
+}
+
+// The dq backward for SMALL problems, as the forward's fwd_tf32x3_split_kernel: kG groups of four warps share a CTA's
+// 64 query rows and take the key tiles in turn; their partial dq tiles are summed through shared memory by group 0.
+// (Every dbias element is still written, or added, by exactly one group.)
+template <int kDBlocks, int kG>
+__global__ void __launch_bounds__(kTiledThreads * kG) bwd_dq_tf32x3_split_kernel(Problem pr, int bias_dtype) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kBM = 64;
+  const int D = pr.D, Dv = pr.Dv;
+  const int LDQ = D + 4, LDV = Dv + 4;
+  float* Qs = smem;                    // [kBM][LDQ]
+  float* Gs = Qs + kBM * LDQ;          // [kBM][LDV]   dout rows
+  float* KV = Gs + kBM * LDV;          // kG x ([kBN][LDQ] + [kBN][LDV]); afterwards the partial dq tiles
+  const int kg = threadIdx.x >> 7, tg = threadIdx.x & 127;
+  const int warp = tg >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV);
+  float* Vs = Ks + kBN * LDQ;
+  const int bh = pr.bh_begin + blockIdx.y;
+  const int b = bh / pr.H, h = bh - b * pr.H;
+  const int row0 = blockIdx.x * kBM;
+  const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
+  const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
+  const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
+  const float* gp = reinterpret_cast<const float*>(pr.dout) + b * pr.dos[0] + h * pr.dos[1];
+  stage_rows_f4(Qs, LDQ, qp, pr.qs[2], row0, kBM, pr.S, D);     // (the launcher checked the 16-byte alignment)
+  stage_rows_f4(Gs, LDV, gp, pr.dos[2], row0, kBM, pr.S, Dv);
+  stage_wait();
+  __syncthreads();
+
+  const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2], dboff[2];
+  float lse[2], delta[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = min(row0 + lr[i], pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+    dboff[i] = b * pr.dbs[0] + h * pr.dbs[1] + rr * pr.dbs[2];
+    const int64_t ridx = (int64_t(b) * pr.H + h) * pr.S + rr;
+    lse[i] = pr.lse[ridx];
+    delta[i] = pr.delta[ridx];
+  }
+  float dq[kDBlocks][4];
+#pragma unroll
+  for (int nb = 0; nb < kDBlocks; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dq[nb][e] = 0.f;
+  const float s2scale = pr.scale * kLog2e;
+  const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
+  const bool want_db = pr.dbias != nullptr || pr.dbias_accum != nullptr;
+  auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + kg) : "memory"); };
+
+  for (int kt = kg * kBN; kt < t_end; kt += kG * kBN) {
+    group_sync();   // the group's previous tile is no longer read
+    stage_rows_f4(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D, tg, kTiledThreads);
+    stage_rows_f4(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv, tg, kTiledThreads);
+    stage_wait();
+    group_sync();
+    bwd_dq_tf32x3_tile<kDBlocks>(pr, bias_dtype, Qs, Gs, Ks, Vs, LDQ, LDV, D, Dv, kt, row0, lr, boff, moff, dboff, lse,
+                                 delta, s2scale, want_db, g, t, dq);
+  }
+
+  // ---- sum the groups' dq tiles: partial [kG - 1][64 rows][D], in the K / V stages ----
+  __syncthreads();
+  if (kg > 0) {
+    float* part = KV + (kg - 1) * kBM * D;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int nb = 0; nb < kDBlocks; ++nb) {
+        part[lr[i] * D + 8 * nb + 2 * t] = dq[nb][2 * i];
+        part[lr[i] * D + 8 * nb + 2 * t + 1] = dq[nb][2 * i + 1];
+      }
+  }
+  __syncthreads();
+  if (kg > 0) return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + lr[i];
+    if (row >= pr.S) continue;
+    // causal rows never visit keys past the CTA's last row, yet a dense dbias is written everywhere: exact zeros
+    if (want_db && !pr.dbias_accum && t_end < pr.T) {
+      for (int key = ((t_end + kBN - 1) / kBN) * kBN + t; key < pr.T; key += 4)
+        store_from_f32(pr.dbias, dboff[i] + key * pr.dbs[3], bias_dtype, 0.f);
+    }
+    float* dqp = reinterpret_cast<float*>(pr.dq) + b * pr.dqs[0] + h * pr.dqs[1] + row * pr.dqs[2];
+#pragma unroll
+    for (int nb = 0; nb < kDBlocks; ++nb) {
+      float x0 = dq[nb][2 * i], x1 = dq[nb][2 * i + 1];
+      for (int j = 0; j < kG - 1; ++j) {
+        x0 += KV[j * kBM * D + lr[i] * D + 8 * nb + 2 * t];
+        x1 += KV[j * kBM * D + lr[i] * D + 8 * nb + 2 * t + 1];
+      }
+      dqp[8 * nb + 2 * t] = x0 * pr.scale;
+      dqp[8 * nb + 2 * t + 1] = x1 * pr.scale;
     }
   }
 }
@@ -1338,6 +1449,38 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   };
   bool dq_done = false;
   if constexpr (sizeof(T) == 4) {
+    // small problems: groups of warps split the key tiles inside each 64-row CTA (bwd_dq_tf32x3_split_kernel)
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    auto rows16 = [](const void* p, const int64_t* st3) {
+      return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && st3[0] % 4 == 0 && st3[1] % 4 == 0 && st3[2] % 4 == 0;
+    };
+    const int64_t ctas = int64_t((pr.S + 63) / 64) * pr.bh_count;
+    const int tiles = (pr.T + kBN - 1) / kBN;
+    if (pr.S > 0 && (pr.D == 32 || pr.D == 64) && (pr.Dv == 32 || pr.Dv == 64) && tiles >= 2 &&
+        ctas <= 2 * int64_t(sms > 0 ? sms : 148) && rows16(pr.q, pr.qs) && rows16(pr.k, pr.ks) && rows16(pr.v, pr.vs) &&
+        rows16(pr.dout, pr.dos)) {
+      const int kg = (tiles >= 5 || tiles == 3) ? 3 : 2;
+      const size_t sm = sizeof(float) * size_t(64 + kg * kBN) * (pr.D + 4 + pr.Dv + 4);
+      dim3 gq((pr.S + 63) / 64, pr.bh_count);
+      int rc = NB200_OK;
+      auto go = [&](auto kernel) {
+        if ((rc = prepare(kernel, sm)) == NB200_OK) kernel<<<gq, kTiledThreads * kg, sm, st>>>(pr, bias_dtype);
+      };
+      if (pr.D == 32) {
+        if (kg == 3) go(bwd_dq_tf32x3_split_kernel<4, 3>); else go(bwd_dq_tf32x3_split_kernel<4, 2>);
+      } else {
+        if (kg == 3) go(bwd_dq_tf32x3_split_kernel<8, 3>); else go(bwd_dq_tf32x3_split_kernel<8, 2>);
+      }
+      if (rc) return join(rc);
+      count_launch();
+      if (int rc2 = check_launch("bwd_dq_tf32x3_kernel")) return join(rc2);
+      dq_done = true;
+    }
+  }
+  if constexpr (sizeof(T) == 4) {
+    if (!dq_done)
     // fp32 operands with head dims in whole 8-column MMA blocks: 3 x TF32 on the warp-level tensor-core path
     // (a grid of fewer than ~100 CTAs of 64 rows leaves most SMs idle: tiny problems keep the 8-row CUDA-core CTAs)
     if (pr.S > 0 && pr.Dv % 8 == 0 && pr.Dv <= 128 && (pr.D == 32 || pr.D == 64 || pr.D == 128) &&
