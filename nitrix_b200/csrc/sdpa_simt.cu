@@ -12,16 +12,20 @@
 //   simt_fwd_tiled_kernel  head dims multiples of 4 / 32 (<= 128): register-tiled FMA, float4 shared-memory operands
 //   simt_fwd_kernel        everything else: one warp per query row, 32 lanes over 32 keys
 // Backward, fp32 operands on grids of >= 96 CTAs: bwd_dq_tf32x3_kernel and bwd_dkv_tf32x3_kernel
-// (D == Dv in {32, 64, 128}), the same 3 x TF32 tiling.  Otherwise:
+// (D == Dv in {32, 64, 128}), the same 3 x TF32 tiling; smaller problems at head dims 32 / 64 split each CTA's
+// tiles of the opposite operand over groups of warps (dq) or over the CTAs of a cluster (dk / dv).  Otherwise:
 // one warp owns one query row (dq) or one key row (dk/dv); the 32 lanes take 32 consecutive rows of the
 // opposite operand, staged in shared memory as fp32.  Row sums use warp shuffles; nothing is atomically accumulated
 // except the optional broadcast-bias gradient, and every sum runs in a fixed order.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "sdpa_common.cuh"
 
 namespace nb200 {
 namespace {
+
+namespace cg = cooperative_groups;
 
 constexpr int kWarps = 8;           // warps (rows) per CTA
 constexpr int kTile = 32;           // opposite-operand rows per step (one per lane)
@@ -1071,7 +1075,12 @@ __global__ void __launch_bounds__(kTiledThreads * kG) bwd_dq_tf32x3_split_kernel
 // operands (query 2 t / 2 t + 1 of a block stand in operand columns t / t + 4).  lse and delta of the tile's
 // queries sit in shared memory.  Head dims D == Dv in {32, 64, 128} (at 128 the two accumulator sets fill the
 // register file: 255 registers and a few spilled words).
-template <int kBlocks>   // D / 8 == Dv / 8
+//
+// kC > 1 (SMALL problems, launched as clusters of kC CTAs along x): the kC CTAs of a cluster own the same 64 keys and
+// take the query tiles in turn, which puts kC times as many warps on the machine for the same latency-bound chain;
+// ranks 1.. leave their partial dk / dv tiles in their own shared memory and rank 0 sums them over distributed
+// shared memory in a fixed order (deterministic) before it writes.
+template <int kBlocks, int kC = 1>   // D / 8 == Dv / 8
 __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBK = 64;
@@ -1085,7 +1094,8 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
-  const int key0 = blockIdx.x * kBK;
+  const int crank = kC > 1 ? int(blockIdx.x) % kC : 0;   // rank in the cluster (cluster dims (kC, 1, 1))
+  const int key0 = (int(blockIdx.x) / kC) * kBK;
   const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
   const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
   const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
@@ -1120,16 +1130,17 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem p
       Dbuf[buf * kBN + threadIdx.x] = q < pr.S ? pr.delta[rbase + q] : 0.f;
     }
   };
-  if (s_begin < pr.S) prefetch(s_begin, 0);
+  const int q_first = s_begin + crank * kBN;
+  if (q_first < pr.S) prefetch(q_first, 0);
   int it = 0;
-  for (int qt = s_begin; qt < pr.S; qt += kBN, ++it) {
+  for (int qt = q_first; qt < pr.S; qt += kC * kBN, ++it) {
     stage_wait();
     __syncthreads();   // tile `it` (and, the first time, K and V) has landed; nobody reads the other buffers any more
     const float* Qt = Qbuf + (it & 1) * kBN * LD;
     const float* Gt = Gbuf + (it & 1) * kBN * LD;
     const float* Lt = Lbuf + (it & 1) * kBN;
     const float* Dt = Dbuf + (it & 1) * kBN;
-    if (qt + kBN < pr.S) prefetch(qt + kBN, (it + 1) & 1);
+    if (qt + kC * kBN < pr.S) prefetch(qt + kC * kBN, (it + 1) & 1);
     float sc[8][4], dp[8][4];
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb)
@@ -1195,6 +1206,39 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem p
         mma_3xtf32(dk[nb], sh, sl, bh2, bl2);
       }
     }
+  }
+  if constexpr (kC > 1) {
+    // partial tiles [2][kBK][D] (dk, dv) in this CTA's query stages; rank 0 adds ranks 1.. in order
+    cg::cluster_group cluster = cg::this_cluster();
+    float* part = Qbuf;
+    stage_wait();      // (a rank without a query tile still has its K / V copies in flight)
+    __syncthreads();   // the last tile's operands are no longer read
+    if (crank > 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int nb = 0; nb < kBlocks; ++nb) {
+          *reinterpret_cast<float2*>(part + lr[i] * D + 8 * nb + 2 * t) = make_float2(dk[nb][2 * i], dk[nb][2 * i + 1]);
+          *reinterpret_cast<float2*>(part + (kBK + lr[i]) * D + 8 * nb + 2 * t) = make_float2(dv[nb][2 * i], dv[nb][2 * i + 1]);
+        }
+    }
+    cluster.sync();
+    if (crank == 0) {
+      for (int r = 1; r < kC; ++r) {
+        const float* rp = cluster.map_shared_rank(part, r);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int nb = 0; nb < kBlocks; ++nb) {
+            const float2 a = *reinterpret_cast<const float2*>(rp + lr[i] * D + 8 * nb + 2 * t);
+            const float2 c = *reinterpret_cast<const float2*>(rp + (kBK + lr[i]) * D + 8 * nb + 2 * t);
+            dk[nb][2 * i] += a.x; dk[nb][2 * i + 1] += a.y;
+            dv[nb][2 * i] += c.x; dv[nb][2 * i + 1] += c.y;
+          }
+      }
+    }
+    cluster.sync();    // nobody leaves while rank 0 still reads its shared memory
+    if (crank > 0) return;
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -1416,19 +1460,58 @@ int fwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   return check_launch("simt_fwd_kernel");
 }
 
+int sm_count() {
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+
+bool fp32_rows16(const void* p, const int64_t* st3) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && st3[0] % 4 == 0 && st3[1] % 4 == 0 && st3[2] % 4 == 0;
+}
+
+// Small fp32 problems, dq: the number of warp groups that split the key tiles inside each 64-row CTA
+// (bwd_dq_tf32x3_split_kernel), 0 when that kernel does not apply.
+int bwd_dq_split_groups(const Problem& pr) {
+  const int64_t ctas = int64_t((pr.S + 63) / 64) * pr.bh_count;
+  const int tiles = (pr.T + kBN - 1) / kBN;
+  if (!(pr.S > 0 && (pr.D == 32 || pr.D == 64) && (pr.Dv == 32 || pr.Dv == 64) && tiles >= 2 &&
+        ctas <= 2 * int64_t(sm_count()) && fp32_rows16(pr.q, pr.qs) && fp32_rows16(pr.k, pr.ks) &&
+        fp32_rows16(pr.v, pr.vs) && fp32_rows16(pr.dout, pr.dos)))
+    return 0;
+  return (tiles >= 5 || tiles == 3) ? 3 : 2;
+}
+
+// Small fp32 problems, dk / dv: the number of CTAs per cluster that split the query tiles of each 64-key tile
+// (bwd_dkv_tf32x3_kernel<., kC>), 0 when a cluster launch does not apply -- it does as long as every CTA of the
+// launch is resident at once (two per SM: ~200 registers a thread): the point is more warps per SM, not more waves.
+// Measured, fp32 D 64, dk / dv kernel alone: B2 H8 S256 114 -> 39 us (four CTAs per cluster), B4 H6 S344
+// 100 -> 72 us (two), B1 H8 S1024 244 -> 154 us (two).
+int bwd_dkv_cluster_size(const Problem& pr) {
+  const int64_t ctas = int64_t((pr.T + 63) / 64) * pr.bh_count;
+  const int q_tiles = (pr.S + 63) / 64;
+  const int64_t resident = 2 * int64_t(sm_count());
+  if (!(pr.T > 0 && pr.D == pr.Dv && (pr.D == 32 || pr.D == 64) && q_tiles >= 2 && 2 * ctas <= resident)) return 0;
+  return (q_tiles >= 3 && 4 * ctas <= resident) ? 4 : 2;
+}
+
 template <typename T>
 int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   const size_t smem = bwd_smem(pr);
   if (int rc = prepare(simt_bwd_dq_kernel<T>, smem)) return rc;
   if (int rc = prepare(simt_bwd_dkv_kernel<T>, smem)) return rc;
-  // The dq (+ dbias) kernel and the dk / dv kernel are independent.  On a small problem neither fills the GPU (C1:
-  // 256 CTAs of 8 warps each, 80 to 90 us apiece, bound by the latency of one row's pass over the keys), so the
-  // second one runs on a side stream between a fork and a join event and the pair takes as long as the slower one.
+  // The dq (+ dbias) kernel and the dk / dv kernel are independent.  On a small problem neither fills the GPU (each
+  // is bound by the latency of one warp's chain of dependent steps over the opposite operand's tiles, not by
+  // throughput), so the second one runs on a side stream between a fork and a join event and the pair takes about as
+  // long as the slower one.
   cudaStream_t st_kv = st;
   const SideStream* side = nullptr;
   {
     const int64_t ctas_q = int64_t((pr.S + kWarps - 1) / kWarps) * pr.bh_count;
     const int64_t ctas_k = int64_t((pr.T + kWarps - 1) / kWarps) * pr.bh_count;
+    // (C1, fp32 B2 H4 L256: 0.149 -> 0.106 ms per step.  Twice that many rows and the two kernels already cover
+    // the machine between them: B2 H8 S256 73 -> 71 us per backward, B1 H8 S1024 272 -> 298 us.)
     if (pr.S > 0 && pr.T > 0 && ctas_q + ctas_k <= 4 * 148) side = side_stream(st);
     if (side) {
       if (cudaEventRecord(side->fork, st) == cudaSuccess && cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess) {
@@ -1449,19 +1532,8 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   };
   bool dq_done = false;
   if constexpr (sizeof(T) == 4) {
-    // small problems: groups of warps split the key tiles inside each 64-row CTA (bwd_dq_tf32x3_split_kernel)
-    int sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    auto rows16 = [](const void* p, const int64_t* st3) {
-      return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && st3[0] % 4 == 0 && st3[1] % 4 == 0 && st3[2] % 4 == 0;
-    };
-    const int64_t ctas = int64_t((pr.S + 63) / 64) * pr.bh_count;
-    const int tiles = (pr.T + kBN - 1) / kBN;
-    if (pr.S > 0 && (pr.D == 32 || pr.D == 64) && (pr.Dv == 32 || pr.Dv == 64) && tiles >= 2 &&
-        ctas <= 2 * int64_t(sms > 0 ? sms : 148) && rows16(pr.q, pr.qs) && rows16(pr.k, pr.ks) && rows16(pr.v, pr.vs) &&
-        rows16(pr.dout, pr.dos)) {
-      const int kg = (tiles >= 5 || tiles == 3) ? 3 : 2;
+    // small problems: groups of warps split the key tiles inside each 64-row CTA
+    if (const int kg = bwd_dq_split_groups(pr)) {
       const size_t sm = sizeof(float) * size_t(64 + kg * kBN) * (pr.D + 4 + pr.Dv + 4);
       dim3 gq((pr.S + 63) / 64, pr.bh_count);
       int rc = NB200_OK;
@@ -1508,6 +1580,35 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
     if (int rc = check_launch("simt_bwd_dq_kernel")) return join(rc);
   }
   if constexpr (sizeof(T) == 4) {
+    // small problems: clusters of CTAs split the query tiles of each 64-key tile
+    if (const int kc = bwd_dkv_cluster_size(pr)) {
+      const size_t sm = sizeof(float) * (size_t(6 * 64) * (pr.D + 4) + 4 * kBN);
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(unsigned((pr.T + 63) / 64) * kc, pr.bh_count);
+      cfg.blockDim = dim3(kTiledThreads);
+      cfg.dynamicSmemBytes = sm;
+      cfg.stream = st_kv;
+      cudaLaunchAttribute attr{};
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = kc;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int rc = NB200_OK;
+      auto go = [&](auto kernel) {
+        if ((rc = prepare(kernel, sm)) != NB200_OK) return;
+        (void)cudaLaunchKernelEx(&cfg, kernel, pr, bias_dtype);   // a failure is read by check_launch below
+      };
+      if (pr.D == 32) {
+        if (kc == 4) go(bwd_dkv_tf32x3_kernel<4, 4>); else go(bwd_dkv_tf32x3_kernel<4, 2>);
+      } else {
+        if (kc == 4) go(bwd_dkv_tf32x3_kernel<8, 4>); else go(bwd_dkv_tf32x3_kernel<8, 2>);
+      }
+      if (rc) return join(rc);
+      count_launch();
+      return join(check_launch("bwd_dkv_tf32x3_kernel"));
+    }
     if (pr.T > 0 && pr.D == pr.Dv && (pr.D == 32 || pr.D == 64 || pr.D == 128) &&
         int64_t((pr.T + 63) / 64) * pr.bh_count >= 96) {
       const size_t sm = sizeof(float) * (size_t(6 * 64) * (pr.D + 4) + 4 * kBN);
@@ -1542,8 +1643,10 @@ bool simt_family_uses_tensor_path(const Problem& pr, int dtype, int pass) {
   const bool dv_ok = pr.Dv == 32 || pr.Dv == 64 || pr.Dv == 128;
   if (pass == NB200_PASS_FWD) return pr.D % 8 == 0 && pr.D <= 128 && dv_ok;
   const bool d_ok = pr.D == 32 || pr.D == 64 || pr.D == 128;
-  const bool dq = pr.S > 0 && pr.Dv % 8 == 0 && pr.Dv <= 128 && d_ok && int64_t((pr.S + 63) / 64) * pr.bh_count >= 96;
-  const bool dkv = pr.T > 0 && pr.D == pr.Dv && d_ok && int64_t((pr.T + 63) / 64) * pr.bh_count >= 96;
+  const bool dq = bwd_dq_split_groups(pr) != 0 ||
+                  (pr.S > 0 && pr.Dv % 8 == 0 && pr.Dv <= 128 && d_ok && int64_t((pr.S + 63) / 64) * pr.bh_count >= 96);
+  const bool dkv = bwd_dkv_cluster_size(pr) != 0 ||
+                   (pr.T > 0 && pr.D == pr.Dv && d_ok && int64_t((pr.T + 63) / 64) * pr.bh_count >= 96);
   return dq && dkv;
 }
 

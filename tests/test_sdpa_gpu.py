@@ -159,6 +159,21 @@ def test_fp32_small_forward_splits_keys_over_warp_groups(name, t):
     assert float((out[~dead] - ref[~dead]).abs().max()) <= FP32_REL * float(ref[~dead].abs().max())
 
 
+@pytest.mark.parametrize("d", [32, 64])
+@pytest.mark.parametrize("s,t", [(100, 100), (150, 344), (344, 130), (520, 200), (256, 256)])
+@pytest.mark.parametrize("name", ["dense", "bias_causal", "full_bias_mask", "key_padding"])
+def test_fp32_small_backward_splits_tiles_over_groups_and_clusters(name, s, t, d):
+    """Small fp32 problems, backward: the dq kernel's groups of warps take the key tiles in turn (two or three groups),
+    the dk / dv kernel runs as clusters of two or four CTAs that take the query tiles in turn and sum their partial
+    tiles over distributed shared memory -- with partial last tiles on both sides, causal key tiles that have fewer
+    query tiles than the cluster has CTAs, a random mask, key padding and a bias gradient."""
+    if name == "bias_causal":
+        s = t
+    q, k, v, kw = _cases.kernel_case(name, b=2, h=3, s=s, t=t, d=d)
+    got, ref = run_both(q, k, v, kw, torch.float32, "auto")
+    check(got, ref, torch.float32)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", ["bias_mask", "causal", "key_padding"])
 def test_simt_low_precision_parity(name, dtype):
