@@ -380,21 +380,24 @@ __global__ void __launch_bounds__(kTiledThreads) simt_fwd_tiled_kernel(Problem p
 // ---------------------------------------------------------------------------
 // forward for fp32 operands on the warp-level tensor-core path: 3 x TF32
 // ---------------------------------------------------------------------------
-// Every fp32 operand x is split as hi = tf32(x), lo = tf32(x - hi); a product a b is taken as
+// Every fp32 operand x is split as hi = tf32(x), lo = x - hi; a product a b is taken as
 // a_hi b_hi + a_hi b_lo + a_lo b_hi (three mma.sync.m16n8k8 TF32 instructions, fp32 accumulate), which keeps about
-// 21 bits -- inside the 1e-4 relative budget of the fp32 path.  A CTA of 4 warps owns 64 query rows, a warp 16 of
+// 20 bits -- inside the 1e-4 relative budget of the fp32 path.  A CTA of 4 warps owns 64 query rows, a warp 16 of
 // them against the whole 64-key tile: scores and output live in accumulator fragments (row g = lane / 4 and g + 8,
 // columns 2 t, 2 t + 1 with t = lane % 4), so row maxima / sums need the 4 lanes of a quad.  The probabilities go
 // from the score fragment straight into the A operand of P V: within an 8-key block operand column t stands for
 // key 2 t and column t + 4 for key 2 t + 1, and the V rows are fetched in that order.
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
-}
+//
+// The split itself is two instructions: hi keeps the top 19 bits of x (sign, exponent, 10 mantissa bits -- a TF32
+// number), lo = x - hi is exact in fp32, and the tensor core reads only the TF32 bits of lo's register.  (Rounding
+// both terms with cvt.rna.tf32 costs several integer instructions per conversion, and the splits -- 320 per warp
+// and tile -- were then a third of all instructions issued.)  What is dropped is a_lo b_lo and the truncated tails
+// of the lo terms, each below 2^-20 of |a| |b|.  Measured against fp64 (max error over max |reference|, out and
+// gradients, S 344..2048): 2.3e-6..4.7e-6, against 1.4e-6..3.1e-6 with both terms rounded and 1.3e-6..3.5e-6 with
+// hi rounded (one more instruction); the kernels run 1.25x (forward) to 1.7x (dk / dv at head dim 128) faster.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-  hi = to_tf32(x);
-  lo = to_tf32(x - __uint_as_float(hi));
+  hi = __float_as_uint(x) & 0xffffe000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
 }
 __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile(
@@ -410,14 +413,71 @@ __device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4
   mma_tf32(c, ah, bh);
 }
 
+// The additive logit tile of a [64 query rows] x [64 keys] block, in base 2: log2(e) * bias where the key is kept and
+// -inf where it is not (past T or S, behind the causal diagonal, mask false).  128 threads stage it cooperatively,
+// four consecutive keys each, all loads first: the global reads are coalesced and in flight together, and the
+// per-element code in the MMA fragment layout shrinks to one shared-memory load (the fragment layout's own
+// scattered loads with their bounds, stride and dtype logic were two thirds of a tile's instructions).
+constexpr int kLDB = kBN + 8;   // a thread's (key, key + 1) pairs are 8-byte loads: 72 keeps a half-warp conflict-free
+template <typename BT>
+__device__ __forceinline__ void stage_logit_tile_t(float* Bt, int ld, const Problem& pr, int b, int h, int row0, int kt,
+                                                   int tid) {
+  constexpr int kIters = 64 * (kBN / 4) / kTiledThreads;   // 8: thread tid has keys 4 (tid & 15) .. + 3 of rows (tid >> 4) + 8 it
+  const int rl0 = tid >> 4, c = 4 * (tid & 15), key = kt + c;
+  // (64-bit index arithmetic once per thread, not once per element: it was most of the instructions of a tile)
+  const BT* bp = reinterpret_cast<const BT*>(pr.bias);
+  const uint8_t* mp = pr.mask;
+  if (bp) bp += b * pr.bs[0] + h * pr.bs[1] + int64_t(row0 + rl0) * pr.bs[2] + int64_t(key) * pr.bs[3];
+  if (mp) mp += b * pr.ms[0] + h * pr.ms[1] + int64_t(row0 + rl0) * pr.ms[2] + int64_t(key) * pr.ms[3];
+  const int64_t bstep = 8 * pr.bs[2], mstep = 8 * pr.ms[2], bs3 = pr.bs[3], ms3 = pr.ms[3];
+  float bv[kIters][4];
+  uint32_t keep[kIters];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int row = row0 + rl0 + 8 * it;
+    keep[it] = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      bool k1 = row < pr.S && key + j < pr.T && !(pr.causal && key + j > row);
+      if (k1 && mp) k1 = mp[j * ms3] != 0;
+      bv[it][j] = (k1 && bp) ? to_f32<BT>(bp[j * bs3]) : 0.f;
+      keep[it] |= uint32_t(k1) << j;
+    }
+    if (bp) bp += bstep;
+    if (mp) mp += mstep;
+  }
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    float4 v;
+    v.x = (keep[it] & 1) ? kLog2e * bv[it][0] : -INFINITY;
+    v.y = (keep[it] & 2) ? kLog2e * bv[it][1] : -INFINITY;
+    v.z = (keep[it] & 4) ? kLog2e * bv[it][2] : -INFINITY;
+    v.w = (keep[it] & 8) ? kLog2e * bv[it][3] : -INFINITY;
+    *reinterpret_cast<float4*>(Bt + (rl0 + 8 * it) * ld + c) = v;
+  }
+}
+__device__ __forceinline__ void stage_logit_tile(float* Bt, int ld, const Problem& pr, int bias_dtype, int b, int h,
+                                                 int row0, int kt, int tid) {
+  if (!pr.bias || bias_dtype == NB200_F32) stage_logit_tile_t<float>(Bt, ld, pr, b, h, row0, kt, tid);
+  else if (bias_dtype == NB200_BF16) stage_logit_tile_t<__nv_bfloat16>(Bt, ld, pr, b, h, row0, kt, tid);
+  else stage_logit_tile_t<__half>(Bt, ld, pr, b, h, row0, kt, tid);
+}
+// 2^x for x <= 0 (and -inf -> 0): one MUFU instruction, relative error 2^-22
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One 64-key tile of the 3 x TF32 forward for this warp's 16 query rows: scores, logits and masks, online softmax,
-// out += P V.  Ks / Vs: the tile in shared memory (rows past T zero-filled); kt: its first key.
-template <int kDvBlocks>
-__device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtype, const float* Qs, const float* Ks,
-                                                const float* Vs, int LDQ, int LDV, int D, int kt, int row0,
-                                                const int (&lr)[2], const int64_t (&boff)[2], const int64_t (&moff)[2],
-                                                float s2scale, int g, int t, float (&o)[kDvBlocks][4], float (&m)[2],
-                                                float (&l)[2]) {
+// out += P V.  Ks / Vs: the tile in shared memory (rows past T zero-filled); Bt: its logit tile (stage_logit_tile),
+// complete once `sync()` returns.
+// Without a bias and a mask nothing is staged (Bt == nullptr): keeping a key is then three integer comparisons.
+template <int kDvBlocks, typename Sync>
+__device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, const float* Qs, const float* Ks, const float* Vs,
+                                                const float* Bt, int LDQ, int LDV, int D, int kt, int row0,
+                                                const int (&lr)[2], float s2scale, int g, int t,
+                                                float (&o)[kDvBlocks][4], float (&m)[2], float (&l)[2], Sync sync) {
   // ---- scores: 8 blocks of 8 keys ----
   float sc[8][4];
 #pragma unroll
@@ -440,18 +500,33 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtyp
   }
   // ---- logits in base 2, masks, online softmax (rows g and g + 8 of the warp's 16) ----
   float mx[2] = {-INFINITY, -INFINITY};
+  if (Bt) {
+    sync();
 #pragma unroll
-  for (int nb = 0; nb < 8; ++nb)
+    for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = e >> 1;
-      const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
-      bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
-      if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
-      const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
-      sc[nb][e] = keep ? fmaf(sc[nb][e], s2scale, bias) : -INFINITY;
-      mx[i] = fmaxf(mx[i], sc[nb][e]);
+      for (int i = 0; i < 2; ++i) {
+        const float2 bt = *reinterpret_cast<const float2*>(Bt + lr[i] * kLDB + 8 * nb + 2 * t);
+        sc[nb][2 * i] = fmaf(sc[nb][2 * i], s2scale, bt.x);
+        sc[nb][2 * i + 1] = fmaf(sc[nb][2 * i + 1], s2scale, bt.y);
+        mx[i] = fmaxf(mx[i], fmaxf(sc[nb][2 * i], sc[nb][2 * i + 1]));
+      }
+  } else {
+    // the last key each row keeps in this tile, as an index into the tile
+    int last[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + lr[i];
+      last[i] = row < pr.S ? (pr.causal ? min(pr.T - 1, row) : pr.T - 1) - kt : -1;
     }
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sc[nb][e] = 8 * nb + 2 * t + (e & 1) <= last[e >> 1] ? sc[nb][e] * s2scale : -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], sc[nb][e]);
+      }
+  }
   float alpha[2], m_ref[2], sum[2] = {0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -466,7 +541,7 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtyp
   for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float p = exp2f(sc[nb][e] - m_ref[e >> 1]);
+      const float p = ex2_fast(sc[nb][e] - m_ref[e >> 1]);
       sc[nb][e] = p;
       sum[e >> 1] += p;
     }
@@ -512,6 +587,7 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   float* Qs = smem;                  // [kBM][LDQ]
   float* Kbuf = Qs + kBM * LDQ;      // 2 x [kBN][LDQ]
   float* Vbuf = Kbuf + 2 * kBN * LDQ;  // 2 x [kBN][LDV]
+  float* Bt = (pr.bias || pr.mask) ? Vbuf + 2 * kBN * LDV : nullptr;   // [kBM][kLDB]  logit tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
@@ -523,13 +599,6 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
 
   // this thread's two rows: r[0] = 16 warp + g, r[1] = r[0] + 8
   const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
-  int64_t boff[2], moff[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int rr = min(row0 + lr[i], pr.S - 1);
-    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
-    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
-  }
   float o[kDvBlocks][4];
 #pragma unroll
   for (int nb = 0; nb < kDvBlocks; ++nb)
@@ -554,7 +623,11 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
       stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
       stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
     }
-    fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
+    // (the top barrier also says that nobody reads the previous logit tile any more; the one before the softmax
+    // that this tile's is complete)
+    if (Bt) stage_logit_tile(Bt, kLDB, pr, bias_dtype, b, h, row0, kt, threadIdx.x);
+    fwd_tf32x3_tile<kDvBlocks>(pr, Qs, Ks, Vs, Bt, LDQ, LDV, D, kt, row0, lr, s2scale, g, t, o, m, l,
+                               [] { __syncthreads(); });
   }
   // ---- out = o / l (NaN for a row with no kept key, as the reference's softmax gives), lse ----
 #pragma unroll
@@ -584,11 +657,12 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
   const int D = pr.D, Dv = pr.Dv;
   const int LDQ = D + 4, LDV = Dv + 4;
   float* Qs = smem;                          // [kBM][LDQ]
-  float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV]); afterwards the partial results
+  float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV] + [kBM][kLDB]); afterwards the partial results
   const int kg = threadIdx.x >> 7, tg = threadIdx.x & 127;
   const int warp = tg >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV);
+  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV + kBM * kLDB);
   float* Vs = Ks + kBN * LDQ;
+  float* Bt = (pr.bias || pr.mask) ? Vs + kBN * LDV : nullptr;   // the group's logit tile
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
   const int row0 = blockIdx.x * kBM;
@@ -600,13 +674,6 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
   __syncthreads();
 
   const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
-  int64_t boff[2], moff[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int rr = min(row0 + lr[i], pr.S - 1);
-    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
-    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
-  }
   float o[kDvBlocks][4];
 #pragma unroll
   for (int nb = 0; nb < kDvBlocks; ++nb)
@@ -621,9 +688,10 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
     group_sync();   // the group's previous tile is no longer read
     stage_rows_f4(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D, tg, kTiledThreads);
     stage_rows_f4(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv, tg, kTiledThreads);
+    if (Bt) stage_logit_tile(Bt, kLDB, pr, bias_dtype, b, h, row0, kt, tg);
     stage_wait();
     group_sync();
-    fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
+    fwd_tf32x3_tile<kDvBlocks>(pr, Qs, Ks, Vs, Bt, LDQ, LDV, D, kt, row0, lr, s2scale, g, t, o, m, l, [] {});
   }
 
   // ---- merge the groups: partial [kG - 1][64 rows][Dv + 2] = (out, m, l), in the K / V stages ----
@@ -850,6 +918,23 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
     }
   }
   // ---- p = exp2(logit2 - lse), ds = p (dP - delta); ds replaces the score fragment ----
+  if (!pr.bias && !pr.mask && !want_db) {
+    // nothing to load: keeping a key is a comparison with the last key of the row in this tile
+    int last[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + lr[i];
+      last[i] = row < pr.S ? (pr.causal ? min(pr.T - 1, row) : pr.T - 1) - kt : -1;
+    }
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const float p = 8 * nb + 2 * t + (e & 1) <= last[i] ? ex2_fast(fmaf(sc[nb][e], s2scale, -lse[i])) : 0.f;
+        sc[nb][e] = p * (dp[nb][e] - delta[i]);
+      }
+  } else
 #pragma unroll
   for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
@@ -859,7 +944,7 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
       bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
       if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
       const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
-      const float p = keep ? exp2f(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
+      const float p = keep ? ex2_fast(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
       const float ds = p * (dp[nb][e] - delta[i]);
       sc[nb][e] = ds;
       if (want_db && key < pr.T && row < pr.S) {
@@ -1168,6 +1253,24 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem p
       }
     }
     // ---- p (kept in sc) and ds (kept in dp); row = key, column = query ----
+    if (!pr.bias && !pr.mask) {
+      // nothing to load: a query keeps the keys up to a last one (none past S)
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int ql = 8 * nb + 2 * t + c, q = qt + ql;
+          const int last = q < pr.S ? (pr.causal ? min(pr.T - 1, q) : pr.T - 1) - key0 : -1;
+          const float lq = Lt[ql], dq_ = Dt[ql];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int e = 2 * i + c;
+            const float p = lr[i] <= last ? ex2_fast(fmaf(sc[nb][e], s2scale, -lq)) : 0.f;
+            sc[nb][e] = p;
+            dp[nb][e] = p * (dp[nb][e] - dq_);
+          }
+        }
+    } else
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
@@ -1177,7 +1280,7 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem p
         bool keep = key < pr.T && q < pr.S && !(pr.causal && key > q);
         if (keep && pr.mask) keep = pr.mask[moff[i] + q * pr.ms[2]] != 0;
         const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + q * pr.bs[2], bias_dtype) : 0.f;
-        const float p = keep ? exp2f(fmaf(sc[nb][e], s2scale, bias) - Lt[ql]) : 0.f;
+        const float p = keep ? ex2_fast(fmaf(sc[nb][e], s2scale, bias) - Lt[ql]) : 0.f;
         sc[nb][e] = p;
         dp[nb][e] = p * (dp[nb][e] - Dt[ql]);
       }
@@ -1393,7 +1496,7 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
 
 template <int kDvBlocks, int kG>
 int fwd_tf32x3_split_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
-  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) + size_t(kG) * kBN * (pr.D + 4 + pr.Dv + 4));
+  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) + size_t(kG) * (kBN * (pr.D + 4 + pr.Dv + 4) + 64 * kLDB));
   if (int rc = prepare(fwd_tf32x3_split_kernel<kDvBlocks, kG>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_split_kernel<kDvBlocks, kG><<<grid, kTiledThreads * kG, smem, st>>>(pr, bias_dtype);
@@ -1422,7 +1525,7 @@ int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       return fwd_tf32x3_split_t<kDvBlocks, 2>(pr, bias_dtype, st);
     }
   }
-  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4));
+  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4) + 64 * kLDB);
   if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_kernel<kDvBlocks><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
