@@ -934,28 +934,55 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
         const float p = 8 * nb + 2 * t + (e & 1) <= last[i] ? ex2_fast(fmaf(sc[nb][e], s2scale, -lse[i])) : 0.f;
         sc[nb][e] = p * (dp[nb][e] - delta[i]);
       }
-  } else
+  } else {
+    // bias / mask / dbias in the fragment layout: this thread's elements are keys kt + 2 t + (8 nb + c) of rows
+    // lr[0], lr[1].  Pointers to the first of them once per tile, the dtype decided once per tile (a 64-bit
+    // index product and a dtype switch per element were most of a tile's instructions).
+    int last[2];
 #pragma unroll
-  for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = e >> 1;
-      const int row = row0 + lr[i], key = kt + 8 * nb + 2 * t + (e & 1);
-      bool keep = key < pr.T && row < pr.S && !(pr.causal && key > row);
-      if (keep && pr.mask) keep = pr.mask[moff[i] + key * pr.ms[3]] != 0;
-      const float bias = (keep && pr.bias) ? kLog2e * load_as_f32(pr.bias, boff[i] + key * pr.bs[3], bias_dtype) : 0.f;
-      const float p = keep ? ex2_fast(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
-      const float ds = p * (dp[nb][e] - delta[i]);
-      sc[nb][e] = ds;
-      if (want_db && key < pr.T && row < pr.S) {
-        const int64_t off = dboff[i] + key * pr.dbs[3];
-        if (pr.dbias_accum) {
-          if (ds != 0.f) atomicAdd(pr.dbias_accum + off, ds);
-        } else {
-          store_from_f32(pr.dbias, off, bias_dtype, ds);
-        }
-      }
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + lr[i];
+      last[i] = row < pr.S ? (pr.causal ? min(pr.T - 1, row) : pr.T - 1) - kt : -1;
     }
+    const int k0 = kt + 2 * t;
+    auto ew = [&](auto tag) {
+      using BT = decltype(tag);
+      const BT* bp[2];
+      BT* dbp[2];
+      const uint8_t* mp[2];
+      float* ap[2];
+      const int64_t bs3 = pr.bs[3], ms3 = pr.ms[3], dbs3 = pr.dbs[3];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        bp[i] = pr.bias ? reinterpret_cast<const BT*>(pr.bias) + boff[i] + k0 * bs3 : nullptr;
+        mp[i] = pr.mask ? pr.mask + moff[i] + k0 * ms3 : nullptr;
+        dbp[i] = pr.dbias ? reinterpret_cast<BT*>(pr.dbias) + dboff[i] + k0 * dbs3 : nullptr;
+        ap[i] = pr.dbias_accum ? pr.dbias_accum + dboff[i] + k0 * dbs3 : nullptr;
+      }
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1, col = 8 * nb + (e & 1);      // key = k0 + col
+          bool keep = col + 2 * t <= last[i];
+          if (keep && mp[i]) keep = mp[i][col * ms3] != 0;
+          const float bias = (keep && bp[i]) ? kLog2e * to_f32<BT>(bp[i][col * bs3]) : 0.f;
+          const float p = keep ? ex2_fast(fmaf(sc[nb][e], s2scale, bias) - lse[i]) : 0.f;
+          const float ds = p * (dp[nb][e] - delta[i]);
+          sc[nb][e] = ds;
+          if (want_db && k0 + col < pr.T && row0 + lr[i] < pr.S) {
+            if (ap[i]) {
+              if (ds != 0.f) atomicAdd(ap[i] + col * dbs3, ds);
+            } else {
+              dbp[i][col * dbs3] = from_f32<BT>(ds);
+            }
+          }
+        }
+    };
+    if (bias_dtype == NB200_F32) ew(float{});
+    else if (bias_dtype == NB200_BF16) ew(__nv_bfloat16{});
+    else ew(__half{});
+  }
   // ---- dQ += ds K ----
 #pragma unroll
   for (int kb = 0; kb < 8; ++kb) {
