@@ -660,9 +660,10 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
   float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV] + [kBM][kLDB]); afterwards the partial results
   const int kg = threadIdx.x >> 7, tg = threadIdx.x & 127;
   const int warp = tg >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV + kBM * kLDB);
+  const bool logits = pr.bias || pr.mask;    // (the launcher sizes the stages the same way)
+  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV + (logits ? kBM * kLDB : 0));
   float* Vs = Ks + kBN * LDQ;
-  float* Bt = (pr.bias || pr.mask) ? Vs + kBN * LDV : nullptr;   // the group's logit tile
+  float* Bt = logits ? Vs + kBN * LDV : nullptr;   // the group's logit tile
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
   const int row0 = blockIdx.x * kBM;
@@ -1523,7 +1524,8 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
 
 template <int kDvBlocks, int kG>
 int fwd_tf32x3_split_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
-  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) + size_t(kG) * (kBN * (pr.D + 4 + pr.Dv + 4) + 64 * kLDB));
+  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) +
+                                       size_t(kG) * (kBN * (pr.D + 4 + pr.Dv + 4) + ((pr.bias || pr.mask) ? 64 * kLDB : 0)));
   if (int rc = prepare(fwd_tf32x3_split_kernel<kDvBlocks, kG>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_split_kernel<kDvBlocks, kG><<<grid, kTiledThreads * kG, smem, st>>>(pr, bias_dtype);
@@ -1552,7 +1554,8 @@ int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       return fwd_tf32x3_split_t<kDvBlocks, 2>(pr, bias_dtype, st);
     }
   }
-  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4) + 64 * kLDB);
+  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4) +
+                                       ((pr.bias || pr.mask) ? 64 * kLDB : 0));
   if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_kernel<kDvBlocks><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
