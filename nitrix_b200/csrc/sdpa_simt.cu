@@ -413,55 +413,6 @@ __device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4
   mma_tf32(c, ah, bh);
 }
 
-// The additive logit tile of a [64 query rows] x [64 keys] block, in base 2: log2(e) * bias where the key is kept and
-// -inf where it is not (past T or S, behind the causal diagonal, mask false).  128 threads stage it cooperatively,
-// four consecutive keys each, all loads first: the global reads are coalesced and in flight together, and the
-// per-element code in the MMA fragment layout shrinks to one shared-memory load (the fragment layout's own
-// scattered loads with their bounds, stride and dtype logic were two thirds of a tile's instructions).
-constexpr int kLDB = kBN + 8;   // a thread's (key, key + 1) pairs are 8-byte loads: 72 keeps a half-warp conflict-free
-template <typename BT>
-__device__ __forceinline__ void stage_logit_tile_t(float* Bt, int ld, const Problem& pr, int b, int h, int row0, int kt,
-                                                   int tid) {
-  constexpr int kIters = 64 * (kBN / 4) / kTiledThreads;   // 8: thread tid has keys 4 (tid & 15) .. + 3 of rows (tid >> 4) + 8 it
-  const int rl0 = tid >> 4, c = 4 * (tid & 15), key = kt + c;
-  // (64-bit index arithmetic once per thread, not once per element: it was most of the instructions of a tile)
-  const BT* bp = reinterpret_cast<const BT*>(pr.bias);
-  const uint8_t* mp = pr.mask;
-  if (bp) bp += b * pr.bs[0] + h * pr.bs[1] + int64_t(row0 + rl0) * pr.bs[2] + int64_t(key) * pr.bs[3];
-  if (mp) mp += b * pr.ms[0] + h * pr.ms[1] + int64_t(row0 + rl0) * pr.ms[2] + int64_t(key) * pr.ms[3];
-  const int64_t bstep = 8 * pr.bs[2], mstep = 8 * pr.ms[2], bs3 = pr.bs[3], ms3 = pr.ms[3];
-  float bv[kIters][4];
-  uint32_t keep[kIters];
-#pragma unroll
-  for (int it = 0; it < kIters; ++it) {
-    const int row = row0 + rl0 + 8 * it;
-    keep[it] = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      bool k1 = row < pr.S && key + j < pr.T && !(pr.causal && key + j > row);
-      if (k1 && mp) k1 = mp[j * ms3] != 0;
-      bv[it][j] = (k1 && bp) ? to_f32<BT>(bp[j * bs3]) : 0.f;
-      keep[it] |= uint32_t(k1) << j;
-    }
-    if (bp) bp += bstep;
-    if (mp) mp += mstep;
-  }
-#pragma unroll
-  for (int it = 0; it < kIters; ++it) {
-    float4 v;
-    v.x = (keep[it] & 1) ? kLog2e * bv[it][0] : -INFINITY;
-    v.y = (keep[it] & 2) ? kLog2e * bv[it][1] : -INFINITY;
-    v.z = (keep[it] & 4) ? kLog2e * bv[it][2] : -INFINITY;
-    v.w = (keep[it] & 8) ? kLog2e * bv[it][3] : -INFINITY;
-    *reinterpret_cast<float4*>(Bt + (rl0 + 8 * it) * ld + c) = v;
-  }
-}
-__device__ __forceinline__ void stage_logit_tile(float* Bt, int ld, const Problem& pr, int bias_dtype, int b, int h,
-                                                 int row0, int kt, int tid) {
-  if (!pr.bias || bias_dtype == NB200_F32) stage_logit_tile_t<float>(Bt, ld, pr, b, h, row0, kt, tid);
-  else if (bias_dtype == NB200_BF16) stage_logit_tile_t<__nv_bfloat16>(Bt, ld, pr, b, h, row0, kt, tid);
-  else stage_logit_tile_t<__half>(Bt, ld, pr, b, h, row0, kt, tid);
-}
 // 2^x for x <= 0 (and -inf -> 0): one MUFU instruction, relative error 2^-22
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
@@ -470,14 +421,14 @@ __device__ __forceinline__ float ex2_fast(float x) {
 }
 
 // One 64-key tile of the 3 x TF32 forward for this warp's 16 query rows: scores, logits and masks, online softmax,
-// out += P V.  Ks / Vs: the tile in shared memory (rows past T zero-filled); Bt: its logit tile (stage_logit_tile),
-// complete once `sync()` returns.
-// Without a bias and a mask nothing is staged (Bt == nullptr): keeping a key is then three integer comparisons.
-template <int kDvBlocks, typename Sync>
-__device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, const float* Qs, const float* Ks, const float* Vs,
-                                                const float* Bt, int LDQ, int LDV, int D, int kt, int row0,
-                                                const int (&lr)[2], float s2scale, int g, int t,
-                                                float (&o)[kDvBlocks][4], float (&m)[2], float (&l)[2], Sync sync) {
+// out += P V.  Ks / Vs: the tile in shared memory (rows past T zero-filled); kt: its first key.  boff / moff: element
+// offsets of the bias / mask rows of this thread's two query rows.
+template <int kDvBlocks>
+__device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtype, const float* Qs, const float* Ks,
+                                                const float* Vs, int LDQ, int LDV, int D, int kt, int row0,
+                                                const int (&lr)[2], const int64_t (&boff)[2], const int64_t (&moff)[2],
+                                                float s2scale, int g, int t, float (&o)[kDvBlocks][4], float (&m)[2],
+                                                float (&l)[2]) {
   // ---- scores: 8 blocks of 8 keys ----
   float sc[8][4];
 #pragma unroll
@@ -499,26 +450,19 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, const float* 
     }
   }
   // ---- logits in base 2, masks, online softmax (rows g and g + 8 of the warp's 16) ----
+  // ---- logits in base 2, masks, online softmax (rows g and g + 8 of the warp's 16) ----
+  // The last key each row keeps in this tile (as an index into the tile) covers T, S and the causal diagonal.
+  // Bias and mask are read in the fragment layout -- this thread's keys are kt + 2 t + (8 nb + c) -- through
+  // pointers set up once per tile, with the dtype decided once per tile: a 64-bit index product, bounds tests and
+  // a dtype switch per element were two thirds of a tile's instructions.
   float mx[2] = {-INFINITY, -INFINITY};
-  if (Bt) {
-    sync();
+  int last[2];
 #pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const float2 bt = *reinterpret_cast<const float2*>(Bt + lr[i] * kLDB + 8 * nb + 2 * t);
-        sc[nb][2 * i] = fmaf(sc[nb][2 * i], s2scale, bt.x);
-        sc[nb][2 * i + 1] = fmaf(sc[nb][2 * i + 1], s2scale, bt.y);
-        mx[i] = fmaxf(mx[i], fmaxf(sc[nb][2 * i], sc[nb][2 * i + 1]));
-      }
-  } else {
-    // the last key each row keeps in this tile, as an index into the tile
-    int last[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int row = row0 + lr[i];
-      last[i] = row < pr.S ? (pr.causal ? min(pr.T - 1, row) : pr.T - 1) - kt : -1;
-    }
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + lr[i];
+    last[i] = row < pr.S ? (pr.causal ? min(pr.T - 1, row) : pr.T - 1) - kt : -1;
+  }
+  if (!pr.bias && !pr.mask) {
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
@@ -526,6 +470,33 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, const float* 
         sc[nb][e] = 8 * nb + 2 * t + (e & 1) <= last[e >> 1] ? sc[nb][e] * s2scale : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], sc[nb][e]);
       }
+  } else {
+    const int k0 = kt + 2 * t;
+    auto logits = [&](auto tag) {
+      using BT = decltype(tag);
+      const BT* bp[2];
+      const uint8_t* mp[2];
+      const int64_t bs3 = pr.bs[3], ms3 = pr.ms[3];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        bp[i] = pr.bias ? reinterpret_cast<const BT*>(pr.bias) + boff[i] + k0 * bs3 : nullptr;
+        mp[i] = pr.mask ? pr.mask + moff[i] + k0 * ms3 : nullptr;
+      }
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1, col = 8 * nb + (e & 1);      // key = k0 + col
+          bool keep = col + 2 * t <= last[i];
+          if (keep && mp[i]) keep = mp[i][col * ms3] != 0;
+          const float bias = (keep && bp[i]) ? kLog2e * to_f32<BT>(bp[i][col * bs3]) : 0.f;
+          sc[nb][e] = keep ? fmaf(sc[nb][e], s2scale, bias) : -INFINITY;
+          mx[i] = fmaxf(mx[i], sc[nb][e]);
+        }
+    };
+    if (bias_dtype == NB200_F32) logits(float{});
+    else if (bias_dtype == NB200_BF16) logits(__nv_bfloat16{});
+    else logits(__half{});
   }
   float alpha[2], m_ref[2], sum[2] = {0.f, 0.f};
 #pragma unroll
@@ -587,7 +558,6 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   float* Qs = smem;                  // [kBM][LDQ]
   float* Kbuf = Qs + kBM * LDQ;      // 2 x [kBN][LDQ]
   float* Vbuf = Kbuf + 2 * kBN * LDQ;  // 2 x [kBN][LDV]
-  float* Bt = (pr.bias || pr.mask) ? Vbuf + 2 * kBN * LDV : nullptr;   // [kBM][kLDB]  logit tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
@@ -599,6 +569,13 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
 
   // this thread's two rows: r[0] = 16 warp + g, r[1] = r[0] + 8
   const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = min(row0 + lr[i], pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+  }
   float o[kDvBlocks][4];
 #pragma unroll
   for (int nb = 0; nb < kDvBlocks; ++nb)
@@ -623,11 +600,7 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
       stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
       stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
     }
-    // (the top barrier also says that nobody reads the previous logit tile any more; the one before the softmax
-    // that this tile's is complete)
-    if (Bt) stage_logit_tile(Bt, kLDB, pr, bias_dtype, b, h, row0, kt, threadIdx.x);
-    fwd_tf32x3_tile<kDvBlocks>(pr, Qs, Ks, Vs, Bt, LDQ, LDV, D, kt, row0, lr, s2scale, g, t, o, m, l,
-                               [] { __syncthreads(); });
+    fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
   }
   // ---- out = o / l (NaN for a row with no kept key, as the reference's softmax gives), lse ----
 #pragma unroll
@@ -657,13 +630,11 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
   const int D = pr.D, Dv = pr.Dv;
   const int LDQ = D + 4, LDV = Dv + 4;
   float* Qs = smem;                          // [kBM][LDQ]
-  float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV] + [kBM][kLDB]); afterwards the partial results
+  float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV]); afterwards the partial results
   const int kg = threadIdx.x >> 7, tg = threadIdx.x & 127;
   const int warp = tg >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const bool logits = pr.bias || pr.mask;    // (the launcher sizes the stages the same way)
-  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV + (logits ? kBM * kLDB : 0));
+  float* Ks = KV + kg * (kBN * LDQ + kBN * LDV);
   float* Vs = Ks + kBN * LDQ;
-  float* Bt = logits ? Vs + kBN * LDV : nullptr;   // the group's logit tile
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
   const int row0 = blockIdx.x * kBM;
@@ -675,6 +646,13 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
   __syncthreads();
 
   const int lr[2] = {16 * warp + g, 16 * warp + g + 8};
+  int64_t boff[2], moff[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = min(row0 + lr[i], pr.S - 1);
+    boff[i] = pr.bias ? b * pr.bs[0] + h * pr.bs[1] + rr * pr.bs[2] : 0;
+    moff[i] = pr.mask ? b * pr.ms[0] + h * pr.ms[1] + rr * pr.ms[2] : 0;
+  }
   float o[kDvBlocks][4];
 #pragma unroll
   for (int nb = 0; nb < kDvBlocks; ++nb)
@@ -689,10 +667,9 @@ __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Pr
     group_sync();   // the group's previous tile is no longer read
     stage_rows_f4(Ks, LDQ, kp, pr.ks[2], kt, kBN, pr.T, D, tg, kTiledThreads);
     stage_rows_f4(Vs, LDV, vp, pr.vs[2], kt, kBN, pr.T, Dv, tg, kTiledThreads);
-    if (Bt) stage_logit_tile(Bt, kLDB, pr, bias_dtype, b, h, row0, kt, tg);
     stage_wait();
     group_sync();
-    fwd_tf32x3_tile<kDvBlocks>(pr, Qs, Ks, Vs, Bt, LDQ, LDV, D, kt, row0, lr, s2scale, g, t, o, m, l, [] {});
+    fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
   }
 
   // ---- merge the groups: partial [kG - 1][64 rows][Dv + 2] = (out, m, l), in the K / V stages ----
@@ -1524,8 +1501,7 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
 
 template <int kDvBlocks, int kG>
 int fwd_tf32x3_split_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
-  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) +
-                                       size_t(kG) * (kBN * (pr.D + 4 + pr.Dv + 4) + ((pr.bias || pr.mask) ? 64 * kLDB : 0)));
+  const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) + size_t(kG) * kBN * (pr.D + 4 + pr.Dv + 4));
   if (int rc = prepare(fwd_tf32x3_split_kernel<kDvBlocks, kG>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_split_kernel<kDvBlocks, kG><<<grid, kTiledThreads * kG, smem, st>>>(pr, bias_dtype);
@@ -1554,8 +1530,7 @@ int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       return fwd_tf32x3_split_t<kDvBlocks, 2>(pr, bias_dtype, st);
     }
   }
-  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4) +
-                                       ((pr.bias || pr.mask) ? 64 * kLDB : 0));
+  const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4));
   if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
   fwd_tf32x3_kernel<kDvBlocks><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);

@@ -174,6 +174,27 @@ def test_fp32_small_backward_splits_tiles_over_groups_and_clusters(name, s, t, d
     check(got, ref, torch.float32)
 
 
+@pytest.mark.parametrize("shape", [dict(b=2, h=4, s=512, d=64), dict(b=1, h=2, s=2048, d=128), dict(b=2, h=4, s=344, d=32)])
+def test_fp32_operand_split_keeps_the_fp32_budget_at_long_sequences(shape):
+    """The 3 x TF32 kernels split every operand as hi = top 19 bits, lo = x - hi (the tensor core reads lo's TF32
+    bits): out and all gradients against an fp64 restatement on the device, at lengths where thousands of products
+    accumulate -- max error over max |reference| inside the fp32 budget of 1e-4 (measured: 2e-6 .. 3.5e-5)."""
+    _, att = _nb()
+    b, h, s, d = shape["b"], shape["h"], shape["s"], shape["d"]
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q, k, v, dout = (torch.randn(b, h, s, d, device="cuda", generator=g) for _ in range(4))
+    scale = d ** -0.5
+    out, lse = att.sdpa_forward(q, k, v, None, None, scale=scale)
+    dq, dk, dv = att.sdpa_backward(q, k, v, None, None, out, lse, dout, scale=scale)[:3]
+    _device_ok()
+    qd, kd, vd = (x.double().requires_grad_() for x in (q, k, v))
+    ref = torch.softmax(qd @ kd.transpose(-1, -2) * scale, -1) @ vd
+    ref.backward(dout.double())
+    for name, a, r in (("out", out, ref.detach()), ("dq", dq, qd.grad), ("dk", dk, kd.grad), ("dv", dv, vd.grad)):
+        err = float((a.double() - r).abs().max() / r.abs().max())
+        assert err <= FP32_REL, (name, err)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", ["bias_mask", "causal", "key_padding"])
 def test_simt_low_precision_parity(name, dtype):
