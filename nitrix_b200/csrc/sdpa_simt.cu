@@ -435,6 +435,7 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtyp
   for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) sc[nb][e] = 0.f;
+#pragma unroll 2
   for (int kk = 0; kk < D; kk += 8) {
     uint32_t ah[4], al[4];
     split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
@@ -549,11 +550,13 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtyp
   }
 }
 
-template <int kDvBlocks>   // Dv / 8
+// kSquare (D == Dv): both row pitches are compile-time constants, so every fragment offset is an immediate.
+template <int kDvBlocks, bool kSquare>   // Dv / 8
 __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBM = 64;
-  const int D = pr.D, Dv = pr.Dv;
+  constexpr int Dv = 8 * kDvBlocks;
+  const int D = kSquare ? Dv : pr.D;
   const int LDQ = D + 4, LDV = Dv + 4;   // + 4: rows 16 bytes apart modulo 128, fragment loads hit distinct banks
   float* Qs = smem;                  // [kBM][LDQ]
   float* Kbuf = Qs + kBM * LDQ;      // 2 x [kBN][LDQ]
@@ -623,11 +626,12 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
 // groups' partial (m, l, out) are merged through shared memory by group 0.  The 3 x TF32 loop is bound by the
 // latency of its mma.sync chain, not by the tensor pipe (one warp per scheduler keeps it about a tenth busy), and a
 // problem of a hundred-odd CTAs cannot put more than four warps on an SM otherwise.
-template <int kDvBlocks, int kG>
+template <int kDvBlocks, int kG, bool kSquare>
 __global__ void __launch_bounds__(kTiledThreads * kG) fwd_tf32x3_split_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBM = 64;
-  const int D = pr.D, Dv = pr.Dv;
+  constexpr int Dv = 8 * kDvBlocks;
+  const int D = kSquare ? Dv : pr.D;
   const int LDQ = D + 4, LDV = Dv + 4;
   float* Qs = smem;                          // [kBM][LDQ]
   float* KV = Qs + kBM * LDQ;                // kG x ([kBN][LDQ] + [kBN][LDV]); afterwards the partial results
@@ -867,6 +871,7 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
   for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) sc[nb][e] = dp[nb][e] = 0.f;
+#pragma unroll 2
   for (int kk = 0; kk < D; kk += 8) {
     uint32_t ah[4], al[4];
     split_tf32(Qs[lr[0] * LDQ + kk + t], ah[0], al[0]);
@@ -881,6 +886,7 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
       mma_3xtf32(sc[nb], ah, al, bh2, bl2);
     }
   }
+#pragma unroll 2
   for (int kk = 0; kk < Dv; kk += 8) {
     uint32_t ah[4], al[4];
     split_tf32(Gs[lr[0] * LDV + kk + t], ah[0], al[0]);
@@ -981,11 +987,12 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
   }
 }
 
-template <int kDBlocks>   // D / 8
+template <int kDBlocks, bool kSquare>   // D / 8; kSquare: D == Dv, both row pitches compile-time constants
 __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBM = 64;
-  const int D = pr.D, Dv = pr.Dv;
+  constexpr int D = 8 * kDBlocks;
+  const int Dv = kSquare ? D : pr.Dv;
   const int LDQ = D + 4, LDV = Dv + 4;
   float* Qs = smem;                    // [kBM][LDQ]
   float* Gs = Qs + kBM * LDQ;          // [kBM][LDV]   dout rows
@@ -1062,11 +1069,12 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr
 // The dq backward for SMALL problems, as the forward's fwd_tf32x3_split_kernel: kG groups of four warps share a CTA's
 // 64 query rows and take the key tiles in turn; their partial dq tiles are summed through shared memory by group 0.
 // (Every dbias element is still written, or added, by exactly one group.)
-template <int kDBlocks, int kG>
+template <int kDBlocks, int kG, bool kSquare>
 __global__ void __launch_bounds__(kTiledThreads * kG) bwd_dq_tf32x3_split_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBM = 64;
-  const int D = pr.D, Dv = pr.Dv;
+  constexpr int D = 8 * kDBlocks;
+  const int Dv = kSquare ? D : pr.Dv;
   const int LDQ = D + 4, LDV = Dv + 4;
   float* Qs = smem;                    // [kBM][LDQ]
   float* Gs = Qs + kBM * LDQ;          // [kBM][LDV]   dout rows
@@ -1174,7 +1182,7 @@ template <int kBlocks, int kC = 1>   // D / 8 == Dv / 8
 __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBK = 64;
-  const int D = pr.D, LD = D + 4;
+  constexpr int D = 8 * kBlocks, LD = D + 4;   // compile-time row pitch: every fragment offset is an immediate
   float* Ks = smem;                    // [kBK][LD]  owner keys
   float* Vs = Ks + kBK * LD;           // [kBK][LD]
   float* Qbuf = Vs + kBK * LD;         // 2 x [kBN][LD]
@@ -1236,6 +1244,7 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dkv_tf32x3_kernel(Problem p
     for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
       for (int e = 0; e < 4; ++e) sc[nb][e] = dp[nb][e] = 0.f;
+#pragma unroll 2
     for (int kk = 0; kk < D; kk += 8) {
       uint32_t ah[4], al[4], ch[4], cl[4];
       split_tf32(Ks[lr[0] * LD + kk + t], ah[0], al[0]);
@@ -1499,17 +1508,17 @@ int fwd_tiled_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   return fwd_tiled_r<T, kVChunks, 4>(pr, bias_dtype, st);
 }
 
-template <int kDvBlocks, int kG>
+template <int kDvBlocks, int kG, bool kSquare>
 int fwd_tf32x3_split_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   const size_t smem = sizeof(float) * (size_t(64) * (pr.D + 4) + size_t(kG) * kBN * (pr.D + 4 + pr.Dv + 4));
-  if (int rc = prepare(fwd_tf32x3_split_kernel<kDvBlocks, kG>, smem)) return rc;
+  if (int rc = prepare(fwd_tf32x3_split_kernel<kDvBlocks, kG, kSquare>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
-  fwd_tf32x3_split_kernel<kDvBlocks, kG><<<grid, kTiledThreads * kG, smem, st>>>(pr, bias_dtype);
+  fwd_tf32x3_split_kernel<kDvBlocks, kG, kSquare><<<grid, kTiledThreads * kG, smem, st>>>(pr, bias_dtype);
   count_launch();
   return check_launch("fwd_tf32x3_kernel");
 }
 
-template <int kDvBlocks>
+template <int kDvBlocks, bool kSquare>
 int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   // A small problem (fewer 64-row CTAs than two per SM would hold) with several key tiles: groups of warps split the
   // keys inside each CTA (see fwd_tf32x3_split_kernel).  Needs 16-byte aligned fp32 rows for the asynchronous copies.
@@ -1525,15 +1534,15 @@ int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
     const bool aligned = rows16(pr.q, pr.qs) && rows16(pr.k, pr.ks) && rows16(pr.v, pr.vs);
     if constexpr (kDvBlocks <= 8)
     if (aligned && ctas <= 2 * int64_t(sms > 0 ? sms : 148) && tiles >= 2 && pr.D <= 64 && pr.Dv <= 64) {
-      if (tiles >= 4) return fwd_tf32x3_split_t<kDvBlocks, 4>(pr, bias_dtype, st);
-      if (tiles == 3) return fwd_tf32x3_split_t<kDvBlocks, 3>(pr, bias_dtype, st);
-      return fwd_tf32x3_split_t<kDvBlocks, 2>(pr, bias_dtype, st);
+      if (tiles >= 4) return fwd_tf32x3_split_t<kDvBlocks, 4, kSquare>(pr, bias_dtype, st);
+      if (tiles == 3) return fwd_tf32x3_split_t<kDvBlocks, 3, kSquare>(pr, bias_dtype, st);
+      return fwd_tf32x3_split_t<kDvBlocks, 2, kSquare>(pr, bias_dtype, st);
     }
   }
   const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4));
-  if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks>, smem)) return rc;
+  if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks, kSquare>, smem)) return rc;
   dim3 grid((pr.S + 63) / 64, pr.bh_count);
-  fwd_tf32x3_kernel<kDvBlocks><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
+  fwd_tf32x3_kernel<kDvBlocks, kSquare><<<grid, kTiledThreads, smem, st>>>(pr, bias_dtype);
   count_launch();
   return check_launch("fwd_tf32x3_kernel");
 }
@@ -1544,9 +1553,9 @@ int fwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
     // fp32 operands with head dims in whole 8-column MMA blocks: 3 x TF32 on the warp-level tensor-core path
     if (pr.D % 8 == 0 && pr.D <= 128 && pr.Dv % 8 == 0 && pr.Dv <= 128) {
       switch (pr.Dv / 8) {
-        case 4: return fwd_tf32x3_t<4>(pr, bias_dtype, st);
-        case 8: return fwd_tf32x3_t<8>(pr, bias_dtype, st);
-        case 16: return fwd_tf32x3_t<16>(pr, bias_dtype, st);
+        case 4: return pr.D == 32 ? fwd_tf32x3_t<4, true>(pr, bias_dtype, st) : fwd_tf32x3_t<4, false>(pr, bias_dtype, st);
+        case 8: return pr.D == 64 ? fwd_tf32x3_t<8, true>(pr, bias_dtype, st) : fwd_tf32x3_t<8, false>(pr, bias_dtype, st);
+        case 16: return pr.D == 128 ? fwd_tf32x3_t<16, true>(pr, bias_dtype, st) : fwd_tf32x3_t<16, false>(pr, bias_dtype, st);
         default: break;
       }
     }
@@ -1648,10 +1657,13 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       auto go = [&](auto kernel) {
         if ((rc = prepare(kernel, sm)) == NB200_OK) kernel<<<gq, kTiledThreads * kg, sm, st>>>(pr, bias_dtype);
       };
+      const bool sq = pr.D == pr.Dv;
       if (pr.D == 32) {
-        if (kg == 3) go(bwd_dq_tf32x3_split_kernel<4, 3>); else go(bwd_dq_tf32x3_split_kernel<4, 2>);
+        if (kg == 3) { if (sq) go(bwd_dq_tf32x3_split_kernel<4, 3, true>); else go(bwd_dq_tf32x3_split_kernel<4, 3, false>); }
+        else { if (sq) go(bwd_dq_tf32x3_split_kernel<4, 2, true>); else go(bwd_dq_tf32x3_split_kernel<4, 2, false>); }
       } else {
-        if (kg == 3) go(bwd_dq_tf32x3_split_kernel<8, 3>); else go(bwd_dq_tf32x3_split_kernel<8, 2>);
+        if (kg == 3) { if (sq) go(bwd_dq_tf32x3_split_kernel<8, 3, true>); else go(bwd_dq_tf32x3_split_kernel<8, 3, false>); }
+        else { if (sq) go(bwd_dq_tf32x3_split_kernel<8, 2, true>); else go(bwd_dq_tf32x3_split_kernel<8, 2, false>); }
       }
       if (rc) return join(rc);
       count_launch();
@@ -1668,13 +1680,13 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       const size_t sm = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(64 + 2 * kBN) * (pr.Dv + 4));
       dim3 gq((pr.S + 63) / 64, pr.bh_count);
       int rc = NB200_OK;
-      if (pr.D == 32) {
-        if ((rc = prepare(bwd_dq_tf32x3_kernel<4>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<4><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
-      } else if (pr.D == 64) {
-        if ((rc = prepare(bwd_dq_tf32x3_kernel<8>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<8><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
-      } else {
-        if ((rc = prepare(bwd_dq_tf32x3_kernel<16>, sm)) == NB200_OK) bwd_dq_tf32x3_kernel<16><<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
-      }
+      auto go = [&](auto kernel) {
+        if ((rc = prepare(kernel, sm)) == NB200_OK) kernel<<<gq, kTiledThreads, sm, st>>>(pr, bias_dtype);
+      };
+      const bool sq = pr.D == pr.Dv;
+      if (pr.D == 32) { if (sq) go(bwd_dq_tf32x3_kernel<4, true>); else go(bwd_dq_tf32x3_kernel<4, false>); }
+      else if (pr.D == 64) { if (sq) go(bwd_dq_tf32x3_kernel<8, true>); else go(bwd_dq_tf32x3_kernel<8, false>); }
+      else { if (sq) go(bwd_dq_tf32x3_kernel<16, true>); else go(bwd_dq_tf32x3_kernel<16, false>); }
       if (rc) return join(rc);
       count_launch();
       if (int rc2 = check_launch("bwd_dq_tf32x3_kernel")) return join(rc2);
