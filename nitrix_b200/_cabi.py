@@ -64,6 +64,16 @@ class QkNormTensor(C.Structure):
                 ("B", C.c_int32), ("H", C.c_int32), ("N", C.c_int32), ("reserved", C.c_int32)]
 
 
+class LayerNormParams(C.Structure):
+    """``nb200_layer_norm_params`` (include/nitrix_b200_norm.h)."""
+
+    _fields_ = [("struct_size", C.c_size_t), ("x", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p),
+                ("y", C.c_void_p), ("mean", C.c_void_p), ("rstd", C.c_void_p), ("dy", C.c_void_p), ("dx", C.c_void_p),
+                ("dweight", C.c_void_p), ("dbias", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_size_t), ("rows", C.c_int64), ("channels", C.c_int32), ("dtype", C.c_int32),
+                ("eps", C.c_float), ("out_scale", C.c_float)]
+
+
 EXPORTS = (
     "nb200_version",
     "nb200_last_error",
@@ -84,6 +94,9 @@ EXPORTS = (
     "nb200_ipc_close",
     "nb200_qk_rms_norm",
     "nb200_qk_rms_norm_grad",
+    "nb200_layer_norm_fwd",
+    "nb200_layer_norm_bwd",
+    "nb200_layer_norm_workspace_bytes",
 )
 
 
@@ -123,6 +136,9 @@ def lib() -> C.CDLL:
     L.nb200_ipc_close.argtypes = [C.c_void_p]
     L.nb200_qk_rms_norm.argtypes = [C.POINTER(QkNormTensor), C.POINTER(QkNormTensor), C.c_int, C.c_int, C.c_void_p]
     L.nb200_qk_rms_norm_grad.argtypes = [C.POINTER(QkNormTensor), C.POINTER(QkNormTensor), C.c_int, C.c_int, C.c_void_p]
+    L.nb200_layer_norm_fwd.argtypes = [C.POINTER(LayerNormParams), C.c_void_p]
+    L.nb200_layer_norm_bwd.argtypes = [C.POINTER(LayerNormParams), C.c_void_p]
+    L.nb200_layer_norm_workspace_bytes.argtypes = [C.POINTER(LayerNormParams), C.POINTER(C.c_size_t)]
     if L.nb200_version() != ABI_VERSION:
         raise NativeLibraryError(f"{path}: ABI {L.nb200_version()} != expected {ABI_VERSION}")
     return L

@@ -1,0 +1,531 @@
+// LayerNorm over the trailing axis, forward and backward -- the sibling op of the attention path behind the same
+// library (reference src/nitrix/nn/norm/__init__.py:110-176 is the dispatcher, src/nitrix/nn/norm/_reference.py:44-110
+// the recipe: biased variance, rsqrt(var + eps), optional per-channel affine, then the constant `out_scale`; a 16-bit
+// input is upcast to fp32 for the reductions and the affine transform and the result cast back).
+//
+//   forward   xhat = (x - mean) rstd,  y = out_scale (xhat w + b);  mean and rstd (fp32 per row) are kept for the
+//             backward when the caller passes buffers for them
+//   backward  gy = out_scale dy,  dxhat = gy w,  dx = rstd (dxhat - mean(dxhat) - xhat mean(dxhat xhat)),
+//             dw = sum_rows gy xhat,  db = sum_rows gy
+//
+// Rows that are a multiple of 16 bytes (<= 8192 channels, aligned pointers) take the vector kernels below; the rest
+// the scalar ones at the end.  The op is bound by HBM traffic (x once in, y once out; the backward x and dy in, dx
+// out), so a row is read ONCE with 16-byte loads and held in registers between the reductions and the write: by one
+// warp (rows of up to 32 x 16 B x 8) or by one 256-thread CTA (longer rows).  The variance is taken about the mean (two passes over the registers, as
+// the reference's `var` does), not as E[x^2] - mean^2.  dw / db: every CTA walks rows in a grid-stride loop, keeps
+// its column sums in registers, leaves one partial row per CTA in a workspace, and a second kernel adds the partials
+// in CTA order -- deterministic, no atomics.
+#include <math.h>
+
+#include "nitrix_b200_norm.h"
+#include "sdpa_common.cuh"
+
+namespace nb200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct LnArgs {
+  const void* x;
+  const void* w;
+  const void* b;
+  void* y;
+  float* mean;
+  float* rstd;
+  const void* dy;
+  void* dx;
+  float* part;   // [2][grid][C] partial dw, db
+  int64_t rows;
+  int C;
+  float eps, out_scale;
+};
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// sum over the threads that share a row: the warp, or the whole CTA through shared memory (red: 8 floats + result)
+template <bool kCta>
+__device__ __forceinline__ float row_sum(float v, float* red) {
+  v = warp_sum_f(v);
+  if constexpr (kCta) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();   // the previous reduction's result has been read
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    v = 0.f;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) v += red[i];
+  }
+  return v;
+}
+
+template <typename T, int kVec>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[kVec]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) out[i] = to_f32<T>(e[i]);
+}
+template <typename T, int kVec>
+__device__ __forceinline__ void store_vec(T* p, const float (&v)[kVec]) {
+  uint4 w;
+  T* e = reinterpret_cast<T*>(&w);
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) e[i] = from_f32<T>(v[i]);
+  *reinterpret_cast<uint4*>(p) = w;
+}
+
+// A row is split over kCta ? 256 : 32 threads; a thread holds kPer chunks of kVec = 16 / sizeof(T) elements, chunk p
+// at column (p * threads + thread) * kVec.
+template <typename T, int kPer, bool kCta>
+__global__ void __launch_bounds__(kThreads) ln_fwd_kernel(LnArgs a) {
+  constexpr int kVec = 16 / int(sizeof(T));
+  constexpr int kTpr = kCta ? kThreads : 32;
+  __shared__ float red[kThreads / 32];
+  const int tin = kCta ? threadIdx.x : (threadIdx.x & 31);
+  const int64_t row = kCta ? int64_t(blockIdx.x) : int64_t(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+  if (row >= a.rows) return;   // (a whole CTA, or a whole warp of a warp-per-row CTA, which never meets a barrier)
+  const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
+  float xv[kPer][kVec];
+  float s = 0.f;
+#pragma unroll
+  for (int p = 0; p < kPer; ++p) {
+    const int c0 = (p * kTpr + tin) * kVec;
+    if (c0 < a.C) {
+      load_vec<T, kVec>(x + c0, xv[p]);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) s += xv[p][i];
+    }
+  }
+  const float mean = row_sum<kCta>(s, red) / float(a.C);
+  float q = 0.f;
+#pragma unroll
+  for (int p = 0; p < kPer; ++p)
+    if ((p * kTpr + tin) * kVec < a.C) {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const float d = xv[p][i] - mean;
+        q = fmaf(d, d, q);
+      }
+    }
+  const float rstd = rsqrtf(row_sum<kCta>(q, red) / float(a.C) + a.eps);
+  if (tin == 0) {
+    if (a.mean) a.mean[row] = mean;
+    if (a.rstd) a.rstd[row] = rstd;
+  }
+  T* y = reinterpret_cast<T*>(a.y) + row * a.C;
+  const T* w = reinterpret_cast<const T*>(a.w);
+  const T* b = reinterpret_cast<const T*>(a.b);
+#pragma unroll
+  for (int p = 0; p < kPer; ++p) {
+    const int c0 = (p * kTpr + tin) * kVec;
+    if (c0 < a.C) {
+      float wv[kVec], bv[kVec], out[kVec];
+      if (w) load_vec<T, kVec>(w + c0, wv);
+      if (b) load_vec<T, kVec>(b + c0, bv);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        float v = (xv[p][i] - mean) * rstd;
+        if (w) v *= wv[i];
+        if (b) v += bv[i];
+        out[i] = a.out_scale * v;
+      }
+      store_vec<T, kVec>(y + c0, out);
+    }
+  }
+}
+
+// Backward.  Grid-stride over rows (a warp's or a CTA's); column sums of dw, db stay in registers until the end.
+template <typename T, int kPer, bool kCta>
+__global__ void __launch_bounds__(kThreads) ln_bwd_kernel(LnArgs a) {
+  constexpr int kVec = 16 / int(sizeof(T));
+  constexpr int kTpr = kCta ? kThreads : 32;
+  constexpr int kRowsPerCta = kCta ? 1 : kThreads / 32;
+  extern __shared__ float wsum[];   // warp-per-row: [8][C] x 2 for the CTA's column sums
+  __shared__ float red[kThreads / 32];
+  const int tin = kCta ? threadIdx.x : (threadIdx.x & 31);
+  const int sub = kCta ? 0 : (threadIdx.x >> 5);
+  const T* w = reinterpret_cast<const T*>(a.w);
+  float wv[kPer][kVec], dw[kPer][kVec], db[kPer][kVec];
+#pragma unroll
+  for (int p = 0; p < kPer; ++p) {
+    const int c0 = (p * kTpr + tin) * kVec;
+    if (w && c0 < a.C) {
+      load_vec<T, kVec>(w + c0, wv[p]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) wv[p][i] = 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) dw[p][i] = db[p][i] = 0.f;
+  }
+  // (in a CTA-per-row kernel every thread of the CTA runs the same number of iterations: the barriers in row_sum match)
+  for (int64_t row = int64_t(blockIdx.x) * kRowsPerCta + sub; row < a.rows; row += int64_t(gridDim.x) * kRowsPerCta) {
+    const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
+    const T* g = reinterpret_cast<const T*>(a.dy) + row * a.C;
+    const float mean = a.mean[row], rstd = a.rstd[row];
+    float xh[kPer][kVec], dxh[kPer][kVec];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int p = 0; p < kPer; ++p) {
+      const int c0 = (p * kTpr + tin) * kVec;
+      if (c0 < a.C) {
+        float gv[kVec];
+        load_vec<T, kVec>(x + c0, xh[p]);
+        load_vec<T, kVec>(g + c0, gv);
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+          xh[p][i] = (xh[p][i] - mean) * rstd;
+          const float gy = a.out_scale * gv[i];
+          dw[p][i] = fmaf(gy, xh[p][i], dw[p][i]);
+          db[p][i] += gy;
+          dxh[p][i] = gy * wv[p][i];
+          s1 += dxh[p][i];
+          s2 = fmaf(dxh[p][i], xh[p][i], s2);
+        }
+      }
+    }
+    const float c1 = row_sum<kCta>(s1, red) / float(a.C);
+    const float c2 = row_sum<kCta>(s2, red) / float(a.C);
+    T* dx = reinterpret_cast<T*>(a.dx) + row * a.C;
+#pragma unroll
+    for (int p = 0; p < kPer; ++p) {
+      const int c0 = (p * kTpr + tin) * kVec;
+      if (c0 < a.C) {
+        float out[kVec];
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) out[i] = rstd * (dxh[p][i] - c1 - xh[p][i] * c2);
+        store_vec<T, kVec>(dx + c0, out);
+      }
+    }
+  }
+  if (!a.part) return;
+  float* pw = a.part + int64_t(blockIdx.x) * a.C;
+  float* pb = a.part + (int64_t(gridDim.x) + blockIdx.x) * a.C;
+  if constexpr (kCta) {
+#pragma unroll
+    for (int p = 0; p < kPer; ++p) {
+      const int c0 = (p * kTpr + tin) * kVec;
+      if (c0 < a.C) {
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+          pw[c0 + i] = dw[p][i];
+          pb[c0 + i] = db[p][i];
+        }
+      }
+    }
+  } else {
+    // the CTA's eight warps hold sums of the same columns: add them in warp order through shared memory
+    float* sw = wsum + sub * a.C;
+    float* sb = wsum + (kRowsPerCta + sub) * a.C;
+#pragma unroll
+    for (int p = 0; p < kPer; ++p) {
+      const int c0 = (p * kTpr + tin) * kVec;
+      if (c0 < a.C) {
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+          sw[c0 + i] = dw[p][i];
+          sb[c0 + i] = db[p][i];
+        }
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < a.C; c += kThreads) {
+      float tw = 0.f, tb = 0.f;
+#pragma unroll
+      for (int k = 0; k < kRowsPerCta; ++k) {
+        tw += wsum[k * a.C + c];
+        tb += wsum[(kRowsPerCta + k) * a.C + c];
+      }
+      pw[c] = tw;
+      pb[c] = tb;
+    }
+  }
+}
+
+// dw[c] = sum over the CTAs' partial rows, in CTA order; one thread per column
+template <typename T>
+__global__ void __launch_bounds__(kThreads) ln_bwd_finish_kernel(const float* part, int grid, int C, T* dw, T* db) {
+  const int c = blockIdx.x * kThreads + threadIdx.x;
+  if (c >= C) return;
+  float tw = 0.f, tb = 0.f;
+  for (int k = 0; k < grid; ++k) {
+    tw += part[int64_t(k) * C + c];
+    tb += part[(int64_t(grid) + k) * C + c];
+  }
+  if (dw) dw[c] = from_f32<T>(tw);
+  if (db) db[c] = from_f32<T>(tb);
+}
+
+// Any other row (channels not a multiple of 16 bytes, longer than 8192, unaligned pointers): one CTA per row in
+// scalar strided passes; the row is re-read from L1 / L2.  dw / db are added to a zeroed [2][C] fp32 workspace with
+// atomics (the one place where the order of a sum is not fixed).
+template <typename T>
+__global__ void __launch_bounds__(kThreads) ln_fwd_generic_kernel(LnArgs a) {
+  __shared__ float red[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < a.C; c += kThreads) s += to_f32<T>(x[c]);
+  const float mean = row_sum<true>(s, red) / float(a.C);
+  float q = 0.f;
+  for (int c = threadIdx.x; c < a.C; c += kThreads) {
+    const float d = to_f32<T>(x[c]) - mean;
+    q = fmaf(d, d, q);
+  }
+  const float rstd = rsqrtf(row_sum<true>(q, red) / float(a.C) + a.eps);
+  if (threadIdx.x == 0) {
+    if (a.mean) a.mean[row] = mean;
+    if (a.rstd) a.rstd[row] = rstd;
+  }
+  T* y = reinterpret_cast<T*>(a.y) + row * a.C;
+  const T* w = reinterpret_cast<const T*>(a.w);
+  const T* b = reinterpret_cast<const T*>(a.b);
+  for (int c = threadIdx.x; c < a.C; c += kThreads) {
+    float v = (to_f32<T>(x[c]) - mean) * rstd;
+    if (w) v *= to_f32<T>(w[c]);
+    if (b) v += to_f32<T>(b[c]);
+    y[c] = from_f32<T>(a.out_scale * v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) ln_bwd_generic_kernel(LnArgs a) {
+  __shared__ float red[kThreads / 32];
+  const T* w = reinterpret_cast<const T*>(a.w);
+  for (int64_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
+    const T* g = reinterpret_cast<const T*>(a.dy) + row * a.C;
+    const float mean = a.mean[row], rstd = a.rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = threadIdx.x; c < a.C; c += kThreads) {
+      const float xh = (to_f32<T>(x[c]) - mean) * rstd;
+      const float dxh = a.out_scale * to_f32<T>(g[c]) * (w ? to_f32<T>(w[c]) : 1.f);
+      s1 += dxh;
+      s2 = fmaf(dxh, xh, s2);
+    }
+    const float c1 = row_sum<true>(s1, red) / float(a.C);
+    const float c2 = row_sum<true>(s2, red) / float(a.C);
+    T* dx = reinterpret_cast<T*>(a.dx) + row * a.C;
+    for (int c = threadIdx.x; c < a.C; c += kThreads) {
+      const float xh = (to_f32<T>(x[c]) - mean) * rstd;
+      const float gy = a.out_scale * to_f32<T>(g[c]);
+      const float dxh = gy * (w ? to_f32<T>(w[c]) : 1.f);
+      dx[c] = from_f32<T>(rstd * (dxh - c1 - xh * c2));
+      if (a.part) {
+        atomicAdd(a.part + c, gy * xh);
+        atomicAdd(a.part + a.C + c, gy);
+      }
+    }
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+struct Shape {
+  int vec, per;
+  bool cta;
+};
+
+// the smallest per-thread chunk count that covers a row; the backward keeps twice the registers per chunk
+bool pick(int C, int dtype, bool backward, Shape* s) {
+  s->vec = dtype == NB200_F32 ? 4 : 8;
+  if (C <= 0 || C % s->vec) return false;
+  const int max_per = backward ? (dtype == NB200_F32 ? 8 : 4) : 8;
+  const int warp_max = backward ? 4 : 8;
+  for (int per = 1; per <= warp_max; per *= 2)
+    if (C <= 32 * s->vec * per) { s->per = per; s->cta = false; return true; }
+  for (int per = 1; per <= max_per; per *= 2)
+    if (C <= kThreads * s->vec * per) { s->per = per; s->cta = true; return true; }
+  return false;
+}
+
+int bwd_grid(int64_t rows, const Shape& s) {
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const int64_t units = s.cta ? rows : (rows + kThreads / 32 - 1) / (kThreads / 32);
+  const int64_t cap = int64_t(sms) * (s.cta ? 4 : 2);
+  return int(units < cap ? (units > 0 ? units : 1) : cap);
+}
+
+int check_common(const nb200_layer_norm_params* p, const char* what) {
+  if (!p) { set_error("%s: NULL parameter block", what); return NB200_ERR_INVALID; }
+  if (p->struct_size != sizeof(nb200_layer_norm_params)) {
+    set_error("%s: ABI mismatch: struct_size %zu, library expects %zu", what, size_t(p->struct_size),
+              sizeof(nb200_layer_norm_params));
+    return NB200_ERR_INVALID;
+  }
+  if (p->dtype != NB200_F32 && p->dtype != NB200_BF16 && p->dtype != NB200_F16) { set_error("%s: bad dtype", what); return NB200_ERR_INVALID; }
+  if (p->rows < 0 || p->channels <= 0) { set_error("%s: bad extents", what); return NB200_ERR_INVALID; }
+  return NB200_OK;
+}
+
+template <typename T, bool kBwd, typename F>
+int dispatch(const Shape& s, F&& go) {
+  // go(kernel) launches; one instantiation per (chunks, warp / CTA)
+  if (!s.cta) {
+    switch (s.per) {
+      case 1: return go(kBwd ? ln_bwd_kernel<T, 1, false> : ln_fwd_kernel<T, 1, false>);
+      case 2: return go(kBwd ? ln_bwd_kernel<T, 2, false> : ln_fwd_kernel<T, 2, false>);
+      case 4: return go(kBwd ? ln_bwd_kernel<T, 4, false> : ln_fwd_kernel<T, 4, false>);
+      default: return go(kBwd ? ln_bwd_kernel<T, 4, false> : ln_fwd_kernel<T, 8, false>);
+    }
+  }
+  switch (s.per) {
+    case 1: return go(kBwd ? ln_bwd_kernel<T, 1, true> : ln_fwd_kernel<T, 1, true>);
+    case 2: return go(kBwd ? ln_bwd_kernel<T, 2, true> : ln_fwd_kernel<T, 2, true>);
+    case 4: return go(kBwd ? ln_bwd_kernel<T, 4, true> : ln_fwd_kernel<T, 4, true>);
+    default: return go(kBwd ? ln_bwd_kernel<T, sizeof(T) == 4 ? 8 : 4, true> : ln_fwd_kernel<T, 8, true>);
+  }
+}
+
+template <typename T>
+int fwd_t(const nb200_layer_norm_params* p, const Shape& s, cudaStream_t st) {
+  LnArgs a{};
+  a.x = p->x; a.w = p->weight; a.b = p->bias; a.y = p->y; a.mean = p->mean; a.rstd = p->rstd;
+  a.rows = p->rows; a.C = p->channels; a.eps = p->eps; a.out_scale = p->out_scale;
+  const int64_t blocks = s.cta ? p->rows : (p->rows + kThreads / 32 - 1) / (kThreads / 32);
+  if (blocks > 0x7fffffff) { set_error("layer_norm: too many rows"); return NB200_ERR_UNSUPPORTED; }
+  return dispatch<T, false>(s, [&](auto kernel) {
+    kernel<<<unsigned(blocks), kThreads, 0, st>>>(a);
+    count_launch();
+    return check_launch("layer_norm_fwd_kernel");
+  });
+}
+
+template <typename T>
+int bwd_t(const nb200_layer_norm_params* p, const Shape& s, cudaStream_t st) {
+  LnArgs a{};
+  a.x = p->x; a.w = p->weight; a.dy = p->dy; a.dx = p->dx; a.mean = p->mean; a.rstd = p->rstd;
+  a.rows = p->rows; a.C = p->channels; a.eps = p->eps; a.out_scale = p->out_scale;
+  const bool want_params = p->dweight || p->dbias;
+  const int grid = bwd_grid(p->rows, s);
+  if (want_params) {
+    const size_t need = sizeof(float) * 2 * size_t(grid) * size_t(p->channels);
+    if (!p->workspace || p->workspace_bytes < need) {
+      set_error("layer_norm_bwd: workspace of %zu bytes needed (nb200_layer_norm_workspace_bytes), %zu given", need,
+                size_t(p->workspace_bytes));
+      return NB200_ERR_INVALID;
+    }
+    a.part = static_cast<float*>(p->workspace);
+  }
+  const size_t smem = s.cta ? 0 : sizeof(float) * 2 * (kThreads / 32) * size_t(p->channels);
+  int rc = dispatch<T, true>(s, [&](auto kernel) {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+      set_error("layer_norm_bwd: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(cudaGetLastError()));
+      return int(NB200_ERR_LAUNCH);
+    }
+    kernel<<<unsigned(grid), kThreads, smem, st>>>(a);
+    count_launch();
+    return check_launch("layer_norm_bwd_kernel");
+  });
+  if (rc || !want_params) return rc;
+  ln_bwd_finish_kernel<T><<<(p->channels + kThreads - 1) / kThreads, kThreads, 0, st>>>(
+      a.part, grid, p->channels, static_cast<T*>(p->dweight), static_cast<T*>(p->dbias));
+  count_launch();
+  return check_launch("layer_norm_bwd_finish_kernel");
+}
+
+template <typename T>
+int fwd_generic_t(const nb200_layer_norm_params* p, cudaStream_t st) {
+  LnArgs a{};
+  a.x = p->x; a.w = p->weight; a.b = p->bias; a.y = p->y; a.mean = p->mean; a.rstd = p->rstd;
+  a.rows = p->rows; a.C = p->channels; a.eps = p->eps; a.out_scale = p->out_scale;
+  if (p->rows > 0x7fffffff) { set_error("layer_norm: too many rows"); return NB200_ERR_UNSUPPORTED; }
+  ln_fwd_generic_kernel<T><<<unsigned(p->rows), kThreads, 0, st>>>(a);
+  count_launch();
+  return check_launch("layer_norm_fwd_generic_kernel");
+}
+
+template <typename T>
+int bwd_generic_t(const nb200_layer_norm_params* p, cudaStream_t st) {
+  LnArgs a{};
+  a.x = p->x; a.w = p->weight; a.dy = p->dy; a.dx = p->dx; a.mean = p->mean; a.rstd = p->rstd;
+  a.rows = p->rows; a.C = p->channels; a.eps = p->eps; a.out_scale = p->out_scale;
+  const bool want_params = p->dweight || p->dbias;
+  if (want_params) {
+    const size_t need = sizeof(float) * 2 * size_t(p->channels);
+    if (!p->workspace || p->workspace_bytes < need) {
+      set_error("layer_norm_bwd: workspace of %zu bytes needed (nb200_layer_norm_workspace_bytes), %zu given", need,
+                size_t(p->workspace_bytes));
+      return NB200_ERR_INVALID;
+    }
+    a.part = static_cast<float*>(p->workspace);
+    if (cudaMemsetAsync(a.part, 0, need, st) != cudaSuccess) return check_launch("layer_norm_bwd: clearing the workspace");
+  }
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t cap = int64_t(sms > 0 ? sms : 148) * 8;
+  const int grid = int(p->rows < cap ? (p->rows > 0 ? p->rows : 1) : cap);
+  ln_bwd_generic_kernel<T><<<unsigned(grid), kThreads, 0, st>>>(a);
+  count_launch();
+  if (int rc = check_launch("layer_norm_bwd_generic_kernel")) return rc;
+  if (!want_params) return NB200_OK;
+  ln_bwd_finish_kernel<T><<<(p->channels + kThreads - 1) / kThreads, kThreads, 0, st>>>(
+      a.part, 1, p->channels, static_cast<T*>(p->dweight), static_cast<T*>(p->dbias));
+  count_launch();
+  return check_launch("layer_norm_bwd_finish_kernel");
+}
+
+// the vector kernels need 16-byte rows: channels a multiple of 16 bytes (<= 8192) and aligned pointers
+bool vector_path(const nb200_layer_norm_params* p, bool backward, Shape* s) {
+  Shape b;
+  if (!pick(p->channels, p->dtype, true, &b)) return false;       // (one limit for both directions)
+  if (!pick(p->channels, p->dtype, backward, s)) return false;
+  if (!aligned16(p->x) || (p->weight && !aligned16(p->weight))) return false;
+  if (backward) return aligned16(p->dy) && aligned16(p->dx);
+  return aligned16(p->y) && (!p->bias || aligned16(p->bias));
+}
+
+}  // namespace
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" NB200_API int nb200_layer_norm_workspace_bytes(const nb200_layer_norm_params* p, size_t* bytes) {
+  if (!bytes) { set_error("bytes out-pointer is NULL"); return NB200_ERR_INVALID; }
+  if (int rc = check_common(p, "layer_norm_workspace_bytes")) return rc;
+  // (sized for the vector kernels' per-CTA partial rows, which is never less than the scalar kernels' [2][C])
+  Shape s;
+  const int grid = pick(p->channels, p->dtype, true, &s) ? bwd_grid(p->rows, s) : 1;
+  *bytes = sizeof(float) * 2 * size_t(grid) * size_t(p->channels);
+  return NB200_OK;
+}
+
+extern "C" NB200_API int nb200_layer_norm_fwd(const nb200_layer_norm_params* p, void* cuda_stream) {
+  if (int rc = check_common(p, "layer_norm_fwd")) return rc;
+  if (p->rows == 0) return NB200_OK;
+  if (!p->x || !p->y) { set_error("layer_norm_fwd: NULL x or y"); return NB200_ERR_INVALID; }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  Shape s;
+  const bool vec = vector_path(p, false, &s);
+  switch (p->dtype) {
+    case NB200_F32: return vec ? fwd_t<float>(p, s, st) : fwd_generic_t<float>(p, st);
+    case NB200_BF16: return vec ? fwd_t<__nv_bfloat16>(p, s, st) : fwd_generic_t<__nv_bfloat16>(p, st);
+    default: return vec ? fwd_t<__half>(p, s, st) : fwd_generic_t<__half>(p, st);
+  }
+}
+
+extern "C" NB200_API int nb200_layer_norm_bwd(const nb200_layer_norm_params* p, void* cuda_stream) {
+  if (int rc = check_common(p, "layer_norm_bwd")) return rc;
+  if (p->rows == 0 && !p->dweight && !p->dbias) return NB200_OK;
+  if ((p->rows > 0 && (!p->x || !p->dy || !p->dx || !p->mean || !p->rstd))) {
+    set_error("layer_norm_bwd: x, dy, dx, mean and rstd are required");
+    return NB200_ERR_INVALID;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  Shape s;
+  const bool vec = vector_path(p, true, &s);
+  switch (p->dtype) {
+    case NB200_F32: return vec ? bwd_t<float>(p, s, st) : bwd_generic_t<float>(p, st);
+    case NB200_BF16: return vec ? bwd_t<__nv_bfloat16>(p, s, st) : bwd_generic_t<__nv_bfloat16>(p, st);
+    default: return vec ? bwd_t<__half>(p, s, st) : bwd_generic_t<__half>(p, st);
+  }
+}

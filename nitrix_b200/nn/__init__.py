@@ -1,4 +1,5 @@
-"""``nitrix.nn``-shaped namespace: only the attention entry point is provided."""
+"""``nitrix.nn``-shaped namespace: the attention entry point and its sibling, the fused LayerNorm."""
 from .attention import default_scale, qk_rms_norm, scaled_dot_product_attention
+from .norm import layer_norm
 
-__all__ = ["scaled_dot_product_attention", "default_scale", "qk_rms_norm"]
+__all__ = ["scaled_dot_product_attention", "default_scale", "qk_rms_norm", "layer_norm"]

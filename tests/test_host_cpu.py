@@ -16,7 +16,7 @@ ROOT = pathlib.Path(__file__).resolve().parent.parent
 def test_library_exports_every_declared_symbol():
     from nitrix_b200 import _cabi
 
-    header = (ROOT / "include" / "nitrix_b200_attention.h").read_text()
+    header = "".join(f.read_text() for f in sorted((ROOT / "include").glob("*.h")))
     declared = set(re.findall(r"NB200_API\s+[\w\s\*]+?\b(nb200_\w+)\s*\(", header))
     assert declared, "no NB200_API declarations parsed"
     assert declared == set(_cabi.EXPORTS)
