@@ -27,7 +27,9 @@ Rank 0 prints ONE JSON line:
 * ``partition`` (N > 1): the split the configurations name -- c5 with 16 / N heads per GPU, c4 with 32 / N sequences
   per GPU (strong scaling through ``bh_begin / bh_end``-style slices), with the optional output all-gather timed
   both as an NCCL collective after the kernels and fused into the forward kernel's epilogue;
-* ``cpu_baseline``: the CPU oracle (torch, all host threads) on a fixed, bounded sample.
+* ``cpu_baseline``: the CPU oracle (torch, all host threads) on a fixed, bounded sample;
+* ``layer_norm`` (1 GPU): the sibling op on the shapes the reference's own norm benchmark uses -- time per forward
+  and per backward call, and the algorithmic bytes each moves per second against the measured copy bandwidth.
 
 ``--impl reference`` times only that CPU implementation (the reference's own ``jnp`` path cannot run: jax is not
 installed; the op-for-op torch restatement stands in, ``cpu_baseline.kind = "port"``).
@@ -634,6 +636,15 @@ def main():
                 workloads.append({"workload": name, "error": str(exc)[:200]})
                 torch.cuda.synchronize()
 
+    # ---- the sibling op: fused LayerNorm on the reference's norm-benchmark shapes (HBM-bound) ----
+    layer_norm = None
+    if world == 1 and not args.no_extra and not args.batch:
+        try:
+            layer_norm = layer_norm_record(dev, peaks)
+        except Exception as exc:  # noqa: BLE001
+            layer_norm = {"error": str(exc)[:200]}
+            torch.cuda.synchronize()
+
     # ---- the split the configurations name: c5 heads / c4 sequences over the GPUs of the box ----
     partition = None
     if world > 1 and not args.no_extra:
@@ -655,10 +666,79 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": config, "clocks": headline_clocks, "e2e": e2e,
             "gpu_launches": int(headline_launches) * args.steps * m["blocks"], "launches_per_step": headline_launches,
-            "roofline": roofline, "cpu_baseline": cpu, "workloads": workloads, "partition": partition}
+            "roofline": roofline, "cpu_baseline": cpu, "workloads": workloads, "partition": partition,
+            "layer_norm": layer_norm}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+# (batch, tokens, channels) of the reference's norm benchmark (its bench/PERF_LAYER_NORM.md:17-32); each moves more
+# than the 126 MB L2 per pass except the smallest, so the L2 is flushed between calls
+LAYER_NORM_SHAPES = [("bf16", (8, 1024, 2048)), ("bf16", (8, 1024, 8192)), ("bf16", (32, 512, 1024)),
+                     ("f32", (8, 1024, 1024)), ("f32", (8, 1024, 4096))]
+
+
+def layer_norm_record(dev, peaks):
+    """Forward and backward of the fused LayerNorm on device-resident operands.  K independent sets of operands,
+    together several times the L2, run back to back as one replayed CUDA graph (so every call finds its inputs in
+    HBM, and launch gaps are the graph's, not Python's); time per call = median replay / K.  Algorithmic bytes --
+    forward x in and y out, backward x and dy in and dx out; the [c] vectors, the fp32 row statistics and the
+    partial column sums are noise -- over that time, against the measured copy bandwidth."""
+    from nitrix_b200.nn import norm
+
+    out = []
+    for dt_name, shape in LAYER_NORM_SHAPES:
+        dt = torch.bfloat16 if dt_name == "bf16" else torch.float32
+        rows, c = shape[0] * shape[1], shape[2]
+        nbytes = rows * c * (2 if dt_name == "bf16" else 4)
+        k_sets = int(min(32, max(4, -(-3 * L2_BYTES // (2 * nbytes)))))
+        g = torch.Generator(device=dev).manual_seed(0)
+        xs = [torch.randn(rows, c, device=dev, generator=g).to(dt) for _ in range(k_sets)]
+        dys = [torch.randn(rows, c, device=dev, generator=g).to(dt) for _ in range(k_sets)]
+        w = torch.ones(c, device=dev, dtype=dt)
+        b = torch.zeros(c, device=dev, dtype=dt)
+        stats = [norm.layer_norm_forward(x, w, b, 1e-5, 1.0)[1:] for x in xs]
+
+        def graph_ms(fn):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    fn()
+            ts = []
+            for _ in range(8):
+                a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                graph.replay()
+                e.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(e))
+            return statistics.median(ts[3:]) / k_sets
+
+        def fwd_all():
+            for x in xs:
+                norm.layer_norm_forward(x, w, b, 1e-5, 1.0)
+
+        def bwd_all():
+            for x, dy, (mean, rstd) in zip(xs, dys, stats):
+                norm.layer_norm_backward(x, w, dy, mean, rstd, 1e-5, 1.0, True, True)
+
+        t_f, t_b = graph_ms(fwd_all), graph_ms(bwd_all)
+        rec = {"shape": list(shape), "dtype": dt_name, "operand_sets": k_sets, "fwd_ms": t_f, "bwd_ms": t_b,
+               "fwd_gbs": 2 * nbytes / (t_f * 1e-3) / 1e9, "bwd_gbs": 3 * nbytes / (t_b * 1e-3) / 1e9}
+        if peaks:
+            rec["fwd_frac_of_hbm"] = rec["fwd_gbs"] / peaks["hbm"]
+            rec["bwd_frac_of_hbm"] = rec["bwd_gbs"] / peaks["hbm"]
+        out.append(rec)
+        del xs, dys, stats
+        torch.cuda.empty_cache()
+    return {"unit": "GB/s of algorithmic bytes per call; peak = measured copy bandwidth",
+            "peak_gbs": peaks["hbm"] if peaks else None, "shapes": out}
 
 
 def partition_record(world, rank, local_rank, dev, args, barrier, peaks):

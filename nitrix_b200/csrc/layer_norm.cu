@@ -11,10 +11,10 @@
 // Rows that are a multiple of 16 bytes (<= 8192 channels, aligned pointers) take the vector kernels below; the rest
 // the scalar ones at the end.  The op is bound by HBM traffic (x once in, y once out; the backward x and dy in, dx
 // out), so a row is read ONCE with 16-byte loads and held in registers between the reductions and the write: by one
-// warp (rows of up to 32 x 16 B x 8) or by one 256-thread CTA (longer rows).  The variance is taken about the mean (two passes over the registers, as
-// the reference's `var` does), not as E[x^2] - mean^2.  dw / db: every CTA walks rows in a grid-stride loop, keeps
-// its column sums in registers, leaves one partial row per CTA in a workspace, and a second kernel adds the partials
-// in CTA order -- deterministic, no atomics.
+// warp (rows of up to 32 x 16 B x 8) or by one 256-thread CTA (longer rows).  The variance is taken about the mean
+// (two passes over the registers, as the reference's `var` does), not as E[x^2] - mean^2.  dw / db: every CTA walks
+// rows in a grid-stride loop, keeps its column sums in shared memory, leaves one partial row per CTA in a
+// workspace, and a second kernel adds the partials in a fixed order -- deterministic, no atomics.
 #include <math.h>
 
 #include "nitrix_b200_norm.h"
@@ -138,29 +138,38 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_kernel(LnArgs a) {
   }
 }
 
-// Backward.  Grid-stride over rows (a warp's or a CTA's); column sums of dw, db stay in registers until the end.
+// Backward.  Grid-stride over rows (a warp's or a CTA's).  The column sums of dw, db live in shared memory, every
+// thread adding only to its own columns (in registers they cost 2 x kPer x kVec registers and left one CTA per SM).
 template <typename T, int kPer, bool kCta>
 __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(LnArgs a) {
   constexpr int kVec = 16 / int(sizeof(T));
   constexpr int kTpr = kCta ? kThreads : 32;
   constexpr int kRowsPerCta = kCta ? 1 : kThreads / 32;
-  extern __shared__ float wsum[];   // warp-per-row: [8][C] x 2 for the CTA's column sums
+  // [2][kRowsPerCta][kPad]: dw sums, then db sums, per row owner.  Column c of an owner sits at slot(c): the two
+  // 16-byte halves of a 16-bit thread's chunk go to separate planes, so that the threads of a quarter-warp touch
+  // consecutive 16-byte words (bank-conflict free) when they update their sums.
+  extern __shared__ __align__(16) float wsum[];
+  constexpr int kPad = kPer * kTpr * kVec;
+  auto slot4 = [](int p, int i4, int tin_) { return ((p * (kVec / 4) + i4) * kTpr + tin_) * 4; };
   __shared__ float red[kThreads / 32];
   const int tin = kCta ? threadIdx.x : (threadIdx.x & 31);
   const int sub = kCta ? 0 : (threadIdx.x >> 5);
   const T* w = reinterpret_cast<const T*>(a.w);
-  float wv[kPer][kVec], dw[kPer][kVec], db[kPer][kVec];
+  float* sw = wsum + sub * kPad;
+  float* sb = wsum + (kRowsPerCta + sub) * kPad;
+  const bool sums = a.part != nullptr;
+  if (sums) {
 #pragma unroll
-  for (int p = 0; p < kPer; ++p) {
-    const int c0 = (p * kTpr + tin) * kVec;
-    if (w && c0 < a.C) {
-      load_vec<T, kVec>(w + c0, wv[p]);
-    } else {
+    for (int p = 0; p < kPer; ++p) {
+      const int c0 = (p * kTpr + tin) * kVec;
+      if (c0 < a.C) {
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) wv[p][i] = 1.f;
+        for (int i = 0; i < kVec; i += 4) {
+          *reinterpret_cast<float4*>(sw + slot4(p, i / 4, tin)) = make_float4(0.f, 0.f, 0.f, 0.f);
+          *reinterpret_cast<float4*>(sb + slot4(p, i / 4, tin)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
     }
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) dw[p][i] = db[p][i] = 0.f;
   }
   // (in a CTA-per-row kernel every thread of the CTA runs the same number of iterations: the barriers in row_sum match)
   for (int64_t row = int64_t(blockIdx.x) * kRowsPerCta + sub; row < a.rows; row += int64_t(gridDim.x) * kRowsPerCta) {
@@ -173,18 +182,41 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(LnArgs a) {
     for (int p = 0; p < kPer; ++p) {
       const int c0 = (p * kTpr + tin) * kVec;
       if (c0 < a.C) {
-        float gv[kVec];
         load_vec<T, kVec>(x + c0, xh[p]);
-        load_vec<T, kVec>(g + c0, gv);
+        load_vec<T, kVec>(g + c0, dxh[p]);
+      }
+    }
 #pragma unroll
-        for (int i = 0; i < kVec; ++i) {
-          xh[p][i] = (xh[p][i] - mean) * rstd;
-          const float gy = a.out_scale * gv[i];
-          dw[p][i] = fmaf(gy, xh[p][i], dw[p][i]);
-          db[p][i] += gy;
-          dxh[p][i] = gy * wv[p][i];
-          s1 += dxh[p][i];
-          s2 = fmaf(dxh[p][i], xh[p][i], s2);
+    for (int p = 0; p < kPer; ++p) {
+      const int c0 = (p * kTpr + tin) * kVec;
+      if (c0 < a.C) {
+        float wv[kVec];
+        if (w) load_vec<T, kVec>(w + c0, wv);   // (a few KB that stay in L1)
+#pragma unroll
+        for (int i = 0; i < kVec; i += 4) {
+          float4 aw, ab;
+          if (sums) {
+            aw = *reinterpret_cast<const float4*>(sw + slot4(p, i / 4, tin));
+            ab = *reinterpret_cast<const float4*>(sb + slot4(p, i / 4, tin));
+          }
+          float* pw = reinterpret_cast<float*>(&aw);
+          float* pb = reinterpret_cast<float*>(&ab);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float xhv = (xh[p][i + u] - mean) * rstd;
+            const float gy = a.out_scale * dxh[p][i + u];
+            pw[u] = fmaf(gy, xhv, pw[u]);
+            pb[u] += gy;
+            const float d = w ? gy * wv[i + u] : gy;
+            xh[p][i + u] = xhv;
+            dxh[p][i + u] = d;
+            s1 += d;
+            s2 = fmaf(d, xhv, s2);
+          }
+          if (sums) {
+            *reinterpret_cast<float4*>(sw + slot4(p, i / 4, tin)) = aw;
+            *reinterpret_cast<float4*>(sb + slot4(p, i / 4, tin)) = ab;
+          }
         }
       }
     }
@@ -202,62 +234,63 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(LnArgs a) {
       }
     }
   }
-  if (!a.part) return;
+  if (!sums) return;
+  // this CTA's partial row: the row owners' sums added in owner order
   float* pw = a.part + int64_t(blockIdx.x) * a.C;
   float* pb = a.part + (int64_t(gridDim.x) + blockIdx.x) * a.C;
-  if constexpr (kCta) {
+  __syncthreads();
+  for (int c = threadIdx.x; c < a.C; c += kThreads) {
+    const int chunk = c / kVec, i = c % kVec;
+    const int at = slot4(chunk / kTpr, i / 4, chunk % kTpr) + (i & 3);
+    float tw = 0.f, tb = 0.f;
 #pragma unroll
-    for (int p = 0; p < kPer; ++p) {
-      const int c0 = (p * kTpr + tin) * kVec;
-      if (c0 < a.C) {
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) {
-          pw[c0 + i] = dw[p][i];
-          pb[c0 + i] = db[p][i];
-        }
-      }
+    for (int k = 0; k < kRowsPerCta; ++k) {
+      tw += wsum[k * kPad + at];
+      tb += wsum[(kRowsPerCta + k) * kPad + at];
     }
-  } else {
-    // the CTA's eight warps hold sums of the same columns: add them in warp order through shared memory
-    float* sw = wsum + sub * a.C;
-    float* sb = wsum + (kRowsPerCta + sub) * a.C;
-#pragma unroll
-    for (int p = 0; p < kPer; ++p) {
-      const int c0 = (p * kTpr + tin) * kVec;
-      if (c0 < a.C) {
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) {
-          sw[c0 + i] = dw[p][i];
-          sb[c0 + i] = db[p][i];
-        }
-      }
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < a.C; c += kThreads) {
-      float tw = 0.f, tb = 0.f;
-#pragma unroll
-      for (int k = 0; k < kRowsPerCta; ++k) {
-        tw += wsum[k * a.C + c];
-        tb += wsum[(kRowsPerCta + k) * a.C + c];
-      }
-      pw[c] = tw;
-      pb[c] = tb;
-    }
+    pw[c] = tw;
+    pb[c] = tb;
   }
 }
 
-// dw[c] = sum over the CTAs' partial rows, in CTA order; one thread per column
+// dw[c] = sum over the CTAs' partial rows.  A CTA takes 32 columns (lane = column: 128-byte reads); its eight warps
+// take the partial rows in turn, four loads in flight each, and their eight sums are added in warp order -- the
+// order of the whole sum is fixed by (grid, column) alone.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) ln_bwd_finish_kernel(const float* part, int grid, int C, T* dw, T* db) {
-  const int c = blockIdx.x * kThreads + threadIdx.x;
-  if (c >= C) return;
-  float tw = 0.f, tb = 0.f;
-  for (int k = 0; k < grid; ++k) {
-    tw += part[int64_t(k) * C + c];
-    tb += part[(int64_t(grid) + k) * C + c];
+  __shared__ float sw[kThreads / 32][32], sb[kThreads / 32][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 32 + lane;
+  float tw[4] = {0.f, 0.f, 0.f, 0.f}, tb[4] = {0.f, 0.f, 0.f, 0.f};
+  if (c < C) {
+    const float* pw = part + c;
+    const float* pb = part + int64_t(grid) * C + c;
+    int k = warp;
+    for (; k + 3 * (kThreads / 32) < grid; k += 4 * (kThreads / 32)) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        tw[u] += pw[int64_t(k + u * (kThreads / 32)) * C];
+        tb[u] += pb[int64_t(k + u * (kThreads / 32)) * C];
+      }
+    }
+    for (; k < grid; k += kThreads / 32) {
+      tw[0] += pw[int64_t(k) * C];
+      tb[0] += pb[int64_t(k) * C];
+    }
   }
-  if (dw) dw[c] = from_f32<T>(tw);
-  if (db) db[c] = from_f32<T>(tb);
+  sw[warp][lane] = (tw[0] + tw[1]) + (tw[2] + tw[3]);
+  sb[warp][lane] = (tb[0] + tb[1]) + (tb[2] + tb[3]);
+  __syncthreads();
+  if (warp == 0 && c < C) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) {
+      a += sw[i][lane];
+      b += sb[i][lane];
+    }
+    if (dw) dw[c] = from_f32<T>(a);
+    if (db) db[c] = from_f32<T>(b);
+  }
 }
 
 // Any other row (channels not a multiple of 16 bytes, longer than 8192, unaligned pointers): one CTA per row in
@@ -414,7 +447,10 @@ int bwd_t(const nb200_layer_norm_params* p, const Shape& s, cudaStream_t st) {
     }
     a.part = static_cast<float*>(p->workspace);
   }
-  const size_t smem = s.cta ? 0 : sizeof(float) * 2 * (kThreads / 32) * size_t(p->channels);
+  // (rows padded to the kernel's per * threads * vec columns)
+  const size_t smem = want_params ? sizeof(float) * 2 * (s.cta ? 1 : kThreads / 32) * size_t(s.per) *
+                                        (s.cta ? kThreads : 32) * s.vec
+                                  : 0;
   int rc = dispatch<T, true>(s, [&](auto kernel) {
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
@@ -426,7 +462,7 @@ int bwd_t(const nb200_layer_norm_params* p, const Shape& s, cudaStream_t st) {
     return check_launch("layer_norm_bwd_kernel");
   });
   if (rc || !want_params) return rc;
-  ln_bwd_finish_kernel<T><<<(p->channels + kThreads - 1) / kThreads, kThreads, 0, st>>>(
+  ln_bwd_finish_kernel<T><<<(p->channels + 31) / 32, kThreads, 0, st>>>(
       a.part, grid, p->channels, static_cast<T*>(p->dweight), static_cast<T*>(p->dbias));
   count_launch();
   return check_launch("layer_norm_bwd_finish_kernel");
@@ -468,7 +504,7 @@ int bwd_generic_t(const nb200_layer_norm_params* p, cudaStream_t st) {
   count_launch();
   if (int rc = check_launch("layer_norm_bwd_generic_kernel")) return rc;
   if (!want_params) return NB200_OK;
-  ln_bwd_finish_kernel<T><<<(p->channels + kThreads - 1) / kThreads, kThreads, 0, st>>>(
+  ln_bwd_finish_kernel<T><<<(p->channels + 31) / 32, kThreads, 0, st>>>(
       a.part, 1, p->channels, static_cast<T*>(p->dweight), static_cast<T*>(p->dbias));
   count_launch();
   return check_launch("layer_norm_bwd_finish_kernel");
