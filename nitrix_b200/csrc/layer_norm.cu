@@ -81,7 +81,7 @@ __device__ __forceinline__ void store_vec(T* p, const float (&v)[kVec]) {
 // A row is split over kCta ? 256 : 32 threads; a thread holds kPer chunks of kVec = 16 / sizeof(T) elements, chunk p
 // at column (p * threads + thread) * kVec.
 template <typename T, int kPer, bool kCta>
-__global__ void __launch_bounds__(kThreads) ln_fwd_kernel(LnArgs a) {
+__global__ void __launch_bounds__(kThreads, kPer <= 4 ? 4 : 2) ln_fwd_kernel(LnArgs a) {
   constexpr int kVec = 16 / int(sizeof(T));
   constexpr int kTpr = kCta ? kThreads : 32;
   __shared__ float red[kThreads / 32];
