@@ -505,7 +505,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-workload table and the partition record")
+    ap.add_argument("--layer-norm-only", action="store_true",
+                    help="print only the sibling op's record (small: for profiling captures)")
     args = ap.parse_args()
+
+    if args.layer_norm_only:
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        print(json.dumps({"layer_norm": layer_norm_record(dev, load_peaks())}))
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

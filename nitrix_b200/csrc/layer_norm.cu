@@ -46,13 +46,14 @@ __device__ __forceinline__ float warp_sum_f(float v) {
   return v;
 }
 
-// sum over the threads that share a row: the warp, or the whole CTA through shared memory (red: 8 floats + result)
+// Sum over the threads that share a row: the warp, or the whole CTA through shared memory.  `red` holds eight
+// floats per use; consecutive uses alternate between buffers (the callers pass red + 8 k), so that ONE barrier per
+// reduction is enough: a buffer is rewritten only after a later barrier has shown that every thread has read it.
 template <bool kCta>
 __device__ __forceinline__ float row_sum(float v, float* red) {
   v = warp_sum_f(v);
   if constexpr (kCta) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();   // the previous reduction's result has been read
     if (lane == 0) red[warp] = v;
     __syncthreads();
     v = 0.f;
@@ -60,6 +61,27 @@ __device__ __forceinline__ float row_sum(float v, float* red) {
     for (int i = 0; i < kThreads / 32; ++i) v += red[i];
   }
   return v;
+}
+// two sums at once (red: 16 floats per use)
+template <bool kCta>
+__device__ __forceinline__ float2 row_sum2(float a, float b, float* red) {
+  a = warp_sum_f(a);
+  b = warp_sum_f(b);
+  if constexpr (kCta) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+      red[warp] = a;
+      red[8 + warp] = b;
+    }
+    __syncthreads();
+    a = b = 0.f;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) {
+      a += red[i];
+      b += red[8 + i];
+    }
+  }
+  return make_float2(a, b);
 }
 
 template <typename T, int kVec>
@@ -84,7 +106,7 @@ template <typename T, int kPer, bool kCta>
 __global__ void __launch_bounds__(kThreads, kPer <= 4 ? 4 : 2) ln_fwd_kernel(LnArgs a) {
   constexpr int kVec = 16 / int(sizeof(T));
   constexpr int kTpr = kCta ? kThreads : 32;
-  __shared__ float red[kThreads / 32];
+  __shared__ float red[2 * (kThreads / 32)];
   const int tin = kCta ? threadIdx.x : (threadIdx.x & 31);
   const int64_t row = kCta ? int64_t(blockIdx.x) : int64_t(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
   if (row >= a.rows) return;   // (a whole CTA, or a whole warp of a warp-per-row CTA, which never meets a barrier)
@@ -111,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, kPer <= 4 ? 4 : 2) ln_fwd_kernel(LnA
         q = fmaf(d, d, q);
       }
     }
-  const float rstd = rsqrtf(row_sum<kCta>(q, red) / float(a.C) + a.eps);
+  const float rstd = rsqrtf(row_sum<kCta>(q, red + 8) / float(a.C) + a.eps);
   if (tin == 0) {
     if (a.mean) a.mean[row] = mean;
     if (a.rstd) a.rstd[row] = rstd;
@@ -151,9 +173,10 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(LnArgs a) {
   extern __shared__ __align__(16) float wsum[];
   constexpr int kPad = kPer * kTpr * kVec;
   auto slot4 = [](int p, int i4, int tin_) { return ((p * (kVec / 4) + i4) * kTpr + tin_) * 4; };
-  __shared__ float red[kThreads / 32];
+  __shared__ float red[4 * (kThreads / 32)];   // two uses of 16 floats, alternating by row
   const int tin = kCta ? threadIdx.x : (threadIdx.x & 31);
   const int sub = kCta ? 0 : (threadIdx.x >> 5);
+  int flip = 0;
   const T* w = reinterpret_cast<const T*>(a.w);
   float* sw = wsum + sub * kPad;
   float* sb = wsum + (kRowsPerCta + sub) * kPad;
@@ -220,8 +243,9 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(LnArgs a) {
         }
       }
     }
-    const float c1 = row_sum<kCta>(s1, red) / float(a.C);
-    const float c2 = row_sum<kCta>(s2, red) / float(a.C);
+    const float2 cs = row_sum2<kCta>(s1, s2, red + 16 * flip);
+    flip ^= 1;
+    const float c1 = cs.x / float(a.C), c2 = cs.y / float(a.C);
     T* dx = reinterpret_cast<T*>(a.dx) + row * a.C;
 #pragma unroll
     for (int p = 0; p < kPer; ++p) {
@@ -298,7 +322,7 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_finish_kernel(const float* pa
 // atomics (the one place where the order of a sum is not fixed).
 template <typename T>
 __global__ void __launch_bounds__(kThreads) ln_fwd_generic_kernel(LnArgs a) {
-  __shared__ float red[kThreads / 32];
+  __shared__ float red[2 * (kThreads / 32)];
   const int64_t row = blockIdx.x;
   const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
   float s = 0.f;
@@ -309,7 +333,7 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_generic_kernel(LnArgs a) {
     const float d = to_f32<T>(x[c]) - mean;
     q = fmaf(d, d, q);
   }
-  const float rstd = rsqrtf(row_sum<true>(q, red) / float(a.C) + a.eps);
+  const float rstd = rsqrtf(row_sum<true>(q, red + 8) / float(a.C) + a.eps);
   if (threadIdx.x == 0) {
     if (a.mean) a.mean[row] = mean;
     if (a.rstd) a.rstd[row] = rstd;
@@ -327,8 +351,9 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_generic_kernel(LnArgs a) {
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) ln_bwd_generic_kernel(LnArgs a) {
-  __shared__ float red[kThreads / 32];
+  __shared__ float red[4 * (kThreads / 32)];
   const T* w = reinterpret_cast<const T*>(a.w);
+  int flip = 0;
   for (int64_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
     const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
     const T* g = reinterpret_cast<const T*>(a.dy) + row * a.C;
@@ -340,8 +365,9 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_generic_kernel(LnArgs a) {
       s1 += dxh;
       s2 = fmaf(dxh, xh, s2);
     }
-    const float c1 = row_sum<true>(s1, red) / float(a.C);
-    const float c2 = row_sum<true>(s2, red) / float(a.C);
+    const float2 cs = row_sum2<true>(s1, s2, red + 16 * flip);
+    flip ^= 1;
+    const float c1 = cs.x / float(a.C), c2 = cs.y / float(a.C);
     T* dx = reinterpret_cast<T*>(a.dx) + row * a.C;
     for (int c = threadIdx.x; c < a.C; c += kThreads) {
       const float xh = (to_f32<T>(x[c]) - mean) * rstd;
@@ -376,13 +402,15 @@ bool pick(int C, int dtype, bool backward, Shape* s) {
   return false;
 }
 
-int bwd_grid(int64_t rows, const Shape& s) {
+// The backward's grid: as many CTAs as are resident at once (`per_sm` from the occupancy calculator; more CTAs only
+// add partial rows to sum), at most one per row unit.  per_sm = 8 bounds it for sizing the workspace.
+int bwd_grid(int64_t rows, const Shape& s, int per_sm) {
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
   const int64_t units = s.cta ? rows : (rows + kThreads / 32 - 1) / (kThreads / 32);
-  const int64_t cap = int64_t(sms) * (s.cta ? 4 : 2);
+  const int64_t cap = int64_t(sms) * per_sm;
   return int(units < cap ? (units > 0 ? units : 1) : cap);
 }
 
@@ -437,7 +465,7 @@ int bwd_t(const nb200_layer_norm_params* p, const Shape& s, cudaStream_t st) {
   a.x = p->x; a.w = p->weight; a.dy = p->dy; a.dx = p->dx; a.mean = p->mean; a.rstd = p->rstd;
   a.rows = p->rows; a.C = p->channels; a.eps = p->eps; a.out_scale = p->out_scale;
   const bool want_params = p->dweight || p->dbias;
-  const int grid = bwd_grid(p->rows, s);
+  int grid = bwd_grid(p->rows, s, 8);
   if (want_params) {
     const size_t need = sizeof(float) * 2 * size_t(grid) * size_t(p->channels);
     if (!p->workspace || p->workspace_bytes < need) {
@@ -457,6 +485,12 @@ int bwd_t(const nb200_layer_norm_params* p, const Shape& s, cudaStream_t st) {
       set_error("layer_norm_bwd: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(cudaGetLastError()));
       return int(NB200_ERR_LAUNCH);
     }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess || per_sm < 1) {
+      cudaGetLastError();
+      per_sm = 1;
+    }
+    grid = bwd_grid(p->rows, s, per_sm < 8 ? per_sm : 8);
     kernel<<<unsigned(grid), kThreads, smem, st>>>(a);
     count_launch();
     return check_launch("layer_norm_bwd_kernel");
@@ -530,7 +564,7 @@ extern "C" NB200_API int nb200_layer_norm_workspace_bytes(const nb200_layer_norm
   if (int rc = check_common(p, "layer_norm_workspace_bytes")) return rc;
   // (sized for the vector kernels' per-CTA partial rows, which is never less than the scalar kernels' [2][C])
   Shape s;
-  const int grid = pick(p->channels, p->dtype, true, &s) ? bwd_grid(p->rows, s) : 1;
+  const int grid = pick(p->channels, p->dtype, true, &s) ? bwd_grid(p->rows, s, 8) : 1;
   *bytes = sizeof(float) * 2 * size_t(grid) * size_t(p->channels);
   return NB200_OK;
 }
