@@ -91,6 +91,54 @@ __device__ __forceinline__ void load_vec(const T* p, float (&out)[kVec]) {
 #pragma unroll
   for (int i = 0; i < kVec; ++i) out[i] = to_f32<T>(e[i]);
 }
+// The same as pairs: the arithmetic below runs on the packed fp32x2 pipe (one instruction per two elements; each
+// lane rounds as the scalar instruction would, so results do not change).  At 16-bit widths the kernels are bound
+// by instruction issue as much as by memory.
+template <typename T>
+__device__ __forceinline__ float2 unpack_pair(uint32_t w);
+template <>
+__device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack_pair<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float2 v);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 r = __floats2bfloat162_rn(v.x, v.y);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float2 v) {
+  const __half2 r = __floats2half2_rn(v.x, v.y);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <typename T, int kVec>
+__device__ __forceinline__ void load_pairs(const T* p, float2 (&out)[kVec / 2]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(p);
+  if constexpr (sizeof(T) == 4) {
+    out[0] = make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
+    out[1] = make_float2(__uint_as_float(w.z), __uint_as_float(w.w));
+  } else {
+    out[0] = unpack_pair<T>(w.x);
+    out[1] = unpack_pair<T>(w.y);
+    out[2] = unpack_pair<T>(w.z);
+    out[3] = unpack_pair<T>(w.w);
+  }
+}
+template <typename T, int kVec>
+__device__ __forceinline__ void store_pairs(T* p, const float2 (&v)[kVec / 2]) {
+  uint4 w;
+  if constexpr (sizeof(T) == 4) {
+    w = make_uint4(__float_as_uint(v[0].x), __float_as_uint(v[0].y), __float_as_uint(v[1].x), __float_as_uint(v[1].y));
+  } else {
+    w = make_uint4(pack_pair<T>(v[0]), pack_pair<T>(v[1]), pack_pair<T>(v[2]), pack_pair<T>(v[3]));
+  }
+  *reinterpret_cast<uint4*>(p) = w;
+}
 template <typename T, int kVec>
 __device__ __forceinline__ void store_vec(T* p, const float (&v)[kVec]) {
   uint4 w;
@@ -111,29 +159,31 @@ __global__ void __launch_bounds__(kThreads, kPer <= 4 ? 4 : 2) ln_fwd_kernel(LnA
   const int64_t row = kCta ? int64_t(blockIdx.x) : int64_t(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
   if (row >= a.rows) return;   // (a whole CTA, or a whole warp of a warp-per-row CTA, which never meets a barrier)
   const T* x = reinterpret_cast<const T*>(a.x) + row * a.C;
-  float xv[kPer][kVec];
-  float s = 0.f;
+  constexpr int kPairs = kVec / 2;
+  float2 xv[kPer][kPairs];
+  float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int p = 0; p < kPer; ++p) {
     const int c0 = (p * kTpr + tin) * kVec;
     if (c0 < a.C) {
-      load_vec<T, kVec>(x + c0, xv[p]);
+      load_pairs<T, kVec>(x + c0, xv[p]);
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) s += xv[p][i];
+      for (int i = 0; i < kPairs; ++i) s2 = __fadd2_rn(s2, xv[p][i]);
     }
   }
-  const float mean = row_sum<kCta>(s, red) / float(a.C);
-  float q = 0.f;
+  const float mean = row_sum<kCta>(s2.x + s2.y, red) / float(a.C);
+  const float2 nmean = make_float2(-mean, -mean);
+  float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int p = 0; p < kPer; ++p)
     if ((p * kTpr + tin) * kVec < a.C) {
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) {
-        const float d = xv[p][i] - mean;
-        q = fmaf(d, d, q);
+      for (int i = 0; i < kPairs; ++i) {
+        xv[p][i] = __fadd2_rn(xv[p][i], nmean);      // x - mean, kept
+        q2 = __ffma2_rn(xv[p][i], xv[p][i], q2);
       }
     }
-  const float rstd = rsqrtf(row_sum<kCta>(q, red + 8) / float(a.C) + a.eps);
+  const float rstd = rsqrtf(row_sum<kCta>(q2.x + q2.y, red + 8) / float(a.C) + a.eps);
   if (tin == 0) {
     if (a.mean) a.mean[row] = mean;
     if (a.rstd) a.rstd[row] = rstd;
@@ -141,21 +191,22 @@ __global__ void __launch_bounds__(kThreads, kPer <= 4 ? 4 : 2) ln_fwd_kernel(LnA
   T* y = reinterpret_cast<T*>(a.y) + row * a.C;
   const T* w = reinterpret_cast<const T*>(a.w);
   const T* b = reinterpret_cast<const T*>(a.b);
+  const float2 rstd2 = make_float2(rstd, rstd), os2 = make_float2(a.out_scale, a.out_scale);
 #pragma unroll
   for (int p = 0; p < kPer; ++p) {
     const int c0 = (p * kTpr + tin) * kVec;
     if (c0 < a.C) {
-      float wv[kVec], bv[kVec], out[kVec];
-      if (w) load_vec<T, kVec>(w + c0, wv);
-      if (b) load_vec<T, kVec>(b + c0, bv);
+      float2 wv[kPairs], bv[kPairs], out[kPairs];
+      if (w) load_pairs<T, kVec>(w + c0, wv);
+      if (b) load_pairs<T, kVec>(b + c0, bv);
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) {
-        float v = (xv[p][i] - mean) * rstd;
-        if (w) v *= wv[i];
-        if (b) v += bv[i];
-        out[i] = a.out_scale * v;
+      for (int i = 0; i < kPairs; ++i) {
+        float2 v = __fmul2_rn(xv[p][i], rstd2);
+        if (w) v = __fmul2_rn(v, wv[i]);
+        if (b) v = __fadd2_rn(v, bv[i]);
+        out[i] = __fmul2_rn(os2, v);
       }
-      store_vec<T, kVec>(y + c0, out);
+      store_pairs<T, kVec>(y + c0, out);
     }
   }
 }
