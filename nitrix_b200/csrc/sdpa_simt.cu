@@ -987,7 +987,13 @@ __device__ __forceinline__ void bwd_dq_tf32x3_tile(const Problem& pr, int bias_d
   }
 }
 
-template <int kDBlocks, bool kSquare>   // D / 8; kSquare: D == Dv, both row pitches compile-time constants
+//
+// kC > 1 (the SMALLEST problems, launched as clusters of kC CTAs along x): the CTAs of a cluster own the same 64
+// query rows and take the key tiles in turn -- kC times as many warps for the same latency-bound chain, each with a
+// full register file (the in-CTA split above is capped at 128 registers a thread from four groups on); ranks 1..
+// leave their partial dq tile in their own shared memory and rank 0 adds them over distributed shared memory in
+// rank order.  Every dbias element is still written, or added, by exactly one CTA.
+template <int kDBlocks, bool kSquare, int kC = 1>   // D / 8; kSquare: D == Dv, both row pitches compile-time constants
 __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBM = 64;
@@ -1001,7 +1007,8 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
-  const int row0 = blockIdx.x * kBM;
+  const int crank = kC > 1 ? int(blockIdx.x) % kC : 0;   // rank in the cluster (cluster dims (kC, 1, 1))
+  const int row0 = (int(blockIdx.x) / kC) * kBM;
   const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
   const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
   const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
@@ -1031,22 +1038,53 @@ __global__ void __launch_bounds__(kTiledThreads) bwd_dq_tf32x3_kernel(Problem pr
   const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
   const bool want_db = pr.dbias != nullptr || pr.dbias_accum != nullptr;
 
-  if (t_end > 0) {
-    stage_rows_any<float>(Kbuf, LDQ, kp, pr.ks[2], 0, kBN, pr.T, D, false);
-    stage_rows_any<float>(Vbuf, LDV, vp, pr.vs[2], 0, kBN, pr.T, Dv, false);
+  const int k_first = crank * kBN;
+  if (k_first < t_end) {
+    stage_rows_any<float>(Kbuf, LDQ, kp, pr.ks[2], k_first, kBN, pr.T, D, false);
+    stage_rows_any<float>(Vbuf, LDV, vp, pr.vs[2], k_first, kBN, pr.T, Dv, false);
   }
   int it = 0;
-  for (int kt = 0; kt < t_end; kt += kBN, ++it) {
+  for (int kt = k_first; kt < t_end; kt += kC * kBN, ++it) {
     stage_wait();
     __syncthreads();
     const float* Ks = Kbuf + (it & 1) * kBN * LDQ;
     const float* Vs = Vbuf + (it & 1) * kBN * LDV;
-    if (kt + kBN < t_end) {
-      stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
-      stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
+    if (kt + kC * kBN < t_end) {
+      stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kC * kBN, kBN, pr.T, D, false);
+      stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kC * kBN, kBN, pr.T, Dv, false);
     }
     bwd_dq_tf32x3_tile<kDBlocks>(pr, bias_dtype, Qs, Gs, Ks, Vs, LDQ, LDV, D, Dv, kt, row0, lr, boff, moff, dboff, lse,
                                  delta, s2scale, want_db, g, t, dq);
+  }
+  if constexpr (kC > 1) {
+    // partial tiles [kBM][D] in this CTA's K stages; rank 0 adds ranks 1.. in order
+    cg::cluster_group cluster = cg::this_cluster();
+    float* part = Kbuf;
+    stage_wait();      // (a rank without a key tile still has its Q / dout copies in flight)
+    __syncthreads();   // the last tile's operands are no longer read
+    if (crank > 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int nb = 0; nb < kDBlocks; ++nb)
+          *reinterpret_cast<float2*>(part + lr[i] * D + 8 * nb + 2 * t) = make_float2(dq[nb][2 * i], dq[nb][2 * i + 1]);
+    }
+    cluster.sync();
+    if (crank == 0) {
+      for (int r = 1; r < kC; ++r) {
+        const float* rp = cluster.map_shared_rank(part, r);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int nb = 0; nb < kDBlocks; ++nb) {
+            const float2 a = *reinterpret_cast<const float2*>(rp + lr[i] * D + 8 * nb + 2 * t);
+            dq[nb][2 * i] += a.x;
+            dq[nb][2 * i + 1] += a.y;
+          }
+      }
+    }
+    cluster.sync();    // nobody leaves while rank 0 still reads its shared memory
+    if (crank > 0) return;
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -1600,6 +1638,17 @@ int bwd_dq_split_groups(const Problem& pr) {
   return (tiles >= 5 || tiles == 3) ? 3 : 2;
 }
 
+// The smallest fp32 problems, dq: the number of CTAs per cluster that split the key tiles of each 64-row tile
+// (bwd_dq_tf32x3_kernel<., ., kC>), 0 when that does not apply: every CTA of the launch must be resident at once
+// (two per SM: ~236 registers a thread), and it has to beat the in-CTA split, which shares the Q / dout stage --
+// so only where the in-CTA split cannot give every key tile a warp group of its own.
+int bwd_dq_cluster_size(const Problem& pr) {
+  const int64_t ctas = int64_t((pr.S + 63) / 64) * pr.bh_count;
+  const int tiles = (pr.T + kBN - 1) / kBN;
+  if (!(pr.S > 0 && (pr.D == 32 || pr.D == 64) && (pr.Dv == 32 || pr.Dv == 64) && tiles >= 4)) return 0;
+  return 4 * ctas <= 2 * int64_t(sm_count()) ? 4 : 0;
+}
+
 // Small fp32 problems, dk / dv: the number of CTAs per cluster that split the query tiles of each 64-key tile
 // (bwd_dkv_tf32x3_kernel<., kC>), 0 when a cluster launch does not apply -- it does as long as every CTA of the
 // launch is resident at once (two per SM: ~200 registers a thread): the point is more warps per SM, not more waves.
@@ -1649,7 +1698,36 @@ int bwd_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
   };
   bool dq_done = false;
   if constexpr (sizeof(T) == 4) {
+    // the smallest problems: clusters of CTAs split the key tiles of each 64-row tile
+    if (const int kc = bwd_dq_cluster_size(pr)) {
+      const size_t sm = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(64 + 2 * kBN) * (pr.Dv + 4));
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(unsigned((pr.S + 63) / 64) * kc, pr.bh_count);
+      cfg.blockDim = dim3(kTiledThreads);
+      cfg.dynamicSmemBytes = sm;
+      cfg.stream = st;
+      cudaLaunchAttribute attr{};
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = kc;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int rc = NB200_OK;
+      auto go = [&](auto kernel) {
+        if ((rc = prepare(kernel, sm)) != NB200_OK) return;
+        (void)cudaLaunchKernelEx(&cfg, kernel, pr, bias_dtype);   // a failure is read by check_launch below
+      };
+      const bool sq = pr.D == pr.Dv;
+      if (pr.D == 32) { if (sq) go(bwd_dq_tf32x3_kernel<4, true, 4>); else go(bwd_dq_tf32x3_kernel<4, false, 4>); }
+      else { if (sq) go(bwd_dq_tf32x3_kernel<8, true, 4>); else go(bwd_dq_tf32x3_kernel<8, false, 4>); }
+      if (rc) return join(rc);
+      count_launch();
+      if (int rc2 = check_launch("bwd_dq_tf32x3_kernel")) return join(rc2);
+      dq_done = true;
+    }
     // small problems: groups of warps split the key tiles inside each 64-row CTA
+    if (!dq_done)
     if (const int kg = bwd_dq_split_groups(pr)) {
       const size_t sm = sizeof(float) * size_t(64 + kg * kBN) * (pr.D + 4 + pr.Dv + 4);
       dim3 gq((pr.S + 63) / 64, pr.bh_count);
@@ -1763,7 +1841,7 @@ bool simt_family_uses_tensor_path(const Problem& pr, int dtype, int pass) {
   const bool dv_ok = pr.Dv == 32 || pr.Dv == 64 || pr.Dv == 128;
   if (pass == NB200_PASS_FWD) return pr.D % 8 == 0 && pr.D <= 128 && dv_ok;
   const bool d_ok = pr.D == 32 || pr.D == 64 || pr.D == 128;
-  const bool dq = bwd_dq_split_groups(pr) != 0 ||
+  const bool dq = bwd_dq_cluster_size(pr) != 0 || bwd_dq_split_groups(pr) != 0 ||
                   (pr.S > 0 && pr.Dv % 8 == 0 && pr.Dv <= 128 && d_ok && int64_t((pr.S + 63) / 64) * pr.bh_count >= 96);
   const bool dkv = bwd_dkv_cluster_size(pr) != 0 ||
                    (pr.T > 0 && pr.D == pr.Dv && d_ok && int64_t((pr.T + 63) / 64) * pr.bh_count >= 96);
