@@ -13,7 +13,8 @@
 //   simt_fwd_kernel        everything else: one warp per query row, 32 lanes over 32 keys
 // Backward, fp32 operands on grids of >= 96 CTAs: bwd_dq_tf32x3_kernel and bwd_dkv_tf32x3_kernel
 // (D == Dv in {32, 64, 128}), the same 3 x TF32 tiling; smaller problems at head dims 32 / 64 split each CTA's
-// tiles of the opposite operand over groups of warps (dq) or over the CTAs of a cluster (dk / dv).  Otherwise:
+// tiles of the opposite operand over groups of warps (forward, dq) or over the CTAs of a cluster (dk / dv; the
+// smallest problems: forward and dq as well).  Otherwise:
 // one warp owns one query row (dq) or one key row (dk/dv); the 32 lanes take 32 consecutive rows of the
 // opposite operand, staged in shared memory as fp32.  Row sums use warp shuffles; nothing is atomically accumulated
 // except the optional broadcast-bias gradient, and every sum runs in a fixed order.
@@ -551,7 +552,10 @@ __device__ __forceinline__ void fwd_tf32x3_tile(const Problem& pr, int bias_dtyp
 }
 
 // kSquare (D == Dv): both row pitches are compile-time constants, so every fragment offset is an immediate.
-template <int kDvBlocks, bool kSquare>   // Dv / 8
+// kC > 1 (the SMALLEST problems, launched as clusters of kC CTAs along x): the CTAs of a cluster own the same 64 query
+// rows and take the key tiles in turn, each with a full register file; ranks 1.. leave their partial (out, m, l) in
+// their own shared memory and rank 0 merges them over distributed shared memory in rank order.
+template <int kDvBlocks, bool kSquare, int kC = 1>   // Dv / 8
 __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, int bias_dtype) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kBM = 64;
@@ -564,7 +568,8 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = pr.bh_begin + blockIdx.y;
   const int b = bh / pr.H, h = bh - b * pr.H;
-  const int row0 = blockIdx.x * kBM;
+  const int crank = kC > 1 ? int(blockIdx.x) % kC : 0;   // rank in the cluster (cluster dims (kC, 1, 1))
+  const int row0 = (int(blockIdx.x) / kC) * kBM;
   const float* qp = reinterpret_cast<const float*>(pr.q) + b * pr.qs[0] + h * pr.qs[1];
   const float* kp = reinterpret_cast<const float*>(pr.k) + b * pr.ks[0] + h * pr.ks[1];
   const float* vp = reinterpret_cast<const float*>(pr.v) + b * pr.vs[0] + h * pr.vs[1];
@@ -589,21 +594,64 @@ __global__ void __launch_bounds__(kTiledThreads) fwd_tf32x3_kernel(Problem pr, i
   const int t_end = pr.causal ? min(pr.T, min(row0 + kBM, pr.S)) : pr.T;
 
   // K / V tiles are double-buffered: tile i + 1 is copied while tile i is computed, one barrier per tile
-  if (t_end > 0) {
-    stage_rows_any<float>(Kbuf, LDQ, kp, pr.ks[2], 0, kBN, pr.T, D, false);
-    stage_rows_any<float>(Vbuf, LDV, vp, pr.vs[2], 0, kBN, pr.T, Dv, false);
+  const int k_first = crank * kBN;
+  if (k_first < t_end) {
+    stage_rows_any<float>(Kbuf, LDQ, kp, pr.ks[2], k_first, kBN, pr.T, D, false);
+    stage_rows_any<float>(Vbuf, LDV, vp, pr.vs[2], k_first, kBN, pr.T, Dv, false);
   }
   int it = 0;
-  for (int kt = 0; kt < t_end; kt += kBN, ++it) {
+  for (int kt = k_first; kt < t_end; kt += kC * kBN, ++it) {
     stage_wait();
     __syncthreads();   // tile `it` (and, the first time, Q) has landed; nobody reads the other buffer any more
     const float* Ks = Kbuf + (it & 1) * kBN * LDQ;
     const float* Vs = Vbuf + (it & 1) * kBN * LDV;
-    if (kt + kBN < t_end) {
-      stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kBN, kBN, pr.T, D, false);
-      stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kBN, kBN, pr.T, Dv, false);
+    if (kt + kC * kBN < t_end) {
+      stage_rows_any<float>(Kbuf + ((it + 1) & 1) * kBN * LDQ, LDQ, kp, pr.ks[2], kt + kC * kBN, kBN, pr.T, D, false);
+      stage_rows_any<float>(Vbuf + ((it + 1) & 1) * kBN * LDV, LDV, vp, pr.vs[2], kt + kC * kBN, kBN, pr.T, Dv, false);
     }
     fwd_tf32x3_tile<kDvBlocks>(pr, bias_dtype, Qs, Ks, Vs, LDQ, LDV, D, kt, row0, lr, boff, moff, s2scale, g, t, o, m, l);
+  }
+  if constexpr (kC > 1) {
+    // partial [kBM][Dv + 2] = (out, m, l) in this CTA's K stages; rank 0 merges ranks 1.. in order
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int LDP = Dv + 2;
+    float* part = Kbuf;
+    stage_wait();      // (a rank without a key tile still has its Q copy in flight)
+    __syncthreads();   // the last tile's operands are no longer read
+    if (crank > 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float* prow = part + lr[i] * LDP;
+#pragma unroll
+        for (int nb = 0; nb < kDvBlocks; ++nb)
+          *reinterpret_cast<float2*>(prow + 8 * nb + 2 * t) = make_float2(o[nb][2 * i], o[nb][2 * i + 1]);
+        if (t == 0) *reinterpret_cast<float2*>(prow + Dv) = make_float2(m[i], l[i]);
+      }
+    }
+    cluster.sync();
+    if (crank == 0) {
+      for (int r = 1; r < kC; ++r) {
+        const float* rp = cluster.map_shared_rank(part, r);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float* prow = rp + lr[i] * LDP;
+          const float2 ml = *reinterpret_cast<const float2*>(prow + Dv);
+          const float m_new = fmaxf(m[i], ml.x);
+          const float m_ref = m_new == -INFINITY ? 0.f : m_new;   // nothing kept on either side: both weights are 0
+          const float wa = exp2f(m[i] - m_ref), wb = exp2f(ml.x - m_ref);
+          l[i] = l[i] * wa + ml.y * wb;
+          m[i] = m_new;
+#pragma unroll
+          for (int nb = 0; nb < kDvBlocks; ++nb) {
+            const float2 a = *reinterpret_cast<const float2*>(prow + 8 * nb + 2 * t);
+            o[nb][2 * i] = o[nb][2 * i] * wa + a.x * wb;
+            o[nb][2 * i + 1] = o[nb][2 * i + 1] * wa + a.y * wb;
+          }
+        }
+      }
+    }
+    cluster.sync();    // nobody leaves while rank 0 still reads its shared memory
+    if (crank > 0) return;
   }
   // ---- out = o / l (NaN for a row with no kept key, as the reference's softmax gives), lse ----
 #pragma unroll
@@ -1570,6 +1618,28 @@ int fwd_tf32x3_t(const Problem& pr, int bias_dtype, cudaStream_t st) {
       return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && st3[0] % 4 == 0 && st3[1] % 4 == 0 && st3[2] % 4 == 0;
     };
     const bool aligned = rows16(pr.q, pr.qs) && rows16(pr.k, pr.ks) && rows16(pr.v, pr.vs);
+    // the smallest problems: clusters of four CTAs per 64-row tile, while all of them are resident at once and the
+    // in-CTA split below could not give every key tile a warp group with a full register file
+    if constexpr (kDvBlocks <= 8)
+    if (tiles >= 4 && pr.D <= 64 && 4 * ctas <= 2 * int64_t(sms > 0 ? sms : 148)) {
+      const size_t smem = sizeof(float) * (size_t(64 + 2 * kBN) * (pr.D + 4) + size_t(2 * kBN) * (pr.Dv + 4));
+      if (int rc = prepare(fwd_tf32x3_kernel<kDvBlocks, kSquare, 4>, smem)) return rc;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(unsigned((pr.S + 63) / 64) * 4, pr.bh_count);
+      cfg.blockDim = dim3(kTiledThreads);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr{};
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 4;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      (void)cudaLaunchKernelEx(&cfg, fwd_tf32x3_kernel<kDvBlocks, kSquare, 4>, pr, bias_dtype);   // errors: check_launch
+      count_launch();
+      return check_launch("fwd_tf32x3_kernel");
+    }
     if constexpr (kDvBlocks <= 8)
     if (aligned && ctas <= 2 * int64_t(sms > 0 ? sms : 148) && tiles >= 2 && pr.D <= 64 && pr.Dv <= 64) {
       if (tiles >= 4) return fwd_tf32x3_split_t<kDvBlocks, 4, kSquare>(pr, bias_dtype, st);
