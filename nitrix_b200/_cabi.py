@@ -74,6 +74,18 @@ class LayerNormParams(C.Structure):
                 ("eps", C.c_float), ("out_scale", C.c_float)]
 
 
+class SelectiveScanParams(C.Structure):
+    """``nb200_selective_scan_params`` (include/nitrix_b200_scan.h)."""
+
+    _fields_ = [("struct_size", C.c_size_t), ("x", C.c_void_p), ("delta", C.c_void_p), ("A", C.c_void_p),
+                ("B", C.c_void_p), ("C", C.c_void_p), ("D", C.c_void_p), ("y", C.c_void_p),
+                ("checkpoints", C.c_void_p), ("dy", C.c_void_p), ("dx", C.c_void_p), ("ddelta", C.c_void_p),
+                ("dA", C.c_void_p), ("dB", C.c_void_p), ("dC", C.c_void_p), ("dD", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("batch", C.c_int32),
+                ("length", C.c_int32), ("channels", C.c_int32), ("states", C.c_int32), ("dtype", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
 EXPORTS = (
     "nb200_version",
     "nb200_last_error",
@@ -97,6 +109,10 @@ EXPORTS = (
     "nb200_layer_norm_fwd",
     "nb200_layer_norm_bwd",
     "nb200_layer_norm_workspace_bytes",
+    "nb200_selective_scan_fwd",
+    "nb200_selective_scan_bwd",
+    "nb200_selective_scan_workspace_bytes",
+    "nb200_selective_scan_checkpoint_bytes",
 )
 
 
@@ -139,6 +155,10 @@ def lib() -> C.CDLL:
     L.nb200_layer_norm_fwd.argtypes = [C.POINTER(LayerNormParams), C.c_void_p]
     L.nb200_layer_norm_bwd.argtypes = [C.POINTER(LayerNormParams), C.c_void_p]
     L.nb200_layer_norm_workspace_bytes.argtypes = [C.POINTER(LayerNormParams), C.POINTER(C.c_size_t)]
+    L.nb200_selective_scan_fwd.argtypes = [C.POINTER(SelectiveScanParams), C.c_void_p]
+    L.nb200_selective_scan_bwd.argtypes = [C.POINTER(SelectiveScanParams), C.c_void_p]
+    L.nb200_selective_scan_workspace_bytes.argtypes = [C.POINTER(SelectiveScanParams), C.POINTER(C.c_size_t)]
+    L.nb200_selective_scan_checkpoint_bytes.argtypes = [C.POINTER(SelectiveScanParams), C.POINTER(C.c_size_t)]
     if L.nb200_version() != ABI_VERSION:
         raise NativeLibraryError(f"{path}: ABI {L.nb200_version()} != expected {ABI_VERSION}")
     return L

@@ -1,0 +1,349 @@
+// Mamba / S6 selective scan, forward and backward -- the second sibling op behind the same library (reference
+// src/nitrix/nn/ssm/__init__.py:127- is the dispatcher, src/nitrix/nn/ssm/_reference.py:60-98 the recipe):
+//
+//   a_t = exp(delta_t A),  b_t = (delta_t B_t) x_t,  h_t = a_t h_{t-1} + b_t  (h_{-1} = 0),
+//   y_t = sum_n C_{t,n} h_{t,n} (+ D x_t)
+//
+// per batch element, channel d and state n; x, delta (batch, l, d), A (d, n), B, C (batch, l, n), D (d); fp32
+// recurrence and readout whatever the storage dtype (reference _reference.py:262-279).
+//
+// One thread owns one channel of one batch element and walks the sequence with its n states in registers (the
+// recurrence is sequential in t; the parallelism is batch x channels); a CTA is 64 channels, and the B_t / C_t rows
+// its threads share are staged through shared memory eight steps at a time.  Nothing of size (l, d, n) is ever
+// materialised: the forward leaves the state after every eighth step in a checkpoint array (batch, l / 8, n, d), and
+// the backward walks the chunks in reverse, recomputes a chunk's eight states from its checkpoint into shared
+// memory and runs the adjoint recurrence g_{t-1} = a_t g_t, g_t += C_t dy_t through them.  dB_t and dC_t are sums
+// over channels: reduced by shuffles inside a warp, then added to fp32 accumulators (one atomic per warp and
+// element); dA and dD are sums over batch and time: kept per thread and added once per CTA.  A second kernel
+// converts the accumulators to the storage dtype.
+#include <math.h>
+
+#include "nitrix_b200_scan.h"
+#include "sdpa_common.cuh"
+
+namespace nb200 {
+namespace {
+
+constexpr int kCh = 64;     // channels (threads) per CTA
+constexpr int kStep = 8;    // steps per staged chunk = checkpoint interval
+
+struct SsArgs {
+  const void *x, *delta, *A, *B, *C, *D, *dy;
+  void *y, *dx, *ddelta;
+  float* ckpt;            // [batch][chunks][N][Dc]
+  float *accB, *accC;     // [batch][L][N]
+  float *accA, *accD;     // [Dc][N], [Dc]
+  int batch, L, Dc, N, chunks;
+};
+
+__device__ __forceinline__ float warp_sum_ss(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T, int kN>
+__global__ void __launch_bounds__(kCh) ss_fwd_kernel(SsArgs a) {
+  __shared__ float sB[kStep][kN], sC[kStep][kN];
+  const int tid = threadIdx.x, d = blockIdx.x * kCh + tid, b = blockIdx.y;
+  const bool live = d < a.Dc;
+  const T* xp = reinterpret_cast<const T*>(a.x) + int64_t(b) * a.L * a.Dc + d;
+  const T* dp = reinterpret_cast<const T*>(a.delta) + int64_t(b) * a.L * a.Dc + d;
+  T* yp = reinterpret_cast<T*>(a.y) + int64_t(b) * a.L * a.Dc + d;
+  const T* Bp = reinterpret_cast<const T*>(a.B) + int64_t(b) * a.L * a.N;
+  const T* Cp = reinterpret_cast<const T*>(a.C) + int64_t(b) * a.L * a.N;
+  float Ar[kN], h[kN];
+#pragma unroll
+  for (int n = 0; n < kN; ++n) {
+    Ar[n] = (live && n < a.N) ? to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
+    h[n] = 0.f;
+  }
+  const float Dd = (a.D && live) ? to_f32<T>(reinterpret_cast<const T*>(a.D)[d]) : 0.f;
+  for (int c = 0; c < a.chunks; ++c) {
+    const int t0 = c * kStep;
+    __syncthreads();   // the previous chunk's rows are no longer read
+    for (int i = tid; i < kStep * a.N; i += kCh) {
+      const int s = i / a.N, n = i - s * a.N;
+      const bool in = t0 + s < a.L;
+      sB[s][n] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
+      sC[s][n] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
+    }
+    __syncthreads();
+    if (live) {
+#pragma unroll
+      for (int s = 0; s < kStep; ++s) {
+        const int t = t0 + s;
+        if (t < a.L) {
+          const float dl = to_f32<T>(dp[int64_t(t) * a.Dc]), xv = to_f32<T>(xp[int64_t(t) * a.Dc]);
+          float y = 0.f;
+#pragma unroll
+          for (int n = 0; n < kN; ++n)
+            if (n < a.N) {
+              h[n] = fmaf(expf(dl * Ar[n]), h[n], (dl * sB[s][n]) * xv);
+              y = fmaf(sC[s][n], h[n], y);
+            }
+          if (a.D) y = fmaf(Dd, xv, y);
+          yp[int64_t(t) * a.Dc] = from_f32<T>(y);
+        }
+      }
+      if (a.ckpt) {
+        float* ck = a.ckpt + (int64_t(b) * a.chunks + c) * a.N * a.Dc + d;
+#pragma unroll
+        for (int n = 0; n < kN; ++n)
+          if (n < a.N) ck[int64_t(n) * a.Dc] = h[n];
+      }
+    }
+  }
+}
+
+// Backward: chunks in reverse.  hs[0] = the state before the chunk (checkpoint c - 1, zero for the first chunk),
+// hs[s + 1] = the state after step s of the chunk, recomputed; then the adjoint recurrence from the chunk's last
+// step down.
+template <typename T, int kN>
+__global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
+  extern __shared__ float smem_ss[];
+  float* hs = smem_ss;                                   // [kStep + 1][kN][kCh]
+  float* sB = hs + (kStep + 1) * kN * kCh;               // [kStep][kN]
+  float* sC = sB + kStep * kN;                           // [kStep][kN]
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int d = blockIdx.x * kCh + tid, b = blockIdx.y;
+  const bool live = d < a.Dc;
+  const int64_t base = int64_t(b) * a.L * a.Dc + d;
+  const T* xp = reinterpret_cast<const T*>(a.x) + base;
+  const T* dp = reinterpret_cast<const T*>(a.delta) + base;
+  const T* gp = reinterpret_cast<const T*>(a.dy) + base;
+  T* dxp = reinterpret_cast<T*>(a.dx) + base;
+  T* ddp = reinterpret_cast<T*>(a.ddelta) + base;
+  const T* Bp = reinterpret_cast<const T*>(a.B) + int64_t(b) * a.L * a.N;
+  const T* Cp = reinterpret_cast<const T*>(a.C) + int64_t(b) * a.L * a.N;
+  float Ar[kN], g[kN], dA[kN];
+#pragma unroll
+  for (int n = 0; n < kN; ++n) {
+    Ar[n] = (live && n < a.N) ? to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
+    g[n] = dA[n] = 0.f;
+  }
+  const float Dd = (a.D && live) ? to_f32<T>(reinterpret_cast<const T*>(a.D)[d]) : 0.f;
+  float dD = 0.f;
+  for (int c = a.chunks - 1; c >= 0; --c) {
+    const int t0 = c * kStep;
+    __syncthreads();   // the previous chunk's rows and states are no longer read
+    for (int i = tid; i < kStep * a.N; i += kCh) {
+      const int s = i / a.N, n = i - s * a.N;
+      const bool in = t0 + s < a.L;
+      sB[s * kN + n] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
+      sC[s * kN + n] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
+    }
+    __syncthreads();
+    // ---- recompute the chunk's states ----
+    {
+      float h[kN];
+      const float* ck = c > 0 ? a.ckpt + (int64_t(b) * a.chunks + (c - 1)) * a.N * a.Dc + d : nullptr;
+#pragma unroll
+      for (int n = 0; n < kN; ++n) {
+        h[n] = (live && ck && n < a.N) ? ck[int64_t(n) * a.Dc] : 0.f;
+        hs[(0 * kN + n) * kCh + tid] = h[n];
+      }
+#pragma unroll
+      for (int s = 0; s < kStep; ++s) {
+        const int t = t0 + s;
+        if (live && t < a.L) {
+          const float dl = to_f32<T>(dp[int64_t(t) * a.Dc]), xv = to_f32<T>(xp[int64_t(t) * a.Dc]);
+#pragma unroll
+          for (int n = 0; n < kN; ++n)
+            if (n < a.N) h[n] = fmaf(expf(dl * Ar[n]), h[n], (dl * sB[s * kN + n]) * xv);
+        }
+#pragma unroll
+        for (int n = 0; n < kN; ++n) hs[((s + 1) * kN + n) * kCh + tid] = h[n];
+      }
+    }
+    // ---- adjoint recurrence, last step of the chunk first ----
+    for (int s = kStep - 1; s >= 0; --s) {
+      const int t = t0 + s;
+      if (t >= a.L) continue;   // (uniform over the CTA)
+      float dl = 0.f, xv = 0.f, gy = 0.f;
+      if (live) {
+        dl = to_f32<T>(dp[int64_t(t) * a.Dc]);
+        xv = to_f32<T>(xp[int64_t(t) * a.Dc]);
+        gy = to_f32<T>(gp[int64_t(t) * a.Dc]);
+      }
+      float ddl = 0.f, dxv = a.D ? Dd * gy : 0.f;
+      dD = fmaf(gy, xv, dD);
+#pragma unroll
+      for (int n = 0; n < kN; ++n) {
+        if (n < a.N) {   // (uniform over the CTA: the shuffles below are executed by whole warps)
+          // a dead lane (past the last channel) carries zeros throughout: dl = xv = gy = 0, g = 0
+          const float hprev = hs[(s * kN + n) * kCh + tid], hcur = hs[((s + 1) * kN + n) * kCh + tid];
+          const float av = expf(dl * Ar[n]);
+          const float bt = sB[s * kN + n];
+          g[n] = fmaf(sC[s * kN + n], gy, g[n]);       // dL/dh_t
+          const float da = g[n] * hprev * av;          // dL/d(delta_t A_n)
+          ddl = fmaf(da, Ar[n], ddl);
+          dA[n] = fmaf(da, dl, dA[n]);
+          ddl = fmaf(g[n] * bt, xv, ddl);
+          dxv = fmaf(g[n] * dl, bt, dxv);
+          // dB_t, dC_t: sums over the channels -- the warp by shuffles, then one atomic per warp and element
+          const float vb = warp_sum_ss(g[n] * dl * xv), vc = warp_sum_ss(gy * hcur);
+          if (lane == 0) {
+            atomicAdd(a.accB + (int64_t(b) * a.L + t) * a.N + n, vb);
+            atomicAdd(a.accC + (int64_t(b) * a.L + t) * a.N + n, vc);
+          }
+          g[n] *= av;                                  // dL/dh_{t-1} so far
+        }
+      }
+      if (live) {
+        dxp[int64_t(t) * a.Dc] = from_f32<T>(dxv);
+        ddp[int64_t(t) * a.Dc] = from_f32<T>(ddl);
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int n = 0; n < kN; ++n)
+      if (n < a.N) atomicAdd(a.accA + int64_t(d) * a.N + n, dA[n]);
+    if (a.accD) atomicAdd(a.accD + d, dD);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) ss_finish_kernel(const float* acc, T* out, int64_t n) {
+  const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i < n) out[i] = from_f32<T>(acc[i]);
+}
+
+int pick_n(int N) { return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : 0)); }
+
+int check_common(const nb200_selective_scan_params* p, const char* what) {
+  if (!p) { set_error("%s: NULL parameter block", what); return NB200_ERR_INVALID; }
+  if (p->struct_size != sizeof(nb200_selective_scan_params)) {
+    set_error("%s: ABI mismatch: struct_size %zu, library expects %zu", what, size_t(p->struct_size),
+              sizeof(nb200_selective_scan_params));
+    return NB200_ERR_INVALID;
+  }
+  if (p->dtype != NB200_F32 && p->dtype != NB200_BF16 && p->dtype != NB200_F16) { set_error("%s: bad dtype", what); return NB200_ERR_INVALID; }
+  if (p->batch < 0 || p->length < 0 || p->channels <= 0 || p->states <= 0) { set_error("%s: bad extents", what); return NB200_ERR_INVALID; }
+  if (!pick_n(p->states)) { set_error("%s: more than 64 states per channel (%d)", what, p->states); return NB200_ERR_UNSUPPORTED; }
+  if (p->batch > 65535) { set_error("%s: more than 65535 batch elements", what); return NB200_ERR_UNSUPPORTED; }
+  return NB200_OK;
+}
+
+SsArgs args_of(const nb200_selective_scan_params* p) {
+  SsArgs a{};
+  a.x = p->x; a.delta = p->delta; a.A = p->A; a.B = p->B; a.C = p->C; a.D = p->D; a.dy = p->dy;
+  a.y = p->y; a.dx = p->dx; a.ddelta = p->ddelta; a.ckpt = p->checkpoints;
+  a.batch = p->batch; a.L = p->length; a.Dc = p->channels; a.N = p->states;
+  a.chunks = (p->length + kStep - 1) / kStep;
+  return a;
+}
+
+template <typename T>
+int fwd_t(const nb200_selective_scan_params* p, cudaStream_t st) {
+  SsArgs a = args_of(p);
+  dim3 grid((p->channels + kCh - 1) / kCh, p->batch);
+  switch (pick_n(p->states)) {
+    case 16: ss_fwd_kernel<T, 16><<<grid, kCh, 0, st>>>(a); break;
+    case 32: ss_fwd_kernel<T, 32><<<grid, kCh, 0, st>>>(a); break;
+    default: ss_fwd_kernel<T, 64><<<grid, kCh, 0, st>>>(a); break;
+  }
+  count_launch();
+  return check_launch("selective_scan_fwd_kernel");
+}
+
+size_t acc_floats(const nb200_selective_scan_params* p) {
+  return 2 * size_t(p->batch) * p->length * p->states + size_t(p->channels) * p->states + size_t(p->channels);
+}
+
+template <typename T, int kN>
+int bwd_launch(const SsArgs& a, dim3 grid, cudaStream_t st) {
+  const size_t smem = sizeof(float) * (size_t(kStep + 1) * kN * kCh + 2 * kStep * kN);
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(ss_bwd_kernel<T, kN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+    set_error("selective_scan_bwd: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(cudaGetLastError()));
+    return NB200_ERR_LAUNCH;
+  }
+  ss_bwd_kernel<T, kN><<<grid, kCh, smem, st>>>(a);
+  count_launch();
+  return check_launch("selective_scan_bwd_kernel");
+}
+
+template <typename T>
+int bwd_t(const nb200_selective_scan_params* p, cudaStream_t st) {
+  SsArgs a = args_of(p);
+  const size_t need = sizeof(float) * acc_floats(p);
+  if (!p->workspace || p->workspace_bytes < need) {
+    set_error("selective_scan_bwd: workspace of %zu bytes needed (nb200_selective_scan_workspace_bytes), %zu given",
+              need, size_t(p->workspace_bytes));
+    return NB200_ERR_WORKSPACE;
+  }
+  float* acc = static_cast<float*>(p->workspace);
+  if (cudaMemsetAsync(acc, 0, need, st) != cudaSuccess) return check_launch("selective_scan_bwd: clearing the workspace");
+  const size_t bln = size_t(p->batch) * p->length * p->states, dn = size_t(p->channels) * p->states;
+  a.accB = acc; a.accC = acc + bln; a.accA = acc + 2 * bln; a.accD = p->D ? acc + 2 * bln + dn : nullptr;
+  if (p->batch > 0 && p->length > 0) {   // (nothing to walk otherwise: dA and dD are the zeros just written)
+    dim3 grid((p->channels + kCh - 1) / kCh, p->batch);
+    int rc;
+    switch (pick_n(p->states)) {
+      case 16: rc = bwd_launch<T, 16>(a, grid, st); break;
+      case 32: rc = bwd_launch<T, 32>(a, grid, st); break;
+      default: rc = bwd_launch<T, 64>(a, grid, st); break;
+    }
+    if (rc) return rc;
+  }
+  auto finish = [&](const float* src, void* dst, size_t n) {
+    if (!dst || n == 0) return;
+    ss_finish_kernel<T><<<unsigned((n + 255) / 256), 256, 0, st>>>(src, static_cast<T*>(dst), int64_t(n));
+    count_launch();
+  };
+  finish(a.accB, p->dB, bln);
+  finish(a.accC, p->dC, bln);
+  finish(a.accA, p->dA, dn);
+  if (p->D) finish(a.accD, p->dD, size_t(p->channels));
+  return check_launch("selective_scan_finish_kernel");
+}
+
+}  // namespace
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" NB200_API int nb200_selective_scan_workspace_bytes(const nb200_selective_scan_params* p, size_t* bytes) {
+  if (!bytes) { set_error("bytes out-pointer is NULL"); return NB200_ERR_INVALID; }
+  if (int rc = check_common(p, "selective_scan_workspace_bytes")) return rc;
+  *bytes = sizeof(float) * acc_floats(p);
+  return NB200_OK;
+}
+
+extern "C" NB200_API int nb200_selective_scan_checkpoint_bytes(const nb200_selective_scan_params* p, size_t* bytes) {
+  if (!bytes) { set_error("bytes out-pointer is NULL"); return NB200_ERR_INVALID; }
+  if (int rc = check_common(p, "selective_scan_checkpoint_bytes")) return rc;
+  *bytes = sizeof(float) * size_t(p->batch) * ((p->length + kStep - 1) / kStep) * p->states * p->channels;
+  return NB200_OK;
+}
+
+extern "C" NB200_API int nb200_selective_scan_fwd(const nb200_selective_scan_params* p, void* cuda_stream) {
+  if (int rc = check_common(p, "selective_scan_fwd")) return rc;
+  if (p->batch == 0 || p->length == 0) return NB200_OK;
+  if (!p->x || !p->delta || !p->A || !p->B || !p->C || !p->y) { set_error("selective_scan_fwd: NULL operand"); return NB200_ERR_INVALID; }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  switch (p->dtype) {
+    case NB200_F32: return fwd_t<float>(p, st);
+    case NB200_BF16: return fwd_t<__nv_bfloat16>(p, st);
+    default: return fwd_t<__half>(p, st);
+  }
+}
+
+extern "C" NB200_API int nb200_selective_scan_bwd(const nb200_selective_scan_params* p, void* cuda_stream) {
+  if (int rc = check_common(p, "selective_scan_bwd")) return rc;
+  const bool empty = p->batch == 0 || p->length == 0;
+  if (!p->dA || (p->D && !p->dD) ||
+      (!empty && (!p->x || !p->delta || !p->A || !p->B || !p->C || !p->dy || !p->dx || !p->ddelta || !p->dB || !p->dC ||
+                  (p->length > kStep && !p->checkpoints)))) {
+    set_error("selective_scan_bwd: NULL operand (x, delta, A, B, C, dy, checkpoints and every gradient are required)");
+    return NB200_ERR_INVALID;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  switch (p->dtype) {
+    case NB200_F32: return bwd_t<float>(p, st);
+    case NB200_BF16: return bwd_t<__nv_bfloat16>(p, st);
+    default: return bwd_t<__half>(p, st);
+  }
+}

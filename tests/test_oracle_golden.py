@@ -37,7 +37,7 @@ def _load(name):
 
 def test_manifest_digests():
     manifest = json.loads((GOLD / "MANIFEST.json").read_text())
-    assert len(manifest) == 6
+    assert len(manifest) == 7
     for fn, digest in manifest.items():
         assert hashlib.sha256((GOLD / fn).read_bytes()).hexdigest() == digest, fn
 
