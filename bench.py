@@ -29,7 +29,8 @@ Rank 0 prints ONE JSON line:
   both as an NCCL collective after the kernels and fused into the forward kernel's epilogue;
 * ``cpu_baseline``: the CPU oracle (torch, all host threads) on a fixed, bounded sample;
 * ``layer_norm`` (1 GPU): the sibling op on the shapes the reference's own norm benchmark uses -- time per forward
-  and per backward call, and the algorithmic bytes each moves per second against the measured copy bandwidth.
+  and per backward call, and the algorithmic bytes each moves per second against the measured copy bandwidth;
+* ``selective_scan`` (1 GPU): the second sibling op on a Mamba-block shape, time per forward and backward call.
 
 ``--impl reference`` times only that CPU implementation (the reference's own ``jnp`` path cannot run: jax is not
 installed; the op-for-op torch restatement stands in, ``cpu_baseline.kind = "port"``).
@@ -506,13 +507,14 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-workload table and the partition record")
     ap.add_argument("--layer-norm-only", action="store_true",
-                    help="print only the sibling op's record (small: for profiling captures)")
+                    help="print only the sibling ops' records (small: for profiling captures)")
     args = ap.parse_args()
 
     if args.layer_norm_only:
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(dev)
-        print(json.dumps({"layer_norm": layer_norm_record(dev, load_peaks())}))
+        print(json.dumps({"layer_norm": layer_norm_record(dev, load_peaks()),
+                          "selective_scan": selective_scan_record(dev, load_peaks())}))
         return
 
     rank = int(os.environ.get("RANK", "0"))
@@ -653,6 +655,14 @@ def main():
             layer_norm = {"error": str(exc)[:200]}
             torch.cuda.synchronize()
 
+    selective_scan = None
+    if world == 1 and not args.no_extra and not args.batch:
+        try:
+            selective_scan = selective_scan_record(dev, peaks)
+        except Exception as exc:  # noqa: BLE001
+            selective_scan = {"error": str(exc)[:200]}
+            torch.cuda.synchronize()
+
     # ---- the split the configurations name: c5 heads / c4 sequences over the GPUs of the box ----
     partition = None
     if world > 1 and not args.no_extra:
@@ -675,7 +685,7 @@ def main():
             "config": config, "clocks": headline_clocks, "e2e": e2e,
             "gpu_launches": int(headline_launches) * args.steps * m["blocks"], "launches_per_step": headline_launches,
             "roofline": roofline, "cpu_baseline": cpu, "workloads": workloads, "partition": partition,
-            "layer_norm": layer_norm}
+            "layer_norm": layer_norm, "selective_scan": selective_scan}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -746,6 +756,81 @@ def layer_norm_record(dev, peaks):
         del xs, dys, stats
         torch.cuda.empty_cache()
     return {"unit": "GB/s of algorithmic bytes per call; peak = measured copy bandwidth",
+            "peak_gbs": peaks["hbm"] if peaks else None, "shapes": out}
+
+
+# (batch, length, channels, states): a Mamba block's scan at model width 1024 (d_inner 2048, 16 states)
+SELECTIVE_SCAN_SHAPES = [("f32", (8, 1024, 2048, 16)), ("bf16", (8, 2048, 2048, 16))]
+
+
+def selective_scan_record(dev, peaks):
+    """Forward and backward of the selective scan on device-resident operands: four operand sets replayed back to
+    back as one CUDA graph; time per call = median replay / 4.  Reported with the state updates per second
+    (batch x length x channels x states per pass) and the algorithmic bytes per second -- forward x, delta in and y
+    out; backward x, delta, dy in and dx, ddelta out, plus the checkpoints either way -- against the measured copy
+    bandwidth.  The recurrence is sequential in time: the parallelism is batch x channels threads."""
+    from nitrix_b200.nn import ssm
+
+    out = []
+    for dt_name, (bsz, length, d, n) in SELECTIVE_SCAN_SHAPES:
+        dt = torch.bfloat16 if dt_name == "bf16" else torch.float32
+        esz = 2 if dt_name == "bf16" else 4
+        g = torch.Generator(device=dev).manual_seed(0)
+        sets = []
+        for _ in range(4):
+            x = torch.randn(bsz, length, d, device=dev, generator=g).to(dt)
+            delta = (torch.rand(bsz, length, d, device=dev, generator=g) * 0.5 + 0.01).to(dt)
+            a_mat = (-(torch.rand(d, n, device=dev, generator=g) * 1.5 + 0.2)).to(dt)
+            b_mat = torch.randn(bsz, length, n, device=dev, generator=g).to(dt)
+            c_mat = torch.randn(bsz, length, n, device=dev, generator=g).to(dt)
+            skip = torch.randn(d, device=dev, generator=g).to(dt)
+            dy = torch.randn(bsz, length, d, device=dev, generator=g).to(dt)
+            ck = ssm.selective_scan_forward(x, delta, a_mat, b_mat, c_mat, skip, True)[1]
+            sets.append((x, delta, a_mat, b_mat, c_mat, skip, ck, dy))
+
+        def graph_ms(fn):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    fn()
+            ts = []
+            for _ in range(6):
+                a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                graph.replay()
+                e.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(e))
+            return statistics.median(ts[2:]) / len(sets)
+
+        def fwd_all():
+            for x, delta, a_mat, b_mat, c_mat, skip, _, _ in sets:
+                ssm.selective_scan_forward(x, delta, a_mat, b_mat, c_mat, skip, True)
+
+        def bwd_all():
+            for x, delta, a_mat, b_mat, c_mat, skip, ck, dy in sets:
+                ssm.selective_scan_backward(x, delta, a_mat, b_mat, c_mat, skip, ck, dy)
+
+        t_f, t_b = graph_ms(fwd_all), graph_ms(bwd_all)
+        updates = bsz * length * d * n
+        ck_bytes = bsz * ((length + 7) // 8) * d * n * 4
+        f_bytes = 3 * bsz * length * d * esz + ck_bytes
+        b_bytes = 5 * bsz * length * d * esz + ck_bytes
+        rec = {"shape": [bsz, length, d, n], "dtype": dt_name, "fwd_ms": t_f, "bwd_ms": t_b,
+               "fwd_gupdates_per_s": updates / (t_f * 1e-3) / 1e9, "bwd_gupdates_per_s": updates / (t_b * 1e-3) / 1e9,
+               "fwd_gbs": f_bytes / (t_f * 1e-3) / 1e9, "bwd_gbs": b_bytes / (t_b * 1e-3) / 1e9}
+        if peaks:
+            rec["fwd_frac_of_hbm"] = rec["fwd_gbs"] / peaks["hbm"]
+            rec["bwd_frac_of_hbm"] = rec["bwd_gbs"] / peaks["hbm"]
+        out.append(rec)
+        del sets
+        torch.cuda.empty_cache()
+    return {"unit": "state updates per second; GB/s of algorithmic bytes against the measured copy bandwidth",
             "peak_gbs": peaks["hbm"] if peaks else None, "shapes": out}
 
 

@@ -36,15 +36,61 @@ struct SsArgs {
   int batch, L, Dc, N, chunks;
 };
 
+// a_t = exp(delta_t A) as one multiply and one ex2.approx (relative error 2^-22): A is held pre-multiplied by log2(e)
+__device__ __forceinline__ float ex2_ss(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kLog2eSs = 1.4426950408889634f;
+
 __device__ __forceinline__ float warp_sum_ss(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
+// A chunk's operands as this thread holds them between the loads and their use: its channel's delta, x (and dy) for
+// the eight steps, and its share of the chunk's B / C rows (element tid + 64 j of the [8][N] block).  The loads for
+// chunk c + 1 are issued before chunk c is computed, so that their latency is covered by a chunk of arithmetic.
+template <int kN, bool kDy>
+struct ChunkRegs {
+  static constexpr int kShare = kStep * kN / kCh;   // 2, 4 or 8
+  float dl[kStep], xv[kStep], gy[kDy ? kStep : 1];
+  float bq[kShare], cq[kShare];
+};
+
+template <typename T, int kN, bool kDy>
+__device__ __forceinline__ void load_chunk(ChunkRegs<kN, kDy>& r, const SsArgs& a, bool live, const T* dp, const T* xp,
+                                           const T* gp, const T* Bp, const T* Cp, int t0, int tid) {
+#pragma unroll
+  for (int s = 0; s < kStep; ++s) {
+    const bool in = live && t0 + s < a.L;
+    r.dl[s] = in ? to_f32<T>(dp[int64_t(t0 + s) * a.Dc]) : 0.f;
+    r.xv[s] = in ? to_f32<T>(xp[int64_t(t0 + s) * a.Dc]) : 0.f;
+    if constexpr (kDy) r.gy[s] = in ? to_f32<T>(gp[int64_t(t0 + s) * a.Dc]) : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < ChunkRegs<kN, kDy>::kShare; ++j) {
+    const int i = tid + kCh * j, s = i / kN, n = i - s * kN;   // (compile-time divisor)
+    const bool in = n < a.N && t0 + s < a.L;
+    r.bq[j] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
+    r.cq[j] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
+  }
+}
+
+template <int kN, bool kDy>
+__device__ __forceinline__ void put_rows(const ChunkRegs<kN, kDy>& r, float* sB, float* sC, int tid) {
+#pragma unroll
+  for (int j = 0; j < ChunkRegs<kN, kDy>::kShare; ++j) {
+    sB[tid + kCh * j] = r.bq[j];   // [kStep][kN] row-major = element tid + 64 j
+    sC[tid + kCh * j] = r.cq[j];
+  }
+}
+
 template <typename T, int kN>
 __global__ void __launch_bounds__(kCh) ss_fwd_kernel(SsArgs a) {
-  __shared__ float sB[kStep][kN], sC[kStep][kN];
+  __shared__ float sB[2][kStep * kN], sC[2][kStep * kN];   // double-buffered: one barrier per chunk
   const int tid = threadIdx.x, d = blockIdx.x * kCh + tid, b = blockIdx.y;
   const bool live = d < a.Dc;
   const T* xp = reinterpret_cast<const T*>(a.x) + int64_t(b) * a.L * a.Dc + d;
@@ -55,32 +101,32 @@ __global__ void __launch_bounds__(kCh) ss_fwd_kernel(SsArgs a) {
   float Ar[kN], h[kN];
 #pragma unroll
   for (int n = 0; n < kN; ++n) {
-    Ar[n] = (live && n < a.N) ? to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
+    Ar[n] = (live && n < a.N) ? kLog2eSs * to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
     h[n] = 0.f;
   }
   const float Dd = (a.D && live) ? to_f32<T>(reinterpret_cast<const T*>(a.D)[d]) : 0.f;
+  ChunkRegs<kN, false> next;
+  load_chunk<T, kN, false>(next, a, live, dp, xp, nullptr, Bp, Cp, 0, tid);
   for (int c = 0; c < a.chunks; ++c) {
     const int t0 = c * kStep;
-    __syncthreads();   // the previous chunk's rows are no longer read
-    for (int i = tid; i < kStep * a.N; i += kCh) {
-      const int s = i / a.N, n = i - s * a.N;
-      const bool in = t0 + s < a.L;
-      sB[s][n] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
-      sC[s][n] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
-    }
-    __syncthreads();
+    const ChunkRegs<kN, false> cur = next;
+    float* rb = sB[c & 1];
+    float* rc = sC[c & 1];
+    put_rows<kN, false>(cur, rb, rc, tid);
+    __syncthreads();   // (the buffer written two chunks ago was last read before the previous barrier)
+    if (c + 1 < a.chunks) load_chunk<T, kN, false>(next, a, live, dp, xp, nullptr, Bp, Cp, t0 + kStep, tid);
     if (live) {
 #pragma unroll
       for (int s = 0; s < kStep; ++s) {
         const int t = t0 + s;
         if (t < a.L) {
-          const float dl = to_f32<T>(dp[int64_t(t) * a.Dc]), xv = to_f32<T>(xp[int64_t(t) * a.Dc]);
+          const float dl = cur.dl[s], xv = cur.xv[s];
           float y = 0.f;
 #pragma unroll
           for (int n = 0; n < kN; ++n)
             if (n < a.N) {
-              h[n] = fmaf(expf(dl * Ar[n]), h[n], (dl * sB[s][n]) * xv);
-              y = fmaf(sC[s][n], h[n], y);
+              h[n] = fmaf(ex2_ss(dl * Ar[n]), h[n], (dl * rb[s * kN + n]) * xv);
+              y = fmaf(rc[s * kN + n], h[n], y);
             }
           if (a.D) y = fmaf(Dd, xv, y);
           yp[int64_t(t) * a.Dc] = from_f32<T>(y);
@@ -103,8 +149,8 @@ template <typename T, int kN>
 __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
   extern __shared__ float smem_ss[];
   float* hs = smem_ss;                                   // [kStep + 1][kN][kCh]
-  float* sB = hs + (kStep + 1) * kN * kCh;               // [kStep][kN]
-  float* sC = sB + kStep * kN;                           // [kStep][kN]
+  float* sBb = hs + (kStep + 1) * kN * kCh;              // 2 x [kStep][kN]
+  float* sCb = sBb + 2 * kStep * kN;                     // 2 x [kStep][kN]
   const int tid = threadIdx.x, lane = tid & 31;
   const int d = blockIdx.x * kCh + tid, b = blockIdx.y;
   const bool live = d < a.Dc;
@@ -119,21 +165,24 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
   float Ar[kN], g[kN], dA[kN];
 #pragma unroll
   for (int n = 0; n < kN; ++n) {
-    Ar[n] = (live && n < a.N) ? to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
+    Ar[n] = (live && n < a.N) ? kLog2eSs * to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
     g[n] = dA[n] = 0.f;
   }
   const float Dd = (a.D && live) ? to_f32<T>(reinterpret_cast<const T*>(a.D)[d]) : 0.f;
   float dD = 0.f;
+  ChunkRegs<kN, true> next;
+  if (a.chunks > 0) load_chunk<T, kN, true>(next, a, live, dp, xp, gp, Bp, Cp, (a.chunks - 1) * kStep, tid);
   for (int c = a.chunks - 1; c >= 0; --c) {
     const int t0 = c * kStep;
-    __syncthreads();   // the previous chunk's rows and states are no longer read
-    for (int i = tid; i < kStep * a.N; i += kCh) {
-      const int s = i / a.N, n = i - s * a.N;
-      const bool in = t0 + s < a.L;
-      sB[s * kN + n] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
-      sC[s * kN + n] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
-    }
-    __syncthreads();
+    const ChunkRegs<kN, true> cur = next;
+    const float* dls = cur.dl;
+    const float* xvs = cur.xv;
+    const float* gys = cur.gy;
+    float* sB = sBb + (c & 1) * kStep * kN;
+    float* sC = sCb + (c & 1) * kStep * kN;
+    put_rows<kN, true>(cur, sB, sC, tid);
+    __syncthreads();   // (the buffer written two chunks ago was last read before the previous barrier)
+    if (c > 0) load_chunk<T, kN, true>(next, a, live, dp, xp, gp, Bp, Cp, t0 - kStep, tid);
     // ---- recompute the chunk's states ----
     {
       float h[kN];
@@ -147,25 +196,21 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
       for (int s = 0; s < kStep; ++s) {
         const int t = t0 + s;
         if (live && t < a.L) {
-          const float dl = to_f32<T>(dp[int64_t(t) * a.Dc]), xv = to_f32<T>(xp[int64_t(t) * a.Dc]);
+          const float dl = dls[s], xv = xvs[s];
 #pragma unroll
           for (int n = 0; n < kN; ++n)
-            if (n < a.N) h[n] = fmaf(expf(dl * Ar[n]), h[n], (dl * sB[s * kN + n]) * xv);
+            if (n < a.N) h[n] = fmaf(ex2_ss(dl * Ar[n]), h[n], (dl * sB[s * kN + n]) * xv);
         }
 #pragma unroll
         for (int n = 0; n < kN; ++n) hs[((s + 1) * kN + n) * kCh + tid] = h[n];
       }
     }
     // ---- adjoint recurrence, last step of the chunk first ----
+#pragma unroll
     for (int s = kStep - 1; s >= 0; --s) {
       const int t = t0 + s;
       if (t >= a.L) continue;   // (uniform over the CTA)
-      float dl = 0.f, xv = 0.f, gy = 0.f;
-      if (live) {
-        dl = to_f32<T>(dp[int64_t(t) * a.Dc]);
-        xv = to_f32<T>(xp[int64_t(t) * a.Dc]);
-        gy = to_f32<T>(gp[int64_t(t) * a.Dc]);
-      }
+      const float dl = dls[s], xv = xvs[s], gy = gys[s];
       float ddl = 0.f, dxv = a.D ? Dd * gy : 0.f;
       dD = fmaf(gy, xv, dD);
 #pragma unroll
@@ -173,11 +218,11 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
         if (n < a.N) {   // (uniform over the CTA: the shuffles below are executed by whole warps)
           // a dead lane (past the last channel) carries zeros throughout: dl = xv = gy = 0, g = 0
           const float hprev = hs[(s * kN + n) * kCh + tid], hcur = hs[((s + 1) * kN + n) * kCh + tid];
-          const float av = expf(dl * Ar[n]);
+          const float av = ex2_ss(dl * Ar[n]);
           const float bt = sB[s * kN + n];
           g[n] = fmaf(sC[s * kN + n], gy, g[n]);       // dL/dh_t
-          const float da = g[n] * hprev * av;          // dL/d(delta_t A_n)
-          ddl = fmaf(da, Ar[n], ddl);
+          const float da = g[n] * hprev * av;          // dL/d(delta_t A_n), natural units
+          ddl = fmaf(da, Ar[n] * (1.f / kLog2eSs), ddl);
           dA[n] = fmaf(da, dl, dA[n]);
           ddl = fmaf(g[n] * bt, xv, ddl);
           dxv = fmaf(g[n] * dl, bt, dxv);
@@ -254,7 +299,7 @@ size_t acc_floats(const nb200_selective_scan_params* p) {
 
 template <typename T, int kN>
 int bwd_launch(const SsArgs& a, dim3 grid, cudaStream_t st) {
-  const size_t smem = sizeof(float) * (size_t(kStep + 1) * kN * kCh + 2 * kStep * kN);
+  const size_t smem = sizeof(float) * (size_t(kStep + 1) * kN * kCh + 4 * kStep * kN);
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(ss_bwd_kernel<T, kN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
     set_error("selective_scan_bwd: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(cudaGetLastError()));
