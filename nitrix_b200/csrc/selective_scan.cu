@@ -13,9 +13,10 @@
 // materialised: the forward leaves the state after every eighth step in a checkpoint array (batch, l / 8, n, d), and
 // the backward walks the chunks in reverse, recomputes a chunk's eight states from its checkpoint into shared
 // memory and runs the adjoint recurrence g_{t-1} = a_t g_t, g_t += C_t dy_t through them.  dB_t and dC_t are sums
-// over channels: reduced by shuffles inside a warp, then added to fp32 accumulators (one atomic per warp and
-// element); dA and dD are sums over batch and time: kept per thread and added once per CTA.  A second kernel
-// converts the accumulators to the storage dtype.
+// over channels: the threads' terms of a chunk go into a shared-memory tile whose columns the CTA adds once per chunk
+// (up to 32 states; at 64 the warps reduce by shuffles), then one atomic per sum into fp32 accumulators; dA and dD
+// are sums over batch and time: kept per thread and added once at the end.  A second kernel converts the
+// accumulators to the storage dtype.
 #include <math.h>
 
 #include "nitrix_b200_scan.h"
@@ -151,6 +152,10 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
   float* hs = smem_ss;                                   // [kStep + 1][kN][kCh]
   float* sBb = hs + (kStep + 1) * kN * kCh;              // 2 x [kStep][kN]
   float* sCb = sBb + 2 * kStep * kN;                     // 2 x [kStep][kN]
+  // up to 32 states: the chunk's dB / dC terms as a tile [kStep][2][kN][kCh] (128 KB at 32 states); 64 states would
+  // not fit beside the states and use warp shuffles instead
+  constexpr bool kTile = kN <= 32;
+  float* ct = sCb + 2 * kStep * kN;
   const int tid = threadIdx.x, lane = tid & 31;
   const int d = blockIdx.x * kCh + tid, b = blockIdx.y;
   const bool live = d < a.Dc;
@@ -226,11 +231,18 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
           dA[n] = fmaf(da, dl, dA[n]);
           ddl = fmaf(g[n] * bt, xv, ddl);
           dxv = fmaf(g[n] * dl, bt, dxv);
-          // dB_t, dC_t: sums over the channels -- the warp by shuffles, then one atomic per warp and element
-          const float vb = warp_sum_ss(g[n] * dl * xv), vc = warp_sum_ss(gy * hcur);
-          if (lane == 0) {
-            atomicAdd(a.accB + (int64_t(b) * a.L + t) * a.N + n, vb);
-            atomicAdd(a.accC + (int64_t(b) * a.L + t) * a.N + n, vc);
+          // dB_t, dC_t: sums over the channels
+          if constexpr (kTile) {
+            // this thread's terms go into the chunk's tile; the CTA adds the columns once per chunk (below)
+            ct[((s * 2 + 0) * kN + n) * kCh + tid] = g[n] * dl * xv;
+            ct[((s * 2 + 1) * kN + n) * kCh + tid] = gy * hcur;
+          } else {
+            // the warp by shuffles, then one atomic per warp and element
+            const float vb = warp_sum_ss(g[n] * dl * xv), vc = warp_sum_ss(gy * hcur);
+            if (lane == 0) {
+              atomicAdd(a.accB + (int64_t(b) * a.L + t) * a.N + n, vb);
+              atomicAdd(a.accC + (int64_t(b) * a.L + t) * a.N + n, vc);
+            }
           }
           g[n] *= av;                                  // dL/dh_{t-1} so far
         }
@@ -239,6 +251,23 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
         dxp[int64_t(t) * a.Dc] = from_f32<T>(dxv);
         ddp[int64_t(t) * a.Dc] = from_f32<T>(ddl);
       }
+    }
+    if constexpr (kTile) {
+      // column sums of the chunk's tile: sum v = (step, B or C, n) over the 64 channels, read with a per-thread skew
+      // so that the threads of a warp hit different banks; then one atomic per sum and CTA
+      __syncthreads();
+      for (int v = tid; v < kStep * 2 * kN; v += kCh) {
+        const int sv = v / (2 * kN), rest = v - sv * 2 * kN, which = rest / kN, n = rest - which * kN;
+        const int t = t0 + sv;
+        if (n < a.N && t < a.L) {
+          const float* col = ct + v * kCh;
+          float acc = 0.f;
+#pragma unroll 8
+          for (int k = 0; k < kCh; ++k) acc += col[(k + tid) & (kCh - 1)];
+          atomicAdd((which ? a.accC : a.accB) + (int64_t(b) * a.L + t) * a.N + n, acc);
+        }
+      }
+      // (the tile is rewritten only after the next chunk's barrier)
     }
   }
   if (live) {
@@ -299,7 +328,8 @@ size_t acc_floats(const nb200_selective_scan_params* p) {
 
 template <typename T, int kN>
 int bwd_launch(const SsArgs& a, dim3 grid, cudaStream_t st) {
-  const size_t smem = sizeof(float) * (size_t(kStep + 1) * kN * kCh + 4 * kStep * kN);
+  const size_t smem = sizeof(float) * (size_t(kStep + 1) * kN * kCh + 4 * kStep * kN +
+                                       (kN <= 32 ? size_t(kStep) * 2 * kN * kCh : 0));
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(ss_bwd_kernel<T, kN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
     set_error("selective_scan_bwd: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(cudaGetLastError()));
