@@ -89,55 +89,97 @@ __device__ __forceinline__ void put_rows(const ChunkRegs<kN, kDy>& r, float* sB,
   }
 }
 
+// Forward.  Four adjacent lanes share a channel and hold a quarter of its states each (the readout is a sum over
+// the four lanes: two shuffles per step): four times the warps of one-thread-per-channel for the same work, which is
+// what the sequential recurrence lacks -- one warp per scheduler left the issue slots 20 % busy.  A CTA is 64 channels
+// = 256 threads.
+constexpr int kSplit = 4;
+constexpr int kFwdThreads = kCh * kSplit;
+
 template <typename T, int kN>
-__global__ void __launch_bounds__(kCh) ss_fwd_kernel(SsArgs a) {
-  __shared__ float sB[2][kStep * kN], sC[2][kStep * kN];   // double-buffered: one barrier per chunk
-  const int tid = threadIdx.x, d = blockIdx.x * kCh + tid, b = blockIdx.y;
+__global__ void __launch_bounds__(kFwdThreads) ss_fwd_kernel(SsArgs a) {
+  constexpr int kQ = kN / kSplit;                            // states per thread
+  constexpr int kRows = kStep * kN;                          // elements of a chunk's B (or C) block
+  constexpr int kShare = (kRows + kFwdThreads - 1) / kFwdThreads;
+  __shared__ float sB[2][kRows], sC[2][kRows];               // double-buffered: one barrier per chunk
+  const int tid = threadIdx.x, part = tid & (kSplit - 1);
+  const int d = blockIdx.x * kCh + (tid >> 2), b = blockIdx.y;
   const bool live = d < a.Dc;
   const T* xp = reinterpret_cast<const T*>(a.x) + int64_t(b) * a.L * a.Dc + d;
   const T* dp = reinterpret_cast<const T*>(a.delta) + int64_t(b) * a.L * a.Dc + d;
   T* yp = reinterpret_cast<T*>(a.y) + int64_t(b) * a.L * a.Dc + d;
   const T* Bp = reinterpret_cast<const T*>(a.B) + int64_t(b) * a.L * a.N;
   const T* Cp = reinterpret_cast<const T*>(a.C) + int64_t(b) * a.L * a.N;
-  float Ar[kN], h[kN];
+  float Ar[kQ], h[kQ];
 #pragma unroll
-  for (int n = 0; n < kN; ++n) {
-    Ar[n] = (live && n < a.N) ? kLog2eSs * to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
-    h[n] = 0.f;
+  for (int q = 0; q < kQ; ++q) {
+    const int n = part * kQ + q;
+    Ar[q] = (live && n < a.N) ? kLog2eSs * to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
+    h[q] = 0.f;
   }
   const float Dd = (a.D && live) ? to_f32<T>(reinterpret_cast<const T*>(a.D)[d]) : 0.f;
-  ChunkRegs<kN, false> next;
-  load_chunk<T, kN, false>(next, a, live, dp, xp, nullptr, Bp, Cp, 0, tid);
+  // the next chunk's operands: issued before the current chunk is computed
+  float ndl[kStep], nxv[kStep], nbq[kShare], ncq[kShare];
+  auto load = [&](int t0) {
+#pragma unroll
+    for (int s = 0; s < kStep; ++s) {
+      const bool in = live && t0 + s < a.L;
+      ndl[s] = in ? to_f32<T>(dp[int64_t(t0 + s) * a.Dc]) : 0.f;
+      nxv[s] = in ? to_f32<T>(xp[int64_t(t0 + s) * a.Dc]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kShare; ++j) {
+      const int i = tid + kFwdThreads * j, s = i / kN, n = i - s * kN;   // (compile-time divisor)
+      const bool in = i < kRows && n < a.N && t0 + s < a.L;
+      nbq[j] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
+      ncq[j] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
+    }
+  };
+  load(0);
   for (int c = 0; c < a.chunks; ++c) {
     const int t0 = c * kStep;
-    const ChunkRegs<kN, false> cur = next;
+    float dls[kStep], xvs[kStep];
+#pragma unroll
+    for (int s = 0; s < kStep; ++s) {
+      dls[s] = ndl[s];
+      xvs[s] = nxv[s];
+    }
     float* rb = sB[c & 1];
     float* rc = sC[c & 1];
-    put_rows<kN, false>(cur, rb, rc, tid);
-    __syncthreads();   // (the buffer written two chunks ago was last read before the previous barrier)
-    if (c + 1 < a.chunks) load_chunk<T, kN, false>(next, a, live, dp, xp, nullptr, Bp, Cp, t0 + kStep, tid);
-    if (live) {
 #pragma unroll
-      for (int s = 0; s < kStep; ++s) {
-        const int t = t0 + s;
-        if (t < a.L) {
-          const float dl = cur.dl[s], xv = cur.xv[s];
-          float y = 0.f;
-#pragma unroll
-          for (int n = 0; n < kN; ++n)
-            if (n < a.N) {
-              h[n] = fmaf(ex2_ss(dl * Ar[n]), h[n], (dl * rb[s * kN + n]) * xv);
-              y = fmaf(rc[s * kN + n], h[n], y);
-            }
-          if (a.D) y = fmaf(Dd, xv, y);
-          yp[int64_t(t) * a.Dc] = from_f32<T>(y);
-        }
+    for (int j = 0; j < kShare; ++j) {
+      const int i = tid + kFwdThreads * j;
+      if (i < kRows) {
+        rb[i] = nbq[j];
+        rc[i] = ncq[j];
       }
-      if (a.ckpt) {
-        float* ck = a.ckpt + (int64_t(b) * a.chunks + c) * a.N * a.Dc + d;
+    }
+    __syncthreads();   // (the buffer written two chunks ago was last read before the previous barrier)
+    if (c + 1 < a.chunks) load(t0 + kStep);
 #pragma unroll
-        for (int n = 0; n < kN; ++n)
-          if (n < a.N) ck[int64_t(n) * a.Dc] = h[n];
+    for (int s = 0; s < kStep; ++s) {
+      const int t = t0 + s;
+      if (t < a.L) {   // (uniform over the CTA: the shuffles below are executed by whole warps)
+        const float dl = dls[s], xv = xvs[s];
+        float y = 0.f;
+#pragma unroll
+        for (int q = 0; q < kQ; ++q) {
+          const int n = part * kQ + q;
+          h[q] = fmaf(ex2_ss(dl * Ar[q]), h[q], (dl * rb[s * kN + n]) * xv);   // (rows past N are zero)
+          y = fmaf(rc[s * kN + n], h[q], y);
+        }
+        y += __shfl_xor_sync(0xffffffffu, y, 1);
+        y += __shfl_xor_sync(0xffffffffu, y, 2);
+        if (a.D) y = fmaf(Dd, xv, y);
+        if (live && part == 0) yp[int64_t(t) * a.Dc] = from_f32<T>(y);
+      }
+    }
+    if (a.ckpt && live) {
+      float* ck = a.ckpt + (int64_t(b) * a.chunks + c) * a.N * a.Dc + d;
+#pragma unroll
+      for (int q = 0; q < kQ; ++q) {
+        const int n = part * kQ + q;
+        if (n < a.N) ck[int64_t(n) * a.Dc] = h[q];
       }
     }
   }
@@ -314,9 +356,9 @@ int fwd_t(const nb200_selective_scan_params* p, cudaStream_t st) {
   SsArgs a = args_of(p);
   dim3 grid((p->channels + kCh - 1) / kCh, p->batch);
   switch (pick_n(p->states)) {
-    case 16: ss_fwd_kernel<T, 16><<<grid, kCh, 0, st>>>(a); break;
-    case 32: ss_fwd_kernel<T, 32><<<grid, kCh, 0, st>>>(a); break;
-    default: ss_fwd_kernel<T, 64><<<grid, kCh, 0, st>>>(a); break;
+    case 16: ss_fwd_kernel<T, 16><<<grid, kFwdThreads, 0, st>>>(a); break;
+    case 32: ss_fwd_kernel<T, 32><<<grid, kFwdThreads, 0, st>>>(a); break;
+    default: ss_fwd_kernel<T, 64><<<grid, kFwdThreads, 0, st>>>(a); break;
   }
   count_launch();
   return check_launch("selective_scan_fwd_kernel");
