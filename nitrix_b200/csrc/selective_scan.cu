@@ -7,9 +7,10 @@
 // per batch element, channel d and state n; x, delta (batch, l, d), A (d, n), B, C (batch, l, n), D (d); fp32
 // recurrence and readout whatever the storage dtype (reference _reference.py:262-279).
 //
-// One thread owns one channel of one batch element and walks the sequence with its n states in registers (the
-// recurrence is sequential in t; the parallelism is batch x channels); a CTA is 64 channels, and the B_t / C_t rows
-// its threads share are staged through shared memory eight steps at a time.  Nothing of size (l, d, n) is ever
+// Four lanes own one channel of one batch element, a quarter of its n states each, and walk the sequence with them in
+// registers (the recurrence is sequential in t; the parallelism is batch x channels x 4); a CTA is 64 channels, and
+// the B_t / C_t rows its threads share are staged through shared memory eight steps at a time, double-buffered, with
+// the next chunk's operands already in flight.  Nothing of size (l, d, n) is ever
 // materialised: the forward leaves the state after every eighth step in a checkpoint array (batch, l / 8, n, d), and
 // the backward walks the chunks in reverse, recomputes a chunk's eight states from its checkpoint into shared
 // memory and runs the adjoint recurrence g_{t-1} = a_t g_t, g_t += C_t dy_t through them.  dB_t and dC_t are sums
@@ -44,50 +45,6 @@ __device__ __forceinline__ float ex2_ss(float x) {
   return y;
 }
 constexpr float kLog2eSs = 1.4426950408889634f;
-
-__device__ __forceinline__ float warp_sum_ss(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-
-// A chunk's operands as this thread holds them between the loads and their use: its channel's delta, x (and dy) for
-// the eight steps, and its share of the chunk's B / C rows (element tid + 64 j of the [8][N] block).  The loads for
-// chunk c + 1 are issued before chunk c is computed, so that their latency is covered by a chunk of arithmetic.
-template <int kN, bool kDy>
-struct ChunkRegs {
-  static constexpr int kShare = kStep * kN / kCh;   // 2, 4 or 8
-  float dl[kStep], xv[kStep], gy[kDy ? kStep : 1];
-  float bq[kShare], cq[kShare];
-};
-
-template <typename T, int kN, bool kDy>
-__device__ __forceinline__ void load_chunk(ChunkRegs<kN, kDy>& r, const SsArgs& a, bool live, const T* dp, const T* xp,
-                                           const T* gp, const T* Bp, const T* Cp, int t0, int tid) {
-#pragma unroll
-  for (int s = 0; s < kStep; ++s) {
-    const bool in = live && t0 + s < a.L;
-    r.dl[s] = in ? to_f32<T>(dp[int64_t(t0 + s) * a.Dc]) : 0.f;
-    r.xv[s] = in ? to_f32<T>(xp[int64_t(t0 + s) * a.Dc]) : 0.f;
-    if constexpr (kDy) r.gy[s] = in ? to_f32<T>(gp[int64_t(t0 + s) * a.Dc]) : 0.f;
-  }
-#pragma unroll
-  for (int j = 0; j < ChunkRegs<kN, kDy>::kShare; ++j) {
-    const int i = tid + kCh * j, s = i / kN, n = i - s * kN;   // (compile-time divisor)
-    const bool in = n < a.N && t0 + s < a.L;
-    r.bq[j] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
-    r.cq[j] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
-  }
-}
-
-template <int kN, bool kDy>
-__device__ __forceinline__ void put_rows(const ChunkRegs<kN, kDy>& r, float* sB, float* sC, int tid) {
-#pragma unroll
-  for (int j = 0; j < ChunkRegs<kN, kDy>::kShare; ++j) {
-    sB[tid + kCh * j] = r.bq[j];   // [kStep][kN] row-major = element tid + 64 j
-    sC[tid + kCh * j] = r.cq[j];
-  }
-}
 
 // Forward.  Four adjacent lanes share a channel and hold a quarter of its states each (the readout is a sum over
 // the four lanes: two shuffles per step): four times the warps of one-thread-per-channel for the same work, which is
@@ -185,21 +142,24 @@ __global__ void __launch_bounds__(kFwdThreads) ss_fwd_kernel(SsArgs a) {
   }
 }
 
-// Backward: chunks in reverse.  hs[0] = the state before the chunk (checkpoint c - 1, zero for the first chunk),
-// hs[s + 1] = the state after step s of the chunk, recomputed; then the adjoint recurrence from the chunk's last
-// step down.
+// Backward: chunks in reverse, four lanes per channel as in the forward.  hs[0] = the state before the chunk
+// (checkpoint c - 1, zero for the first chunk), hs[s + 1] = the state after step s of the chunk, recomputed; then the
+// adjoint recurrence from the chunk's last step down.  A thread reads and writes only its own states in hs.
 template <typename T, int kN>
-__global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
+__global__ void __launch_bounds__(kFwdThreads) ss_bwd_kernel(SsArgs a) {
+  constexpr int kQ = kN / kSplit;                            // states per thread
+  constexpr int kRows = kStep * kN;
+  constexpr int kShare = (kRows + kFwdThreads - 1) / kFwdThreads;
   extern __shared__ float smem_ss[];
   float* hs = smem_ss;                                   // [kStep + 1][kN][kCh]
   float* sBb = hs + (kStep + 1) * kN * kCh;              // 2 x [kStep][kN]
-  float* sCb = sBb + 2 * kStep * kN;                     // 2 x [kStep][kN]
+  float* sCb = sBb + 2 * kRows;                          // 2 x [kStep][kN]
   // up to 32 states: the chunk's dB / dC terms as a tile [kStep][2][kN][kCh] (128 KB at 32 states); 64 states would
-  // not fit beside the states and use warp shuffles instead
+  // not fit beside the states and reduce over the warp's eight channels by shuffles instead
   constexpr bool kTile = kN <= 32;
-  float* ct = sCb + 2 * kStep * kN;
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int d = blockIdx.x * kCh + tid, b = blockIdx.y;
+  float* ct = sCb + 2 * kRows;
+  const int tid = threadIdx.x, lane = tid & 31, part = tid & (kSplit - 1), ch = tid >> 2;
+  const int d = blockIdx.x * kCh + ch, b = blockIdx.y;
   const bool live = d < a.Dc;
   const int64_t base = int64_t(b) * a.L * a.Dc + d;
   const T* xp = reinterpret_cast<const T*>(a.x) + base;
@@ -209,47 +169,74 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
   T* ddp = reinterpret_cast<T*>(a.ddelta) + base;
   const T* Bp = reinterpret_cast<const T*>(a.B) + int64_t(b) * a.L * a.N;
   const T* Cp = reinterpret_cast<const T*>(a.C) + int64_t(b) * a.L * a.N;
-  float Ar[kN], g[kN], dA[kN];
+  float Ar[kQ], g[kQ], dA[kQ];
 #pragma unroll
-  for (int n = 0; n < kN; ++n) {
-    Ar[n] = (live && n < a.N) ? kLog2eSs * to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
-    g[n] = dA[n] = 0.f;
+  for (int q = 0; q < kQ; ++q) {
+    const int n = part * kQ + q;
+    Ar[q] = (live && n < a.N) ? kLog2eSs * to_f32<T>(reinterpret_cast<const T*>(a.A)[int64_t(d) * a.N + n]) : 0.f;
+    g[q] = dA[q] = 0.f;
   }
   const float Dd = (a.D && live) ? to_f32<T>(reinterpret_cast<const T*>(a.D)[d]) : 0.f;
   float dD = 0.f;
-  ChunkRegs<kN, true> next;
-  if (a.chunks > 0) load_chunk<T, kN, true>(next, a, live, dp, xp, gp, Bp, Cp, (a.chunks - 1) * kStep, tid);
+  // the next chunk's operands: issued before the current chunk is computed
+  float ndl[kStep], nxv[kStep], ngy[kStep], nbq[kShare], ncq[kShare];
+  auto load = [&](int t0) {
+#pragma unroll
+    for (int s = 0; s < kStep; ++s) {
+      const bool in = live && t0 + s < a.L;
+      ndl[s] = in ? to_f32<T>(dp[int64_t(t0 + s) * a.Dc]) : 0.f;
+      nxv[s] = in ? to_f32<T>(xp[int64_t(t0 + s) * a.Dc]) : 0.f;
+      ngy[s] = in ? to_f32<T>(gp[int64_t(t0 + s) * a.Dc]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kShare; ++j) {
+      const int i = tid + kFwdThreads * j, s = i / kN, n = i - s * kN;   // (compile-time divisor)
+      const bool in = i < kRows && n < a.N && t0 + s < a.L;
+      nbq[j] = in ? to_f32<T>(Bp[int64_t(t0 + s) * a.N + n]) : 0.f;
+      ncq[j] = in ? to_f32<T>(Cp[int64_t(t0 + s) * a.N + n]) : 0.f;
+    }
+  };
+  if (a.chunks > 0) load((a.chunks - 1) * kStep);
   for (int c = a.chunks - 1; c >= 0; --c) {
     const int t0 = c * kStep;
-    const ChunkRegs<kN, true> cur = next;
-    const float* dls = cur.dl;
-    const float* xvs = cur.xv;
-    const float* gys = cur.gy;
-    float* sB = sBb + (c & 1) * kStep * kN;
-    float* sC = sCb + (c & 1) * kStep * kN;
-    put_rows<kN, true>(cur, sB, sC, tid);
-    __syncthreads();   // (the buffer written two chunks ago was last read before the previous barrier)
-    if (c > 0) load_chunk<T, kN, true>(next, a, live, dp, xp, gp, Bp, Cp, t0 - kStep, tid);
+    float dls[kStep], xvs[kStep], gys[kStep];
+#pragma unroll
+    for (int s = 0; s < kStep; ++s) {
+      dls[s] = ndl[s];
+      xvs[s] = nxv[s];
+      gys[s] = ngy[s];
+    }
+    float* sB = sBb + (c & 1) * kRows;
+    float* sC = sCb + (c & 1) * kRows;
+#pragma unroll
+    for (int j = 0; j < kShare; ++j) {
+      const int i = tid + kFwdThreads * j;
+      if (i < kRows) {
+        sB[i] = nbq[j];
+        sC[i] = ncq[j];
+      }
+    }
+    __syncthreads();   // (the buffer written two chunks ago, and the tile, were last read before the previous barrier)
+    if (c > 0) load(t0 - kStep);
     // ---- recompute the chunk's states ----
     {
-      float h[kN];
+      float h[kQ];
       const float* ck = c > 0 ? a.ckpt + (int64_t(b) * a.chunks + (c - 1)) * a.N * a.Dc + d : nullptr;
 #pragma unroll
-      for (int n = 0; n < kN; ++n) {
-        h[n] = (live && ck && n < a.N) ? ck[int64_t(n) * a.Dc] : 0.f;
-        hs[(0 * kN + n) * kCh + tid] = h[n];
+      for (int q = 0; q < kQ; ++q) {
+        const int n = part * kQ + q;
+        h[q] = (live && ck && n < a.N) ? ck[int64_t(n) * a.Dc] : 0.f;
+        hs[(0 * kN + n) * kCh + ch] = h[q];
       }
 #pragma unroll
       for (int s = 0; s < kStep; ++s) {
-        const int t = t0 + s;
-        if (live && t < a.L) {
-          const float dl = dls[s], xv = xvs[s];
+        const float dl = dls[s], xv = xvs[s];   // (zeros past the sequence's end: the state stays as it is)
 #pragma unroll
-          for (int n = 0; n < kN; ++n)
-            if (n < a.N) h[n] = fmaf(ex2_ss(dl * Ar[n]), h[n], (dl * sB[s * kN + n]) * xv);
+        for (int q = 0; q < kQ; ++q) {
+          const int n = part * kQ + q;
+          h[q] = fmaf(ex2_ss(dl * Ar[q]), h[q], (dl * sB[s * kN + n]) * xv);
+          hs[((s + 1) * kN + n) * kCh + ch] = h[q];
         }
-#pragma unroll
-        for (int n = 0; n < kN; ++n) hs[((s + 1) * kN + n) * kCh + tid] = h[n];
       }
     }
     // ---- adjoint recurrence, last step of the chunk first ----
@@ -258,38 +245,48 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
       const int t = t0 + s;
       if (t >= a.L) continue;   // (uniform over the CTA)
       const float dl = dls[s], xv = xvs[s], gy = gys[s];
-      float ddl = 0.f, dxv = a.D ? Dd * gy : 0.f;
-      dD = fmaf(gy, xv, dD);
+      float ddl = 0.f, dxv = 0.f;
+      if (part == 0) dD = fmaf(gy, xv, dD);
 #pragma unroll
-      for (int n = 0; n < kN; ++n) {
-        if (n < a.N) {   // (uniform over the CTA: the shuffles below are executed by whole warps)
-          // a dead lane (past the last channel) carries zeros throughout: dl = xv = gy = 0, g = 0
-          const float hprev = hs[(s * kN + n) * kCh + tid], hcur = hs[((s + 1) * kN + n) * kCh + tid];
-          const float av = ex2_ss(dl * Ar[n]);
-          const float bt = sB[s * kN + n];
-          g[n] = fmaf(sC[s * kN + n], gy, g[n]);       // dL/dh_t
-          const float da = g[n] * hprev * av;          // dL/d(delta_t A_n), natural units
-          ddl = fmaf(da, Ar[n] * (1.f / kLog2eSs), ddl);
-          dA[n] = fmaf(da, dl, dA[n]);
-          ddl = fmaf(g[n] * bt, xv, ddl);
-          dxv = fmaf(g[n] * dl, bt, dxv);
-          // dB_t, dC_t: sums over the channels
-          if constexpr (kTile) {
-            // this thread's terms go into the chunk's tile; the CTA adds the columns once per chunk (below)
-            ct[((s * 2 + 0) * kN + n) * kCh + tid] = g[n] * dl * xv;
-            ct[((s * 2 + 1) * kN + n) * kCh + tid] = gy * hcur;
-          } else {
-            // the warp by shuffles, then one atomic per warp and element
-            const float vb = warp_sum_ss(g[n] * dl * xv), vc = warp_sum_ss(gy * hcur);
-            if (lane == 0) {
-              atomicAdd(a.accB + (int64_t(b) * a.L + t) * a.N + n, vb);
-              atomicAdd(a.accC + (int64_t(b) * a.L + t) * a.N + n, vc);
-            }
+      for (int q = 0; q < kQ; ++q) {
+        const int n = part * kQ + q;
+        // a dead lane (past the last channel) and a state past N carry zeros throughout
+        const float hprev = hs[(s * kN + n) * kCh + ch], hcur = hs[((s + 1) * kN + n) * kCh + ch];
+        const float av = ex2_ss(dl * Ar[q]);
+        const float bt = sB[s * kN + n];
+        g[q] = fmaf(sC[s * kN + n], gy, g[q]);       // dL/dh_t
+        const float da = g[q] * hprev * av;          // dL/d(delta_t A_n), natural units
+        ddl = fmaf(da, Ar[q] * (1.f / kLog2eSs), ddl);
+        dA[q] = fmaf(da, dl, dA[q]);
+        ddl = fmaf(g[q] * bt, xv, ddl);
+        dxv = fmaf(g[q] * dl, bt, dxv);
+        // dB_t, dC_t: sums over the channels
+        if constexpr (kTile) {
+          // this thread's terms go into the chunk's tile; the CTA adds the columns once per chunk (below)
+          ct[((s * 2 + 0) * kN + n) * kCh + ch] = g[q] * dl * xv;
+          ct[((s * 2 + 1) * kN + n) * kCh + ch] = gy * hcur;
+        } else {
+          // the warp's eight channels by shuffles (lanes 4 apart hold the same states), then one atomic each
+          float vb = g[q] * dl * xv, vc = gy * hcur;
+#pragma unroll
+          for (int o = 16; o >= kSplit; o >>= 1) {
+            vb += __shfl_xor_sync(0xffffffffu, vb, o);
+            vc += __shfl_xor_sync(0xffffffffu, vc, o);
           }
-          g[n] *= av;                                  // dL/dh_{t-1} so far
+          if (lane < kSplit && n < a.N) {
+            atomicAdd(a.accB + (int64_t(b) * a.L + t) * a.N + n, vb);
+            atomicAdd(a.accC + (int64_t(b) * a.L + t) * a.N + n, vc);
+          }
         }
+        g[q] *= av;                                  // dL/dh_{t-1} so far
       }
-      if (live) {
+      // dx_t, ddelta_t: sums over the channel's states, i.e. over the four lanes
+      ddl += __shfl_xor_sync(0xffffffffu, ddl, 1);
+      ddl += __shfl_xor_sync(0xffffffffu, ddl, 2);
+      dxv += __shfl_xor_sync(0xffffffffu, dxv, 1);
+      dxv += __shfl_xor_sync(0xffffffffu, dxv, 2);
+      if (a.D) dxv = fmaf(Dd, gy, dxv);
+      if (live && part == 0) {
         dxp[int64_t(t) * a.Dc] = from_f32<T>(dxv);
         ddp[int64_t(t) * a.Dc] = from_f32<T>(ddl);
       }
@@ -298,7 +295,7 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
       // column sums of the chunk's tile: sum v = (step, B or C, n) over the 64 channels, read with a per-thread skew
       // so that the threads of a warp hit different banks; then one atomic per sum and CTA
       __syncthreads();
-      for (int v = tid; v < kStep * 2 * kN; v += kCh) {
+      for (int v = tid; v < kStep * 2 * kN; v += kFwdThreads) {
         const int sv = v / (2 * kN), rest = v - sv * 2 * kN, which = rest / kN, n = rest - which * kN;
         const int t = t0 + sv;
         if (n < a.N && t < a.L) {
@@ -314,9 +311,11 @@ __global__ void __launch_bounds__(kCh) ss_bwd_kernel(SsArgs a) {
   }
   if (live) {
 #pragma unroll
-    for (int n = 0; n < kN; ++n)
-      if (n < a.N) atomicAdd(a.accA + int64_t(d) * a.N + n, dA[n]);
-    if (a.accD) atomicAdd(a.accD + d, dD);
+    for (int q = 0; q < kQ; ++q) {
+      const int n = part * kQ + q;
+      if (n < a.N) atomicAdd(a.accA + int64_t(d) * a.N + n, dA[q]);
+    }
+    if (a.accD && part == 0) atomicAdd(a.accD + d, dD);
   }
 }
 
@@ -377,7 +376,7 @@ int bwd_launch(const SsArgs& a, dim3 grid, cudaStream_t st) {
     set_error("selective_scan_bwd: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(cudaGetLastError()));
     return NB200_ERR_LAUNCH;
   }
-  ss_bwd_kernel<T, kN><<<grid, kCh, smem, st>>>(a);
+  ss_bwd_kernel<T, kN><<<grid, kFwdThreads, smem, st>>>(a);
   count_launch();
   return check_launch("selective_scan_bwd_kernel");
 }
