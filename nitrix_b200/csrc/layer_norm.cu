@@ -625,6 +625,7 @@ extern "C" NB200_API int nb200_layer_norm_fwd(const nb200_layer_norm_params* p, 
   if (p->rows == 0) return NB200_OK;
   if (!p->x || !p->y) { set_error("layer_norm_fwd: NULL x or y"); return NB200_ERR_INVALID; }
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  prof_call_begin(st);
   Shape s;
   const bool vec = vector_path(p, false, &s);
   switch (p->dtype) {
@@ -642,6 +643,7 @@ extern "C" NB200_API int nb200_layer_norm_bwd(const nb200_layer_norm_params* p, 
     return NB200_ERR_INVALID;
   }
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  prof_call_begin(st);
   Shape s;
   const bool vec = vector_path(p, true, &s);
   switch (p->dtype) {

@@ -152,6 +152,7 @@ int launch(const nb200_qk_norm_tensor* q, const nb200_qk_norm_tensor* k, int D, 
   const int64_t blocks = (rows + 7) / 8;
   if (blocks > 0x7fffffff) { set_error("qk_rms_norm: too many rows"); return NB200_ERR_UNSUPPORTED; }
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  prof_call_begin(st);
   if (dtype == NB200_F32) qk_rms_norm_kernel<float, kGrad><<<unsigned(blocks), 256, 0, st>>>(a, b, D);
   else if (dtype == NB200_BF16) qk_rms_norm_kernel<__nv_bfloat16, kGrad><<<unsigned(blocks), 256, 0, st>>>(a, b, D);
   else qk_rms_norm_kernel<__half, kGrad><<<unsigned(blocks), 256, 0, st>>>(a, b, D);

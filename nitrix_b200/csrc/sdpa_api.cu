@@ -51,6 +51,13 @@ void prof_mark(const char* name) {
 }
 }  // namespace
 
+// Start of one entry point's kernels on `st`: the per-kernel timing brackets every kernel between this marker (or the
+// previous kernel's) and its own.
+void prof_call_begin(cudaStream_t st) {
+  g_prof_stream = st;
+  prof_mark(nullptr);
+}
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -79,6 +79,8 @@ __host__ __device__ __forceinline__ int dtype_size(int dtype) { return dtype == 
 void set_error(const char* fmt, ...);
 void count_launch(int n = 1);
 int check_launch(const char* what);
+// Call once at the start of an entry point that launches kernels on `st` (per-kernel timing: nb200_profile).
+void prof_call_begin(cudaStream_t st);
 // Address (on the current device) of the status word bounded waits report to.
 int* device_status_word();
 // A second stream of the calling thread on the current device, with the two events of a fork / join: small problems

@@ -440,6 +440,7 @@ extern "C" NB200_API int nb200_selective_scan_fwd(const nb200_selective_scan_par
   if (p->batch == 0 || p->length == 0) return NB200_OK;
   if (!p->x || !p->delta || !p->A || !p->B || !p->C || !p->y) { set_error("selective_scan_fwd: NULL operand"); return NB200_ERR_INVALID; }
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  prof_call_begin(st);
   switch (p->dtype) {
     case NB200_F32: return fwd_t<float>(p, st);
     case NB200_BF16: return fwd_t<__nv_bfloat16>(p, st);
@@ -457,6 +458,7 @@ extern "C" NB200_API int nb200_selective_scan_bwd(const nb200_selective_scan_par
     return NB200_ERR_INVALID;
   }
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  prof_call_begin(st);
   switch (p->dtype) {
     case NB200_F32: return bwd_t<float>(p, st);
     case NB200_BF16: return bwd_t<__nv_bfloat16>(p, st);
