@@ -308,3 +308,24 @@ def test_jax_norm_ffi_layer_is_complete_and_consistent():
         assert name in header, name
     # the trace-time workspace query goes through the real library
     assert J.workspace_bytes(8192, 2048, "bfloat16") >= 2 * 2048 * 4
+
+
+def test_jax_scan_ffi_layer_is_complete_and_consistent():
+    """The selective-scan FFI shim and its JAX module: the module compiles and imports without jax, and its handler
+    symbols and attribute lists are the ones the C++ file binds (neither can run here: no jax, no XLA headers)."""
+    import py_compile
+
+    py_compile.compile(str(ROOT / "nitrix_b200" / "jax_scan_ffi.py"), doraise=True)
+    from nitrix_b200 import jax_scan_ffi as J
+
+    shim = (ROOT / "ffi" / "nb200_scan_ffi.cc").read_text()
+    symbols = set(re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\((\w+),", shim))
+    assert symbols == {J.FWD_SYMBOL, J.BWD_SYMBOL}
+    fwd_block, bwd_block = shim.split("XLA_FFI_DEFINE_HANDLER_SYMBOL(")[1:3]
+    assert tuple(re.findall(r'\.Attr<\w+>\("(\w+)"\)', fwd_block)) == J.FWD_ATTRS
+    assert tuple(re.findall(r'\.Attr<\w+>\("(\w+)"\)', bwd_block)) == J.BWD_ATTRS
+    header = (ROOT / "include" / "nitrix_b200_scan.h").read_text()
+    for name in set(re.findall(r"\b(nb200_selective_scan_\w+)\(", shim)) - symbols:
+        assert name in header, name
+    ck, ws = J.scratch_bytes(8, 1024, 2048, 16, "bfloat16")
+    assert ck == 8 * 128 * 2048 * 16 * 4 and ws >= 2 * 8 * 1024 * 16 * 4
